@@ -1,0 +1,156 @@
+// Sampling on the device: greedy, temperature and nucleus (top-p), one block
+// per row of logits.
+//
+// Greedy follows the reference's argmax rules (engine/include/argmax.h:10-13,
+// engine/src/argmax.cu:8-18): the first index wins a tie, a NaN beats every
+// number and the first NaN wins.  The reference's engine samples greedily
+// only; its command line (scripts/complete.py:116-123) adds temperature and
+// top-p, with temperature <= 0 meaning greedy.  Here those are done by the
+// Gumbel-max rule: the chosen token is argmax_v(logit_v / T + g_v) over the
+// kept tokens, g_v = -log(-log(u_v)), u_v a hash of (seed, counter, v).  The
+// draw depends on nothing but the row's own logits and its (seed, counter),
+// so it is the same in every batch, and a host twin can repeat it.
+#include "common.cuh"
+
+MLLM_DEFINE_ERROR_API(mllm_sampling)
+
+__host__ __device__ __forceinline__ uint64_t mix64(uint64_t z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+// Uniform in (0, 1) with 24 bits, from (seed, counter, index).
+__device__ __forceinline__ float uniform_of(uint64_t seed, uint32_t counter, uint32_t index) {
+    uint64_t h = mix64(mix64(seed ^ ((uint64_t)counter << 32)) ^ (uint64_t)index);
+    return ((float)(uint32_t)(h >> 40) + 0.5f) * (1.0f / 16777216.0f);
+}
+
+__device__ __forceinline__ bool better(float va, int ia, float vb, int ib) {
+    bool na = va != va, nb = vb != vb;
+    if (ia < 0) return false;
+    if (ib < 0) return true;
+    if (na != nb) return na;
+    if (na) return ia < ib;
+    if (va != vb) return va > vb;
+    return ia < ib;
+}
+
+__device__ __forceinline__ void block_argmax(float& v, int& i, float* sv, int* si) {
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        int oi = __shfl_xor_sync(0xffffffffu, i, o);
+        if (better(ov, oi, v, i)) { v = ov; i = oi; }
+    }
+    __syncthreads();
+    if (lane == 0) { sv[warp] = v; si[warp] = i; }
+    __syncthreads();
+    if (warp == 0) {
+        v = lane < n_warps ? sv[lane] : 0.0f;
+        i = lane < n_warps ? si[lane] : -1;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            int oi = __shfl_xor_sync(0xffffffffu, i, o);
+            if (better(ov, oi, v, i)) { v = ov; i = oi; }
+        }
+        if (lane == 0) { sv[0] = v; si[0] = i; }
+    }
+    __syncthreads();
+    v = sv[0];
+    i = si[0];
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < n_warps ? scratch[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// temperature[r] <= 0: greedy.  top_p[r] >= 1: no nucleus cut.
+// The nucleus is the smallest set of most probable tokens whose probability
+// reaches top_p, ties at its edge included: tokens with p >= t*, where t* is
+// the largest t with sum_{p_v >= t} p_v >= top_p, found by bisection on the
+// bit pattern of t.
+__global__ void __launch_bounds__(1024)
+sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, long ld, int vocab,
+                   const float* __restrict__ temperature, const float* __restrict__ top_p,
+                   const unsigned long long* __restrict__ seeds, const int* __restrict__ counters) {
+    __shared__ float sv[33];
+    __shared__ int si[32];
+    int r = blockIdx.x;
+    const float* x = logits + (long)r * ld;
+    float temp = temperature ? temperature[r] : 0.0f;
+    float best = 0.0f;
+    int best_i = -1;
+
+    if (!(temp > 0.0f)) {
+        for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
+            float xv = x[v];
+            if (better(xv, v, best, best_i)) { best = xv; best_i = v; }
+        }
+        block_argmax(best, best_i, sv, si);
+        if (threadIdx.x == 0) out[r] = best_i;
+        return;
+    }
+
+    float inv_t = 1.0f / temp;
+    float nucleus = top_p ? top_p[r] : 1.0f;
+    float cut = 0.0f;       // keep tokens with probability >= cut
+    float big = 0.0f, z = 1.0f;
+    if (nucleus < 1.0f) {
+        float mx = -INFINITY;
+        for (int v = threadIdx.x; v < vocab; v += blockDim.x) mx = fmaxf(mx, x[v]);
+        big = block_max(mx, sv);
+        float sum = 0.0f;
+        for (int v = threadIdx.x; v < vocab; v += blockDim.x) sum += expf((x[v] - big) * inv_t);
+        z = block_sum(sum, sv);
+        unsigned lo = 0u, hi = 0x3f800000u;      // bit patterns of 0.0f and 1.0f
+        while (lo < hi) {
+            unsigned mid = lo + (hi - lo + 1u) / 2u;
+            float t = __uint_as_float(mid);
+            float mass = 0.0f;
+            for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
+                float pv = expf((x[v] - big) * inv_t) / z;
+                if (pv >= t) mass += pv;
+            }
+            mass = block_sum(mass, sv);
+            if (mass >= nucleus) lo = mid; else hi = mid - 1u;
+        }
+        cut = __uint_as_float(lo);
+    }
+
+    unsigned long long seed = seeds ? seeds[r] : 0ull;
+    unsigned counter = counters ? (unsigned)counters[r] : 0u;
+    for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
+        float xv = x[v];
+        if (nucleus < 1.0f && !(expf((xv - big) * inv_t) / z >= cut)) continue;
+        float u = uniform_of(seed, counter, (unsigned)v);
+        float score = xv * inv_t - logf(-logf(u));
+        if (better(score, v, best, best_i)) { best = score; best_i = v; }
+    }
+    block_argmax(best, best_i, sv, si);
+    if (threadIdx.x == 0) out[r] = best_i;
+}
+
+extern "C" int mllm_sampling_sample_rows(int* out, const float* logits, long ld, int n_rows, int vocab,
+                                         const float* temperature, const float* top_p,
+                                         const unsigned long long* seeds, const int* counters, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (vocab <= 0) return fail("sample_rows: empty vocabulary");
+    sample_rows_kernel<<<n_rows, 1024, 0, (cudaStream_t)stream>>>(out, logits, ld, vocab, temperature, top_p,
+                                                                  seeds, counters);
+    return check_launch("sample_rows_kernel");
+}

@@ -1,0 +1,219 @@
+"""The engine: a model on one GPU, its caches, and the one step function.
+
+``Engine.step(entries)`` takes a batch of (request, its next tokens): portions
+of prompts beside single decoded tokens, cut anywhere.  It runs only the
+tokens it is given, as one batch, against the cache earlier steps left, and
+returns the logits at the wanted places.  The reference has three entry
+points instead (whole-prompt prefill, single decode, batched decode of up to
+16: engine/include/gpt2_gpu.h:64-68,89-90,161-165) and never mixes a prompt
+with decoding requests.
+
+Like the reference (engine/src/gpt2_gpu.cu:197-207,301-304), a step checks all
+of its input before it launches anything, and a refused step changes nothing.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.storage import CacheStorage
+from ..config.registry import config_from_folder, describe_model
+from ..kernels.dispatch import Kernels
+from .context import ControlBlock, StepContext, Workspace
+from .model import Model
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+class StepError(ValueError):
+    """The step's input is invalid; nothing was run and nothing changed."""
+
+
+class OutOfPages(RuntimeError):
+    """The page pools cannot hold the step's tokens; nothing was run and nothing changed."""
+
+
+@dataclass
+class StepEntry:
+    slot: int                     # the request's slot, from ``open_request``
+    tokens: list                  # its next tokens
+    want: list = field(default_factory=list)     # places among these tokens whose logits are wanted
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 0.0      # <= 0: greedy
+    top_p: float = 1.0            # >= 1: no nucleus cut
+    seed: int = 0
+    counter: int = 0              # how many tokens this request has sampled so far
+
+
+class Engine:
+    def __init__(self, model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0", page_size: int = 16,
+                 cache_tokens: int | None = None, n_pages: int | None = None, max_requests: int = 64,
+                 max_tokens_per_step: int = 2048, plain_kernels: bool = False, cuda_graphs: bool = True):
+        if not torch.cuda.is_available():
+            raise RuntimeError("mini_llm_b200 runs on a CUDA device (sm_100a) only; none is available "
+                               "and there is no CPU path")
+        if dtype not in DTYPES:
+            raise ValueError(f"dtype must be one of {', '.join(sorted(DTYPES))}, got '{dtype}'")
+        self.dtype = DTYPES[dtype]
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        self.config = config_from_folder(model_dir)
+        self.spec = describe_model(self.config)
+        self.model = Model(self.spec)
+        self.kernels = Kernels(self.dtype, plain_only=plain_kernels)
+        self.model.load(model_dir, self.dtype, self.device, runtime=self)
+        self.page_size = int(page_size)
+        self.max_requests = int(max_requests)
+        self.max_tokens_per_step = int(max_tokens_per_step)
+        self.cuda_graphs = bool(cuda_graphs)
+
+        needs = self.model.cache_needs()
+        per_request = self.spec.max_positions
+        if n_pages is None:
+            if cache_tokens is None:
+                cache_tokens = self.max_requests * (per_request if per_request is not None else 4096)
+            n_pages = -(-int(cache_tokens) // self.page_size)
+        if per_request is None:
+            per_request = n_pages * self.page_size
+        self.max_positions = per_request
+        self.cache = CacheManager(needs, self.page_size, int(n_pages), self.max_requests, per_request)
+        self.storage = CacheStorage(self.cache, self.spec.order, self.dtype, self.device, self.max_requests)
+        self.workspace = Workspace(self.device, min_rows=min(self.max_tokens_per_step, 256))
+        self.control = ControlBlock(self.device, self.cache.groups)
+        self.ctx = StepContext(self.kernels, self.workspace, self.dtype, self.device)
+        self.steps = 0
+        self._sampled = None
+
+    # ---- requests ---------------------------------------------------------------------------
+    def open_request(self) -> int | None:
+        """A slot for a new request (its cache starts empty), or None if every slot is taken."""
+        slot = self.cache.open()
+        if slot is not None:
+            self.storage.reset_slot(slot)
+        return slot
+
+    def close_request(self, slot: int) -> None:
+        """Give back what the request holds."""
+        self.cache.close(slot)
+
+    def cached_tokens(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ---- the step ---------------------------------------------------------------------------
+    def _validate(self, entries) -> None:
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        seen = set()
+        vocab = self.spec.vocab_size
+        for index, entry in enumerate(entries):
+            if not self.cache.is_open(entry.slot):
+                raise StepError(f"entry {index}: slot {entry.slot} holds no request")
+            if entry.slot in seen:
+                raise StepError(f"entry {index}: slot {entry.slot} appears twice in one step")
+            seen.add(entry.slot)
+            n = len(entry.tokens)
+            if n == 0:
+                raise StepError(f"entry {index}: no tokens")
+            for token in entry.tokens:
+                if not 0 <= int(token) < vocab:
+                    raise StepError(f"entry {index}: token id {token} is outside the vocabulary [0, {vocab})")
+            have = self.cache.length(entry.slot)
+            if have + n > self.max_positions:
+                raise StepError(f"entry {index}: {have} cached + {n} new tokens exceed the {self.max_positions} "
+                                f"positions a request may hold")
+            for place in entry.want:
+                if not 0 <= int(place) < n:
+                    raise StepError(f"entry {index}: wanted place {place} is not among its {n} tokens")
+
+    def _reserve(self, entries) -> None:
+        needed = [0] * len(self.cache.groups)
+        for entry in entries:
+            for g, count in enumerate(self.cache.pages_needed(entry.slot, len(entry.tokens))):
+                needed[g] += count
+        free = self.cache.pages_free()
+        for g, count in enumerate(needed):
+            if count > free[g]:
+                raise OutOfPages(f"the step needs {count} more pages in cache group {g}, {free[g]} are free")
+        for entry in entries:
+            if not self.cache.reserve(entry.slot, len(entry.tokens)):
+                raise OutOfPages("page reservation failed after it was checked")   # cannot happen
+
+    def step(self, entries, sampling=None):
+        """Run one batch.  Returns fp32 logits ``[wanted, vocab]`` on the device
+        (in the order of the entries and of each ``want``; valid until the next
+        step), or None if nothing is wanted.  With ``sampling`` (one
+        ``SamplingParams`` per wanted row) the chosen tokens are then read with
+        ``sampled_tokens()``."""
+        self._validate(entries)
+        n_want = sum(len(e.want) for e in entries)
+        if sampling is not None and len(sampling) != n_want:
+            raise StepError(f"{len(sampling)} sampling parameters for {n_want} wanted rows")
+        self._reserve(entries)
+
+        n_tokens = sum(len(e.tokens) for e in entries)
+        n_items = len(entries)
+        token_ids = np.empty(n_tokens, dtype=np.int32)
+        positions = np.empty(n_tokens, dtype=np.int32)
+        token_item = np.empty(n_tokens, dtype=np.int32)
+        want_rows = np.empty(n_want, dtype=np.int32)
+        ctx = self.ctx
+        ctx.item_slots, ctx.item_starts, ctx.item_counts, ctx.item_offsets = [], [], [], []
+        row = 0
+        w = 0
+        for index, entry in enumerate(entries):
+            n = len(entry.tokens)
+            start = self.cache.length(entry.slot)
+            token_ids[row:row + n] = entry.tokens
+            positions[row:row + n] = np.arange(start, start + n, dtype=np.int32)
+            token_item[row:row + n] = index
+            for place in entry.want:
+                want_rows[w] = row + int(place)
+                w += 1
+            ctx.item_slots.append(entry.slot)
+            ctx.item_starts.append(start)
+            ctx.item_counts.append(n)
+            ctx.item_offsets.append(row)
+            row += n
+        arrays = {"token_ids": token_ids, "positions": positions, "token_item": token_item, "want_rows": want_rows}
+        for group in self.cache.groups:
+            if group.paged:
+                arrays[("block_table", group.index)] = group.table[ctx.item_slots]
+        if sampling is not None:
+            arrays["temperature"] = np.array([s.temperature for s in sampling], dtype=np.float32)
+            arrays["top_p"] = np.array([s.top_p for s in sampling], dtype=np.float32)
+            arrays["seeds"] = np.array([s.seed & 0xFFFFFFFFFFFFFFFF for s in sampling], dtype=np.uint64)
+            arrays["counters"] = np.array([s.counter for s in sampling], dtype=np.int32)
+        views = self.control.upload(arrays, n_tokens, n_items)
+
+        ctx.n_tokens, ctx.n_items, ctx.n_want = n_tokens, n_items, n_want
+        ctx.token_ids, ctx.positions, ctx.token_item = views["token_ids"], views["positions"], views["token_item"]
+        ctx.want_rows = views["want_rows"][:n_want]
+        ctx.decode_only = all(n == 1 for n in ctx.item_counts)
+        for view in self.storage.views:
+            if view.kind == "paged":
+                view.block_table = views[("block_table", view.group)]
+
+        logits = self.model.forward(ctx, self.storage.views)
+        self._sampled = None
+        if sampling is not None and logits is not None:
+            out = self.workspace.get("sampled", (n_want,), torch.int32)
+            self.kernels.sample_rows(out, logits, views["temperature"][:n_want], views["top_p"][:n_want],
+                                     views["seeds"][:n_want], views["counters"][:n_want])
+            self._sampled = out
+        for entry in entries:
+            self.cache.commit(entry.slot, len(entry.tokens))
+        self.steps += 1
+        return logits
+
+    def sampled_tokens(self) -> list:
+        """The tokens the last step sampled, on the host (waits for the step)."""
+        if self._sampled is None:
+            return []
+        return self._sampled.cpu().tolist()

@@ -1,0 +1,194 @@
+"""The operations of a step, as functions over CUDA tensors.
+
+Every function checks what its kernel assumes (device, element types, inner
+stride, sizes), then launches on torch's current stream.  There is no CPU
+path: a tensor that is not on a CUDA device is an error.  The plain kernels
+take every size; a fast kernel either takes a size or is not chosen for it.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .lib import F, I, L, P, Function, KernelError
+
+DT_F32, DT_BF16 = 0, 1
+EPILOGUES = {"store": 0, "gelu_tanh": 1, "gelu_erf": 2, "add": 3}
+
+_DTYPE_CODE = {torch.float32: DT_F32, torch.bfloat16: DT_BF16}
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"unsupported element type {dtype}") from None
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(t: torch.Tensor, name: str, dtype=None, dims=None) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{name}: expected a CUDA tensor (there is no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
+    if dims is not None and t.dim() != dims:
+        raise KernelError(f"{name}: expected {dims} dimensions, got shape {tuple(t.shape)}")
+    if t.dim() > 0 and t.numel() > 0 and t.stride(-1) != 1:
+        raise KernelError(f"{name}: the last dimension must be contiguous")
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+_embed = Function("plain", "mllm_plain_embed", [P, P, P, P, P, I, I, I, P])
+_add_rows = Function("plain", "mllm_plain_add_rows", [P, P, P, I, I, I, P])
+_layernorm = Function("plain", "mllm_plain_layernorm", [P, P, P, P, P, I, I, F, I, P])
+_linear = Function("plain", "mllm_plain_linear", [P, P, P, P, I, I, I, L, L, I, I, I, P])
+_kv_store = Function("plain", "mllm_plain_kv_store", [P, P, P, P, L, P, P, P, I, I, I, I, I, P])
+_attention = Function("plain", "mllm_plain_attention",
+                      [P, L, P, L, P, P, P, I, P, P, I, I, I, I, I, F, I, I, P])
+_sample_rows = Function("sampling", "mllm_sampling_sample_rows", [P, P, L, I, I, P, P, P, P, P])
+
+
+def embed(out, token_ids, positions, table, position_table=None):
+    """out[t] = table[token_ids[t]] (+ position_table[positions[t]]); out is fp32 [T, width]."""
+    _check(out, "embed.out", torch.float32, 2)
+    _check(token_ids, "embed.token_ids", torch.int32, 1)
+    _check(table, "embed.table", None, 2)
+    n, width = out.shape
+    if not out.is_contiguous() or not table.is_contiguous():
+        raise KernelError("embed: out and table must be contiguous")
+    if table.shape[1] != width or token_ids.shape[0] < n:
+        raise KernelError("embed: sizes do not agree")
+    if position_table is not None:
+        _check(position_table, "embed.position_table", table.dtype, 2)
+        _check(positions, "embed.positions", torch.int32, 1)
+        if position_table.shape[1] != width or not position_table.is_contiguous():
+            raise KernelError("embed: position table has another width")
+    _embed(out.data_ptr(), token_ids.data_ptr(), _ptr(positions), table.data_ptr(), _ptr(position_table),
+           n, width, dtype_code(table.dtype), _stream())
+    return out
+
+
+def add_position_rows(hidden, positions, table):
+    """hidden[t] += table[positions[t]]."""
+    _check(hidden, "add_position_rows.hidden", torch.float32, 2)
+    _check(positions, "add_position_rows.positions", torch.int32, 1)
+    _check(table, "add_position_rows.table", None, 2)
+    if not hidden.is_contiguous() or not table.is_contiguous() or table.shape[1] != hidden.shape[1]:
+        raise KernelError("add_position_rows: sizes do not agree")
+    _add_rows(hidden.data_ptr(), positions.data_ptr(), table.data_ptr(), hidden.shape[0], hidden.shape[1],
+              dtype_code(table.dtype), _stream())
+    return hidden
+
+
+def layernorm(out, x, gamma, beta, eps, rows=None):
+    """out[r] = LN(x[rows[r]] or x[r]); x fp32 [*, width]; out fp32 or bf16 [R, width]."""
+    _check(out, "layernorm.out", None, 2)
+    _check(x, "layernorm.x", torch.float32, 2)
+    _check(gamma, "layernorm.gamma", torch.float32, 1)
+    _check(beta, "layernorm.beta", torch.float32, 1)
+    width = x.shape[1]
+    if not x.is_contiguous() or not out.is_contiguous():
+        raise KernelError("layernorm: x and out must be contiguous")
+    if out.shape[1] != width or gamma.shape[0] != width or beta.shape[0] != width:
+        raise KernelError("layernorm: widths do not agree")
+    if rows is not None:
+        _check(rows, "layernorm.rows", torch.int32, 1)
+        if rows.shape[0] < out.shape[0]:
+            raise KernelError("layernorm: fewer row indices than output rows")
+    elif x.shape[0] < out.shape[0]:
+        raise KernelError("layernorm: fewer input rows than output rows")
+    _layernorm(out.data_ptr(), x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), _ptr(rows),
+               out.shape[0], width, float(eps), dtype_code(out.dtype), _stream())
+    return out
+
+
+def linear_plain(out, a, w, bias=None, epilogue="store"):
+    """out = epilogue(a @ w.T + bias); a [M, K], w [N, K] (K contiguous), out [M, N].
+
+    epilogue "add": out (fp32) += a @ w.T + bias.
+    """
+    _check(out, "linear.out", None, 2)
+    _check(a, "linear.a", None, 2)
+    _check(w, "linear.w", a.dtype, 2)
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape[0] != m or out.shape[1] != n or not w.is_contiguous():
+        raise KernelError(f"linear: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if bias is not None:
+        _check(bias, "linear.bias", torch.float32, 1)
+        if bias.shape[0] != n:
+            raise KernelError("linear: bias has another length")
+    _linear(out.data_ptr(), a.data_ptr(), w.data_ptr(), _ptr(bias), m, n, k, a.stride(0), out.stride(0),
+            dtype_code(a.dtype), dtype_code(out.dtype), EPILOGUES[epilogue], _stream())
+    return out
+
+
+def kv_store(k_pages, v_pages, k_src, v_src, positions, token_item, block_table, page_size):
+    """Write this step's keys and values (rows of k_src, v_src: [T, width]) into their pages."""
+    _check(k_pages, "kv_store.k_pages")
+    _check(v_pages, "kv_store.v_pages", k_pages.dtype)
+    _check(k_src, "kv_store.k_src", k_pages.dtype, 2)
+    _check(v_src, "kv_store.v_src", k_pages.dtype, 2)
+    _check(block_table, "kv_store.block_table", torch.int32, 2)
+    _check(positions, "kv_store.positions", torch.int32, 1)
+    _check(token_item, "kv_store.token_item", torch.int32, 1)
+    n, width = k_src.shape
+    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous():
+        raise KernelError("kv_store: pages and block table must be contiguous")
+    if k_src.stride(0) != v_src.stride(0) or v_src.shape != k_src.shape:
+        raise KernelError("kv_store: keys and values must share shape and row stride")
+    if k_pages.numel() % (page_size * width) != 0:
+        raise KernelError("kv_store: page pool does not hold whole pages of this width")
+    _kv_store(k_pages.data_ptr(), v_pages.data_ptr(), k_src.data_ptr(), v_src.data_ptr(), k_src.stride(0),
+              positions.data_ptr(), token_item.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+              page_size, width, n, dtype_code(k_pages.dtype), _stream())
+
+
+def attention_plain(out, q, k_pages, v_pages, block_table, positions, token_item, n_heads, n_kv_heads,
+                    head_size, page_size, scale, window=0):
+    """Causal attention of every token of the step over its request's pages."""
+    _check(out, "attention.out", q.dtype, 2)
+    _check(q, "attention.q", None, 2)
+    _check(k_pages, "attention.k_pages", q.dtype)
+    _check(v_pages, "attention.v_pages", q.dtype)
+    _check(block_table, "attention.block_table", torch.int32, 2)
+    _check(positions, "attention.positions", torch.int32, 1)
+    _check(token_item, "attention.token_item", torch.int32, 1)
+    n = q.shape[0]
+    if q.shape[1] != n_heads * head_size or out.shape[1] != n_heads * head_size or out.shape[0] != n:
+        raise KernelError("attention: q / out do not have heads * head_size columns")
+    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous():
+        raise KernelError("attention: pages and block table must be contiguous")
+    _attention(out.data_ptr(), out.stride(0), q.data_ptr(), q.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
+               block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), token_item.data_ptr(), n,
+               n_heads, n_kv_heads, head_size, page_size, float(scale), int(window or 0),
+               dtype_code(q.dtype), _stream())
+    return out
+
+
+def sample_rows(out, logits, temperature=None, top_p=None, seeds=None, counters=None):
+    """One token per row of fp32 logits [R, V] into out (int32 [R]).
+
+    temperature / top_p: fp32 [R] or None (greedy / no cut); seeds: int64 [R]
+    (bit pattern of a u64); counters: int32 [R].
+    """
+    _check(out, "sample_rows.out", torch.int32, 1)
+    _check(logits, "sample_rows.logits", torch.float32, 2)
+    r, vocab = logits.shape
+    if out.shape[0] < r:
+        raise KernelError("sample_rows: output too short")
+    for name, t, dt in (("temperature", temperature, torch.float32), ("top_p", top_p, torch.float32),
+                        ("seeds", seeds, torch.int64), ("counters", counters, torch.int32)):
+        if t is not None:
+            _check(t, f"sample_rows.{name}", dt, 1)
+            if t.shape[0] < r:
+                raise KernelError(f"sample_rows: {name} too short")
+    _sample_rows(out.data_ptr(), logits.data_ptr(), logits.stride(0), r, vocab, _ptr(temperature), _ptr(top_p),
+                 _ptr(seeds), _ptr(counters), _stream())
+    return out

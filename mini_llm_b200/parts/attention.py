@@ -1,0 +1,76 @@
+"""Causal self-attention over the paged cache.
+
+One fused projection gives queries, keys and values (the reference splits the
+fused ``c_attn`` matrix into three at load, engine/src/gpt2.c:79-90; here it
+stays one product).  Head ``h`` is the column range ``h*D .. h*D+D-1`` of q, k,
+v and of the output (engine/src/attention.c:78-87).  Scores are
+``(q . k) * score_scale`` over the keys at positions ``<=`` the query's
+(engine/src/attention.c:24-35, engine/src/softmax.c:29-55); the softmax and
+the weighted sum of values run in 32-bit.  The output projection adds its
+result and bias onto the block's input (engine/src/transformer_block.c:60-62).
+
+The keys and values of this step's tokens are first stored into the request's
+pages; attention then reads the cache only, so a prompt portion and a single
+decoded token take the same path.
+"""
+
+from __future__ import annotations
+
+from .base import Mixer, register_part
+from .spec import PagedKV, WeightSpec
+
+
+class CausalSelfAttention(Mixer):
+    def __init__(self, prefix, width: int, n_heads: int, head_size: int, score_scale: float,
+                 n_kv_heads: int | None = None, window: int | None = None,
+                 qkv_name: str = "c_attn", out_name: str = "c_proj", stored_in_out: bool = True):
+        super().__init__(prefix)
+        self.width = int(width)
+        self.n_heads = int(n_heads)
+        self.n_kv_heads = int(n_kv_heads if n_kv_heads is not None else n_heads)
+        self.head_size = int(head_size)
+        self.score_scale = float(score_scale)
+        self.window = int(window) if window else None
+        self.qkv_name, self.out_name = qkv_name, out_name
+        self.stored_in_out = bool(stored_in_out)
+        if self.n_heads % self.n_kv_heads != 0:
+            raise ValueError(f"{prefix}: {self.n_heads} heads are not a multiple of {self.n_kv_heads} key/value heads")
+        if self.head_size % 16 != 0 or not 16 <= self.head_size <= 256:
+            raise ValueError(f"{prefix}: head size {self.head_size} is not a multiple of 16 in 16..256")
+        self.q_width = self.n_heads * self.head_size
+        self.kv_width = self.n_kv_heads * self.head_size
+        self.qkv_width = self.q_width + 2 * self.kv_width
+
+    def _matrix_shape(self, n_in, n_out):
+        return (n_in, n_out) if self.stored_in_out else (n_out, n_in)
+
+    def weight_specs(self):
+        t = self.stored_in_out
+        return [
+            WeightSpec(self.full_name(f"{self.qkv_name}.weight"), self._matrix_shape(self.width, self.qkv_width), transpose=t),
+            WeightSpec(self.full_name(f"{self.qkv_name}.bias"), (self.qkv_width,), role="vector", init="bias"),
+            WeightSpec(self.full_name(f"{self.out_name}.weight"), self._matrix_shape(self.q_width, self.width), transpose=t,
+                       init="residual_matrix"),
+            WeightSpec(self.full_name(f"{self.out_name}.bias"), (self.width,), role="vector", init="bias"),
+        ]
+
+    def cache_need(self):
+        return PagedKV(self.n_kv_heads, self.head_size, self.window)
+
+    def forward(self, ctx, x, hidden, cache):
+        k = ctx.kernels
+        n = x.shape[0]
+        qkv = ctx.buffer("qkv", (n, self.qkv_width), ctx.act_dtype)
+        k.linear(qkv, x, self.w(f"{self.qkv_name}.weight"), self.w(f"{self.qkv_name}.bias"))
+        q = qkv[:, :self.q_width]
+        if cache.writes:
+            k.kv_store(cache.k_pages, cache.v_pages, qkv[:, self.q_width:self.q_width + self.kv_width],
+                       qkv[:, self.q_width + self.kv_width:], ctx.positions, ctx.token_item, cache.block_table,
+                       cache.page_size)
+        mixed = ctx.buffer("attn_out", (n, self.q_width), ctx.act_dtype)
+        k.attention(ctx, mixed, q, cache, self.n_heads, self.n_kv_heads, self.head_size, self.score_scale,
+                    self.window or 0)
+        k.linear(hidden, mixed, self.w(f"{self.out_name}.weight"), self.w(f"{self.out_name}.bias"), epilogue="add")
+
+
+register_part("causal_self_attention", CausalSelfAttention)

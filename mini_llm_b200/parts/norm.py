@@ -1,0 +1,30 @@
+"""Layer norm: mean, biased variance of the centred values, then
+``(x - mean) / sqrt(var + eps) * gain + shift`` (engine/src/layernorm.c:12-33).
+Statistics are 32-bit; the output has the engine's element type."""
+
+from __future__ import annotations
+
+from .base import Norm, register_part
+from .spec import WeightSpec
+
+
+class LayerNorm(Norm):
+    def __init__(self, prefix, width: int, eps: float):
+        super().__init__(prefix)
+        self.width = int(width)
+        self.eps = float(eps)
+
+    def weight_specs(self):
+        return [
+            WeightSpec(self.full_name("weight"), (self.width,), role="vector", init="gain"),
+            WeightSpec(self.full_name("bias"), (self.width,), role="vector", init="shift"),
+        ]
+
+    def forward(self, ctx, x, rows=None, tag="norm"):
+        n_rows = x.shape[0] if rows is None else rows.shape[0]
+        out = ctx.buffer(tag, (n_rows, self.width), ctx.act_dtype)
+        ctx.kernels.layernorm(out, x, self.w("weight"), self.w("bias"), self.eps, rows)
+        return out
+
+
+register_part("layer_norm", LayerNorm)

@@ -1,0 +1,6 @@
+from .loader import WeightsError, collect_specs, load_weights
+from .random_init import random_tensors, write_random_model
+from .safetensors_io import SafetensorsError, SafetensorsFile, write_safetensors
+
+__all__ = ["WeightsError", "collect_specs", "load_weights", "random_tensors", "write_random_model",
+           "SafetensorsError", "SafetensorsFile", "write_safetensors"]
