@@ -1,0 +1,198 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16, under every way
+of cutting the same requests into steps."""
+
+import json
+import os
+import subprocess
+import sys
+import zlib
+
+import numpy as np
+import pytest
+
+from engine_helpers import (F32_ATOL, bf16_atol, make_model, plain_logits, random_tokens, run_schedule,
+                            schedule_mixed, schedule_portions, schedule_tail_one_by_one, schedule_whole)
+from tiny_configs import RECIPES, TINY_A, TINY_B, TINY_C
+
+pytestmark = pytest.mark.gpu
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+PAGE_SIZES = {"A": 16, "B": 8, "C": 16}
+# factor on the query and key weights that brings the scores' spread to about 1 (see
+# engine_helpers.sharpen_attention); it depends on the recipe's weight scale and the width
+SHARPEN = {"A": 6.0, "B": 2.0, "C": 2.0}
+# request lengths per configuration (within n_positions); prompts for the mixed schedule
+LENGTHS = {"A": {"a": 5, "b": 17, "c": 33, "d": 70, "e": 128},
+           "B": {"a": 1, "b": 9, "c": 24, "d": 40, "e": 160, "f": 77},
+           "C": {"a": 300, "b": 45, "c": 131, "d": 2, "e": 640}}
+
+
+@pytest.fixture(scope="session")
+def folders(tmp_path_factory):
+    out = {}
+    for key, raw in CONFIGS.items():
+        recipe, seed = RECIPES[key]
+        out[key] = make_model(str(tmp_path_factory.mktemp(f"tiny_{key}")), raw, recipe, seed, sharpen=SHARPEN[key])
+    return out
+
+
+def requests_of(key):
+    vocab = CONFIGS[key]["vocab_size"]
+    return {name: random_tokens(zlib.crc32(f"{key}/{name}".encode()) % 1000 + i, n, vocab)
+            for i, (name, n) in enumerate(LENGTHS[key].items())}
+
+
+_engines = {}
+
+
+def engine_of(folders, key, dtype, cache_tokens=None, **kw):
+    from mini_llm_b200.engine import Engine
+    handle = (key, dtype, cache_tokens, tuple(sorted(kw.items())))
+    if handle not in _engines:
+        _engines[handle] = Engine(folders[key], dtype=dtype, page_size=PAGE_SIZES[key],
+                                  cache_tokens=cache_tokens or 4096, max_requests=8, **kw)
+    return _engines[handle]
+
+
+def check(key, folders, dtype, got, requests):
+    worst = 0.0
+    for name, tokens in requests.items():
+        expected = plain_logits(folders[key], tokens, bf16_weights=(dtype == "bfloat16"))
+        assert not np.isnan(got[name]).any(), f"request {name}: logits missing"
+        atol = F32_ATOL if dtype == "float32" else bf16_atol(expected)
+        diff = np.abs(got[name] - expected).max(axis=1)
+        first_bad = np.flatnonzero(diff > atol)
+        assert first_bad.size == 0, (f"config {key} {dtype} request {name} (len {len(tokens)}): first wrong position "
+                                     f"{first_bad[0]}, |diff| {diff[first_bad[0]]:.3g} > {atol:.3g}")
+        worst = max(worst, float(diff.max()) / atol)
+    return worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ["A", "B", "C"])
+@pytest.mark.parametrize("cut", ["whole", "tail", "portions"])
+def test_each_request_alone(folders, key, dtype, cut):
+    requests = requests_of(key)
+    steps = {"whole": schedule_whole, "tail": schedule_tail_one_by_one, "portions": schedule_portions}[cut](requests)
+    engine = engine_of(folders, key, dtype)
+    got = run_schedule(engine, requests, steps)
+    check(key, folders, dtype, got, requests)
+    assert engine.cache.pages_in_use() == [0]
+    engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ["A", "B", "C"])
+def test_mixed_batches_with_reused_pages(folders, key, dtype):
+    requests = requests_of(key)
+    longest = sorted(len(t) for t in requests.values())
+    # room for the four longest together, rounded up to pages: later requests must reuse pages
+    page = PAGE_SIZES[key]
+    cache_tokens = sum(-(-n // page) * page for n in longest[-4:])
+    prompts = {name: max(1, (2 * len(t)) // 3) for name, t in requests.items()}
+    engine = engine_of(folders, key, dtype, cache_tokens=cache_tokens)
+    before = engine.cache.groups[0].pool.reused
+    # twice over, in two orders: the second pass runs entirely on used pages
+    for order in (list(requests), list(reversed(list(requests)))):
+        ordered = {n: requests[n] for n in order}
+        steps = schedule_mixed(ordered, prompts, max_live=4)
+        assert max(len(s) for s in steps) == min(4, len(requests))
+        assert any(len({n for _, n in s}) > 1 and min(n for _, n in s) == 1 for s in steps), "no mixed step"
+        got = run_schedule(engine, ordered, steps)
+        check(key, folders, dtype, got, ordered)
+    assert engine.cache.groups[0].pool.reused > before
+    assert engine.cache.pages_in_use() == [0]
+    engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(folders, dtype):
+    key = "C"
+    tokens = random_tokens(11, 400, CONFIGS[key]["vocab_size"])
+    requests = {"long": tokens}
+    steps = [[("long", 3)]] + [[("long", 1)]] * 397
+    got = run_schedule(engine_of(folders, key, dtype), requests, steps)
+    check(key, folders, dtype, got, requests)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ["A", "B"])
+def test_first_tokens_of_a_sequence(folders, key, dtype):
+    vocab = CONFIGS[key]["vocab_size"]
+    requests = {"one": random_tokens(1, 1, vocab), "two": random_tokens(2, 2, vocab), "three": random_tokens(3, 3, vocab)}
+    engine = engine_of(folders, key, dtype)
+    check(key, folders, dtype, run_schedule(engine, requests, schedule_whole(requests)), requests)
+    check(key, folders, dtype, run_schedule(engine, requests, [[("one", 1), ("two", 1), ("three", 1)],
+                                                               [("two", 1), ("three", 1)], [("three", 1)]]), requests)
+
+
+def test_cuts_agree_with_each_other_closely(folders):
+    """Beyond the comparison with the plain implementation: on the 32-bit path, two ways of
+    cutting differ by rounding only."""
+    key = "B"
+    requests = requests_of(key)
+    engine = engine_of(folders, key, "float32")
+    whole = run_schedule(engine, requests, schedule_whole(requests))
+    parts = run_schedule(engine, requests, schedule_portions(requests))
+    for name in requests:
+        np.testing.assert_allclose(parts[name], whole[name], rtol=0, atol=2e-5)
+
+
+def test_refused_steps_change_nothing(folders):
+    from mini_llm_b200.engine import OutOfPages, StepEntry, StepError
+    engine = engine_of(folders, "A", "float32", cache_tokens=64)
+    slot = engine.open_request()
+    other = engine.open_request()
+    for bad in ([StepEntry(slot, [], [])], [StepEntry(slot, [512], [0])], [StepEntry(slot, [-1], [0])],
+                [StepEntry(slot, [1, 2], [2])], [StepEntry(slot, [1], []), StepEntry(slot, [2], [])],
+                [StepEntry(99, [1], [0])], [StepEntry(slot, [1] * 129, [])], []):
+        with pytest.raises(StepError):
+            engine.step(bad)
+    with pytest.raises(OutOfPages):
+        engine.step([StepEntry(slot, [1] * 40, [39]), StepEntry(other, [2] * 40, [39])])
+    assert engine.cached_tokens(slot) == 0 and engine.cache.pages_in_use() == [0]
+    tokens = random_tokens(5, 40, 512)
+    got = engine.step([StepEntry(slot, tokens, [39])]).cpu().numpy()
+    np.testing.assert_allclose(got[0], plain_logits(folders["A"], tokens)[-1], rtol=0, atol=F32_ATOL)
+    engine.close_request(slot)
+    engine.close_request(other)
+    engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(folders, tmp_path, dtype):
+    """bin/trace_run as a user runs it: a subprocess, steps on standard input."""
+    key = "B"
+    requests = {"p": random_tokens(21, 50, 1000), "q": random_tokens(22, 37, 1000), "r": random_tokens(23, 64, 1000)}
+    lines, expected_files = [], {}
+    progress = {n: 0 for n in requests}
+    plan = [[("p", 20)], [("p", 2), ("q", 30)], [("p", 1), ("q", 1)], [("p", 27), ("q", 6)], [("r", 64)]]
+    for step, batch in enumerate(plan):
+        entries, places, end = [], [], []
+        for name, n in batch:
+            start = progress[name]
+            want = [n - 1] if step != 3 else list(range(n))
+            entries.append({"id": name, "tokens": requests[name][start:start + n], "want": want})
+            places.extend((name, start + w) for w in want)
+            progress[name] += n
+            if progress[name] == len(requests[name]):
+                end.append(name)
+        lines.append(json.dumps({"step": step, "entries": entries, "end": end}))
+        expected_files[step] = places
+    lines.insert(3, json.dumps({"step": 77, "entries": [{"id": "p", "tokens": [], "want": []}][:0], "end": []}))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "out"
+    # 128 tokens: p (50 -> 64) and q (37 -> 64) live together; r (64) afterwards on their pages
+    done = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folders[key], "--dtype", dtype,
+                           "--out", str(out), "--max-tokens", "128", "--page-size", "8"],
+                          input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    assert [l for l in done.stdout.split("\n") if l.startswith("done")] == ["done 0", "done 1", "done 2", "done 77",
+                                                                          "done 3", "done 4"]
+    for step, places in expected_files.items():
+        got = np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(len(places), 1000)
+        for row, (name, position) in zip(got, places):
+            expected = plain_logits(folders[key], requests[name], bf16_weights=(dtype == "bfloat16"))
+            atol = F32_ATOL if dtype == "float32" else bf16_atol(expected)
+            assert np.abs(row - expected[position]).max() <= atol, (step, name, position)
+    assert not (out / "77.f32").exists()

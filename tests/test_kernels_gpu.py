@@ -1,0 +1,250 @@
+"""Each kernel alone against a plain computation of the same operation, at sizes other than
+the engine tests' (widths and vocabularies that are no power of two, head sizes from 16 to
+256 in steps of 16, groups of heads, rows that do not fill a tile)."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gpt2 as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, scale=1.0):
+    return (2e-5 if dtype == torch.float32 else 1.6e-2) * scale
+
+
+def dev(array, dtype=None):
+    t = torch.as_tensor(np.asarray(array)).cuda()
+    return t.to(dtype) if dtype is not None else t
+
+
+def f64(t):
+    return t.detach().double().cpu().numpy()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [48, 200, 1600])
+def test_embed(dtype, width):
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(width)
+    table, ptable = dev(rng.normal(size=(301, width)), dtype), dev(rng.normal(size=(77, width)), dtype)
+    ids, pos = rng.integers(0, 301, 29), rng.integers(0, 77, 29)
+    out = torch.empty(29, width, device="cuda")
+    ops.embed(out, dev(ids, torch.int32), dev(pos, torch.int32), table, ptable)
+    np.testing.assert_allclose(f64(out), f64(table)[ids] + f64(ptable)[pos], rtol=0, atol=1e-6)
+    ops.embed(out, dev(ids, torch.int32), None, table, None)
+    np.testing.assert_array_equal(f64(out), f64(table)[ids])
+    ops.add_position_rows(out, dev(pos, torch.int32), ptable)
+    np.testing.assert_allclose(f64(out), f64(table)[ids] + f64(ptable)[pos], rtol=0, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width, eps", [(80, 1e-5), (768, 1e-6), (1600, 1e-3), (3000, 1e-5)])
+def test_layernorm(dtype, width, eps):
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(width)
+    x = dev(rng.normal(3.0, 5.0, size=(23, width)), torch.float32)       # a large mean: one-pass variance would fail
+    gain, shift = dev(rng.uniform(0.5, 1.5, width), torch.float32), dev(rng.normal(0, 0.1, width), torch.float32)
+    out = torch.empty(23, width, device="cuda", dtype=dtype)
+    ops.layernorm(out, x, gain, shift, eps)
+    expected = plain.layer_norm(f64(x), f64(gain), f64(shift), eps)
+    np.testing.assert_allclose(f64(out), expected, rtol=0, atol=tol(dtype, 4))
+    rows = [22, 0, 7, 7]
+    some = torch.empty(4, width, device="cuda", dtype=dtype)
+    ops.layernorm(some, x, gain, shift, eps, dev(rows, torch.int32))
+    np.testing.assert_allclose(f64(some), expected[rows], rtol=0, atol=tol(dtype, 4))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m, n, k", [(1, 50, 96), (7, 1000, 160), (65, 129, 33), (130, 768, 3072), (2, 50257, 64)])
+@pytest.mark.parametrize("epilogue", ["store", "gelu_tanh", "gelu_erf", "add"])
+def test_linear_plain(dtype, m, n, k, epilogue):
+    from mini_llm_b200.kernels import ops
+    if epilogue != "store" and n > 2000:
+        pytest.skip("epilogues are covered at the smaller sizes")
+    rng = np.random.default_rng(m * n + k)
+    a, w = dev(rng.normal(size=(m, k)), dtype), dev(rng.normal(size=(n, k)) / math.sqrt(k), dtype)
+    bias = dev(rng.normal(size=n), torch.float32)
+    acc = f64(a) @ f64(w).T + f64(bias)
+    if epilogue == "add":
+        out = dev(rng.normal(size=(m, n)), torch.float32)
+        expected = f64(out) + acc
+        ops.linear_plain(out, a, w, bias, "add")
+    else:
+        out = torch.full((m, n), float("nan"), device="cuda", dtype=dtype)
+        ops.linear_plain(out, a, w, bias, epilogue)
+        expected = {"store": acc, "gelu_tanh": plain.gelu_tanh(acc), "gelu_erf": plain.gelu_erf(acc)}[epilogue]
+    out_tol = tol(torch.float32 if epilogue == "add" else dtype, 4)
+    np.testing.assert_allclose(f64(out), expected, rtol=0, atol=out_tol)
+    # a strided input (a column slice) and no bias
+    wide = dev(rng.normal(size=(m, k + 24)), dtype)
+    out2 = torch.empty(m, n, device="cuda", dtype=dtype)
+    ops.linear_plain(out2, wide[:, 8:8 + k], w, None, "store")
+    np.testing.assert_allclose(f64(out2), f64(wide)[:, 8:8 + k] @ f64(w).T, rtol=0, atol=tol(dtype, 4))
+
+
+def paged_case(rng, lengths, n_new, n_heads, n_kv_heads, head, page, dtype, extra_pages=5):
+    """Requests with ``lengths[i]`` cached tokens each, of which the last ``n_new[i]`` are this
+    step's; pages handed out in a shuffled order.  Returns device tensors and the dense K, V."""
+    width = n_kv_heads * head
+    max_blocks = max(-(-l // page) for l in lengths) + 1
+    n_pages = sum(-(-l // page) for l in lengths) + extra_pages
+    order = rng.permutation(n_pages)
+    table = np.full((len(lengths), max_blocks), -1, dtype=np.int32)
+    k_pages = np.full((n_pages, page, width), np.nan)
+    v_pages = np.full((n_pages, page, width), np.nan)
+    dense, positions, items = [], [], []
+    used = 0
+    for i, (length, new) in enumerate(zip(lengths, n_new)):
+        k, v = rng.normal(size=(length, width)), rng.normal(size=(length, width))
+        dense.append((k, v))
+        for b in range(-(-length // page)):
+            table[i, b] = order[used]
+            used += 1
+        for p in range(length):
+            k_pages[table[i, p // page], p % page] = k[p]
+            v_pages[table[i, p // page], p % page] = v[p]
+        positions.extend(range(length - new, length))
+        items.extend([i] * new)
+    return (dev(np.nan_to_num(k_pages, nan=1e4), dtype), dev(np.nan_to_num(v_pages, nan=1e4), dtype),
+            dev(table), dev(np.array(positions, dtype=np.int32)), dev(np.array(items, dtype=np.int32)), dense)
+
+
+def attention_expected(q, dense, positions, items, n_heads, n_kv_heads, head, scale, window):
+    out = np.zeros_like(q)
+    for t, (p, i) in enumerate(zip(positions, items)):
+        k, v = dense[i]
+        lo = max(0, p - window + 1) if window else 0
+        for h in range(n_heads):
+            g = h // (n_heads // n_kv_heads)
+            s = (k[lo:p + 1, g * head:(g + 1) * head] @ q[t, h * head:(h + 1) * head]) * scale
+            w = np.exp(s - s.max())
+            out[t, h * head:(h + 1) * head] = (w / w.sum()) @ v[lo:p + 1, g * head:(g + 1) * head]
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_heads, n_kv_heads, head, page, window", [
+    (3, 3, 16, 16, 0), (2, 2, 48, 8, 0), (6, 2, 64, 16, 0), (5, 1, 80, 4, 0), (1, 1, 256, 16, 0),
+    (4, 2, 32, 8, 21), (2, 2, 64, 16, 16), (25, 25, 64, 16, 0)])
+def test_attention_plain_over_pages(dtype, n_heads, n_kv_heads, head, page, window):
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(n_heads * head + page)
+    lengths, n_new = [37, 1, 300, 64, 17], [37, 1, 1, 9, 2]      # a whole prompt, first token, decode, portions
+    k_pages, v_pages, table, positions, items, dense = paged_case(rng, lengths, n_new, n_heads, n_kv_heads, head,
+                                                                  page, dtype)
+    dense = [(f64(dev(k, dtype)), f64(dev(v, dtype))) for k, v in dense]
+    q = dev(rng.normal(size=(len(f64(positions)), n_heads * head)), dtype)
+    out = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(head)
+    ops.attention_plain(out, q, k_pages, v_pages, table, positions, items, n_heads, n_kv_heads, head, page, scale,
+                        window)
+    expected = attention_expected(f64(q), dense, f64(positions).astype(int), f64(items).astype(int), n_heads,
+                                  n_kv_heads, head, scale, window)
+    np.testing.assert_allclose(f64(out), expected, rtol=0, atol=tol(dtype, 2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key_and_respects_the_windows_edge(dtype):
+    """One key among hundreds is made to stand out (query and key scaled), on a page of its
+    own far from the query; its value must come through.  With a window that ends one short
+    of it, it must vanish."""
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(5)
+    head, page, length = 64, 16, 500
+    far = 3 * page + 5                                  # position 53: fourth page
+    k_pages, v_pages, table, positions, items, dense = paged_case(rng, [length], [1], 1, 1, head, page, dtype)
+    k, v = dense[0]
+    q = rng.normal(size=(1, head))
+    k[far] = q[0] * 4.0 / math.sqrt(head)               # score (q.k)/sqrt(D) about 4 |q|^2 / D ... far above the rest
+    k[far] *= 8.0
+    v[far] = 100.0 + np.arange(head)
+    block, offset = int(f64(table)[0, far // page]), far % page
+    k_pages[block, offset] = dev(k[far], dtype)
+    v_pages[block, offset] = dev(v[far], dtype)
+    qd = dev(q, dtype)
+    out = torch.empty_like(qd)
+    scale = 1.0 / math.sqrt(head)
+    ops.attention_plain(out, qd, k_pages, v_pages, table, positions, items, 1, 1, head, page, scale, 0)
+    np.testing.assert_allclose(f64(out)[0], f64(dev(v[far], dtype)), rtol=2e-2, atol=0.5)
+    window = length - 1 - far                           # keys far+1 .. length-1: the far key is just outside
+    ops.attention_plain(out, qd, k_pages, v_pages, table, positions, items, 1, 1, head, page, scale, window)
+    assert float(out.float().abs().max()) < 10.0
+    ops.attention_plain(out, qd, k_pages, v_pages, table, positions, items, 1, 1, head, page, scale, window + 1)
+    np.testing.assert_allclose(f64(out)[0], f64(dev(v[far], dtype)), rtol=2e-2, atol=0.5)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_kv_store_writes_only_its_own_slots(dtype):
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(9)
+    page, width, n_pages = 8, 96, 12
+    k_pages = torch.full((n_pages, page, width), 7.0, device="cuda", dtype=dtype)
+    v_pages = torch.full((n_pages, page, width), 7.0, device="cuda", dtype=dtype)
+    table = dev(np.array([[5, 2, -1], [9, 0, 11]], dtype=np.int32))
+    positions = dev(np.array([6, 7, 8, 9, 17], dtype=np.int32))          # crosses a page edge
+    items = dev(np.array([0, 0, 0, 0, 1], dtype=np.int32))
+    src = dev(rng.normal(size=(5, 3 * width)), dtype)                    # keys and values as column slices
+    ops.kv_store(k_pages, v_pages, src[:, width:2 * width], src[:, 2 * width:], positions, items, table, page)
+    expect_k = torch.full_like(k_pages, 7.0)
+    expect_v = torch.full_like(v_pages, 7.0)
+    for row, (pg, off) in enumerate([(5, 6), (5, 7), (2, 0), (2, 1), (11, 1)]):
+        expect_k[pg, off] = src[row, width:2 * width]
+        expect_v[pg, off] = src[row, 2 * width:]
+    assert torch.equal(k_pages, expect_k) and torch.equal(v_pages, expect_v)
+
+
+def test_sampling_greedy_rules():
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(3)
+    logits = rng.normal(size=(6, 50257)).astype(np.float32)
+    logits[1, 777] = logits[1, 40000] = 9.0           # a tie: the first index wins
+    logits[2, 50256] = 11.0                           # the last column
+    logits[3, 123] = np.nan                           # a NaN beats numbers, the first NaN wins
+    logits[3, 4567] = np.nan
+    logits[4, 0] = 12.0
+    logits[5] = -np.inf
+    out = torch.empty(6, dtype=torch.int32, device="cuda")
+    ops.sample_rows(out, dev(logits))
+    assert out.tolist() == [plain.argmax_first(row) for row in logits]
+    assert out.tolist()[1:] == [777, 50256, 123, 0, 0]
+
+
+@pytest.mark.parametrize("vocab", [1000, 50257])
+def test_sampling_temperature_and_nucleus_match_the_plain_sampler(vocab):
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(vocab)
+    rows = 24
+    logits = (rng.normal(size=(rows, vocab)) * 2.0).astype(np.float32)
+    temperature = np.array([0.8, 1.0, 0.3, 1.7] * 6, dtype=np.float32)
+    top_p = np.array([1.0] * 8 + [0.95] * 8 + [0.5] * 4 + [0.05] * 4, dtype=np.float32)
+    seeds = rng.integers(0, 2 ** 63, rows)
+    counters = rng.integers(0, 1000, rows).astype(np.int32)
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    ops.sample_rows(out, dev(logits), dev(temperature), dev(top_p), dev(seeds.astype(np.int64)), dev(counters))
+    got = out.tolist()
+    near_ties = 0
+    for r in range(rows):
+        choice, margin = plain.sample(logits[r], float(temperature[r]), float(top_p[r]), int(seeds[r]),
+                                      int(counters[r]), return_margin=True)
+        if got[r] != choice:
+            assert margin < 1e-3, f"row {r}: engine chose {got[r]}, plain {choice} with margin {margin}"
+            near_ties += 1
+    assert near_ties <= 1
+    again = torch.empty(rows, dtype=torch.int32, device="cuda")
+    ops.sample_rows(again, dev(logits), dev(temperature), dev(top_p), dev(seeds.astype(np.int64)), dev(counters + 1))
+    assert again.tolist() != got                      # another counter, another draw
+    # the frequencies of many draws follow the softmax
+    few = np.array([[0.0, 1.0, 2.0, -1.0, 0.5]], dtype=np.float32).repeat(4000, axis=0)
+    out = torch.empty(4000, dtype=torch.int32, device="cuda")
+    ops.sample_rows(out, dev(few), dev(np.ones(4000, dtype=np.float32)), None,
+                    dev(np.full(4000, 99, dtype=np.int64)), dev(np.arange(4000, dtype=np.int32)))
+    freq = np.bincount(out.cpu().numpy(), minlength=5) / 4000.0
+    p = np.exp(few[0]) / np.exp(few[0]).sum()
+    assert np.abs(freq - p).max() < 0.03
