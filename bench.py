@@ -1,0 +1,304 @@
+#!/usr/bin/env python3
+"""Benchmark: decode throughput of GPT-2 small (random weights) on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step of a batch of 8 requests whose contexts end at the model's
+context length (1024).  ``value`` is decoded tokens per second, timed on the device with CUDA
+events around exactly K steps; ``e2e`` is the same metric through the Python entry point
+(``LLM.generate``): token ids from the host in, sampled token ids to the host out, every
+step.  The same line carries the prefill of 2,048 tokens (two prompts of 1024), the decode
+step's memory roofline, and decode throughput at batch 1 and 64.
+
+The reference's counterparts are ``engine/bench/bench_batch.c:24-122`` (batched decode:
+prefill untimed, one warm-up step, then timed steps) and ``engine/bench/bench.c`` (prefill).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: GPT-2 small.  Layers may be reduced with --layers where time or
+# memory needs it; the line then names both numbers.
+GPT2_SMALL = {"architectures": ["GPT2LMHeadModel"], "model_type": "gpt2", "n_layer": 12, "n_embd": 768, "n_head": 12,
+              "n_inner": 3072, "vocab_size": 50257, "n_positions": 1024, "activation_function": "gelu_new",
+              "layer_norm_epsilon": 1e-5, "tie_word_embeddings": True}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def parse_args():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=128)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--dtype", default="bfloat16", choices=("bfloat16", "float32"))
+    parser.add_argument("--layers", type=int, default=GPT2_SMALL["n_layer"])
+    parser.add_argument("--plain-kernels", action="store_true")
+    parser.add_argument("--no-extras", action="store_true", help="skip prefill, batch 1/64 and the end-to-end run")
+    return parser.parse_args()
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as handle:
+                raw = json.load(handle)
+            out = dict(FALLBACK_PEAKS)
+            for key in out:
+                if isinstance(raw.get(key), (int, float)):
+                    out[key] = float(raw[key])
+            out["source"] = "measured"
+            return out
+        except (OSError, ValueError):
+            pass
+    return {**FALLBACK_PEAKS, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self):
+        self.process = None
+        self.file = None
+
+    def start(self):
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.process = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                             "-i", "0", "-lms", "100"], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.process = None
+
+    def stop(self) -> dict:
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.process.terminate()
+        self.process.wait()
+        self.file.flush()
+        self.file.seek(0)
+        clocks, top, reasons = [], None, set()
+        for line in self.file.read().splitlines():
+            cells = [c.strip() for c in line.split(",")]
+            if len(cells) < 6:
+                continue
+            try:
+                clocks.append(float(cells[0]))
+                top = float(cells[1])
+            except ValueError:
+                continue
+            for name, cell in zip(self.NAMES, cells[2:6]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        self.file.close()
+        os.unlink(self.file.name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": top,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def model_numbers(config: dict, dtype_bytes: int):
+    e, i, v, layers = config["n_embd"], config["n_inner"], config["vocab_size"], config["n_layer"]
+    matrix_params = layers * (e * 3 * e + e * e + 2 * e * i)
+    vector_params = layers * (3 * e + e + i + e + 4 * e) + 2 * e
+    weight_bytes = (matrix_params + v * e) * dtype_bytes + vector_params * 4      # every weight a decode step uses, once
+    kv_bytes_per_token = layers * 2 * e * dtype_bytes
+    return matrix_params, weight_bytes, kv_bytes_per_token
+
+
+def prefill_flops(config: dict, n_prompts: int, length: int, wanted_rows: int) -> float:
+    e, v, layers = config["n_embd"], config["vocab_size"], config["n_layer"]
+    matrix_params, _, _ = model_numbers(config, 2)
+    tokens = n_prompts * length
+    gemm = 2.0 * tokens * matrix_params
+    attention = layers * n_prompts * 2.0 * length * length * e          # causal half of QK^T and PV
+    head = 2.0 * wanted_rows * v * e
+    return gemm + attention + head
+
+
+def make_model_folder(config: dict, folder: str) -> str:
+    from mini_llm_b200.config import config_from_dict
+    from mini_llm_b200.weights import write_random_model
+    return write_random_model(config_from_dict(config), 0, folder, recipe="gpt2", store_dtype="float32")
+
+
+def decode_run(engine, batch: int, steps: int, warmup: int, context: int, vocab: int):
+    """Device-timed decode: ``batch`` requests prefilled so that the timed steps end at
+    ``context`` tokens.  Token ids are fixed in advance (nothing is read back inside the timed
+    region); every step samples greedily on the device.  Returns (ms per step, launches per
+    step, mean cached tokens per request during the timed steps)."""
+    import numpy as np
+    import torch
+    from mini_llm_b200.engine import SamplingParams, StepEntry
+
+    rng = np.random.default_rng(1234)
+    prompt_len = context - steps - warmup
+    if prompt_len < 1:
+        raise SystemExit(f"--steps + --warmup must stay below the context length {context}")
+    slots = [engine.open_request() for _ in range(batch)]
+    for slot in slots:                                   # untimed prefill, one request per step
+        engine.step([StepEntry(slot, rng.integers(0, vocab, prompt_len).tolist(), [])])
+    feed = rng.integers(0, vocab, (steps + warmup, batch))
+    greedy = [SamplingParams() for _ in range(batch)]
+
+    def one(index):
+        engine.step([StepEntry(slot, [int(feed[index, b])], [0]) for b, slot in enumerate(slots)], greedy)
+
+    for index in range(warmup):
+        one(index)
+    torch.cuda.synchronize()
+    launches_before = engine.kernels.launches
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for index in range(warmup, warmup + steps):
+        one(index)
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / steps
+    launches = (engine.kernels.launches - launches_before) / steps
+    for slot in slots:
+        engine.close_request(slot)
+    mean_cached = prompt_len + warmup + (steps - 1) / 2.0
+    return ms, launches, mean_cached
+
+
+def prefill_run(engine, n_prompts: int, length: int, vocab: int, repeats: int = 5):
+    import numpy as np
+    import torch
+    from mini_llm_b200.engine import StepEntry
+
+    rng = np.random.default_rng(99)
+    prompts = [rng.integers(0, vocab, length).tolist() for _ in range(n_prompts)]
+    times = []
+    for repeat in range(repeats + 2):
+        slots = [engine.open_request() for _ in range(n_prompts)]
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        engine.step([StepEntry(slot, prompt, [length - 1]) for slot, prompt in zip(slots, prompts)])
+        stop.record()
+        torch.cuda.synchronize()
+        if repeat >= 2:
+            times.append(start.elapsed_time(stop))
+        for slot in slots:
+            engine.close_request(slot)
+    return statistics.median(times)
+
+
+def e2e_run(folder, args, context: int, vocab: int):
+    """The same decode metric through ``LLM.generate``: prompts go in as host token ids, every
+    step uploads its control block from pinned host memory and reads the sampled ids back."""
+    import numpy as np
+    from mini_llm_b200.generate import LLM
+
+    steps, warmup, batch = args.steps, args.warmup, args.batch
+    rng = np.random.default_rng(4321)
+    prompt_len = context - steps - warmup
+    prompts = [rng.integers(0, vocab, prompt_len).tolist() for _ in range(batch)]
+    llm = LLM(folder, dtype=args.dtype, max_sessions=batch, cache_tokens=batch * context,
+              max_tokens_per_step=max(2048, batch), plain_kernels=args.plain_kernels)
+    stamps = []
+
+    def on_token(index, token, reason):
+        if index == batch - 1:
+            stamps.append(time.perf_counter())
+
+    launches_before = llm.engine.kernels.launches
+    out = llm.generate(prompts, max_new_tokens=steps + warmup, temperature=0.0, on_token=on_token)
+    assert all(len(tokens) == steps + warmup for tokens in out)
+    seconds = stamps[-1] - stamps[warmup - 1]              # K steps after the warm-up steps
+    control_bytes = 4 * (7 * batch + (batch & 1) + 2 * batch + batch * llm.engine.cache.groups[0].max_blocks)
+    return {"value": batch * steps / seconds, "unit": "tokens/s", "h2d_bytes_per_step": control_bytes,
+            "d2h_bytes_per_step": 4 * batch, "ms_per_step": 1000.0 * seconds / steps}
+
+
+def run_ours(args):
+    import torch
+    from mini_llm_b200.engine import Engine
+
+    config = dict(GPT2_SMALL)
+    config["n_layer"] = args.layers
+    context, vocab = config["n_positions"], config["vocab_size"]
+    dtype_bytes = 2 if args.dtype == "bfloat16" else 4
+    peak = peaks()
+    with tempfile.TemporaryDirectory() as folder:
+        make_model_folder(config, folder)
+        engine = Engine(folder, dtype=args.dtype, max_requests=64, cache_tokens=64 * context,
+                        max_tokens_per_step=2048, plain_kernels=args.plain_kernels)
+        _, weight_bytes, kv_per_token = model_numbers(config, dtype_bytes)
+
+        sampler = ClockSampler()
+        sampler.start()
+        ms, launches, mean_cached = decode_run(engine, args.batch, args.steps, args.warmup, context, vocab)
+        clocks = sampler.stop()
+        step_bytes = weight_bytes + args.batch * mean_cached * kv_per_token
+        achieved = step_bytes / (ms * 1e-3) / 1e9
+        line = {
+            "metric": "decode tokens/s, GPT-2 small, batch 8, context 1024", "value": args.batch / (ms * 1e-3),
+            "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if dtype_bytes == 2 else "fp32",
+            "data": "synthetic: seeded random weights (N(0, 0.02)) and uniform random token ids", "impl": "ours",
+            "config": {"model": "gpt2-small", "n_layer": config["n_layer"], "n_layer_of_model": GPT2_SMALL["n_layer"],
+                       "n_embd": config["n_embd"], "n_head": config["n_head"], "n_inner": config["n_inner"],
+                       "vocab_size": vocab, "n_positions": context, "global_batch": args.batch, "seq_len": context,
+                       "prompt_tokens": context - args.steps - args.warmup, "page_size": engine.page_size,
+                       "parallelism": "single GPU", "l2": "inputs larger than L2 (weights + cache per step)",
+                       "peaks": peak["source"]},
+            "gpu_launches": int(round(launches * args.steps)),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / peak["hbm_gbs"], "bytes_per_step": step_bytes},
+            "clocks": clocks,
+        }
+        if not args.no_extras:
+            points = {}
+            for batch in (1, 64):
+                p_ms, _, _ = decode_run(engine, batch, min(args.steps, 64), max(3, min(args.warmup, 8)), context, vocab)
+                points[f"decode_b{batch}"] = batch / (p_ms * 1e-3)
+            line["points"] = points
+            prefill_ms = prefill_run(engine, 2, 1024, vocab)
+            flops = prefill_flops(config, 2, 1024, 2)
+            peak_flops = (peak["bf16_tflops"] if dtype_bytes == 2 else peak["bf16_tflops"]) * 1e12
+            line["prefill"] = {"value": 2048 / (prefill_ms * 1e-3), "tokens": 2048, "ms": prefill_ms,
+                               "frac": flops / (prefill_ms * 1e-3) / peak_flops, "flops": flops}
+            del engine
+            torch.cuda.empty_cache()
+            line["e2e"] = e2e_run(folder, args, context, vocab)
+    print(json.dumps(line))
+    return 0
+
+
+def run_reference(args):
+    print(json.dumps({"impl": "reference", "unavailable": "the reference arm is not wired up yet"}))
+    return 0
+
+
+def main():
+    args = parse_args()
+    if args.gpus != 1:
+        print(f"this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

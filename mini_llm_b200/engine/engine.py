@@ -23,6 +23,7 @@ from ..cache.manager import CacheManager
 from ..cache.storage import CacheStorage
 from ..config.registry import config_from_folder, describe_model
 from ..kernels.dispatch import Kernels
+from ..sampling import SamplingParams
 from .context import ControlBlock, StepContext, Workspace
 from .model import Model
 
@@ -42,14 +43,6 @@ class StepEntry:
     slot: int                     # the request's slot, from ``open_request``
     tokens: list                  # its next tokens
     want: list = field(default_factory=list)     # places among these tokens whose logits are wanted
-
-
-@dataclass
-class SamplingParams:
-    temperature: float = 0.0      # <= 0: greedy
-    top_p: float = 1.0            # >= 1: no nucleus cut
-    seed: int = 0
-    counter: int = 0              # how many tokens this request has sampled so far
 
 
 class Engine:

@@ -207,6 +207,18 @@ class Scheduler:
                 continue
             take(running, n, n == len(running.pending))
             budget -= n
+        # A new request is admitted only if the pages of its WHOLE prompt (and of its first
+        # new token) are free beyond what this step takes and what the prompts still being
+        # prefilled will take: a request admitted on less would soon be preempted again.
+        promised = [0] * len(cache.groups)
+        for running in self.running:
+            if not running.decoding:
+                rest = len(running.pending) - (len(entries[owners.index(running)].tokens) if running in owners else 0)
+                whole = cache.pages_needed(running.slot, min(len(running.pending) + 1, self.engine.max_positions -
+                                                             cache.length(running.slot)))
+                now = cache.pages_needed(running.slot, len(running.pending) - rest)
+                for g in range(len(promised)):
+                    promised[g] += whole[g] - now[g]
         while budget > 0 and self.waiting and (self.max_batch is None or len(self.running) < self.max_batch):
             request = self.waiting[0]
             if request.cancelled:
@@ -216,21 +228,24 @@ class Scheduler:
             if slot is None:
                 break                         # no slot: wait for a running request to end
             pending = list(request.tokens) + list(request.generated)
-            n = min(len(pending), self.chunk, budget)
-            if not cache.can_reserve(slot, n, spare):
-                n = self._largest_fit(slot, n, spare)
-            if n <= 0:
+            whole = min(len(pending) + 1, self.engine.max_positions)
+            if not cache.can_reserve(slot, whole, [a + b for a, b in zip(spare, promised)]):
                 self.engine.close_request(slot)
                 if not self.running:
                     self.waiting.popleft()
                     self._fail(request, "out of pages: the request does not fit the cache even alone")
                     continue
                 break                         # no pages: wait; nothing overtakes this request
+            n = min(len(pending), self.chunk, budget)
             self.waiting.popleft()
             running = _Running(request, slot, pending, self._admitted)
             self._admitted += 1
             self.running.append(running)
+            needed_whole = cache.pages_needed(slot, whole)
             take(running, n, n == len(pending))
+            needed_now = cache.pages_needed(slot, n)
+            for g in range(len(promised)):
+                promised[g] += needed_whole[g] - needed_now[g]
             budget -= n
         return entries, owners
 

@@ -1,0 +1,118 @@
+"""Generation through the Python entry point and the command line, against the plain
+implementation recomputing the whole sequence for every token."""
+
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import plain_gpt2 as plain
+from engine_helpers import make_model, random_tokens
+from tiny_configs import TINY_A, TINY_B
+
+pytestmark = pytest.mark.gpu
+
+# A chosen token may differ from the plain implementation's only where the two best
+# candidates are this close (logit units, after temperature and noise).
+MARGIN = {"float32": 1e-4, "bfloat16": 3e-2}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return {"A": make_model(str(tmp_path_factory.mktemp("gen_a")), TINY_A, "varied", 0, sharpen=2.0),
+            "B": make_model(str(tmp_path_factory.mktemp("gen_b")), TINY_B, "varied", 1, sharpen=2.0)}
+
+
+def follow(folder, dtype, prompt, tokens, temperature=0.0, top_p=1.0, seed=0):
+    """Teacher-forced comparison: at every step the plain implementation, given the engine's
+    tokens so far, must choose the engine's next token, or be undecided within MARGIN."""
+    config, tensors = plain.load_model(folder, round_matrices_to_bfloat16=(dtype == "bfloat16"))
+    history = list(prompt)
+    undecided = 0
+    for step, token in enumerate(tokens):
+        logits = plain.forward(config, tensors, history)[-1]
+        if temperature > 0:
+            choice, margin = plain.sample(logits, temperature, top_p, seed, step, return_margin=True)
+        else:
+            choice = plain.argmax_first(logits)
+            ordered = np.sort(logits)
+            margin = float(ordered[-1] - ordered[-2])
+        if choice != token:
+            assert margin < MARGIN[dtype], f"step {step}: engine {token}, plain {choice}, margin {margin}"
+            undecided += 1
+        history.append(token)
+    return undecided
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation(folders, dtype):
+    from mini_llm_b200.generate import generate
+    prompts = [random_tokens(i, n, 512) for i, n in enumerate((5, 17, 33))]
+    got = generate(folders["A"], prompts, max_new_tokens=8, temperature=0.0, dtype=dtype, page_size=16)
+    assert [len(t) for t in got] == [8, 8, 8]
+    undecided = sum(follow(folders["A"], dtype, p, t) for p, t in zip(prompts, got))
+    assert undecided <= (0 if dtype == "float32" else 2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_temperature_sampling_in_mixed_batches(folders, dtype):
+    """Four requests, prompts cut into portions of 7 tokens beside decoding requests, pages
+    of 8 tokens, temperature 0.8: each request's tokens are those of the plain sampler with
+    the same seed, whatever it was batched with."""
+    from mini_llm_b200.generate import LLM
+    prompts = [random_tokens(10 + i, n, 1000) for i, n in enumerate((1, 9, 24, 40))]
+    seeds = [101, 102, 103, 104]
+    llm = LLM(folders["B"], dtype=dtype, page_size=8, max_tokens_per_step=7, max_sessions=4)
+    got = llm.generate(prompts, max_new_tokens=12, temperature=0.8, seed=seeds)
+    stats = llm.scheduler.stats()
+    assert stats["tokens"] == 48 and stats["prefill_tokens"] == 74 and stats["mean_batch_size"] > 1.5
+    undecided = sum(follow(folders["B"], dtype, p, t, 0.8, 1.0, s) for p, t, s in zip(prompts, got, seeds))
+    assert undecided <= (0 if dtype == "float32" else 3)
+    alone = LLM(folders["B"], dtype=dtype, page_size=8).generate([prompts[2]], 12, 0.8, seed=[103])
+    assert alone[0] == got[2]                      # the same tokens alone and whole as in the mixed batches
+    nucleus = llm.generate(prompts[1:3], max_new_tokens=6, temperature=1.3, top_p=0.6, seed=[7, 8])
+    for p, t, s in zip(prompts[1:3], nucleus, [7, 8]):
+        follow(folders["B"], dtype, p, t, 1.3, 0.6, s)
+    assert llm.engine.cache.pages_in_use() == [0]
+
+
+def test_preemption_on_the_device_keeps_the_tokens(folders):
+    """So few pages that decoding requests are preempted and recomputed: same tokens."""
+    from mini_llm_b200.generate import LLM
+    prompts = [random_tokens(20 + i, n, 512) for i, n in enumerate((30, 28, 26))]
+    roomy = LLM(folders["A"], dtype="float32", page_size=16).generate(prompts, max_new_tokens=40)
+    tight = LLM(folders["A"], dtype="float32", page_size=16, cache_tokens=176, max_sessions=3)
+    got = tight.generate(prompts, max_new_tokens=40)
+    assert tight.scheduler.stats()["preemptions"] >= 1
+    assert got == roomy
+
+
+def test_stop_context_and_errors(folders):
+    from mini_llm_b200.generate import LLM
+    llm = LLM(folders["A"], dtype="float32")
+    prompt = random_tokens(3, 20, 512)
+    free_run = llm.generate([prompt], max_new_tokens=6)[0]
+    requests = llm.generate([prompt, random_tokens(4, 120, 512)], max_new_tokens=30, eos_token_id=free_run[3],
+                            return_requests=True)
+    assert requests[0].generated == free_run[:4] and requests[0].finish_reason == "stop"
+    assert requests[1].finish_reason == "context" and len(requests[1].generated) == 8
+    with pytest.raises(RuntimeError):
+        llm.generate([[1] * 128], max_new_tokens=1)
+    with pytest.raises(TypeError):
+        LLM(folders["A"], no_such_option=1)
+
+
+def test_command_line(folders):
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    prompt = random_tokens(6, 12, 512)
+    done = subprocess.run([sys.executable, "-m", "mini_llm_b200.cli", "--model", folders["A"], "--dtype", "float32",
+                           "--max-new-tokens", "5", "--temperature", "0", "--prompt-ids",
+                           ",".join(map(str, prompt))], capture_output=True, text=True, cwd=root, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    tokens = [int(t) for t in done.stdout.split()]
+    assert len(tokens) == 5 and follow(folders["A"], "float32", prompt, tokens) == 0
+    refused = subprocess.run([sys.executable, "-m", "mini_llm_b200.cli", "--model", folders["A"], "--device", "cpu"],
+                             capture_output=True, text=True, cwd=root, timeout=600)
+    assert refused.returncode != 0 and "no CPU path" in refused.stderr
