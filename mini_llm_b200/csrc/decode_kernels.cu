@@ -1,0 +1,380 @@
+// Kernels for steps of few tokens (decoding, short prompt portions), bfloat16.
+//
+// With a handful of rows every matrix product is a stream of the weights
+// through the SMs, bound by HBM bandwidth and by launch latency, as in the
+// reference's batched matrix-vector kernel (engine/src/matvec_batch.cu:148-261:
+// rows staged in shared memory, weights streamed once, bias / gelu / residual
+// in the epilogue).  Here:
+//
+//   skinny_linear   out = epilogue(norm?(x) W^T + bias) for up to 16 rows per
+//                   CTA; 16-byte weight loads, fp32 accumulation; optional
+//                   layer-norm prologue (the norm never round-trips through
+//                   memory), optional epilogue that scatters key and value
+//                   columns straight into the cache pages.
+//   split_attention one CTA per (token, head, chunk of keys); partial softmax
+//                   states go to scratch memory and the CTA that finishes
+//                   last for its (token, head) merges them in chunk order, so
+//                   the result does not depend on which CTA came last.
+#include "common.cuh"
+
+MLLM_DEFINE_ERROR_API(mllm_decode)
+
+// ---------------------------------------------------------------------------
+// skinny_linear
+// ---------------------------------------------------------------------------
+struct SkinnyParams {
+    void* out;                 // bf16 [M, ldo] / fp32 [M, ldo] (EPI_ADD, or out_f32)
+    const void* x;             // bf16 [M, ldx], or fp32 [*, K] with the norm prologue
+    const bf16* w;             // [N, K], K contiguous
+    const float* bias;         // [N] or null
+    const float* gamma;        // norm prologue: gain and shift [K], else null
+    const float* beta;
+    const int* rows;           // norm prologue: source row of each output row, or null
+    float eps;
+    int M, N, K;
+    long ldx, ldo;
+    int epilogue;
+    int out_f32;               // EPI_STORE into fp32 (logits)
+    // scatter of key / value columns into pages (null k_pages: off)
+    bf16* k_pages;
+    bf16* v_pages;
+    const int* positions;
+    const int* token_item;
+    const int* block_table;
+    int max_blocks, page_size, q_width, kv_width;
+};
+
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        f[2 * i] = __uint_as_float(u[i] << 16);
+        f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+    }
+}
+
+template <int MT>      // rows of x per CTA (compile-time bound; M may be smaller)
+__global__ void __launch_bounds__(256)
+skinny_linear_kernel(const SkinnyParams p, int n_per_cta) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* xs = reinterpret_cast<bf16*>(smem_raw);            // [MT][K]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * MT;
+    const int m_count = min(MT, p.M - m0);
+    const int K = p.K;
+
+    // ---- stage the rows of x (normalised first, if asked) as bf16 ----
+    if (p.gamma != nullptr) {
+        const float* src = reinterpret_cast<const float*>(p.x);
+        for (int m = warp; m < MT; m += 8) {
+            if (m < m_count) {
+                const float* row = src + (long)(p.rows ? p.rows[m0 + m] : m0 + m) * K;
+                float sum = 0.0f;
+                for (int k = lane; k < K; k += 32) sum += row[k];
+                float mean = warp_sum(sum) / (float)K;
+                float sq = 0.0f;
+                for (int k = lane; k < K; k += 32) {
+                    float c = row[k] - mean;
+                    sq += c * c;
+                }
+                float inv = 1.0f / sqrtf(warp_sum(sq) / (float)K + p.eps);
+                for (int k = lane; k < K; k += 32)
+                    xs[m * K + k] = __float2bfloat16_rn((row[k] - mean) * inv * p.gamma[k] + p.beta[k]);
+            } else {
+                for (int k = lane; k < K; k += 32) xs[m * K + k] = __float2bfloat16_rn(0.0f);
+            }
+        }
+    } else {
+        const bf16* src = reinterpret_cast<const bf16*>(p.x);
+        const int chunks = K / 8;
+        for (int i = threadIdx.x; i < MT * chunks; i += 256) {
+            int m = i / chunks, c = i % chunks;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (m < m_count) v = *reinterpret_cast<const uint4*>(src + (long)(m0 + m) * p.ldx + c * 8);
+            *reinterpret_cast<uint4*>(xs + m * K + c * 8) = v;
+        }
+    }
+    __syncthreads();
+
+    const int n_begin = blockIdx.x * n_per_cta;
+    const int n_end = min(p.N, n_begin + n_per_cta);
+    const int chunks = K / 8;
+    for (int n = n_begin + warp; n < n_end; n += 8) {
+        float acc[MT];
+#pragma unroll
+        for (int m = 0; m < MT; m++) acc[m] = 0.0f;
+        const bf16* wrow = p.w + (long)n * K;
+        int c = lane;
+        // two chunks in flight per lane
+        for (; c + 32 < chunks; c += 64) {
+            uint4 w0 = __ldg(reinterpret_cast<const uint4*>(wrow + c * 8));
+            uint4 w1 = __ldg(reinterpret_cast<const uint4*>(wrow + (c + 32) * 8));
+            float wf0[8], wf1[8];
+            unpack8(w0, wf0);
+            unpack8(w1, wf1);
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                float xf[8];
+                unpack8(*reinterpret_cast<const uint4*>(xs + m * K + c * 8), xf);
+#pragma unroll
+                for (int i = 0; i < 8; i++) acc[m] = fmaf(wf0[i], xf[i], acc[m]);
+                unpack8(*reinterpret_cast<const uint4*>(xs + m * K + (c + 32) * 8), xf);
+#pragma unroll
+                for (int i = 0; i < 8; i++) acc[m] = fmaf(wf1[i], xf[i], acc[m]);
+            }
+        }
+        for (; c < chunks; c += 32) {
+            uint4 w0 = __ldg(reinterpret_cast<const uint4*>(wrow + c * 8));
+            float wf0[8];
+            unpack8(w0, wf0);
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                float xf[8];
+                unpack8(*reinterpret_cast<const uint4*>(xs + m * K + c * 8), xf);
+#pragma unroll
+                for (int i = 0; i < 8; i++) acc[m] = fmaf(wf0[i], xf[i], acc[m]);
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < MT; m++) acc[m] = warp_sum(acc[m]);
+
+        // lane m writes row m
+        float mine = 0.0f;
+#pragma unroll
+        for (int m = 0; m < MT; m++)
+            if (lane == m) mine = acc[m];
+        if (lane < m_count) {
+            const int row = m0 + lane;
+            float v = mine + (p.bias ? p.bias[n] : 0.0f);
+            if (p.epilogue == EPI_GELU_TANH) v = gelu_tanh_f(v);
+            else if (p.epilogue == EPI_GELU_ERF) v = gelu_erf_f(v);
+            if (p.k_pages != nullptr && n >= p.q_width) {
+                int pos = p.positions[row];
+                int page = p.block_table[(long)p.token_item[row] * p.max_blocks + pos / p.page_size];
+                long slot = ((long)page * p.page_size + pos % p.page_size) * p.kv_width;
+                if (n < p.q_width + p.kv_width) p.k_pages[slot + (n - p.q_width)] = __float2bfloat16_rn(v);
+                else p.v_pages[slot + (n - p.q_width - p.kv_width)] = __float2bfloat16_rn(v);
+            } else if (p.epilogue == EPI_ADD) {
+                float* o = reinterpret_cast<float*>(p.out) + (long)row * p.ldo + n;
+                *o += v;
+            } else if (p.out_f32) {
+                reinterpret_cast<float*>(p.out)[(long)row * p.ldo + n] = v;
+            } else {
+                reinterpret_cast<bf16*>(p.out)[(long)row * p.ldo + n] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+}
+
+static int g_smem_optin = -1;
+
+template <int MT>
+static int launch_skinny(const SkinnyParams& p, cudaStream_t s) {
+    size_t smem = (size_t)MT * p.K * sizeof(bf16);
+    if (g_smem_optin < 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    }
+    if (smem > (size_t)g_smem_optin) return fail("skinny_linear: the rows do not fit shared memory");
+    static size_t configured = 0;                 // per instantiation
+    if (smem > 48 * 1024 && smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(skinny_linear_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             g_smem_optin);
+        if (e != cudaSuccess) return fail("skinny_linear: cannot raise the shared memory limit");
+        configured = g_smem_optin;
+    }
+    // columns per CTA: enough CTAs to fill the GPU, at least one column per warp
+    int n_per_cta = p.N >= 8192 ? 32 : (p.N >= 2048 ? 16 : 8);
+    dim3 grid((p.N + n_per_cta - 1) / n_per_cta, (p.M + MT - 1) / MT);
+    skinny_linear_kernel<MT><<<grid, 256, smem, s>>>(p, n_per_cta);
+    return check_launch("skinny_linear_kernel");
+}
+
+extern "C" int mllm_decode_skinny_linear(const SkinnyParams* params, void* stream) {
+    const SkinnyParams& p = *params;
+    if (p.M <= 0 || p.N <= 0) return 0;
+    if (p.K <= 0 || p.K % 8 != 0) return fail("skinny_linear: K must be a positive multiple of 8");
+    if (p.gamma == nullptr && p.ldx % 8 != 0) return fail("skinny_linear: the row stride of x must be a multiple of 8");
+    if (p.epilogue == EPI_ADD && p.k_pages != nullptr) return fail("skinny_linear: no scatter with the residual sum");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (p.M <= 1) return launch_skinny<1>(p, s);
+    if (p.M <= 2) return launch_skinny<2>(p, s);
+    if (p.M <= 4) return launch_skinny<4>(p, s);
+    if (p.M <= 8) return launch_skinny<8>(p, s);
+    return launch_skinny<16>(p, s);
+}
+
+// ---------------------------------------------------------------------------
+// split_attention
+// ---------------------------------------------------------------------------
+// Scratch layout (fp32): for every (token, head, chunk):
+//   acc  [tokens, heads, max_chunks, head_size]   un-normalised weighted values
+//   ml   [tokens, heads, max_chunks, 2]           running maximum, running sum
+// and one int32 counter per (token, head), zero between launches.
+template <int D>       // head size: 16, 32, 64, 128 or 256
+__global__ void __launch_bounds__(128)
+split_attention_kernel(bf16* __restrict__ out, long ld_out, const bf16* __restrict__ q, long ld_q,
+                       const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+                       const int* __restrict__ block_table, int max_blocks, const int* __restrict__ positions,
+                       const int* __restrict__ token_item, int n_heads, int n_kv_heads, int page_size, float scale,
+                       int window, int chunk, int max_chunks, float* __restrict__ part_acc,
+                       float* __restrict__ part_ml, int* __restrict__ counters) {
+    constexpr int LPK = D / 8;             // lanes per key: each lane owns 8 of the head's dimensions
+    constexpr int KPW = 32 / LPK;          // keys per warp per step
+    const int t = blockIdx.x, h = blockIdx.y, c = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane % LPK, group = lane / LPK;
+    const int p = positions[t];
+    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int c_first = lo / chunk, c_last = p / chunk;
+    if (c < c_first || c > c_last) return;
+    const int begin = max(lo, c * chunk), end = min(p, c * chunk + chunk - 1);     // inclusive
+    const int* bt = block_table + (long)token_item[t] * max_blocks;
+    const int hk = h / (n_heads / n_kv_heads);
+    const long kv_width = (long)n_kv_heads * D;
+
+    float qf[8], acc[8];
+    unpack8(*reinterpret_cast<const uint4*>(q + (long)t * ld_q + (long)h * D + sub * 8), qf);
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        qf[i] *= scale;
+        acc[i] = 0.0f;
+    }
+    float m = -INFINITY, l = 0.0f;
+    // Every lane of the warp runs the same trips (the shuffles need all of them); a lane
+    // whose key lies past the end loads nothing and skips the update.  Two keys per lane are
+    // in flight per trip.
+    for (int jb = begin + warp * KPW; jb <= end; jb += 8 * KPW) {
+        int j[2] = {jb + group, jb + group + 4 * KPW};
+        bool valid[2] = {j[0] <= end, j[1] <= end};
+        uint4 kv[2], vv[2];
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            kv[u] = make_uint4(0, 0, 0, 0);
+            vv[u] = make_uint4(0, 0, 0, 0);
+            if (valid[u]) {
+                int page = bt[j[u] / page_size];
+                long base = ((long)page * page_size + (j[u] % page_size)) * kv_width + (long)hk * D + sub * 8;
+                kv[u] = __ldg(reinterpret_cast<const uint4*>(k_pages + base));
+                vv[u] = __ldg(reinterpret_cast<const uint4*>(v_pages + base));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            float kf[8], vf[8];
+            unpack8(kv[u], kf);
+            unpack8(vv[u], vf);
+            float s = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) s = fmaf(qf[i], kf[i], s);
+#pragma unroll
+            for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (valid[u]) {
+                float m_new = fmaxf(m, s);
+                float corr = __expf(m - m_new);
+                float e = __expf(s - m_new);
+                l = l * corr + e;
+#pragma unroll
+                for (int i = 0; i < 8; i++) acc[i] = acc[i] * corr + e * vf[i];
+                m = m_new;
+            }
+        }
+    }
+
+    // merge the key groups of a warp, then the four warps, always in the same order
+    __shared__ float sm_m[4][KPW];
+    __shared__ float sm_l[4][KPW];
+    __shared__ float sm_acc[4][KPW][D];
+    if (sub == 0) {
+        sm_m[warp][group] = m;
+        sm_l[warp][group] = l;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) sm_acc[warp][group][sub * 8 + i] = acc[i];
+    __syncthreads();
+    float big = -INFINITY;
+    for (int w = 0; w < 4; w++)
+        for (int g = 0; g < KPW; g++) big = fmaxf(big, sm_m[w][g]);
+    const long cell = (((long)t * n_heads + h) * max_chunks + c);
+    for (int d = threadIdx.x; d < D; d += 128) {
+        float o = 0.0f;
+        for (int w = 0; w < 4; w++)
+            for (int g = 0; g < KPW; g++) {
+                float mg = sm_m[w][g];
+                if (mg != -INFINITY) o += sm_acc[w][g][d] * __expf(mg - big);
+            }
+        part_acc[cell * D + d] = o;
+    }
+    if (threadIdx.x == 0) {
+        float total = 0.0f;
+        for (int w = 0; w < 4; w++)
+            for (int g = 0; g < KPW; g++) {
+                float mg = sm_m[w][g];
+                if (mg != -INFINITY) total += sm_l[w][g] * __expf(mg - big);
+            }
+        part_ml[cell * 2] = big;
+        part_ml[cell * 2 + 1] = total;
+    }
+
+    // the CTA that arrives last for this (token, head) merges the chunks
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int ticket = atomicAdd(&counters[t * n_heads + h], 1);
+        is_last = (ticket == c_last - c_first);
+        if (is_last) counters[t * n_heads + h] = 0;       // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    const long first = ((long)t * n_heads + h) * max_chunks;
+    float top = -INFINITY;
+    for (int cc = c_first; cc <= c_last; cc++) top = fmaxf(top, __ldcg(part_ml + (first + cc) * 2));
+    float denom = 0.0f;
+    for (int cc = c_first; cc <= c_last; cc++)
+        denom += __ldcg(part_ml + (first + cc) * 2 + 1) * __expf(__ldcg(part_ml + (first + cc) * 2) - top);
+    for (int d = threadIdx.x; d < D; d += 128) {
+        float o = 0.0f;
+        for (int cc = c_first; cc <= c_last; cc++)
+            o += __ldcg(part_acc + (first + cc) * D + d) * __expf(__ldcg(part_ml + (first + cc) * 2) - top);
+        out[(long)t * ld_out + (long)h * D + d] = __float2bfloat16_rn(o / denom);
+    }
+}
+
+extern "C" int mllm_decode_split_attention(void* out, long ld_out, const void* q, long ld_q, const void* k_pages,
+                                           const void* v_pages, const int* block_table, int max_blocks,
+                                           const int* positions, const int* token_item, int n_tokens, int n_heads,
+                                           int n_kv_heads, int head_size, int page_size, float scale, int window,
+                                           int chunk, int max_chunks, float* part_acc, float* part_ml, int* counters,
+                                           void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
+        return fail("split_attention: heads must be a multiple of key/value heads");
+    if (chunk <= 0 || max_chunks <= 0 || max_chunks > 65535 || n_heads > 65535)
+        return fail("split_attention: bad chunking");
+    if (ld_q % 8 != 0) return fail("split_attention: the row stride of q must be a multiple of 8");
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(n_tokens, n_heads, max_chunks);
+#define LAUNCH_SPLIT(D)                                                                                              \
+    split_attention_kernel<D><<<grid, 128, 0, s>>>((bf16*)out, ld_out, (const bf16*)q, ld_q, (const bf16*)k_pages,   \
+                                                   (const bf16*)v_pages, block_table, max_blocks, positions,         \
+                                                   token_item, n_heads, n_kv_heads, page_size, scale, window, chunk, \
+                                                   max_chunks, part_acc, part_ml, counters)
+    switch (head_size) {
+    case 16: LAUNCH_SPLIT(16); break;
+    case 32: LAUNCH_SPLIT(32); break;
+    case 64: LAUNCH_SPLIT(64); break;
+    case 128: LAUNCH_SPLIT(128); break;
+    case 256: LAUNCH_SPLIT(256); break;
+    default: return fail("split_attention: head size must be 16, 32, 64, 128 or 256");
+    }
+#undef LAUNCH_SPLIT
+    return check_launch("split_attention_kernel");
+}
+
+// Whether split_attention takes a head size (the others run the plain kernel).
+extern "C" int mllm_decode_split_attention_takes(int head_size) {
+    return head_size == 16 || head_size == 32 || head_size == 64 || head_size == 128 || head_size == 256;
+}

@@ -83,6 +83,8 @@ class Engine:
         self.ctx = StepContext(self.kernels, self.workspace, self.dtype, self.device)
         self.steps = 0
         self._sampled = None
+        self._graphs = {}
+        self._graph_stamp = None
 
     # ---- requests ---------------------------------------------------------------------------
     def open_request(self) -> int | None:
@@ -193,16 +195,57 @@ class Engine:
             if view.kind == "paged":
                 view.block_table = views[("block_table", view.group)]
 
-        logits = self.model.forward(ctx, self.storage.views)
-        self._sampled = None
-        if sampling is not None and logits is not None:
-            out = self.workspace.get("sampled", (n_want,), torch.int32)
-            self.kernels.sample_rows(out, logits, views["temperature"][:n_want], views["top_p"][:n_want],
-                                     views["seeds"][:n_want], views["counters"][:n_want])
-            self._sampled = out
+        sample_views = None
+        if sampling is not None and n_want > 0:
+            sample_views = (views["temperature"][:n_want], views["top_p"][:n_want], views["seeds"][:n_want],
+                            views["counters"][:n_want])
+        logits = self._run(ctx, sample_views)
         for entry in entries:
             self.cache.commit(entry.slot, len(entry.tokens))
         self.steps += 1
+        return logits
+
+    # ---- running the model: eagerly, or as a replayed CUDA graph ---------------------------------
+    def _forward(self, ctx, sample_views):
+        logits = self.model.forward(ctx, self.storage.views)
+        self._sampled = None
+        if sample_views is not None and logits is not None:
+            out = self.workspace.get("sampled", (ctx.n_want,), torch.int32)
+            self.kernels.sample_rows(out, logits, *sample_views)
+            self._sampled = out
+        return logits
+
+    def _run(self, ctx, sample_views):
+        """Decode-only steps of one shape launch the same kernels with the same arguments
+        (everything that changes lies in the control block on the device), so the second such
+        step is captured into a CUDA graph and later ones replay it: a step then costs one
+        launch on the host instead of one per kernel.  The reference removes host work per
+        step in the same spirit, by keeping sampled tokens on the device
+        (engine/src/gpt2_gpu_greedy.cu:80-119)."""
+        if not (self.cuda_graphs and ctx.decode_only and self.model.graph_safe):
+            return self._forward(ctx, sample_views)
+        stamp = (self.workspace.generation, self.control.generation)
+        if stamp != self._graph_stamp:
+            self._graphs.clear()                      # a buffer moved: captured addresses are stale
+            self._graph_stamp = stamp
+        key = (ctx.n_tokens, ctx.n_want, sample_views is not None)
+        held = self._graphs.get(key)
+        if held is None:
+            self._graphs[key] = "warm"                # run once eagerly: every buffer gets allocated
+            return self._forward(ctx, sample_views)
+        if held == "warm":
+            before = self.kernels.launches
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = self._forward(ctx, sample_views)
+            if (self.workspace.generation, self.control.generation) != stamp:
+                raise RuntimeError("a buffer was allocated while a step was captured")
+            held = (graph, logits, self._sampled, self.kernels.launches - before)
+            self._graphs[key] = held
+            self.kernels.launches = before
+        graph, logits, self._sampled, launches = held
+        graph.replay()
+        self.kernels.launches += launches
         return logits
 
     def sampled_tokens(self) -> list:

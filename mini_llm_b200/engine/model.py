@@ -29,6 +29,9 @@ class Model:
             self.layers.append((arrangement, {role: build_part(p) for role, p in layer.parts.items()}))
         self.final_norm = build_part(spec.final_norm)
         self.head = build_part(spec.head)
+        # A step may be captured into a CUDA graph only if every part launches nothing but
+        # kernels whose arguments stay valid from step to step; parts say so themselves.
+        self.graph_safe = all(getattr(part, "graph_safe", False) for part in self.parts())
 
     def parts(self):
         found = [self.embedding]
@@ -68,5 +71,7 @@ class Model:
             arrangement.run(ctx, parts, hidden, cache_views[index])
         if ctx.n_want == 0:
             return None
-        rows = self.final_norm.forward(ctx, hidden, rows=ctx.want_rows, tag="final_norm")
+        defer = getattr(self.final_norm, "can_defer", False) and getattr(self.head, "accepts_deferred_norm", False)
+        rows = self.final_norm.forward(ctx, hidden, rows=ctx.want_rows, tag="final_norm",
+                                       **({"defer": True} if defer else {}))
         return self.head.forward(ctx, rows)

@@ -37,6 +37,7 @@ NVCC_FLAGS = [
 LIBRARIES = {
     "plain": "plain_kernels.cu",
     "sampling": "sampling_kernels.cu",
+    "decode": "decode_kernels.cu",
 }
 
 _lock = threading.Lock()

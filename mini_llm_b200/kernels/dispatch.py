@@ -4,6 +4,10 @@
 32-bit path) every operation runs its plain kernel.  Otherwise a fast kernel is
 asked first whether it takes the sizes at hand; if it does not, the plain
 kernel runs: never a wrong result, never a CPU path.
+
+A norm whose only consumer is a matrix product may be handed over unevaluated
+(``DeferredNorm``): the product kernel for few rows normalises on the way in;
+every other kernel has it evaluated first.
 """
 
 from __future__ import annotations
@@ -12,12 +16,34 @@ import torch
 
 from . import ops
 
+SKINNY_MAX_ROWS = 64          # above this a step's products are compute-bound: tiled kernels take over
+
+
+class DeferredNorm:
+    """A layer norm that has not run yet: ``rows`` (or all rows) of the fp32 ``x``."""
+
+    def __init__(self, x, gamma, beta, eps, rows, tag):
+        self.x, self.gamma, self.beta, self.eps, self.rows, self.tag = x, gamma, beta, float(eps), rows, tag
+        self._value = None
+
+    @property
+    def shape(self):
+        return (self.x.shape[0] if self.rows is None else self.rows.shape[0], self.x.shape[1])
+
+    def materialize(self, ctx):
+        if self._value is None:
+            out = ctx.buffer(self.tag, self.shape, ctx.act_dtype)
+            ctx.kernels.layernorm(out, self.x, self.gamma, self.beta, self.eps, self.rows)
+            self._value = out
+        return self._value
+
 
 class Kernels:
     def __init__(self, act_dtype: torch.dtype, plain_only: bool = False):
         self.act_dtype = act_dtype
         self.plain_only = bool(plain_only) or act_dtype == torch.float32
-        self.launches = 0            # kernels launched since the counter was last reset
+        self.launches = 0            # kernels launched (or recorded into a graph) since the start
+        self._split_scratch = None
 
     # ---- operations without a fast variant --------------------------------------------------
     def embed(self, out, token_ids, positions, table, position_table=None):
@@ -40,12 +66,71 @@ class Kernels:
         self.launches += 1
         return ops.sample_rows(out, logits, temperature, top_p, seeds, counters)
 
-    # ---- operations with fast variants ------------------------------------------------------
-    def linear(self, out, a, w, bias=None, epilogue="store"):
+    # ---- matrix products --------------------------------------------------------------------
+    def _skinny(self, m, k) -> bool:
+        return not self.plain_only and m <= SKINNY_MAX_ROWS and ops.skinny_linear_takes(m, k)
+
+    def linear(self, ctx, out, a, w, bias=None, epilogue="store"):
+        """out = epilogue(a @ w.T + bias).  ``a``: an activation tensor or a ``DeferredNorm``."""
+        m, k = a.shape
         self.launches += 1
+        if self._skinny(m, k):
+            if isinstance(a, DeferredNorm):
+                return ops.skinny_linear(out, a.x, w, bias, epilogue, norm=(a.gamma, a.beta, a.eps, a.rows))
+            return ops.skinny_linear(out, a, w, bias, epilogue)
+        if isinstance(a, DeferredNorm):
+            a = a.materialize(ctx)
         return ops.linear_plain(out, a, w, bias, epilogue)
 
+    def qkv_projection(self, ctx, a, w, bias, cache, q_width, kv_width):
+        """The fused query/key/value projection.  Keys and values of the step's tokens go into
+        the cache pages (if this entry writes its cache); returns the queries [T, q_width]."""
+        m, k = a.shape
+        if cache.writes and self._skinny(m, k):
+            q = ctx.buffer("q", (m, q_width), ctx.act_dtype)
+            scatter = (cache.k_pages, cache.v_pages, ctx.positions, ctx.token_item, cache.block_table,
+                       cache.page_size, q_width, kv_width)
+            self.launches += 1
+            if isinstance(a, DeferredNorm):
+                ops.skinny_linear(q, a.x, w, bias, "store", norm=(a.gamma, a.beta, a.eps, a.rows), scatter=scatter)
+            else:
+                ops.skinny_linear(q, a, w, bias, "store", scatter=scatter)
+            return q
+        qkv = ctx.buffer("qkv", (m, q_width + 2 * kv_width), ctx.act_dtype)
+        self.linear(ctx, qkv, a, w, bias)
+        if cache.writes:
+            self.kv_store(cache.k_pages, cache.v_pages, qkv[:, q_width:q_width + kv_width],
+                          qkv[:, q_width + kv_width:], ctx.positions, ctx.token_item, cache.block_table,
+                          cache.page_size)
+        return qkv[:, :q_width]
+
+    # ---- attention --------------------------------------------------------------------------
     def attention(self, ctx, out, q, cache, n_heads, n_kv_heads, head_size, scale, window=0):
         self.launches += 1
+        n = q.shape[0]
+        if (not self.plain_only and n <= SKINNY_MAX_ROWS and head_size in ops.SPLIT_ATTENTION_HEAD_SIZES):
+            # chunk of keys per CTA: small when there are few (token, head) pairs, so that the
+            # chunks still fill the GPU
+            pairs = n * n_heads
+            chunk = 64 if pairs < 64 else (128 if pairs < 256 else 256)
+            reach = cache.block_table.shape[1] * cache.page_size
+            max_chunks = -(-reach // chunk)
+            acc, ml, counters = self._scratch(ctx, SKINNY_MAX_ROWS * n_heads, -(-reach // 64), head_size)
+            return ops.split_attention(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
+                                       ctx.token_item, n_heads, n_kv_heads, head_size, cache.page_size, scale,
+                                       window, chunk, max_chunks, acc, ml, counters)
         return ops.attention_plain(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
                                    ctx.token_item, n_heads, n_kv_heads, head_size, cache.page_size, scale, window)
+
+    def _scratch(self, ctx, pairs, chunks, head_size):
+        """Scratch of split_attention, sized for the largest step it takes; allocated once
+        (the counters must start at zero and the kernel leaves them so)."""
+        need = (pairs * chunks * head_size, pairs * chunks * 2, pairs)
+        held = self._split_scratch
+        if held is None or any(h.numel() < n for h, n in zip(held, need)):
+            device = ctx.device
+            self._split_scratch = (torch.empty(need[0], dtype=torch.float32, device=device),
+                                   torch.empty(need[1], dtype=torch.float32, device=device),
+                                   torch.zeros(need[2], dtype=torch.int32, device=device))
+            ctx.workspace.generation += 1
+        return self._split_scratch

@@ -8,6 +8,8 @@ take every size; a fast kernel either takes a size or is not chosen for it.
 
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from .lib import F, I, L, P, Function, KernelError
@@ -191,4 +193,118 @@ def sample_rows(out, logits, temperature=None, top_p=None, seeds=None, counters=
                 raise KernelError(f"sample_rows: {name} too short")
     _sample_rows(out.data_ptr(), logits.data_ptr(), logits.stride(0), r, vocab, _ptr(temperature), _ptr(top_p),
                  _ptr(seeds), _ptr(counters), _stream())
+    return out
+
+
+# ---- kernels for steps of few tokens (bfloat16) --------------------------------------------------
+
+class _SkinnyParams(ctypes.Structure):
+    _fields_ = [("out", P), ("x", P), ("w", P), ("bias", P), ("gamma", P), ("beta", P), ("rows", P),
+                ("eps", F), ("M", I), ("N", I), ("K", I), ("ldx", L), ("ldo", L), ("epilogue", I), ("out_f32", I),
+                ("k_pages", P), ("v_pages", P), ("positions", P), ("token_item", P), ("block_table", P),
+                ("max_blocks", I), ("page_size", I), ("q_width", I), ("kv_width", I)]
+
+
+_skinny = Function("decode", "mllm_decode_skinny_linear", [ctypes.POINTER(_SkinnyParams), P])
+_split_attention = Function("decode", "mllm_decode_split_attention",
+                            [P, L, P, L, P, P, P, I, P, P, I, I, I, I, I, F, I, I, I, P, P, P, P])
+
+SKINNY_MAX_SMEM = 200 * 1024
+SPLIT_ATTENTION_HEAD_SIZES = (16, 32, 64, 128, 256)
+
+
+def skinny_linear_takes(m, k) -> bool:
+    """Whether skinny_linear takes a product with ``m`` rows and inner size ``k``."""
+    rows = 1 if m <= 1 else 2 if m <= 2 else 4 if m <= 4 else 8 if m <= 8 else 16
+    return k % 8 == 0 and rows * k * 2 <= SKINNY_MAX_SMEM
+
+
+def skinny_linear(out, x, w, bias=None, epilogue="store", norm=None, scatter=None):
+    """out = epilogue(norm?(x) @ w.T + bias) for few rows (bf16 weights, fp32 sums).
+
+    norm: (gamma, beta, eps, rows or None): x is then the fp32 residual stream and is
+    layer-normed on the way in.  scatter: (k_pages, v_pages, positions, token_item,
+    block_table, page_size, q_width, kv_width): columns past q_width are written into the
+    cache pages instead of ``out`` (which then has q_width columns).
+    """
+    _check(w, "skinny_linear.w", torch.bfloat16, 2)
+    n, k = w.shape
+    params = _SkinnyParams()
+    if norm is not None:
+        gamma, beta, eps, rows = norm
+        _check(x, "skinny_linear.x", torch.float32, 2)
+        _check(gamma, "skinny_linear.gamma", torch.float32, 1)
+        _check(beta, "skinny_linear.beta", torch.float32, 1)
+        if not x.is_contiguous() or x.shape[1] != k or gamma.shape[0] != k or beta.shape[0] != k:
+            raise KernelError("skinny_linear: the normed input does not have K contiguous columns")
+        if rows is not None:
+            _check(rows, "skinny_linear.rows", torch.int32, 1)
+        m = rows.shape[0] if rows is not None else x.shape[0]
+        params.gamma, params.beta, params.rows, params.eps = gamma.data_ptr(), beta.data_ptr(), _ptr(rows), float(eps)
+    else:
+        _check(x, "skinny_linear.x", torch.bfloat16, 2)
+        if x.shape[1] != k:
+            raise KernelError("skinny_linear: x and w disagree on K")
+        m = x.shape[0]
+    _check(out, "skinny_linear.out", None, 2)
+    if not w.is_contiguous() or not skinny_linear_takes(m, k):
+        raise KernelError(f"skinny_linear does not take M={m}, K={k}")
+    out_cols = n if scatter is None else scatter[6]
+    if out.shape[0] != m or out.shape[1] != out_cols:
+        raise KernelError(f"skinny_linear: out is {tuple(out.shape)}, expected {(m, out_cols)}")
+    if epilogue == "add" and out.dtype != torch.float32:
+        raise KernelError("skinny_linear: the residual sum is kept in 32-bit")
+    if epilogue != "add" and out.dtype not in (torch.float32, torch.bfloat16):
+        raise KernelError("skinny_linear: out must be bfloat16 or float32")
+    if bias is not None:
+        _check(bias, "skinny_linear.bias", torch.float32, 1)
+        if bias.shape[0] != n:
+            raise KernelError("skinny_linear: bias has another length")
+    params.out, params.x, params.w, params.bias = out.data_ptr(), x.data_ptr(), w.data_ptr(), _ptr(bias)
+    params.M, params.N, params.K = m, n, k
+    params.ldx, params.ldo = x.stride(0), out.stride(0)
+    params.epilogue = EPILOGUES[epilogue]
+    params.out_f32 = int(out.dtype == torch.float32 and epilogue != "add")
+    if scatter is not None:
+        k_pages, v_pages, positions, token_item, block_table, page_size, q_width, kv_width = scatter
+        _check(k_pages, "skinny_linear.k_pages", torch.bfloat16)
+        _check(v_pages, "skinny_linear.v_pages", torch.bfloat16)
+        _check(block_table, "skinny_linear.block_table", torch.int32, 2)
+        if q_width + 2 * kv_width != n or not k_pages.is_contiguous() or not v_pages.is_contiguous():
+            raise KernelError("skinny_linear: scatter widths do not add up to N")
+        params.k_pages, params.v_pages = k_pages.data_ptr(), v_pages.data_ptr()
+        params.positions, params.token_item = positions.data_ptr(), token_item.data_ptr()
+        params.block_table, params.max_blocks = block_table.data_ptr(), block_table.shape[1]
+        params.page_size, params.q_width, params.kv_width = page_size, q_width, kv_width
+    _skinny(ctypes.byref(params), _stream())
+    return out
+
+
+def split_attention(out, q, k_pages, v_pages, block_table, positions, token_item, n_heads, n_kv_heads, head_size,
+                    page_size, scale, window, chunk, max_chunks, part_acc, part_ml, counters):
+    """Causal attention over the paged cache for few tokens: one CTA per (token, head, chunk
+    of ``chunk`` keys); needs fp32 scratch ``part_acc`` [T*H*max_chunks*D], ``part_ml``
+    [T*H*max_chunks*2] and zeroed int32 ``counters`` [T*H] (left zero)."""
+    _check(out, "split_attention.out", torch.bfloat16, 2)
+    _check(q, "split_attention.q", torch.bfloat16, 2)
+    _check(k_pages, "split_attention.k_pages", torch.bfloat16)
+    _check(v_pages, "split_attention.v_pages", torch.bfloat16)
+    _check(block_table, "split_attention.block_table", torch.int32, 2)
+    _check(part_acc, "split_attention.part_acc", torch.float32)
+    _check(part_ml, "split_attention.part_ml", torch.float32)
+    _check(counters, "split_attention.counters", torch.int32)
+    n = q.shape[0]
+    cells = n * n_heads * max_chunks
+    if head_size not in SPLIT_ATTENTION_HEAD_SIZES:
+        raise KernelError(f"split_attention does not take head size {head_size}")
+    if q.shape[1] != n_heads * head_size or out.shape != q.shape:
+        raise KernelError("split_attention: q / out do not have heads * head_size columns")
+    if part_acc.numel() < cells * head_size or part_ml.numel() < cells * 2 or counters.numel() < n * n_heads:
+        raise KernelError("split_attention: scratch too small")
+    if max_chunks * chunk < page_size * block_table.shape[1]:
+        raise KernelError("split_attention: the chunks do not cover the longest block table")
+    _split_attention(out.data_ptr(), out.stride(0), q.data_ptr(), q.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
+                     block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), token_item.data_ptr(), n,
+                     n_heads, n_kv_heads, head_size, page_size, float(scale), int(window or 0), int(chunk),
+                     int(max_chunks), part_acc.data_ptr(), part_ml.data_ptr(), counters.data_ptr(), _stream())
     return out

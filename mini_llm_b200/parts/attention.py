@@ -21,6 +21,7 @@ from .spec import PagedKV, WeightSpec
 
 
 class CausalSelfAttention(Mixer):
+    graph_safe = True
     def __init__(self, prefix, width: int, n_heads: int, head_size: int, score_scale: float,
                  n_kv_heads: int | None = None, window: int | None = None,
                  qkv_name: str = "c_attn", out_name: str = "c_proj", stored_in_out: bool = True):
@@ -57,20 +58,17 @@ class CausalSelfAttention(Mixer):
     def cache_need(self):
         return PagedKV(self.n_kv_heads, self.head_size, self.window)
 
+    accepts_deferred_norm = True
+
     def forward(self, ctx, x, hidden, cache):
         k = ctx.kernels
-        n = x.shape[0]
-        qkv = ctx.buffer("qkv", (n, self.qkv_width), ctx.act_dtype)
-        k.linear(qkv, x, self.w(f"{self.qkv_name}.weight"), self.w(f"{self.qkv_name}.bias"))
-        q = qkv[:, :self.q_width]
-        if cache.writes:
-            k.kv_store(cache.k_pages, cache.v_pages, qkv[:, self.q_width:self.q_width + self.kv_width],
-                       qkv[:, self.q_width + self.kv_width:], ctx.positions, ctx.token_item, cache.block_table,
-                       cache.page_size)
-        mixed = ctx.buffer("attn_out", (n, self.q_width), ctx.act_dtype)
+        q = k.qkv_projection(ctx, x, self.w(f"{self.qkv_name}.weight"), self.w(f"{self.qkv_name}.bias"), cache,
+                             self.q_width, self.kv_width)
+        mixed = ctx.buffer("attn_out", (q.shape[0], self.q_width), ctx.act_dtype)
         k.attention(ctx, mixed, q, cache, self.n_heads, self.n_kv_heads, self.head_size, self.score_scale,
                     self.window or 0)
-        k.linear(hidden, mixed, self.w(f"{self.out_name}.weight"), self.w(f"{self.out_name}.bias"), epilogue="add")
+        k.linear(ctx, hidden, mixed, self.w(f"{self.out_name}.weight"), self.w(f"{self.out_name}.bias"),
+                 epilogue="add")
 
 
 register_part("causal_self_attention", CausalSelfAttention)

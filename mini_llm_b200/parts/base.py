@@ -34,7 +34,14 @@ from .spec import NoCache, PartSpec, WeightSpec
 
 
 class Part:
-    """Base of every part."""
+    """Base of every part.
+
+    ``graph_safe``: the part's ``forward`` launches only kernels on the current stream
+    whose arguments (pointers into the context's buffers, sizes that follow from the
+    step's shape) are the same for every step of one shape.  Steps of a model whose parts
+    all say so may be captured into a CUDA graph; the default is not to."""
+
+    graph_safe = False
 
     def __init__(self, prefix: str = ""):
         self.prefix = prefix

@@ -10,13 +10,21 @@ from __future__ import annotations
 from .base import Arrangement, register_arrangement
 
 
+def _defer(norm, consumer) -> dict:
+    if getattr(consumer, "accepts_deferred_norm", False) and getattr(norm, "can_defer", False):
+        return {"defer": True}
+    return {}
+
+
 class PreNorm(Arrangement):
     roles = ("norm_1", "mixer", "norm_2", "feed_forward")
 
     def run(self, ctx, parts, hidden, cache):
-        x = parts["norm_1"].forward(ctx, hidden, tag="norm_1")
+        # A part that states ``accepts_deferred_norm`` may get its input norm unevaluated
+        # (to fuse it into its first product); any other part gets a tensor.
+        x = parts["norm_1"].forward(ctx, hidden, tag="norm_1", **_defer(parts["norm_1"], parts["mixer"]))
         parts["mixer"].forward(ctx, x, hidden, cache)
-        x = parts["norm_2"].forward(ctx, hidden, tag="norm_2")
+        x = parts["norm_2"].forward(ctx, hidden, tag="norm_2", **_defer(parts["norm_2"], parts["feed_forward"]))
         parts["feed_forward"].forward(ctx, x, hidden)
 
 

@@ -18,6 +18,7 @@ from .spec import WeightSpec
 
 
 class TokenEmbedding(Embedding):
+    graph_safe = True
     def __init__(self, prefix, vocab_size: int, width: int, name: str = "wte.weight"):
         super().__init__(prefix)
         self.vocab_size, self.width, self.name = int(vocab_size), int(width), name
@@ -36,6 +37,7 @@ class TokenEmbedding(Embedding):
 
 class LearnedPositions(PositionEncoding):
     """A table row per absolute position, added to the embedded token."""
+    graph_safe = True
 
     def __init__(self, prefix, max_positions: int, width: int, name: str = "wpe.weight"):
         super().__init__(prefix)
@@ -54,6 +56,7 @@ class LearnedPositions(PositionEncoding):
 class LinearHead(Head):
     """logits = x W^T, W [vocab, width].  ``weight_name`` may be the token
     table's name (tied head): the loader then shares the one tensor."""
+    graph_safe = True
 
     def __init__(self, prefix, vocab_size: int, width: int, weight_name: str = "lm_head.weight"):
         super().__init__(prefix)
@@ -62,9 +65,11 @@ class LinearHead(Head):
     def weight_specs(self):
         return [WeightSpec(self.full_name(self.weight_name), (self.vocab_size, self.width), role="table", init="table")]
 
+    accepts_deferred_norm = True
+
     def forward(self, ctx, x):
         logits = ctx.buffer("logits", (x.shape[0], self.vocab_size), torch.float32)
-        ctx.kernels.linear(logits, x, self.w(self.weight_name), None)
+        ctx.kernels.linear(ctx, logits, x, self.w(self.weight_name), None)
         return logits
 
 

@@ -12,6 +12,7 @@ ACTIVATION_EPILOGUES = ("gelu_tanh", "gelu_erf")
 
 
 class DenseMlp(FeedForward):
+    graph_safe = True
     def __init__(self, prefix, width: int, inner: int, activation: str,
                  up_name: str = "c_fc", down_name: str = "c_proj", stored_in_out: bool = True):
         super().__init__(prefix)
@@ -35,11 +36,13 @@ class DenseMlp(FeedForward):
             WeightSpec(self.full_name(f"{self.down_name}.bias"), (self.width,), role="vector", init="bias"),
         ]
 
+    accepts_deferred_norm = True
+
     def forward(self, ctx, x, hidden):
         up = ctx.buffer("mlp_up", (x.shape[0], self.inner), ctx.act_dtype)
-        ctx.kernels.linear(up, x, self.w(f"{self.up_name}.weight"), self.w(f"{self.up_name}.bias"),
+        ctx.kernels.linear(ctx, up, x, self.w(f"{self.up_name}.weight"), self.w(f"{self.up_name}.bias"),
                            epilogue=self.activation)
-        ctx.kernels.linear(hidden, up, self.w(f"{self.down_name}.weight"), self.w(f"{self.down_name}.bias"),
+        ctx.kernels.linear(ctx, hidden, up, self.w(f"{self.down_name}.weight"), self.w(f"{self.down_name}.bias"),
                            epilogue="add")
 
 

@@ -4,11 +4,15 @@ Statistics are 32-bit; the output has the engine's element type."""
 
 from __future__ import annotations
 
+from ..kernels.dispatch import DeferredNorm
 from .base import Norm, register_part
 from .spec import WeightSpec
 
 
 class LayerNorm(Norm):
+    graph_safe = True
+    can_defer = True
+
     def __init__(self, prefix, width: int, eps: float):
         super().__init__(prefix)
         self.width = int(width)
@@ -20,7 +24,9 @@ class LayerNorm(Norm):
             WeightSpec(self.full_name("bias"), (self.width,), role="vector", init="shift"),
         ]
 
-    def forward(self, ctx, x, rows=None, tag="norm"):
+    def forward(self, ctx, x, rows=None, tag="norm", defer=False):
+        if defer:
+            return DeferredNorm(x, self.w("weight"), self.w("bias"), self.eps, rows, tag)
         n_rows = x.shape[0] if rows is None else rows.shape[0]
         out = ctx.buffer(tag, (n_rows, self.width), ctx.act_dtype)
         ctx.kernels.layernorm(out, x, self.w("weight"), self.w("bias"), self.eps, rows)

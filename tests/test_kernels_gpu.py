@@ -248,3 +248,135 @@ def test_sampling_temperature_and_nucleus_match_the_plain_sampler(vocab):
     freq = np.bincount(out.cpu().numpy(), minlength=5) / 4000.0
     p = np.exp(few[0]) / np.exp(few[0]).sum()
     assert np.abs(freq - p).max() < 0.03
+
+
+# ---- kernels for steps of few tokens --------------------------------------------------------
+
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8, 13, 16, 37, 64])
+@pytest.mark.parametrize("n, k", [(768, 768), (100, 96), (1000, 160), (2304, 768), (777, 3072), (50257, 64)])
+@pytest.mark.parametrize("epilogue", ["store", "gelu_tanh", "gelu_erf", "add"])
+def test_skinny_linear(m, n, k, epilogue):
+    from mini_llm_b200.kernels import ops
+    if (epilogue != "store" and n > 3000) or (m not in (1, 5, 16, 37) and epilogue != "store"):
+        pytest.skip("epilogues are covered at fewer sizes")
+    rng = np.random.default_rng(m * 7 + n + k)
+    a, w = dev(rng.normal(size=(m, k + 8)), torch.bfloat16)[:, :k], dev(rng.normal(size=(n, k)) / math.sqrt(k), torch.bfloat16)
+    bias = dev(rng.normal(size=n), torch.float32)
+    acc = f64(a) @ f64(w).T + f64(bias)
+    if epilogue == "add":
+        out = dev(rng.normal(size=(m, n)), torch.float32)
+        expected = f64(out) + acc
+        ops.skinny_linear(out, a, w, bias, "add")
+        np.testing.assert_allclose(f64(out), expected, rtol=0, atol=1e-4)
+        return
+    expected = {"store": acc, "gelu_tanh": plain.gelu_tanh(acc), "gelu_erf": plain.gelu_erf(acc)}[epilogue]
+    out = torch.full((m, n), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.skinny_linear(out, a, w, bias, epilogue)
+    np.testing.assert_allclose(f64(out), expected, rtol=0, atol=tol(torch.bfloat16, 4))
+    wide = torch.full((m, n), float("nan"), device="cuda", dtype=torch.float32)
+    ops.skinny_linear(wide, a, w, None, "store")                       # fp32 output (logits), no bias
+    np.testing.assert_allclose(f64(wide), f64(a) @ f64(w).T, rtol=0, atol=1e-4)
+
+
+@pytest.mark.parametrize("m", [1, 6, 16, 33])
+@pytest.mark.parametrize("k, eps", [(96, 1e-6), (768, 1e-5), (1600, 1e-3)])
+def test_skinny_linear_with_the_norm_on_the_way_in(m, k, eps):
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(m + k)
+    n = 200
+    x = dev(rng.normal(2.0, 3.0, size=(m + 9, k)), torch.float32)
+    gain, shift = dev(rng.uniform(0.5, 1.5, k), torch.float32), dev(rng.normal(0, 0.1, k), torch.float32)
+    w, bias = dev(rng.normal(size=(n, k)) / math.sqrt(k), torch.bfloat16), dev(rng.normal(size=n), torch.float32)
+    rows = rng.integers(0, m + 9, m)
+    normed = plain.round_to_bfloat16(plain.layer_norm(f64(x), f64(gain), f64(shift), eps))
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    ops.skinny_linear(out, x, w, bias, "store", norm=(gain, shift, eps, dev(rows.astype(np.int32))))
+    np.testing.assert_allclose(f64(out), normed[rows] @ f64(w).T + f64(bias), rtol=0, atol=tol(torch.bfloat16, 4))
+    ops.skinny_linear(out, x[:m], w, bias, "store", norm=(gain, shift, eps, None))
+    np.testing.assert_allclose(f64(out), normed[:m] @ f64(w).T + f64(bias), rtol=0, atol=tol(torch.bfloat16, 4))
+
+
+def test_skinny_linear_scatters_keys_and_values_into_pages():
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(4)
+    heads, kv_heads, head, page, k = 4, 2, 16, 8, 96
+    q_width, kv_width = heads * head, kv_heads * head
+    a = dev(rng.normal(size=(5, k)), torch.bfloat16)
+    w = dev(rng.normal(size=(q_width + 2 * kv_width, k)) / math.sqrt(k), torch.bfloat16)
+    bias = dev(rng.normal(size=q_width + 2 * kv_width), torch.float32)
+    k_pages = torch.full((12, page, kv_width), 7.0, device="cuda", dtype=torch.bfloat16)
+    v_pages = torch.full_like(k_pages, 7.0)
+    table = dev(np.array([[5, 2, -1], [9, 0, 11]], dtype=np.int32))
+    positions, items = dev(np.array([6, 7, 8, 9, 17], dtype=np.int32)), dev(np.array([0, 0, 0, 0, 1], dtype=np.int32))
+    q = torch.empty(5, q_width, device="cuda", dtype=torch.bfloat16)
+    ops.skinny_linear(q, a, w, bias, "store", scatter=(k_pages, v_pages, positions, items, table, page, q_width, kv_width))
+    full = torch.empty(5, q_width + 2 * kv_width, device="cuda", dtype=torch.bfloat16)
+    ops.linear_plain(full, a, w, bias, "store")
+    np.testing.assert_allclose(f64(q), f64(full[:, :q_width]), rtol=0, atol=tol(torch.bfloat16))
+    expect_k, expect_v = torch.full_like(k_pages, 7.0), torch.full_like(v_pages, 7.0)
+    for row, (pg, off) in enumerate([(5, 6), (5, 7), (2, 0), (2, 1), (11, 1)]):
+        expect_k[pg, off] = full[row, q_width:q_width + kv_width]
+        expect_v[pg, off] = full[row, q_width + kv_width:]
+    np.testing.assert_allclose(f64(k_pages), f64(expect_k), rtol=0, atol=tol(torch.bfloat16))
+    np.testing.assert_allclose(f64(v_pages), f64(expect_v), rtol=0, atol=tol(torch.bfloat16))
+
+
+def split_scratch(tokens, heads, max_chunks, head):
+    return (torch.full((tokens * heads * max_chunks * head,), float("nan"), device="cuda"),
+            torch.full((tokens * heads * max_chunks * 2,), float("nan"), device="cuda"),
+            torch.zeros(tokens * heads, dtype=torch.int32, device="cuda"))
+
+
+@pytest.mark.parametrize("n_heads, n_kv_heads, head, page, window", [
+    (3, 3, 16, 16, 0), (6, 2, 64, 16, 0), (5, 1, 32, 4, 0), (1, 1, 256, 16, 0), (2, 2, 128, 8, 0),
+    (4, 2, 32, 8, 21), (2, 2, 64, 16, 16), (25, 25, 64, 16, 0)])
+@pytest.mark.parametrize("chunk", [64, 128, 256])
+def test_split_attention_over_pages(n_heads, n_kv_heads, head, page, window, chunk):
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(n_heads * head + page + chunk)
+    lengths, n_new = [37, 1, 300, 64, 17, 129], [37, 1, 1, 9, 2, 1]
+    k_pages, v_pages, table, positions, items, dense = paged_case(rng, lengths, n_new, n_heads, n_kv_heads, head,
+                                                                  page, torch.bfloat16)
+    dense = [(f64(dev(k, torch.bfloat16)), f64(dev(v, torch.bfloat16))) for k, v in dense]
+    n = len(f64(positions))
+    q = dev(rng.normal(size=(n, n_heads * head)), torch.bfloat16)
+    out = torch.full_like(q, float("nan"))
+    scale = 1.0 / math.sqrt(head)
+    max_chunks = -(-(table.shape[1] * page) // chunk)
+    acc, ml, counters = split_scratch(n, n_heads, max_chunks, head)
+    expected = attention_expected(f64(q), dense, f64(positions).astype(int), f64(items).astype(int), n_heads,
+                                  n_kv_heads, head, scale, window)
+    for _ in range(2):                                  # twice on the same scratch: the counters return to zero
+        ops.split_attention(out, q, k_pages, v_pages, table, positions, items, n_heads, n_kv_heads, head, page,
+                            scale, window, chunk, max_chunks, acc, ml, counters)
+        np.testing.assert_allclose(f64(out), expected, rtol=0, atol=tol(torch.bfloat16, 2))
+        assert int(counters.abs().sum()) == 0
+        out.fill_(float("nan"))
+
+
+def test_split_attention_finds_one_far_key_and_respects_the_windows_edge():
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(5)
+    head, page, length, chunk = 64, 16, 500, 64
+    far = 3 * page + 5
+    k_pages, v_pages, table, positions, items, dense = paged_case(rng, [length], [1], 1, 1, head, page, torch.bfloat16)
+    k, v = dense[0]
+    q = rng.normal(size=(1, head))
+    k[far] = q[0] * 4.0
+    v[far] = 100.0 + np.arange(head)
+    block, offset = int(f64(table)[0, far // page]), far % page
+    k_pages[block, offset] = dev(k[far], torch.bfloat16)
+    v_pages[block, offset] = dev(v[far], torch.bfloat16)
+    qd = dev(q, torch.bfloat16)
+    out = torch.empty_like(qd)
+    scale = 1.0 / math.sqrt(head)
+    max_chunks = -(-(table.shape[1] * page) // chunk)
+    scratch = split_scratch(1, 1, max_chunks, head)
+    run = lambda window: ops.split_attention(out, qd, k_pages, v_pages, table, positions, items, 1, 1, head, page,
+                                             scale, window, chunk, max_chunks, *scratch)
+    run(0)
+    np.testing.assert_allclose(f64(out)[0], f64(dev(v[far], torch.bfloat16)), rtol=2e-2, atol=0.5)
+    run(length - 1 - far)
+    assert float(out.float().abs().max()) < 10.0
+    run(length - far)
+    np.testing.assert_allclose(f64(out)[0], f64(dev(v[far], torch.bfloat16)), rtol=2e-2, atol=0.5)

@@ -20,10 +20,11 @@ def tol(dtype):
     return 3e-5 if dtype == torch.float32 else 3e-2
 
 
-def make_ctx(dtype, token_ids, positions, items):
+def make_ctx(dtype, token_ids, positions, items, plain_only=True):
     from mini_llm_b200.engine.context import StepContext, Workspace
     from mini_llm_b200.kernels.dispatch import Kernels
-    ctx = StepContext(Kernels(dtype, plain_only=True), Workspace(torch.device("cuda"), 16), dtype, torch.device("cuda"))
+    ctx = StepContext(Kernels(dtype, plain_only=plain_only), Workspace(torch.device("cuda"), 16), dtype,
+                      torch.device("cuda"))
     as_dev = lambda a: torch.tensor(a, dtype=torch.int32, device="cuda")
     ctx.token_ids, ctx.positions, ctx.token_item = as_dev(token_ids), as_dev(positions), as_dev(items)
     ctx.n_tokens = len(token_ids)
@@ -44,12 +45,15 @@ def bind_random(part, dtype, rng):
     return stored
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_norm_feed_forward_embedding_head(dtype):
+MODES = [(torch.float32, True), (torch.bfloat16, True), (torch.bfloat16, False)]      # (dtype, plain kernels only)
+
+
+@pytest.mark.parametrize("dtype, plain_only", MODES)
+def test_norm_feed_forward_embedding_head(dtype, plain_only):
     from mini_llm_b200.parts import PartSpec, build_part
     rng = np.random.default_rng(0)
-    width, inner, vocab, n = 112, 300, 333, 9
-    ctx = make_ctx(dtype, rng.integers(0, vocab, n).tolist(), list(range(4, 4 + n)), [0] * n)
+    width, inner, vocab, n = 112, 304, 333, 9
+    ctx = make_ctx(dtype, rng.integers(0, vocab, n).tolist(), list(range(4, 4 + n)), [0] * n, plain_only)
 
     emb = build_part(PartSpec("token_embedding", "", {"vocab_size": vocab, "width": width}))
     pos = build_part(PartSpec("learned_positions", "", {"max_positions": 40, "width": width}))
@@ -83,11 +87,18 @@ def test_norm_feed_forward_embedding_head(dtype):
     logits = head.forward(ctx, x[2:5])
     assert logits.dtype == torch.float32 and logits.shape == (3, vocab)
     np.testing.assert_allclose(f64(logits), f64(x[2:5]) @ wh["out.weight"].T, rtol=0, atol=tol(dtype) * 4)
+    # the norm handed over unevaluated, with a gather of rows, as the model's last step does
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32, device="cuda")
+    logits = head.forward(ctx, norm.forward(ctx, hidden, rows=rows, tag="final", defer=True))
+    want = expected_x[[8, 0, 3]]
+    if dtype == torch.bfloat16:
+        want = plain.round_to_bfloat16(want)
+    np.testing.assert_allclose(f64(logits), want @ wh["out.weight"].T, rtol=0, atol=tol(dtype) * 4)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype, plain_only", MODES)
 @pytest.mark.parametrize("n_heads, n_kv_heads, head, window", [(3, 3, 32, None), (4, 2, 16, None), (2, 2, 48, 5)])
-def test_attention_part_with_its_cache(dtype, n_heads, n_kv_heads, head, window):
+def test_attention_part_with_its_cache(dtype, plain_only, n_heads, n_kv_heads, head, window):
     """Two requests; the first comes in two steps, so the second step reads keys the first
     stored.  Compared with plain attention over the whole sequences."""
     from mini_llm_b200.cache import CacheManager
@@ -113,7 +124,7 @@ def test_attention_part_with_its_cache(dtype, n_heads, n_kv_heads, head, window)
             rows.append(xs[s][start:start + n])
             positions += list(range(start, start + n))
             items += [index] * n
-        ctx = make_ctx(dtype, [0] * len(positions), positions, items)
+        ctx = make_ctx(dtype, [0] * len(positions), positions, items, plain_only)
         view.block_table = torch.tensor(np.stack([manager.block_table_row(0, slots[s]) for s, _, _ in step]),
                                         device="cuda")
         x = torch.cat(rows)
