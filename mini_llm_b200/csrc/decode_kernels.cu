@@ -378,3 +378,66 @@ extern "C" int mllm_decode_split_attention(void* out, long ld_out, const void* q
 extern "C" int mllm_decode_split_attention_takes(int head_size) {
     return head_size == 16 || head_size == 32 || head_size == 64 || head_size == 128 || head_size == 256;
 }
+
+// ---------------------------------------------------------------------------
+// split_attention with built-in scratch, for callers that cannot allocate
+// (see split_attention_static.h for who they are and what the limits mean).
+// ---------------------------------------------------------------------------
+#include "split_attention_static.h"
+
+// Device memory.  In host code this name is only a handle for the symbol, not an address a
+// kernel could use: the address is asked for once per device, below.
+static __device__ __align__(256) unsigned char
+    g_static_scratch[(MLLM_STATIC_ACC_FLOATS + MLLM_STATIC_ML_FLOATS) * sizeof(float) +
+                     MLLM_STATIC_COUNTERS * sizeof(int)];
+
+constexpr int STATIC_MAX_DEVICES = 64;
+static unsigned char* g_static_address[STATIC_MAX_DEVICES] = {nullptr};
+
+extern "C" int mllm_decode_split_attention_static(void* out, long ld_out, const void* q, long ld_q,
+                                                  const void* k_pages, const void* v_pages, const int* block_table,
+                                                  int max_blocks, const int* positions, const int* token_item,
+                                                  int n_tokens, int n_heads, int n_kv_heads, int head_size,
+                                                  int page_size, float scale, int window, int chunk, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (n_heads <= 0 || chunk <= 0 || page_size <= 0 || max_blocks <= 0 || head_size <= 0)
+        return fail("split_attention_static: sizes must be positive");
+    const long chunks = ((long)max_blocks * page_size + chunk - 1) / chunk;
+    const long pairs = (long)n_tokens * n_heads;
+    if (pairs > MLLM_STATIC_COUNTERS || pairs * chunks * 2 > MLLM_STATIC_ML_FLOATS ||
+        pairs * chunks * head_size > MLLM_STATIC_ACC_FLOATS) {
+        snprintf(g_error_text, MLLM_ERROR_BUFFER,
+                 "split_attention_static: %d tokens x %d heads x %ld chunks x head size %d exceed the built-in scratch "
+                 "(%d partial floats, %d max/sum floats, %d counters); use mllm_decode_split_attention with your own",
+                 n_tokens, n_heads, chunks, head_size, MLLM_STATIC_ACC_FLOATS, MLLM_STATIC_ML_FLOATS,
+                 MLLM_STATIC_COUNTERS);
+        return 1;
+    }
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= STATIC_MAX_DEVICES)
+        return fail("split_attention_static: cannot tell the current device");
+    if (g_static_address[device] == nullptr) {
+        // set-up, once per device, with that device current
+        void* address = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&address, g_static_scratch);
+        if (e != cudaSuccess || address == nullptr) {
+            snprintf(g_error_text, MLLM_ERROR_BUFFER, "split_attention_static: cudaGetSymbolAddress failed: %s",
+                     cudaGetErrorString(e));
+            return 2;
+        }
+        g_static_address[device] = static_cast<unsigned char*>(address);
+    }
+    float* part_acc = reinterpret_cast<float*>(g_static_address[device]);
+    float* part_ml = part_acc + MLLM_STATIC_ACC_FLOATS;
+    int* counters = reinterpret_cast<int*>(part_ml + MLLM_STATIC_ML_FLOATS);
+    // The array keeps the last call's contents; the counters must start at zero.
+    cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)pairs * sizeof(int), (cudaStream_t)stream);
+    if (e != cudaSuccess) {
+        snprintf(g_error_text, MLLM_ERROR_BUFFER, "split_attention_static: clearing the counters failed: %s",
+                 cudaGetErrorString(e));
+        return 2;
+    }
+    return mllm_decode_split_attention(out, ld_out, q, ld_q, k_pages, v_pages, block_table, max_blocks, positions,
+                                       token_item, n_tokens, n_heads, n_kv_heads, head_size, page_size, scale, window,
+                                       chunk, (int)chunks, part_acc, part_ml, counters, stream);
+}
