@@ -1,0 +1,460 @@
+// Matrix products on the fifth-generation tensor cores: out = epilogue(x W^T + bias),
+// bfloat16 operands, fp32 accumulation in tensor memory.
+//
+// One CTA computes one 128 x BN tile.  A producer warp streams 128 x 64 and BN x 64 operand
+// blocks into a ring of shared-memory stages with TMA (128-byte swizzle); one thread of the
+// MMA warp issues tcgen05.mma on each filled stage (four K=16 instructions per block) and
+// releases the stage with tcgen05.commit; four epilogue warps wait for the accumulator,
+// read their 32 TMEM lanes with tcgen05.ld, and fuse bias, gelu or the residual sum into the
+// store.  The reference runs every prefill product as a naive one-thread-per-output kernel
+// followed by separate bias, gelu and add launches (engine/src/matrixmult.cu:7-34,
+// engine/src/linear.cu:9-18, engine/src/transformer_block.cu:153-202).
+//
+// Two orientations:
+//   rows    the 128 tile rows are rows of x (tokens), the BN tile columns rows of W.
+//   swapped the 128 tile rows are rows of W (outputs), the BN columns are tokens: for steps
+//           of few tokens, where a 128-row token tile would be mostly padding.
+//
+// Every wait on an mbarrier is bounded: when the bound is hit the kernel writes a code to
+// its status word, stops issuing work, waits (bounded again) for its own copies in flight,
+// frees its tensor memory and returns.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+MLLM_DEFINE_ERROR_API(mllm_gemm)
+
+namespace {
+
+constexpr int BM = 128;             // tile rows = TMEM lanes
+constexpr int BK = 64;              // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;        // warps 0-3 epilogue, 4 producer, 5 MMA
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;     // 2 s
+
+enum { STATUS_OK = 0, STATUS_TIMEOUT_PRODUCER = 1, STATUS_TIMEOUT_MMA = 2, STATUS_TIMEOUT_EPILOGUE = 3 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Wait for the phase with `parity` to complete; false if the time limit passed first.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long start = now_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (now_ns() - start > WAIT_LIMIT_NS) return false;
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes,
+// groups of eight rows 1024 bytes apart (the layout TMA writes with SWIZZLE_128B).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t desc = (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    desc |= (uint64_t)1 << 16;                       // leading byte offset: unused with a swizzle
+    desc |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset between 8-row groups
+    desc |= (uint64_t)1 << 46;                       // descriptor version of this architecture
+    desc |= (uint64_t)2 << 61;                       // 128-byte swizzle
+    return desc;
+}
+
+// Instruction descriptor of kind::f16: bf16 x bf16 -> fp32, both operands K-major.
+__device__ __forceinline__ uint32_t make_instr_desc(int m, int n) {
+    return (1u << 4)                     // accumulator fp32
+           | (1u << 7)                   // A bf16
+           | (1u << 10)                  // B bf16
+           | ((uint32_t)(n >> 3) << 17)  // N / 8
+           | ((uint32_t)(m >> 4) << 24); // M / 16
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                     uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, "
+        "[%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+
+struct GemmParams {
+    void* out;                // bf16 or fp32 [rows of x, ldo]
+    const float* bias;        // per output feature, or null
+    int* status;              // device word, non-zero after a bounded wait ran out
+    int M, N, K;              // rows of x, rows of W (output features), inner size
+    long ldo;
+    int epilogue;
+    int out_f32;
+};
+
+template <int EPI>
+__device__ __forceinline__ float finish(float v) {
+    return apply_activation<EPI>(v);
+}
+
+__device__ __forceinline__ float activate(float v, int epilogue) {
+    if (epilogue == EPI_GELU_TANH) return gelu_tanh_f(v);
+    if (epilogue == EPI_GELU_ERF) return gelu_erf_f(v);
+    return v;
+}
+
+template <int BN, int STAGES, bool SWAP>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GemmParams p) {
+    // map_a: the operand whose 128 rows fill the tile's rows; map_b: the operand of BN rows.
+    extern __shared__ unsigned char smem_raw[];
+    // The swizzled tiles must start on 1024-byte boundaries; the launch asks for 1024 spare bytes.
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    unsigned char* stage_a = smem;
+    unsigned char* stage_b = smem + STAGES * A_BYTES;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * (A_BYTES + B_BYTES));
+    uint64_t* empty = full + STAGES;
+    uint64_t* accumulator_ready = empty + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accumulator_ready + 1);
+    volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_a = SWAP ? blockIdx.x : blockIdx.y;      // which block of 128 rows of map_a
+    const int tile_b = SWAP ? blockIdx.y : blockIdx.x;      // which block of BN rows of map_b
+    const int num_k = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(accumulator_ready, 1);
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 4) {
+        // ---- producer ----
+        if (lane == 0) {
+            int issued = 0;
+            for (int kb = 0; kb < num_k; kb++) {
+                const int s = kb % STAGES;
+                if (!mbar_wait(&empty[s], ((kb / STAGES) & 1) ^ 1) || *failed) {
+                    if (!*failed) {
+                        *failed = STATUS_TIMEOUT_PRODUCER;
+                        atomicExch(p.status, STATUS_TIMEOUT_PRODUCER);
+                    }
+                    break;
+                }
+                mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+                tma_load_2d(stage_a + s * A_BYTES, &map_a, &full[s], kb * BK, tile_a * BM);
+                tma_load_2d(stage_b + s * B_BYTES, &map_b, &full[s], kb * BK, tile_b * BN);
+                issued = kb + 1;
+            }
+            if (*failed) {
+                // Copies that were issued still land in shared memory: wait for them (bounded)
+                // so that none is in flight when the CTA ends.
+                for (int kb = max(0, issued - STAGES); kb < issued; kb++)
+                    mbar_wait(&full[kb % STAGES], (kb / STAGES) & 1);
+            }
+        }
+    } else if (warp == 5) {
+        // ---- MMA issue ----
+        if (lane == 0) {
+            const uint32_t idesc = make_instr_desc(BM, BN);
+            for (int kb = 0; kb < num_k; kb++) {
+                const int s = kb % STAGES;
+                if (!mbar_wait(&full[s], (kb / STAGES) & 1) || *failed) {
+                    if (!*failed) {
+                        *failed = STATUS_TIMEOUT_MMA;
+                        atomicExch(p.status, STATUS_TIMEOUT_MMA);
+                    }
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t desc_a = make_smem_desc(smem_u32(stage_a + s * A_BYTES));
+                const uint64_t desc_b = make_smem_desc(smem_u32(stage_b + s * B_BYTES));
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; k++) {
+                    // 16 elements along K = 32 bytes = 2 units of the descriptor's address field
+                    umma(tmem_base, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&empty[s]);          // frees the stage once these MMAs have read it
+            }
+            umma_commit(accumulator_ready);      // arrives when every MMA above has finished
+        }
+    } else {
+        // ---- epilogue: warp w owns TMEM lanes 32w .. 32w+31 ----
+        bool ok = true;
+        if (lane == 0) ok = mbar_wait(accumulator_ready, 0);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok || *failed) {
+            if (lane == 0 && !*failed) {
+                *failed = STATUS_TIMEOUT_EPILOGUE;
+                atomicExch(p.status, STATUS_TIMEOUT_EPILOGUE);
+            }
+        } else {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int r = tile_a * BM + warp * 32 + lane;          // row of map_a's operand
+            const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+            if (!SWAP) {
+                // r: a row of x (token); columns: output features
+                const bool row_ok = r < p.M;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    float v[16];
+                    __syncwarp();                    // the TMEM load is warp-wide: rejoin first
+                    tmem_load_16(lane_base + c0, v);
+                    const int n0 = tile_b * BN + c0;
+                    if (!row_ok || n0 >= p.N) continue;
+#pragma unroll
+                    for (int i = 0; i < 16; i++)
+                        if (p.bias != nullptr && n0 + i < p.N) v[i] += p.bias[n0 + i];
+                    const bool whole = n0 + 16 <= p.N;
+                    if (p.epilogue == EPI_ADD) {
+                        float* o = reinterpret_cast<float*>(p.out) + (long)r * p.ldo + n0;
+                        if (whole && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+                            for (int i = 0; i < 16; i += 4) {
+                                float4 old = *reinterpret_cast<float4*>(o + i);
+                                old.x += v[i]; old.y += v[i + 1]; old.z += v[i + 2]; old.w += v[i + 3];
+                                *reinterpret_cast<float4*>(o + i) = old;
+                            }
+                        } else {
+                            for (int i = 0; i < 16 && n0 + i < p.N; i++) o[i] += v[i];
+                        }
+                    } else if (p.out_f32) {
+                        float* o = reinterpret_cast<float*>(p.out) + (long)r * p.ldo + n0;
+                        if (whole && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+                            for (int i = 0; i < 16; i += 4)
+                                *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                        } else {
+                            for (int i = 0; i < 16 && n0 + i < p.N; i++) o[i] = v[i];
+                        }
+                    } else {
+                        bf16* o = reinterpret_cast<bf16*>(p.out) + (long)r * p.ldo + n0;
+#pragma unroll
+                        for (int i = 0; i < 16; i++) v[i] = activate(v[i], p.epilogue);
+                        if (whole && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+                            uint32_t packed[8];
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                __nv_bfloat162 two = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                                packed[i] = *reinterpret_cast<uint32_t*>(&two);
+                            }
+                            *reinterpret_cast<uint4*>(o) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                            *reinterpret_cast<uint4*>(o + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        } else {
+                            for (int i = 0; i < 16 && n0 + i < p.N; i++) o[i] = __float2bfloat16_rn(v[i]);
+                        }
+                    }
+                }
+            } else {
+                // r: an output feature; columns: tokens.  Consecutive lanes write consecutive
+                // features of one token: coalesced.
+                const bool row_ok = r < p.N;
+                const float b = (row_ok && p.bias != nullptr) ? p.bias[r] : 0.0f;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    float v[16];
+                    __syncwarp();
+                    tmem_load_16(lane_base + c0, v);
+                    if (!row_ok) continue;
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const int t = tile_b * BN + c0 + i;
+                        if (t >= p.M) break;
+                        const float x = v[i] + b;
+                        const long at = (long)t * p.ldo + r;
+                        if (p.epilogue == EPI_ADD) reinterpret_cast<float*>(p.out)[at] += x;
+                        else if (p.out_f32) reinterpret_cast<float*>(p.out)[at] = x;
+                        else reinterpret_cast<bf16*>(p.out)[at] = __float2bfloat16_rn(activate(x, p.epilogue));
+                    }
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 5) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
+    }
+}
+
+// ---- host side: tensor maps ------------------------------------------------------------
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled g_encode = nullptr;
+std::mutex g_lock;
+
+struct MapKey {
+    const void* base;
+    long rows, cols, ld;
+    int box_rows;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = reinterpret_cast<size_t>(k.base);
+        h = h * 1000003u ^ (size_t)k.rows;
+        h = h * 1000003u ^ (size_t)k.cols;
+        h = h * 1000003u ^ (size_t)k.ld;
+        return h * 1000003u ^ (size_t)k.box_rows;
+    }
+};
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+// A [rows, cols] bf16 matrix with row stride ld; boxes of box_rows x 64 elements, 128-byte
+// swizzle, zero fill outside the matrix.
+int tensor_map(const void* base, long rows, long cols, long ld, int box_rows, CUtensorMap* out) {
+    std::lock_guard<std::mutex> guard(g_lock);
+    if (g_encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &result) != cudaSuccess ||
+            fn == nullptr || result != cudaDriverEntryPointSuccess)
+            return fail("gemm: the driver does not offer cuTensorMapEncodeTiled");
+        g_encode = reinterpret_cast<EncodeTiled>(fn);
+    }
+    MapKey key{base, rows, cols, ld, box_rows};
+    auto found = g_maps.find(key);
+    if (found != g_maps.end()) {
+        *out = found->second;
+        return 0;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_error_text, MLLM_ERROR_BUFFER, "gemm: cuTensorMapEncodeTiled failed with code %d", (int)r);
+        return 3;
+    }
+    if (g_maps.size() > 4096) g_maps.clear();
+    g_maps.emplace(key, *out);
+    return 0;
+}
+
+template <int BN, int STAGES, bool SWAP>
+int launch(const CUtensorMap& a, const CUtensorMap& b, const GemmParams& p, dim3 grid, cudaStream_t s) {
+    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, SWAP>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail("gemm: cannot raise the shared memory limit");
+        configured = true;
+    }
+    gemm_tcgen05_kernel<BN, STAGES, SWAP><<<grid, THREADS, smem, s>>>(a, b, p);
+    return check_launch("gemm_tcgen05_kernel");
+}
+
+}  // namespace
+
+// Whether the kernel takes a product: K a multiple of 8 (rows of both operands start on
+// 16-byte boundaries) and 16-byte aligned bases and row strides.
+extern "C" int mllm_gemm_takes(long K, long ldx, const void* x, const void* w) {
+    return K > 0 && K % 8 == 0 && ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+           (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+}
+
+// out[M, N] = epilogue(x[M, K] w[N, K]^T + bias).  x, w bf16 (K contiguous; x with row stride
+// ldx); out bf16, or fp32 with out_f32 or the residual epilogue.  status: a device int that
+// must be zero; a non-zero value afterwards means a bounded wait inside the kernel ran out.
+extern "C" int mllm_gemm_bf16(void* out, const void* x, const void* w, const float* bias, int M, int N, int K,
+                              long ldx, long ldo, int epilogue, int out_f32, int* status, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (!mllm_gemm_takes(K, ldx, x, w)) return fail("gemm: K and the row stride of x must be multiples of 8, bases 16-byte aligned");
+    if (epilogue == EPI_ADD && !out_f32) return fail("gemm: the residual sum is kept in 32-bit");
+    if (status == nullptr) return fail("gemm: a status word is required");
+    cudaStream_t s = (cudaStream_t)stream;
+    GemmParams p{out, bias, status, M, N, K, ldo, epilogue, out_f32};
+    CUtensorMap map_x, map_w;
+    const bool swap = M <= 64;
+    int bn = 128;
+    if (swap) bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    int rc = tensor_map(x, M, K, ldx, swap ? bn : BM, &map_x);
+    if (rc) return rc;
+    rc = tensor_map(w, N, K, K, swap ? BM : bn, &map_w);
+    if (rc) return rc;
+    if (!swap) {
+        dim3 grid((N + 127) / 128, (M + BM - 1) / BM);
+        return launch<128, 6, false>(map_x, map_w, p, grid, s);
+    }
+    dim3 grid((N + BM - 1) / BM, (M + bn - 1) / bn);
+    if (bn == 16) return launch<16, 8, true>(map_w, map_x, p, grid, s);
+    if (bn == 32) return launch<32, 8, true>(map_w, map_x, p, grid, s);
+    return launch<64, 8, true>(map_w, map_x, p, grid, s);
+}

@@ -85,6 +85,7 @@ class Engine:
         self._sampled = None
         self._graphs = {}
         self._graph_stamp = None
+        self._status_checks = 0
 
     # ---- requests ---------------------------------------------------------------------------
     def open_request(self) -> int | None:
@@ -252,4 +253,12 @@ class Engine:
         """The tokens the last step sampled, on the host (waits for the step)."""
         if self._sampled is None:
             return []
-        return self._sampled.cpu().tolist()
+        tokens = self._sampled.cpu().tolist()
+        self._status_checks += 1
+        if self._status_checks % 64 == 1:
+            self.kernels.check_status()
+        return tokens
+
+    def check_status(self) -> None:
+        """Raise if a kernel gave up on one of its bounded waits since the last check."""
+        self.kernels.check_status()

@@ -67,6 +67,7 @@ def replay(args, lines, out=sys.stdout):
             logits = engine.step(entries)
             if logits is not None:
                 host = logits.to("cpu", copy=True).numpy().astype("<f4", copy=False)
+                engine.check_status()
                 host.tofile(os.path.join(args.out, f"{step}.f32"))
         for name in record.get("end", []):
             if name in slots:

@@ -38,6 +38,7 @@ LIBRARIES = {
     "plain": "plain_kernels.cu",
     "sampling": "sampling_kernels.cu",
     "decode": "decode_kernels.cu",
+    "gemm": "gemm_tcgen05.cu",
 }
 
 _lock = threading.Lock()

@@ -16,7 +16,8 @@ import torch
 
 from . import ops
 
-SKINNY_MAX_ROWS = 64          # above this a step's products are compute-bound: tiled kernels take over
+SKINNY_MAX_ROWS = 16          # up to here a product streams the weights once through the SIMT kernel
+SPLIT_ATTENTION_MAX_ROWS = 64 # up to here attention runs one CTA per (token, head, chunk of keys)
 
 
 class DeferredNorm:
@@ -44,6 +45,7 @@ class Kernels:
         self.plain_only = bool(plain_only) or act_dtype == torch.float32
         self.launches = 0            # kernels launched (or recorded into a graph) since the start
         self._split_scratch = None
+        self._status = None          # device word the tensor-core kernels report a timed-out wait in
 
     # ---- operations without a fast variant --------------------------------------------------
     def embed(self, out, token_ids, positions, table, position_table=None):
@@ -79,8 +81,24 @@ class Kernels:
                 return ops.skinny_linear(out, a.x, w, bias, epilogue, norm=(a.gamma, a.beta, a.eps, a.rows))
             return ops.skinny_linear(out, a, w, bias, epilogue)
         if isinstance(a, DeferredNorm):
+            self.launches += 1
             a = a.materialize(ctx)
+        if not self.plain_only and ops.gemm_takes(a, w):
+            return ops.gemm_bf16(out, a, w, bias, epilogue, self.status(ctx.device))
         return ops.linear_plain(out, a, w, bias, epilogue)
+
+    def status(self, device):
+        if self._status is None:
+            self._status = torch.zeros(1, dtype=torch.int32, device=device)
+        return self._status
+
+    def check_status(self) -> None:
+        """Raise if a kernel reported that one of its bounded waits ran out (synchronises)."""
+        if self._status is not None:
+            code = int(self._status.item())
+            if code != 0:
+                self._status.zero_()
+                raise ops.KernelError(f"a tensor-core kernel gave up waiting (code {code}): its result is invalid")
 
     def qkv_projection(self, ctx, a, w, bias, cache, q_width, kv_width):
         """The fused query/key/value projection.  Keys and values of the step's tokens go into
@@ -108,14 +126,14 @@ class Kernels:
     def attention(self, ctx, out, q, cache, n_heads, n_kv_heads, head_size, scale, window=0):
         self.launches += 1
         n = q.shape[0]
-        if (not self.plain_only and n <= SKINNY_MAX_ROWS and head_size in ops.SPLIT_ATTENTION_HEAD_SIZES):
+        if (not self.plain_only and n <= SPLIT_ATTENTION_MAX_ROWS and head_size in ops.SPLIT_ATTENTION_HEAD_SIZES):
             # chunk of keys per CTA: small when there are few (token, head) pairs, so that the
             # chunks still fill the GPU
             pairs = n * n_heads
             chunk = 64 if pairs < 64 else (128 if pairs < 256 else 256)
             reach = cache.block_table.shape[1] * cache.page_size
             max_chunks = -(-reach // chunk)
-            acc, ml, counters = self._scratch(ctx, SKINNY_MAX_ROWS * n_heads, -(-reach // 64), head_size)
+            acc, ml, counters = self._scratch(ctx, SPLIT_ATTENTION_MAX_ROWS * n_heads, -(-reach // 64), head_size)
             return ops.split_attention(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
                                        ctx.token_item, n_heads, n_kv_heads, head_size, cache.page_size, scale,
                                        window, chunk, max_chunks, acc, ml, counters)

@@ -308,3 +308,47 @@ def split_attention(out, q, k_pages, v_pages, block_table, positions, token_item
                      n_heads, n_kv_heads, head_size, page_size, float(scale), int(window or 0), int(chunk),
                      int(max_chunks), part_acc.data_ptr(), part_ml.data_ptr(), counters.data_ptr(), _stream())
     return out
+
+
+# ---- tensor-core matrix product (bfloat16) -------------------------------------------------------
+
+_gemm_bf16 = Function("gemm", "mllm_gemm_bf16", [P, P, P, P, I, I, I, L, L, I, I, P, P])
+
+
+def gemm_takes(a, w) -> bool:
+    """Whether the tensor-core kernel takes ``a @ w.T``: bf16, K a multiple of 8, 16-byte
+    aligned bases and row strides (what its TMA copies need)."""
+    if not isinstance(a, torch.Tensor) or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return False
+    k = a.shape[1]
+    return (k % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) == 1 and a.data_ptr() % 16 == 0
+            and w.is_contiguous() and w.data_ptr() % 16 == 0)
+
+
+def gemm_bf16(out, a, w, bias, epilogue, status):
+    """out = epilogue(a @ w.T + bias) on the tensor cores (tcgen05, TMEM accumulators, TMA).
+
+    a [M, K] and w [N, K] bf16; out bf16, or fp32 for logits and for the residual epilogue
+    "add".  ``status``: a zeroed int32 device word the kernel writes a code to if one of its
+    bounded waits runs out."""
+    _check(a, "gemm.a", torch.bfloat16, 2)
+    _check(w, "gemm.w", torch.bfloat16, 2)
+    _check(out, "gemm.out", None, 2)
+    _check(status, "gemm.status", torch.int32)
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape[0] != m or out.shape[1] != n:
+        raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if not gemm_takes(a, w):
+        raise KernelError("gemm: operands are not laid out for the tensor-core kernel")
+    if out.dtype not in (torch.bfloat16, torch.float32) or (epilogue == "add" and out.dtype != torch.float32):
+        raise KernelError("gemm: out must be bfloat16, or float32 for logits and the residual sum")
+    if out.dtype == torch.float32 and epilogue not in ("add", "store"):
+        raise KernelError("gemm: an activation is stored in bfloat16")
+    if bias is not None:
+        _check(bias, "gemm.bias", torch.float32, 1)
+        if bias.shape[0] != n:
+            raise KernelError("gemm: bias has another length")
+    _gemm_bf16(out.data_ptr(), a.data_ptr(), w.data_ptr(), _ptr(bias), m, n, k, a.stride(0), out.stride(0),
+               EPILOGUES[epilogue], int(out.dtype == torch.float32), status.data_ptr(), _stream())
+    return out

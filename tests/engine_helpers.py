@@ -149,6 +149,7 @@ def run_schedule(engine, requests, steps, want_all=True):
             places.extend((name, start + w) for w in want)
             progress[name] += n
         logits = engine.step(entries).cpu().numpy()
+        engine.check_status()
         assert logits.shape == (len(places), vocab)
         for row, (name, position) in zip(logits, places):
             out[name][position] = row

@@ -380,3 +380,55 @@ def test_split_attention_finds_one_far_key_and_respects_the_windows_edge():
     assert float(out.float().abs().max()) < 10.0
     run(length - far)
     np.testing.assert_allclose(f64(out)[0], f64(dev(v[far], torch.bfloat16)), rtol=2e-2, atol=0.5)
+
+
+# ---- tensor-core matrix product --------------------------------------------------------------
+
+@pytest.mark.parametrize("m, n, k", [
+    (128, 128, 64), (128, 128, 256), (256, 384, 768), (300, 1000, 160), (2048, 768, 768), (1, 256, 64),
+    (8, 2304, 768), (17, 777, 96), (40, 768, 3072), (64, 1000, 160), (65, 136, 72), (5, 50257, 64),
+    (1024, 3072, 768), (513, 768, 3072)])
+@pytest.mark.parametrize("epilogue", ["store", "gelu_tanh", "gelu_erf", "add", "logits"])
+def test_gemm_tcgen05(m, n, k, epilogue):
+    from mini_llm_b200.kernels import ops
+    if epilogue != "store" and (m, n, k) not in [(128, 128, 256), (300, 1000, 160), (17, 777, 96), (64, 1000, 160),
+                                                 (513, 768, 3072), (5, 50257, 64)]:
+        pytest.skip("epilogues are covered at fewer sizes")
+    rng = np.random.default_rng(m + n + k)
+    a, w = dev(rng.normal(size=(m, k)), torch.bfloat16), dev(rng.normal(size=(n, k)) / math.sqrt(k), torch.bfloat16)
+    bias = dev(rng.normal(size=n), torch.float32)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    acc = f64(a) @ f64(w).T + f64(bias)
+    if epilogue == "add":
+        out = dev(rng.normal(size=(m, n)), torch.float32)
+        expected = f64(out) + acc
+        ops.gemm_bf16(out, a, w, bias, "add", status)
+        atol = 2e-4
+    elif epilogue == "logits":
+        out = torch.full((m, n), float("nan"), device="cuda", dtype=torch.float32)
+        ops.gemm_bf16(out, a, w, None, "store", status)
+        expected, atol = f64(a) @ f64(w).T, 2e-4
+    else:
+        out = torch.full((m, n), float("nan"), device="cuda", dtype=torch.bfloat16)
+        ops.gemm_bf16(out, a, w, bias, epilogue, status)
+        expected = {"store": acc, "gelu_tanh": plain.gelu_tanh(acc), "gelu_erf": plain.gelu_erf(acc)}[epilogue]
+        atol = tol(torch.bfloat16, 4)
+    assert int(status.item()) == 0, "a bounded wait inside the kernel ran out"
+    np.testing.assert_allclose(f64(out), expected, rtol=0, atol=atol)
+
+
+def test_gemm_tcgen05_strided_input_and_twin():
+    """A column slice as input (the row stride differs from K), against the plain twin."""
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(77)
+    m, n, k = 200, 520, 192
+    wide = dev(rng.normal(size=(m, 3 * k)), torch.bfloat16)
+    w = dev(rng.normal(size=(n, k)) / math.sqrt(k), torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    a = wide[:, k:2 * k]
+    assert ops.gemm_takes(a, w) and not ops.gemm_takes(wide[:, 4:4 + k], w)
+    fast, slow = torch.empty(m, n, device="cuda", dtype=torch.bfloat16), torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_bf16(fast, a, w, None, "store", status)
+    ops.linear_plain(slow, a, w, None, "store")
+    assert int(status.item()) == 0
+    np.testing.assert_allclose(f64(fast), f64(slow), rtol=0, atol=tol(torch.bfloat16, 2))
