@@ -1,0 +1,431 @@
+// Causal attention for prompt portions on the fifth-generation tensor cores, reading keys
+// and values from the paged cache.
+//
+// One CTA takes 128 consecutive tokens of one request (a "tile" of queries) and one head.
+// For every block of 128 keys up to the tile's last position:
+//   producer warp   TMA-loads the block's keys and values page by page (the block table
+//                   names the pages) into shared memory, 128-byte swizzle;
+//   MMA warp        S = Q K^T with tcgen05.mma into tensor memory, later O_blk = P V;
+//   softmax warps   one thread per query row reads its row of S from tensor memory, applies
+//                   scale, causal (and window) mask and the online softmax in 32-bit, writes
+//                   P as bfloat16 into shared memory for the second product, and folds
+//                   O_blk into its running output row with the usual rescaling.
+// The reference's prefill attention is one thread per (query, head) walking all keys serially
+// with the same online softmax (engine/src/attention.cu:71-124); its math is kept, the
+// products move to the tensor cores.
+//
+// Two CTAs fit one SM (256 TMEM columns and ~100 KB of shared memory each): while one waits
+// for its softmax the other's products run.  Every mbarrier wait is bounded (tcgen05.cuh).
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+MLLM_DEFINE_ERROR_API(mllm_attention)
+
+namespace {
+
+constexpr int TILE = 128;          // queries per CTA = keys per block = TMEM lanes
+constexpr int KV_STAGES = 2;
+constexpr int THREADS = 192;       // warps 0-3 softmax, 4 producer, 5 MMA
+constexpr int TMEM_COLS = 256;     // S: columns 0..127, O_blk: columns 128..128+D-1
+
+struct AttentionParams {
+    bf16* out;                     // [T, ld_out]
+    long ld_out;
+    const int* tiles;              // per tile: item, first row, rows, position of the first row
+    const int* block_table;        // [items, max_blocks]
+    int max_blocks;
+    int n_heads, n_kv_heads;
+    int page_size, n_pages;
+    float scale_log2;              // score scale * log2(e)
+    int window;                    // 0: all keys
+    int* status;
+};
+
+template <int D>
+__global__ void __launch_bounds__(THREADS, 2)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                         const __grid_constant__ CUtensorMap map_v, const AttentionParams p) {
+    constexpr int DB = D / 64;                     // 64-column blocks of the head size
+    constexpr int TILE_BYTES = TILE * 64 * 2;      // one [128 x 64] bf16 block, 16 KB
+    // Swizzled tiles start on 1024-byte boundaries.  There is no static shared memory in this
+    // kernel, so the dynamic part starts the CTA's window; should it ever not be aligned, the
+    // CTA reports that and does nothing (two CTAs per SM leave no room for slack).
+    extern __shared__ __align__(1024) unsigned char smem[];
+    if ((smem_u32(smem) & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicExch(p.status, 14);
+        return;
+    }
+    unsigned char* q_tile = smem;                                   // DB blocks
+    unsigned char* k_stage = q_tile + DB * TILE_BYTES;              // KV_STAGES x DB blocks
+    unsigned char* v_stage = k_stage + KV_STAGES * DB * TILE_BYTES; // KV_STAGES x DB blocks
+    unsigned char* p_tile = v_stage + KV_STAGES * DB * TILE_BYTES;  // 2 blocks: keys 0..63, 64..127
+    uint64_t* bars = reinterpret_cast<uint64_t*>(p_tile + 2 * TILE_BYTES);
+    uint64_t* q_full = bars;
+    uint64_t* kv_full = bars + 1;                  // [KV_STAGES]
+    uint64_t* kv_empty = kv_full + KV_STAGES;      // [KV_STAGES]
+    uint64_t* s_ready = kv_empty + KV_STAGES;
+    uint64_t* p_ready = s_ready + 1;
+    uint64_t* o_ready = p_ready + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + 1);
+    volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int* tile = p.tiles + 4 * blockIdx.x;
+    const int item = tile[0], row0 = tile[1], n_rows = tile[2], pos0 = tile[3];
+    const int head = blockIdx.y;
+    const int kv_head = head / (p.n_heads / p.n_kv_heads);
+    const int last_pos = pos0 + n_rows - 1;
+    const int first_key = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
+    const int block_lo = first_key / TILE, block_hi = last_pos / TILE;       // inclusive
+    const int n_blocks = block_hi - block_lo + 1;
+    const int pages_per_block = TILE / p.page_size;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < KV_STAGES; s++) {
+            mbar_init(&kv_full[s], 1);
+            mbar_init(&kv_empty[s], 1);
+        }
+        mbar_init(s_ready, 1);
+        mbar_init(p_ready, 1);
+        mbar_init(o_ready, 1);
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) tmem_alloc(tmem_slot, TMEM_COLS);
+    tcgen05_before_sync();
+    __syncthreads();
+    tcgen05_after_sync();
+    const uint32_t tmem_s = *tmem_slot;
+    const uint32_t tmem_o = tmem_s + 128;
+
+    if (warp == 4) {
+        // ---- producer ----
+        if (lane == 0) {
+            mbar_expect_tx(q_full, DB * TILE_BYTES);
+            for (int db = 0; db < DB; db++)
+                tma_load_2d(q_tile + db * TILE_BYTES, &map_q, q_full, head * D + db * 64, row0);
+            const int* bt = p.block_table + (long)item * p.max_blocks;
+            int issued = 0;
+            for (int j = 0; j < n_blocks; j++) {
+                const int s = j % KV_STAGES;
+                if (!mbar_wait(&kv_empty[s], ((j / KV_STAGES) & 1) ^ 1) || *failed) {
+                    if (!*failed) {
+                        *failed = 1;
+                        atomicExch(p.status, 11);
+                    }
+                    break;
+                }
+                mbar_expect_tx(&kv_full[s], 2 * DB * TILE_BYTES);
+                const int first_page = (block_lo + j) * pages_per_block;
+                for (int g = 0; g < pages_per_block; g++) {
+                    const int index = first_page + g;
+                    // A page past the request's last one is read outside the pool: zeros.
+                    int page = (index < p.max_blocks && index * p.page_size <= last_pos) ? bt[index] : -1;
+                    if (page < 0) page = p.n_pages;
+                    const int offset = g * p.page_size * 128;           // rows of 128 bytes
+                    for (int db = 0; db < DB; db++) {
+                        tma_load_4d(k_stage + (s * DB + db) * TILE_BYTES + offset, &map_k, &kv_full[s], db * 64,
+                                    kv_head, 0, page);
+                        tma_load_4d(v_stage + (s * DB + db) * TILE_BYTES + offset, &map_v, &kv_full[s], db * 64,
+                                    kv_head, 0, page);
+                    }
+                }
+                issued = j + 1;
+            }
+            if (*failed) {
+                mbar_wait(q_full, 0);
+                for (int j = max(0, issued - KV_STAGES); j < issued; j++)
+                    mbar_wait(&kv_full[j % KV_STAGES], (j / KV_STAGES) & 1);
+            }
+        }
+    } else if (warp == 5) {
+        // ---- MMA issue ----
+        if (lane == 0) {
+            const uint32_t idesc_s = make_instr_desc(TILE, TILE);
+            const uint32_t idesc_o = make_instr_desc(TILE, D) | IDESC_B_MN_MAJOR;
+            bool ok = mbar_wait(q_full, 0);
+            auto issue_s = [&](int j) {
+                const int s = j % KV_STAGES;
+                tcgen05_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < D / UMMA_K; kk++) {
+                    const uint64_t a = make_smem_desc(smem_u32(q_tile + (kk / 4) * TILE_BYTES)) + 2 * (kk % 4);
+                    const uint64_t b = make_smem_desc(smem_u32(k_stage + (s * DB + kk / 4) * TILE_BYTES)) + 2 * (kk % 4);
+                    umma(tmem_s, a, b, idesc_s, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(s_ready);
+            };
+            if (ok && n_blocks > 0) ok = mbar_wait(&kv_full[0], 0);
+            if (ok) issue_s(0);
+            for (int j = 0; ok && j < n_blocks; j++) {
+                const int s = j % KV_STAGES;
+                ok = mbar_wait(p_ready, j & 1) && !*failed;       // P is in shared memory, S has been read
+                if (!ok) break;
+                tcgen05_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < TILE / UMMA_K; kk++) {
+                    const uint64_t a = make_smem_desc(smem_u32(p_tile + (kk / 4) * TILE_BYTES)) + 2 * (kk % 4);
+                    // 16 keys = two 8-row groups of the value tile; head dims beyond 64 lie one tile further
+                    const uint64_t b = make_smem_desc_mn(smem_u32(v_stage + s * DB * TILE_BYTES + kk * 2048), TILE_BYTES);
+                    umma(tmem_o, a, b, idesc_o, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(o_ready);
+                umma_commit(&kv_empty[s]);
+                if (j + 1 < n_blocks) {
+                    ok = mbar_wait(&kv_full[(j + 1) % KV_STAGES], ((j + 1) / KV_STAGES) & 1) && !*failed;
+                    if (ok) issue_s(j + 1);
+                }
+            }
+            if (!ok && !*failed) {
+                *failed = 1;
+                atomicExch(p.status, 12);
+            }
+        }
+    } else {
+        // ---- softmax and output: thread r owns query row r ----
+        const int r = warp * 32 + lane;
+        const int my_pos = pos0 + min(r, n_rows - 1);
+        const int my_first = (p.window > 0 && my_pos - p.window + 1 > 0) ? my_pos - p.window + 1 : 0;
+        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+        float o[D];
+#pragma unroll
+        for (int d = 0; d < D; d++) o[d] = 0.0f;
+        float m = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_blocks; j++) {
+            if (lane == 0) ok = mbar_wait(s_ready, j & 1) && !*failed;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            tcgen05_after_sync();
+            const int key0 = (block_lo + j) * TILE;
+            const bool needs_mask = key0 + TILE - 1 > pos0 || key0 < my_first || (p.window > 0);
+            // pass 1: the row's maximum
+            float block_max = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < TILE; c += 32) {
+                float v[32];
+                tmem_load_32(tmem_s + lane_addr + c, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    const int key = key0 + c + i;
+                    const bool seen = !needs_mask || (key <= my_pos && key >= my_first);
+                    if (seen) block_max = fmaxf(block_max, v[i]);
+                }
+            }
+            const float m_new = fmaxf(m, block_max * p.scale_log2);
+            const float corr = (m == -INFINITY) ? 0.0f : exp2f(m - m_new);
+            const float base = (m_new == -INFINITY) ? 0.0f : m_new;
+            // pass 2: probabilities, as bfloat16 into shared memory (swizzled like a TMA tile)
+            float row_sum = 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < TILE; c += 32) {
+                float v[32];
+                tmem_load_32(tmem_s + lane_addr + c, v);
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float e[2];
+#pragma unroll
+                    for (int u = 0; u < 2; u++) {
+                        const int key = key0 + c + i + u;
+                        const bool seen = !needs_mask || (key <= my_pos && key >= my_first);
+                        e[u] = seen ? exp2f(v[i + u] * p.scale_log2 - base) : 0.0f;
+                    }
+                    __nv_bfloat162 two = __floats2bfloat162_rn(e[0], e[1]);
+                    // the sum uses the rounded values the second product will see
+                    row_sum += __low2float(two) + __high2float(two);
+                    packed[i / 2] = *reinterpret_cast<uint32_t*>(&two);
+                }
+                unsigned char* block = p_tile + (c / 64) * TILE_BYTES + r * 128;
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const int chunk = ((c % 64) / 8 + q) ^ (r & 7);
+                    *reinterpret_cast<uint4*>(block + chunk * 16) =
+                        make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                }
+            }
+            l = l * corr + row_sum;
+            m = m_new;
+            // hand P to the tensor core: writes visible to the async proxy, all 128 rows done
+            fence_async_smem();
+            tcgen05_before_sync();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 0) mbar_arrive(p_ready);
+            // fold this block's product into the running output
+            if (lane == 0) ok = mbar_wait(o_ready, j & 1) && !*failed;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            tcgen05_after_sync();
+#pragma unroll
+            for (int c = 0; c < D; c += 32) {
+                float v[32];
+                tmem_load_32(tmem_o + lane_addr + c, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) o[c + i] = o[c + i] * corr + v[i];
+            }
+            tcgen05_before_sync();
+        }
+        if (!ok) {
+            if (lane == 0 && !*failed) {
+                *failed = 1;
+                atomicExch(p.status, 13);
+            }
+        } else if (r < n_rows) {
+            const float inv = 1.0f / l;
+            bf16* dst = p.out + (long)(row0 + r) * p.ld_out + (long)head * D;
+#pragma unroll
+            for (int d = 0; d < D; d += 8) {
+                uint32_t packed[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    __nv_bfloat162 two = __floats2bfloat162_rn(o[d + 2 * i] * inv, o[d + 2 * i + 1] * inv);
+                    packed[i] = *reinterpret_cast<uint32_t*>(&two);
+                }
+                *reinterpret_cast<uint4*>(dst + d) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+        }
+    }
+
+    tcgen05_before_sync();
+    __syncthreads();
+    if (warp == 5) tmem_free(tmem_s, TMEM_COLS);
+}
+
+// ---- host side -------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled g_encode = nullptr;
+std::mutex g_lock;
+
+int encoder() {
+    if (g_encode != nullptr) return 0;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &result) != cudaSuccess ||
+        fn == nullptr || result != cudaDriverEntryPointSuccess)
+        return fail("attention: the driver does not offer cuTensorMapEncodeTiled");
+    g_encode = reinterpret_cast<EncodeTiled>(fn);
+    return 0;
+}
+
+int encode(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
+           const cuuint32_t* box) {
+    cuuint32_t elem[4] = {1, 1, 1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_error_text, MLLM_ERROR_BUFFER, "attention: cuTensorMapEncodeTiled failed with code %d", (int)r);
+        return 3;
+    }
+    return 0;
+}
+
+struct Key {
+    const void* base;
+    long a, b, c, d;
+    bool operator==(const Key& o) const { return base == o.base && a == o.a && b == o.b && c == o.c && d == o.d; }
+};
+struct KeyHash {
+    size_t operator()(const Key& k) const {
+        size_t h = reinterpret_cast<size_t>(k.base);
+        for (long v : {k.a, k.b, k.c, k.d}) h = h * 1000003u ^ (size_t)v;
+        return h;
+    }
+};
+std::unordered_map<Key, CUtensorMap, KeyHash> g_maps;
+
+// queries: a [rows, cols] view with row stride ld; boxes of 128 rows x 64 columns
+int query_map(const void* base, long rows, long cols, long ld, CUtensorMap* out) {
+    Key key{base, rows, cols, ld, -1};
+    auto found = g_maps.find(key);
+    if (found != g_maps.end()) { *out = found->second; return 0; }
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)TILE};
+    int rc = encode(out, base, 2, dims, strides, box);
+    if (rc == 0) g_maps.emplace(key, *out);
+    return rc;
+}
+
+// pages: [n_pages, page_size, kv_heads, head_size]; boxes of one page x one head x 64 columns
+int page_map(const void* base, long n_pages, long page_size, long kv_heads, long head_size, CUtensorMap* out) {
+    Key key{base, n_pages, page_size, kv_heads, head_size};
+    auto found = g_maps.find(key);
+    if (found != g_maps.end()) { *out = found->second; return 0; }
+    cuuint64_t dims[4] = {(cuuint64_t)head_size, (cuuint64_t)kv_heads, (cuuint64_t)page_size, (cuuint64_t)n_pages};
+    cuuint64_t strides[3] = {(cuuint64_t)head_size * 2, (cuuint64_t)kv_heads * head_size * 2,
+                             (cuuint64_t)page_size * kv_heads * head_size * 2};
+    cuuint32_t box[4] = {64, 1, (cuuint32_t)page_size, 1};
+    int rc = encode(out, base, 4, dims, strides, box);
+    if (rc == 0) g_maps.emplace(key, *out);
+    return rc;
+}
+
+template <int D>
+int launch(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v, const AttentionParams& p, int n_tiles,
+           cudaStream_t s) {
+    constexpr int DB = D / 64;
+    constexpr size_t smem = (size_t)(DB + 2 * KV_STAGES * DB + 2) * TILE * 64 * 2 + (2 * KV_STAGES + 4) * 8 + 16;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attention_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+            cudaSuccess)
+            return fail("attention: cannot raise the shared memory limit");
+        configured = true;
+    }
+    dim3 grid(n_tiles, p.n_heads);
+    attention_tcgen05_kernel<D><<<grid, THREADS, smem, s>>>(q, k, v, p);
+    return check_launch("attention_tcgen05_kernel");
+}
+
+}  // namespace
+
+// Whether the kernel takes a layout: head size 64 or 128, pages of 8, 16, 32, 64 or 128
+// tokens, query rows that start on 16-byte boundaries.
+extern "C" int mllm_attention_takes(int head_size, int page_size, long ld_q, const void* q) {
+    const bool page_ok = page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
+    return (head_size == 64 || head_size == 128) && page_ok && ld_q % 8 == 0 &&
+           (reinterpret_cast<uintptr_t>(q) & 15) == 0;
+}
+
+// tiles: device int32 [n_tiles, 4] = (entry of the step, first row among the step's tokens,
+// rows (1..128), position of the first row); rows of one tile belong to one request and
+// are consecutive.  status: zeroed device word, see the matrix-product kernel.
+extern "C" int mllm_attention_prefill(void* out, long ld_out, const void* q, long q_rows, long q_cols, long ld_q,
+                                      const void* k_pages, const void* v_pages, int n_pages, int page_size,
+                                      const int* block_table, int max_blocks, const int* tiles, int n_tiles,
+                                      int n_heads, int n_kv_heads, int head_size, float scale, int window,
+                                      int* status, void* stream) {
+    if (n_tiles <= 0) return 0;
+    if (!mllm_attention_takes(head_size, page_size, ld_q, q))
+        return fail("attention: head size must be 64 or 128, the page size a power of two in 8..128, q 16-byte aligned");
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_heads > 65535)
+        return fail("attention: heads must be a multiple of key/value heads");
+    if (ld_out % 8 != 0 || (reinterpret_cast<uintptr_t>(out) & 15) != 0)
+        return fail("attention: output rows must start on 16-byte boundaries");
+    CUtensorMap map_q, map_k, map_v;
+    {
+        std::lock_guard<std::mutex> guard(g_lock);
+        int rc = encoder();
+        if (rc) return rc;
+        if (g_maps.size() > 4096) g_maps.clear();
+        rc = query_map(q, q_rows, q_cols, ld_q, &map_q);
+        if (rc) return rc;
+        rc = page_map(k_pages, n_pages, page_size, n_kv_heads, head_size, &map_k);
+        if (rc) return rc;
+        rc = page_map(v_pages, n_pages, page_size, n_kv_heads, head_size, &map_v);
+        if (rc) return rc;
+    }
+    AttentionParams p{(bf16*)out, ld_out, tiles, block_table, max_blocks, n_heads, n_kv_heads, page_size, n_pages,
+                      scale * 1.4426950408889634f, window, status};
+    cudaStream_t s = (cudaStream_t)stream;
+    if (head_size == 64) return launch<64>(map_q, map_k, map_v, p, n_tiles, s);
+    return launch<128>(map_q, map_k, map_v, p, n_tiles, s);
+}

@@ -63,6 +63,8 @@ class ControlBlock:
         cursor += cursor & 1                      # 8-byte alignment for the 64-bit seeds
         offsets["seeds"] = cursor
         cursor += 2 * n_tokens
+        offsets["att_tiles"] = cursor             # work list of the prompt-attention kernel
+        cursor += 4 * (n_tokens // 128 + n_items)
         for index, max_blocks in self.groups:
             offsets[("block_table", index)] = cursor
             cursor += n_items * max_blocks
@@ -102,6 +104,8 @@ class ControlBlock:
                 views[name] = buffer[start:start + 2 * n_tokens].view(torch.int64)
             elif name in ("temperature", "top_p"):
                 views[name] = buffer[start:start + n_tokens].view(torch.float32)
+            elif name == "att_tiles":
+                views[name] = buffer[start:start + 4 * (n_tokens // 128 + n_items)]
             elif isinstance(name, tuple):
                 max_blocks = dict(self.groups)[name[1]]
                 views[name] = buffer[start:start + n_items * max_blocks].view(n_items, max_blocks)
@@ -127,6 +131,8 @@ class StepContext:
         self.item_counts = []         # host: tokens of each entry
         self.item_offsets = []        # host: row of each entry's first token
         self.decode_only = False      # every entry brings exactly one token
+        self.att_tiles = None         # device work list (tiles of up to 128 tokens of one entry), or None
+        self.n_att_tiles = 0
 
     def buffer(self, tag: str, shape, dtype):
         return self.workspace.get(tag, shape, dtype)

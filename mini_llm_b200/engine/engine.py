@@ -22,6 +22,7 @@ import torch
 from ..cache.manager import CacheManager
 from ..cache.storage import CacheStorage
 from ..config.registry import config_from_folder, describe_model
+from ..kernels import ops
 from ..kernels.dispatch import Kernels
 from ..sampling import SamplingParams
 from .context import ControlBlock, StepContext, Workspace
@@ -181,6 +182,8 @@ class Engine:
         for group in self.cache.groups:
             if group.paged:
                 arrays[("block_table", group.index)] = group.table[ctx.item_slots]
+        tiles = ops.attention_tiles(ctx.item_offsets, ctx.item_counts, ctx.item_starts)
+        arrays["att_tiles"] = np.array(tiles, dtype=np.int32)
         if sampling is not None:
             arrays["temperature"] = np.array([s.temperature for s in sampling], dtype=np.float32)
             arrays["top_p"] = np.array([s.top_p for s in sampling], dtype=np.float32)
@@ -192,6 +195,7 @@ class Engine:
         ctx.token_ids, ctx.positions, ctx.token_item = views["token_ids"], views["positions"], views["token_item"]
         ctx.want_rows = views["want_rows"][:n_want]
         ctx.decode_only = all(n == 1 for n in ctx.item_counts)
+        ctx.att_tiles, ctx.n_att_tiles = views["att_tiles"], len(tiles)
         for view in self.storage.views:
             if view.kind == "paged":
                 view.block_table = views[("block_table", view.group)]

@@ -39,6 +39,7 @@ LIBRARIES = {
     "sampling": "sampling_kernels.cu",
     "decode": "decode_kernels.cu",
     "gemm": "gemm_tcgen05.cu",
+    "attention": "attention_tcgen05.cu",
 }
 
 _lock = threading.Lock()

@@ -137,6 +137,11 @@ class Kernels:
             return ops.split_attention(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
                                        ctx.token_item, n_heads, n_kv_heads, head_size, cache.page_size, scale,
                                        window, chunk, max_chunks, acc, ml, counters)
+        if (not self.plain_only and ctx.att_tiles is not None
+                and ops.attention_prefill_takes(q, head_size, cache.page_size)):
+            return ops.attention_prefill(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.att_tiles,
+                                         ctx.n_att_tiles, n_heads, n_kv_heads, head_size, cache.page_size, scale,
+                                         window, self.status(ctx.device))
         return ops.attention_plain(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
                                    ctx.token_item, n_heads, n_kv_heads, head_size, cache.page_size, scale, window)
 

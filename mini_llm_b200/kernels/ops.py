@@ -352,3 +352,55 @@ def gemm_bf16(out, a, w, bias, epilogue, status):
     _gemm_bf16(out.data_ptr(), a.data_ptr(), w.data_ptr(), _ptr(bias), m, n, k, a.stride(0), out.stride(0),
                EPILOGUES[epilogue], int(out.dtype == torch.float32), status.data_ptr(), _stream())
     return out
+
+
+# ---- tensor-core attention for prompt portions (bfloat16) ----------------------------------------
+
+_attention_prefill = Function("attention", "mllm_attention_prefill",
+                              [P, L, P, L, L, L, P, P, I, I, P, I, P, I, I, I, I, F, I, P, P])
+
+PREFILL_ATTENTION_HEAD_SIZES = (64, 128)
+PREFILL_ATTENTION_PAGE_SIZES = (8, 16, 32, 64, 128)
+ATTENTION_TILE = 128
+
+
+def attention_prefill_takes(q, head_size, page_size) -> bool:
+    return (q.dtype == torch.bfloat16 and head_size in PREFILL_ATTENTION_HEAD_SIZES
+            and page_size in PREFILL_ATTENTION_PAGE_SIZES and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
+
+
+def attention_tiles(item_offsets, item_counts, item_starts):
+    """The work list of attention_prefill: tiles of up to 128 consecutive tokens of one
+    entry, as rows (entry, first row, rows, position of the first row)."""
+    tiles = []
+    for item, (offset, count, start) in enumerate(zip(item_offsets, item_counts, item_starts)):
+        for first in range(0, count, ATTENTION_TILE):
+            tiles.append((item, offset + first, min(ATTENTION_TILE, count - first), start + first))
+    return tiles
+
+
+def attention_prefill(out, q, k_pages, v_pages, block_table, tiles, n_tiles, n_heads, n_kv_heads, head_size,
+                      page_size, scale, window, status):
+    """Causal attention over the paged cache on the tensor cores (tcgen05): one CTA per
+    (tile of 128 queries, head).  ``tiles``: device int32 [>= n_tiles, 4] from ``attention_tiles``."""
+    _check(out, "attention_prefill.out", torch.bfloat16, 2)
+    _check(q, "attention_prefill.q", torch.bfloat16, 2)
+    _check(k_pages, "attention_prefill.k_pages", torch.bfloat16, 4)
+    _check(v_pages, "attention_prefill.v_pages", torch.bfloat16, 4)
+    _check(block_table, "attention_prefill.block_table", torch.int32, 2)
+    _check(tiles, "attention_prefill.tiles", torch.int32)
+    _check(status, "attention_prefill.status", torch.int32)
+    if not attention_prefill_takes(q, head_size, page_size):
+        raise KernelError(f"attention_prefill does not take head size {head_size} with pages of {page_size}")
+    n_pages = k_pages.shape[0]
+    if tuple(k_pages.shape) != (n_pages, page_size, n_kv_heads, head_size) or v_pages.shape != k_pages.shape:
+        raise KernelError("attention_prefill: pages must be [n_pages, page_size, kv_heads, head_size]")
+    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous():
+        raise KernelError("attention_prefill: pages and block table must be contiguous")
+    if q.shape[1] != n_heads * head_size or out.shape != q.shape or tiles.numel() < 4 * n_tiles:
+        raise KernelError("attention_prefill: q / out / tiles do not fit")
+    _attention_prefill(out.data_ptr(), out.stride(0), q.data_ptr(), q.shape[0], q.shape[1], q.stride(0),
+                       k_pages.data_ptr(), v_pages.data_ptr(), n_pages, page_size, block_table.data_ptr(),
+                       block_table.shape[1], tiles.data_ptr(), n_tiles, n_heads, n_kv_heads, head_size, float(scale),
+                       int(window or 0), status.data_ptr(), _stream())
+    return out

@@ -432,3 +432,63 @@ def test_gemm_tcgen05_strided_input_and_twin():
     ops.linear_plain(slow, a, w, None, "store")
     assert int(status.item()) == 0
     np.testing.assert_allclose(f64(fast), f64(slow), rtol=0, atol=tol(torch.bfloat16, 2))
+
+
+# ---- tensor-core attention for prompt portions -----------------------------------------------
+
+@pytest.mark.parametrize("n_heads, n_kv_heads, head, page, window", [
+    (2, 2, 64, 16, 0), (3, 1, 64, 8, 0), (2, 2, 128, 16, 0), (4, 2, 64, 32, 0), (1, 1, 64, 128, 0),
+    (2, 1, 128, 64, 0), (2, 2, 64, 16, 100), (2, 2, 64, 8, 128), (2, 2, 128, 16, 300), (12, 12, 64, 16, 0)])
+def test_attention_prefill_over_pages(n_heads, n_kv_heads, head, page, window):
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(n_heads * head + page + window)
+    # whole prompts (one not a multiple of the tile), a portion after 300 cached tokens, single tokens
+    lengths, n_new = [300, 500, 1, 128, 641, 77, 260], [300, 200, 1, 128, 129, 1, 4]
+    k_pages, v_pages, table, positions, items, dense = paged_case(rng, lengths, n_new, n_heads, n_kv_heads, head,
+                                                                  page, torch.bfloat16)
+    kv_shape = (k_pages.shape[0], page, n_kv_heads, head)
+    dense = [(f64(dev(k, torch.bfloat16)), f64(dev(v, torch.bfloat16))) for k, v in dense]
+    n = len(f64(positions))
+    q = dev(rng.normal(size=(n, n_heads * head)), torch.bfloat16)
+    out = torch.full_like(q, float("nan"))
+    offsets = np.concatenate([[0], np.cumsum(n_new)[:-1]]).tolist()
+    starts = [l - m for l, m in zip(lengths, n_new)]
+    tiles = ops.attention_tiles(offsets, n_new, starts)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    scale = 1.0 / math.sqrt(head)
+    ops.attention_prefill(out, q, k_pages.view(kv_shape), v_pages.view(kv_shape), table,
+                          dev(np.array(tiles, dtype=np.int32)), len(tiles), n_heads, n_kv_heads, head, page, scale,
+                          window, status)
+    assert int(status.item()) == 0
+    expected = attention_expected(f64(q), dense, f64(positions).astype(int), f64(items).astype(int), n_heads,
+                                  n_kv_heads, head, scale, window)
+    np.testing.assert_allclose(f64(out), expected, rtol=0, atol=tol(torch.bfloat16, 2))
+
+
+def test_attention_prefill_finds_one_far_key_and_respects_the_windows_edge():
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(6)
+    head, page, length, new = 64, 16, 700, 150
+    far = 3 * page + 5
+    k_pages, v_pages, table, positions, items, dense = paged_case(rng, [length], [new], 1, 1, head, page, torch.bfloat16)
+    k, v = dense[0]
+    q = rng.normal(size=(new, head))
+    k[far] = q[-1] * 4.0                                  # stands out for the last query
+    v[far] = 100.0 + np.arange(head)
+    block, offset = int(f64(table)[0, far // page]), far % page
+    k_pages[block, offset] = dev(k[far], torch.bfloat16)
+    v_pages[block, offset] = dev(v[far], torch.bfloat16)
+    kv_shape = (k_pages.shape[0], page, 1, head)
+    qd = dev(q, torch.bfloat16)
+    out = torch.empty_like(qd)
+    tiles = dev(np.array(ops.attention_tiles([0], [new], [length - new]), dtype=np.int32))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    run = lambda window: ops.attention_prefill(out, qd, k_pages.view(kv_shape), v_pages.view(kv_shape), table, tiles,
+                                               2, 1, 1, head, page, 1.0 / math.sqrt(head), window, status)
+    run(0)
+    np.testing.assert_allclose(f64(out)[-1], f64(dev(v[far], torch.bfloat16)), rtol=2e-2, atol=0.5)
+    run(length - 1 - far)
+    assert float(out[-1].float().abs().max()) < 10.0
+    run(length - far)
+    np.testing.assert_allclose(f64(out)[-1], f64(dev(v[far], torch.bfloat16)), rtol=2e-2, atol=0.5)
+    assert int(status.item()) == 0
