@@ -87,12 +87,15 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 __global__ void __launch_bounds__(1024)
 sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, long ld, int vocab,
                    const float* __restrict__ temperature, const float* __restrict__ top_p,
-                   const unsigned long long* __restrict__ seeds, const int* __restrict__ counters) {
+                   const unsigned long long* __restrict__ seeds, const int* __restrict__ counters,
+                   int only_nucleus) {
     __shared__ float sv[33];
     __shared__ int si[32];
     int r = blockIdx.x;
     const float* x = logits + (long)r * ld;
     float temp = temperature ? temperature[r] : 0.0f;
+    // only_nucleus: the sliced kernel has drawn every row but those with a nucleus cut
+    if (only_nucleus && !(temp > 0.0f && top_p != nullptr && top_p[r] < 1.0f)) return;
     float best = 0.0f;
     int best_i = -1;
 
@@ -145,12 +148,90 @@ sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, long
     if (threadIdx.x == 0) out[r] = best_i;
 }
 
+// The same draw for rows without a nucleus cut, spread over SLICES blocks per row: each
+// block finds the best candidate of its slice of the vocabulary, and the block that
+// finishes last for a row picks the best of the slices (ties to the lower index, so the
+// result is the one-block kernel's).  Rows with top_p < 1 are left to sample_rows_kernel.
+// scratch: floats [rows * SLICES], ints [rows * SLICES], zeroed int counters [rows].
+constexpr int SAMPLE_SLICES = 32;
+
+__global__ void __launch_bounds__(256)
+sample_rows_sliced_kernel(int* __restrict__ out, const float* __restrict__ logits, long ld, int vocab,
+                          const float* __restrict__ temperature, const float* __restrict__ top_p,
+                          const unsigned long long* __restrict__ seeds, const int* __restrict__ counters,
+                          float* __restrict__ part_value, int* __restrict__ part_index, int* __restrict__ done) {
+    __shared__ float sv[33];
+    __shared__ int si[32];
+    __shared__ int is_last;
+    const int r = blockIdx.x, slice = blockIdx.y;
+    if (top_p != nullptr && top_p[r] < 1.0f && temperature != nullptr && temperature[r] > 0.0f) return;
+    const float* x = logits + (long)r * ld;
+    const float temp = temperature ? temperature[r] : 0.0f;
+    const int per = (vocab + SAMPLE_SLICES - 1) / SAMPLE_SLICES;
+    const int begin = slice * per, end = min(vocab, begin + per);
+    float best = 0.0f;
+    int best_i = -1;
+    if (!(temp > 0.0f)) {
+        for (int v = begin + threadIdx.x; v < end; v += blockDim.x) {
+            float xv = x[v];
+            if (better(xv, v, best, best_i)) { best = xv; best_i = v; }
+        }
+    } else {
+        const float inv_t = 1.0f / temp;
+        const unsigned long long seed = seeds ? seeds[r] : 0ull;
+        const unsigned counter = counters ? (unsigned)counters[r] : 0u;
+        for (int v = begin + threadIdx.x; v < end; v += blockDim.x) {
+            float score = x[v] * inv_t - logf(-logf(uniform_of(seed, counter, (unsigned)v)));
+            if (better(score, v, best, best_i)) { best = score; best_i = v; }
+        }
+    }
+    block_argmax(best, best_i, sv, si);
+    if (threadIdx.x == 0) {
+        part_value[r * SAMPLE_SLICES + slice] = best;
+        part_index[r * SAMPLE_SLICES + slice] = best_i;
+        __threadfence();
+        int ticket = atomicAdd(&done[r], 1);
+        is_last = ticket == SAMPLE_SLICES - 1;
+        if (is_last) done[r] = 0;
+    }
+    __syncthreads();
+    if (!is_last || threadIdx.x >= 32) return;
+    __threadfence();
+    float v = __ldcg(part_value + r * SAMPLE_SLICES + threadIdx.x);
+    int i = __ldcg(part_index + r * SAMPLE_SLICES + threadIdx.x);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        int oi = __shfl_xor_sync(0xffffffffu, i, o);
+        if (better(ov, oi, v, i)) { v = ov; i = oi; }
+    }
+    if (threadIdx.x == 0) out[r] = i;
+}
+
+// any_nucleus: some row has temperature > 0 and top_p < 1 (the host knows); those rows are
+// then drawn by the one-block kernel, which skips all others.
+extern "C" int mllm_sampling_sample_rows_sliced(int* out, const float* logits, long ld, int n_rows, int vocab,
+                                                const float* temperature, const float* top_p,
+                                                const unsigned long long* seeds, const int* counters,
+                                                float* part_value, int* part_index, int* done, int any_nucleus,
+                                                void* stream) {
+    if (n_rows <= 0) return 0;
+    if (vocab <= 0) return fail("sample_rows: empty vocabulary");
+    cudaStream_t s = (cudaStream_t)stream;
+    sample_rows_sliced_kernel<<<dim3(n_rows, SAMPLE_SLICES), 256, 0, s>>>(out, logits, ld, vocab, temperature, top_p,
+                                                                         seeds, counters, part_value, part_index, done);
+    if (any_nucleus) {
+        sample_rows_kernel<<<n_rows, 1024, 0, s>>>(out, logits, ld, vocab, temperature, top_p, seeds, counters, 1);
+    }
+    return check_launch("sample_rows_sliced_kernel");
+}
+
 extern "C" int mllm_sampling_sample_rows(int* out, const float* logits, long ld, int n_rows, int vocab,
                                          const float* temperature, const float* top_p,
                                          const unsigned long long* seeds, const int* counters, void* stream) {
     if (n_rows <= 0) return 0;
     if (vocab <= 0) return fail("sample_rows: empty vocabulary");
     sample_rows_kernel<<<n_rows, 1024, 0, (cudaStream_t)stream>>>(out, logits, ld, vocab, temperature, top_p,
-                                                                  seeds, counters);
+                                                                  seeds, counters, 0);
     return check_launch("sample_rows_kernel");
 }

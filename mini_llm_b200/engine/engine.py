@@ -201,6 +201,7 @@ class Engine:
                 view.block_table = views[("block_table", view.group)]
 
         sample_views = None
+        self._any_nucleus = sampling is not None and any(s.temperature > 0 and s.top_p < 1 for s in sampling)
         if sampling is not None and n_want > 0:
             sample_views = (views["temperature"][:n_want], views["top_p"][:n_want], views["seeds"][:n_want],
                             views["counters"][:n_want])
@@ -216,7 +217,7 @@ class Engine:
         self._sampled = None
         if sample_views is not None and logits is not None:
             out = self.workspace.get("sampled", (ctx.n_want,), torch.int32)
-            self.kernels.sample_rows(out, logits, *sample_views)
+            self.kernels.sample_rows(out, logits, *sample_views, any_nucleus=self._any_nucleus)
             self._sampled = out
         return logits
 
@@ -229,11 +230,11 @@ class Engine:
         (engine/src/gpt2_gpu_greedy.cu:80-119)."""
         if not (self.cuda_graphs and ctx.decode_only and self.model.graph_safe):
             return self._forward(ctx, sample_views)
-        stamp = (self.workspace.generation, self.control.generation)
+        stamp = (self.workspace.generation, self.control.generation, self.kernels.scratch_generation)
         if stamp != self._graph_stamp:
             self._graphs.clear()                      # a buffer moved: captured addresses are stale
             self._graph_stamp = stamp
-        key = (ctx.n_tokens, ctx.n_want, sample_views is not None)
+        key = (ctx.n_tokens, ctx.n_want, sample_views is not None, self._any_nucleus)
         held = self._graphs.get(key)
         if held is None:
             self._graphs[key] = "warm"                # run once eagerly: every buffer gets allocated
@@ -243,7 +244,7 @@ class Engine:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 logits = self._forward(ctx, sample_views)
-            if (self.workspace.generation, self.control.generation) != stamp:
+            if (self.workspace.generation, self.control.generation, self.kernels.scratch_generation) != stamp:
                 raise RuntimeError("a buffer was allocated while a step was captured")
             held = (graph, logits, self._sampled, self.kernels.launches - before)
             self._graphs[key] = held

@@ -45,6 +45,8 @@ class Kernels:
         self.plain_only = bool(plain_only) or act_dtype == torch.float32
         self.launches = 0            # kernels launched (or recorded into a graph) since the start
         self._split_scratch = None
+        self._sample_scratch = None
+        self.scratch_generation = 0  # grows when scratch moves (captured graphs are then stale)
         self._status = None          # device word the tensor-core kernels report a timed-out wait in
 
     # ---- operations without a fast variant --------------------------------------------------
@@ -64,9 +66,22 @@ class Kernels:
         self.launches += 1
         return ops.kv_store(k_pages, v_pages, k_src, v_src, positions, token_item, block_table, page_size)
 
-    def sample_rows(self, out, logits, temperature=None, top_p=None, seeds=None, counters=None):
+    def sample_rows(self, out, logits, temperature=None, top_p=None, seeds=None, counters=None, any_nucleus=True):
+        """One token per row.  ``any_nucleus``: whether some row may have a nucleus cut (top_p < 1
+        with temperature > 0); rows without are drawn by many blocks each."""
         self.launches += 1
-        return ops.sample_rows(out, logits, temperature, top_p, seeds, counters)
+        rows = logits.shape[0]
+        held = self._sample_scratch
+        if held is None or held[2].numel() < rows:
+            capacity = max(rows, 256)
+            device = logits.device
+            held = self._sample_scratch = (torch.empty(capacity * ops.SAMPLE_SLICES, dtype=torch.float32, device=device),
+                                           torch.empty(capacity * ops.SAMPLE_SLICES, dtype=torch.int32, device=device),
+                                           torch.zeros(capacity, dtype=torch.int32, device=device))
+            self.scratch_generation += 1
+        if any_nucleus:
+            self.launches += 1
+        return ops.sample_rows_sliced(out, logits, temperature, top_p, seeds, counters, held, any_nucleus)
 
     # ---- matrix products --------------------------------------------------------------------
     def _skinny(self, m, k) -> bool:
@@ -155,5 +170,5 @@ class Kernels:
             self._split_scratch = (torch.empty(need[0], dtype=torch.float32, device=device),
                                    torch.empty(need[1], dtype=torch.float32, device=device),
                                    torch.zeros(need[2], dtype=torch.int32, device=device))
-            ctx.workspace.generation += 1
+            self.scratch_generation += 1
         return self._split_scratch

@@ -404,3 +404,32 @@ def attention_prefill(out, q, k_pages, v_pages, block_table, tiles, n_tiles, n_h
                        block_table.shape[1], tiles.data_ptr(), n_tiles, n_heads, n_kv_heads, head_size, float(scale),
                        int(window or 0), status.data_ptr(), _stream())
     return out
+
+
+_sample_rows_sliced = Function("sampling", "mllm_sampling_sample_rows_sliced",
+                               [P, P, L, I, I, P, P, P, P, P, P, P, I, P])
+SAMPLE_SLICES = 32
+
+
+def sample_rows_sliced(out, logits, temperature, top_p, seeds, counters, scratch, any_nucleus):
+    """``sample_rows`` spread over 32 blocks per row.  scratch: (fp32 [R*32], int32 [R*32],
+    zeroed int32 [R]); any_nucleus: whether some row has temperature > 0 and top_p < 1."""
+    _check(out, "sample_rows.out", torch.int32, 1)
+    _check(logits, "sample_rows.logits", torch.float32, 2)
+    r, vocab = logits.shape
+    values, indices, done = scratch
+    _check(values, "sample_rows.scratch", torch.float32)
+    _check(indices, "sample_rows.scratch", torch.int32)
+    _check(done, "sample_rows.scratch", torch.int32)
+    if values.numel() < r * SAMPLE_SLICES or indices.numel() < r * SAMPLE_SLICES or done.numel() < r or out.shape[0] < r:
+        raise KernelError("sample_rows_sliced: scratch or output too small")
+    for name, t, dt in (("temperature", temperature, torch.float32), ("top_p", top_p, torch.float32),
+                        ("seeds", seeds, torch.int64), ("counters", counters, torch.int32)):
+        if t is not None:
+            _check(t, f"sample_rows.{name}", dt, 1)
+            if t.shape[0] < r:
+                raise KernelError(f"sample_rows: {name} too short")
+    _sample_rows_sliced(out.data_ptr(), logits.data_ptr(), logits.stride(0), r, vocab, _ptr(temperature), _ptr(top_p),
+                        _ptr(seeds), _ptr(counters), values.data_ptr(), indices.data_ptr(), done.data_ptr(),
+                        int(bool(any_nucleus)), _stream())
+    return out

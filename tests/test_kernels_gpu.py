@@ -492,3 +492,25 @@ def test_attention_prefill_finds_one_far_key_and_respects_the_windows_edge():
     run(length - far)
     np.testing.assert_allclose(f64(out)[-1], f64(dev(v[far], torch.bfloat16)), rtol=2e-2, atol=0.5)
     assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("vocab", [1000, 50257])
+def test_sliced_sampling_draws_what_the_one_block_kernel_draws(vocab):
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(vocab + 1)
+    rows = 20
+    logits = (rng.normal(size=(rows, vocab)) * 2.0).astype(np.float32)
+    logits[3, 17] = logits[3, vocab - 1] = 30.0                      # a tie across slices: the first index wins
+    logits[4, vocab // 2] = np.nan
+    temperature = dev(np.array([0.0, 0.8, 1.0, 0.0, 0.0] * 4, dtype=np.float32))
+    top_p = dev(np.array([1.0] * 10 + [0.9] * 10, dtype=np.float32))
+    seeds, counters = dev(rng.integers(0, 2 ** 63, rows).astype(np.int64)), dev(rng.integers(0, 99, rows).astype(np.int32))
+    one, many = torch.empty(rows, dtype=torch.int32, device="cuda"), torch.full((rows,), -7, dtype=torch.int32, device="cuda")
+    ops.sample_rows(one, dev(logits), temperature, top_p, seeds, counters)
+    scratch = (torch.empty(rows * 32, device="cuda"), torch.empty(rows * 32, dtype=torch.int32, device="cuda"),
+               torch.zeros(rows, dtype=torch.int32, device="cuda"))
+    for _ in range(2):
+        ops.sample_rows_sliced(many, dev(logits), temperature, top_p, seeds, counters, scratch, True)
+        assert many.tolist() == one.tolist()
+        assert int(scratch[2].sum()) == 0
+    assert one.tolist()[3] == 17 and one.tolist()[4] == vocab // 2

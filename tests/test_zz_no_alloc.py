@@ -68,17 +68,23 @@ def test_static_scratch_entry_point_matches_the_allocating_one_twice_in_a_row():
                             torch.empty(n * heads * max_chunks * head, device="cuda"),
                             torch.empty(n * heads * max_chunks * 2, device="cuda"),
                             torch.zeros(n * heads, dtype=torch.int32, device="cuda"))
-        before = torch.cuda.memory_allocated()
-        for _ in range(2):
+        for call in range(2):
             got = torch.full_like(q, float("nan"))
+            torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info()[0]
+            torch_before = torch.cuda.memory_stats()["allocation.all.allocated"]
             status = fn(got.data_ptr(), got.stride(0), q.data_ptr(), q.stride(0), k_pages.data_ptr(),
                         v_pages.data_ptr(), table.data_ptr(), table.shape[1], positions.data_ptr(), items.data_ptr(),
                         n, heads, kv_heads, head, page, scale, window, chunk, stream)
             assert status == 0, lib.mllm_decode_last_error().decode()
             torch.cuda.synchronize()
+            # nothing was allocated: neither through torch nor from the driver (the first call on
+            # a device may make the driver load the library's module, so the driver's figure is
+            # compared on the later calls)
+            assert torch.cuda.memory_stats()["allocation.all.allocated"] == torch_before
+            if call > 0 or seed > 0:
+                assert torch.cuda.mem_get_info()[0] == free_before
             np.testing.assert_allclose(got.float().cpu().numpy(), want.float().cpu().numpy(), rtol=0, atol=ATOL)
-            del got
-        assert torch.cuda.memory_allocated() == before
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():
