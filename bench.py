@@ -283,8 +283,131 @@ def run_ours(args):
     return 0
 
 
+REFERENCE = os.path.join(ROOT, "baseline", "_ref")
+
+
+def unavailable(why: str) -> int:
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def build_reference_library(target: str) -> str | None:
+    """The reference's ``make gpu-lib`` (Makefile:165-180 of WillyBruhn/mini_llm) with its
+    sources unchanged and only the target architecture replaced (it names sm_86 and sm_61)."""
+    import glob
+    import shutil
+    engine = os.path.join(REFERENCE, "engine")
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.isdir(engine) or not os.path.isfile(nvcc):
+        return "the reference's engine sources or nvcc are missing"
+    pic = os.path.join(REFERENCE, "build", "pic")
+    os.makedirs(pic, exist_ok=True)
+    include = ["-I" + os.path.join(engine, "include"), "-I" + os.path.join(engine, "tests")]
+    objects = []
+    for source in sorted(glob.glob(os.path.join(engine, "src", "*.c"))):
+        obj = os.path.join(pic, os.path.basename(source)[:-2] + ".o")
+        done = subprocess.run(["gcc", "-O2", "-std=c11", *include, "-fPIC", "-c", "-o", obj, source], capture_output=True)
+        if done.returncode != 0:
+            return "gcc failed on the reference's sources"
+        objects.append(obj)
+    done = subprocess.run([nvcc, "-O2", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a", *include, "-Xcompiler",
+                           "-fPIC", "-shared", "-o", target, *sorted(glob.glob(os.path.join(engine, "src", "*.cu"))),
+                           *objects, "-lm"], capture_output=True)
+    return None if done.returncode == 0 else "nvcc failed on the reference's sources"
+
+
+def export_reference_weights(config: dict, folder: str) -> None:
+    """The same seeded random weights as our arm, in the reference's format: one raw
+    little-endian fp32 file per tensor, named ``transformer.<name>.bin``
+    (scripts/dump_weights.py:37-53, engine/src/gpt2.c:21-34,131-137)."""
+    from mini_llm_b200.config import config_from_dict, describe_model
+    from mini_llm_b200.weights import random_tensors
+    for name, values in random_tensors(describe_model(config_from_dict(config)), 0, "gpt2").items():
+        values.astype("<f4").tofile(os.path.join(folder, f"transformer.{name}.bin"))
+
+
 def run_reference(args):
-    print(json.dumps({"impl": "reference", "unavailable": "the reference arm is not wired up yet"}))
+    """The unmodified reference through its own public API: ``NativeGPT2`` (ctypes binding),
+    ``prefill_greedy`` per request, then ``decode_batch`` steps
+    (pytorch/src/mini_llm/batch_api.py:44-70), fp16 decode weights as in its published runs."""
+    if not os.path.isdir(os.path.join(REFERENCE, "mini_llm")):
+        return unavailable("the reference is not installed under baseline/_ref")
+    if args.batch > 16:
+        return unavailable("the reference's batched decode takes at most 16 sequences")
+    library = os.path.join(REFERENCE, "build", "libmini_llm_gpu.so")
+    if not os.path.isfile(library):
+        problem = build_reference_library(library)
+        if problem:
+            return unavailable(problem)
+    import numpy as np
+    import torch
+    if not torch.cuda.is_available():
+        return unavailable("no CUDA device")
+    sys.path.insert(0, REFERENCE)
+    try:
+        from mini_llm.native import EngineOptions, NativeGPT2
+    except Exception as error:
+        return unavailable(f"the reference's binding does not import: {error}")
+    config = dict(GPT2_SMALL)                # the reference's sizes are compile-time constants: GPT-2 small only
+    context, vocab = config["n_positions"], config["vocab_size"]
+    steps, warmup, batch = args.steps, args.warmup, args.batch
+    prompt_len = context - steps - warmup
+    rng = np.random.default_rng(1234)
+    with tempfile.TemporaryDirectory() as folder:
+        export_reference_weights(config, folder)
+        engine = NativeGPT2(folder, library, backend="gpu",
+                            options=EngineOptions(use_kv_cache=True, max_sessions=16, fp16_decode=True))
+    sampler = ClockSampler()
+    caches = [engine.try_take_cache() for _ in range(batch)]
+    tokens = [engine.prefill_greedy(cache, rng.integers(0, vocab, prompt_len).tolist()) for cache in caches]
+    for _ in range(warmup):
+        tokens = engine.decode_batch(caches, tokens)
+    torch.cuda.synchronize()
+    sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    wall = time.perf_counter()
+    start.record()
+    for _ in range(steps):
+        tokens = engine.decode_batch(caches, tokens)       # host tokens in and out, every step
+    stop.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - wall
+    clocks = sampler.stop()
+    ms = start.elapsed_time(stop) / steps
+    for cache in caches:
+        engine.release_cache(cache)
+    line = {"metric": "decode tokens/s, GPT-2 small, batch 8, context 1024", "value": batch / (ms * 1e-3),
+            "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16 weights, fp32 arithmetic",
+            "data": "synthetic: seeded random weights (N(0, 0.02)) and uniform random token ids", "impl": "reference",
+            "config": {"model": "gpt2-small", "n_layer": 12, "n_embd": 768, "n_head": 12, "n_inner": 3072,
+                       "vocab_size": vocab, "n_positions": context, "global_batch": batch, "seq_len": context,
+                       "prompt_tokens": prompt_len, "parallelism": "single GPU", "arch": "sources rebuilt for sm_100a"},
+            "e2e": {"value": batch * steps / wall, "unit": "tokens/s", "h2d_bytes_per_step": 4 * batch,
+                    "d2h_bytes_per_step": 4 * batch},
+            "clocks": clocks}
+    if not args.no_extras:
+        cache = engine.try_take_cache()
+        token = engine.prefill_greedy(cache, rng.integers(0, vocab, prompt_len).tolist())
+        torch.cuda.synchronize()
+        begin = time.perf_counter()
+        for _ in range(min(steps, 64)):
+            token = engine.decode_batch([cache], [token])[0]
+        torch.cuda.synchronize()
+        line["points"] = {"decode_b1": min(steps, 64) / (time.perf_counter() - begin)}
+        engine.release_cache(cache)
+        cache = engine.try_take_cache()
+        prompts = [rng.integers(0, vocab, 1024).tolist() for _ in range(2)]
+        torch.cuda.synchronize()
+        begin = time.perf_counter()
+        for prompt in prompts:                               # a prompt is never batched: one after the other
+            engine.prefill_greedy(cache, prompt)
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - begin
+        line["prefill"] = {"value": 2048 / seconds, "tokens": 2048, "ms": 1000.0 * seconds}
+        engine.release_cache(cache)
+    engine.close()
+    print(json.dumps(line))
     return 0
 
 
