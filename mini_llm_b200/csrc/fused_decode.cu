@@ -1,0 +1,906 @@
+// One kernel for a whole decode step of a stack of pre-norm attention + dense feed-forward
+// layers (bfloat16 weights, up to 16 tokens).
+//
+// A decode step of few tokens is a chain of ~60 tiny, dependent operations; launched as
+// separate kernels each pays a launch gap and a cold start, which together cost an order of
+// magnitude more than the step's memory traffic (the reference meets the same wall: 87
+// launches per token, docs/kernels/007_fewer_launches.md:188).  Here one persistent CTA per
+// SM walks the phases of every layer, separated by grid-wide barriers instead of kernel
+// boundaries.  What a phase needs and what does not depend on the phase before it (its
+// weight fragments, biases, norm gains, the values a residual sum adds to) is copied into
+// shared memory asynchronously while the previous phase finishes and the grid synchronises;
+// after the barrier only the activations remain to be read.
+//
+// Phases of a layer (every CTA takes an equal share of the 16-row blocks of each product):
+//   1  q, k, v = LN1(hidden) W_qkv^T + b     k, v go straight into the cache pages
+//   2  attention over the paged cache, one CTA per (token, head), its warps sharing the keys
+//   3  hidden += attn W_o^T + b
+//   4  up = act(LN2(hidden) W_fc^T + b)
+//   5  hidden += up W_proj^T + b
+// before them the embedding, after them the final norm on the wanted rows, the output head
+// and the sampling candidates.  Products run on the tensor cores (mma.sync m16n8k16: the
+// weights stream into the A fragments, up to sixteen tokens are the B fragments).
+//
+// The grid must be co-resident (cooperative launch).  Every barrier wait is bounded: a CTA
+// that waits longer than the limit writes a status code; every CTA that sees the code set
+// leaves the kernel.
+#include "common.cuh"
+
+MLLM_DEFINE_ERROR_API(mllm_fused)
+
+struct FusedLayer {
+    const float *ln1_g, *ln1_b;
+    const bf16* w_qkv;
+    const float* b_qkv;
+    const bf16* w_o;
+    const float* b_o;
+    const float *ln2_g, *ln2_b;
+    const bf16* w_fc;
+    const float* b_fc;
+    const bf16* w_proj;
+    const float* b_proj;
+    bf16* k_pages;
+    bf16* v_pages;
+    float score_scale, eps1, eps2;
+    int activation;            // EPI_GELU_TANH or EPI_GELU_ERF
+    int window;                // 0: all keys
+};
+
+struct FusedParams {
+    const FusedLayer* layers;
+    int n_layers;
+    int E, H, Hkv, D, I, V;
+    int T;                      // tokens of the step, one per entry
+    const int* token_ids;
+    const int* positions;
+    const int* token_item;
+    const int* block_table;
+    int max_blocks, page_size;
+    const int* want_rows;
+    int n_want;
+    const bf16* wte;
+    const bf16* wpe;            // null: no learned positions
+    const float *lnf_g, *lnf_b;
+    float eps_f;
+    const bf16* w_head;
+    float* hidden;              // [T, E]
+    bf16* q;                    // [T, H*D]
+    bf16* attn;                 // [T, H*D]
+    bf16* up;                   // [T, I]
+    float* logits;              // [n_want, V]
+    int sample;                 // 0: no sampling, 1: fill out_tokens
+    const float* temperature;
+    const float* top_p;
+    const unsigned long long* seeds;
+    const int* counters;
+    int* out_tokens;
+    float* cand_value;          // [n_want, gridDim.x]
+    int* cand_index;
+    int* cand_done;             // one zeroed counter
+    unsigned long long* barrier;    // monotonically increasing arrival counter
+    int* status;
+    unsigned long long* timeline;   // null, or room for 5 * layers + 3 time stamps
+};
+
+namespace {
+
+constexpr int THREADS = 512;
+constexpr int WARPS = THREADS / 32;
+constexpr int MAX_TOKENS = 16;
+constexpr int XS_PAD = 32;           // bf16 elements between the rows staged in shared memory
+// K steps of weights a warp prefetches into shared memory per phase: with one token tile
+// there is room for every step of the widest product of GPT-2 small, with two for fewer.
+__host__ __device__ constexpr int resident_of(int nt) { return nt == 1 ? 6 : 4; }
+constexpr unsigned long long BARRIER_LIMIT_NS = 2000000000ull;
+enum { OUT_BF16 = 0, OUT_ADD = 1, OUT_QKV = 2, OUT_LOGITS = 3 };
+
+// One product phase, as data.
+struct Phase {
+    const bf16* w;             // [N, K]; null: no phase
+    const float* bias;
+    int N, K, kind;
+    const float *gamma, *beta; // norm applied to the phase's input, or null
+};
+
+// Regions of the dynamic shared memory.
+struct Shared {
+    bf16* xs;                  // staged activations [NT * 8][k_max + XS_PAD]
+    float* red;                // partial tiles [WARPS][32][NT * 4]
+    float* att;                // attention merge [WARPS][2 + 256]
+    uint4* wbuf;               // prefetched weight fragments [2 * resident_of(NT)][THREADS]
+    float* bias;               // [2][THREADS][2], by phase parity
+    float* old;                // [THREADS][NT * 4]
+    float* gb;                 // norm gain and shift [2][E]
+    long* kv_base;             // [MAX_TOKENS] element offset of each token's slot in the pages
+    int* pos;                  // [MAX_TOKENS]
+    int* table;                // [T][max_blocks]
+};
+
+__host__ __device__ inline size_t shared_bytes(int nt, int E, int I, int HD, int max_blocks) {
+    const int k_max = E > I ? (E > HD ? E : HD) : (I > HD ? I : HD);
+    return (size_t)nt * 8 * (k_max + XS_PAD) * 2 + (size_t)WARPS * 32 * nt * 4 * 4 + (size_t)WARPS * (2 + 256) * 4 +
+           (size_t)2 * resident_of(nt) * THREADS * 16 + (size_t)2 * THREADS * 2 * 4 + (size_t)THREADS * nt * 4 * 4 +
+           (size_t)2 * E * 4 + MAX_TOKENS * 8 + MAX_TOKENS * 4 + (size_t)MAX_TOKENS * max_blocks * 4 + 64;
+}
+
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        f[2 * i] = __uint_as_float(u[i] << 16);
+        f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+    }
+}
+
+__device__ __forceinline__ void copy_async_16(void* smem_dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void copy_async_4(void* smem_dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src)
+                 : "memory");
+}
+
+// Grid-wide barrier: release-add, then poll with acquire loads.  Returns false if the step
+// has failed (limit hit here or elsewhere).
+__device__ bool grid_barrier(const FusedParams& p) {
+    __shared__ int ok;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        ok = 1;
+        unsigned long long ticket;
+        asm volatile("atom.add.release.gpu.global.u64 %0, [%1], 1;" : "=l"(ticket) : "l"(p.barrier) : "memory");
+        const unsigned long long target = (ticket / gridDim.x + 1) * gridDim.x;
+        unsigned long long start = 0;
+        for (unsigned spins = 0;; spins++) {
+            unsigned long long seen;
+            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(p.barrier) : "memory");
+            if (seen >= target) break;
+            if ((spins & 255u) == 255u) {
+                if (start == 0) start = now_ns();
+                int failed;
+                asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(failed) : "l"(p.status) : "memory");
+                if (failed != 0 || now_ns() - start > BARRIER_LIMIT_NS) {
+                    if (failed == 0) atomicExch(p.status, 21);
+                    ok = 0;
+                    break;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    return ok != 0;
+}
+
+__device__ __forceinline__ void share_of(int n, int& first, int& count) {
+    const int per = (n + gridDim.x - 1) / gridDim.x;
+    first = blockIdx.x * per;
+    count = max(0, min(n, first + per) - first);
+}
+
+// How a product phase is split over the CTA's warps (the same for prefetch and compute).
+struct Split {
+    int first, count;          // this CTA's 16-row blocks
+    int split;                 // warps per block
+    int blocks_at_a_time;      // blocks the CTA works on at a time
+    int per_part;              // K steps (of 32) per warp
+};
+
+__device__ __forceinline__ Split split_of(int N, int K, int kind) {
+    Split s;
+    share_of((N + 15) / 16, s.first, s.count);
+    s.split = 1;
+    s.blocks_at_a_time = WARPS;
+    if (kind != OUT_LOGITS && s.count < WARPS) {
+        int pow2 = 1;
+        while (pow2 < s.count) pow2 *= 2;
+        s.split = WARPS / pow2;
+        s.blocks_at_a_time = pow2;
+    }
+    s.per_part = (K / 32 + s.split - 1) / s.split;
+    return s;
+}
+
+// Start copying what `phase` needs and what is final already: this thread's first weight
+// fragments (its private slots of wbuf), the biases of its rows, the values its results are
+// added to, and (all threads together) the gain and shift of the phase's input norm.
+template <int NT>
+__device__ void prefetch_phase(const FusedParams& p, const Shared& sm, const Phase& phase, int parity, int n_rows) {
+    if (phase.w != nullptr) {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        const int g = lane >> 2, q = lane & 3;
+        const Split s = split_of(phase.N, phase.K, phase.kind);
+        const int b = warp / s.split, part = warp % s.split;
+        if (b < s.count) {
+            const int row_lo = (s.first + b) * 16 + g, row_hi = row_lo + 8;
+            const bf16* w_lo = phase.w + (long)min(row_lo, phase.N - 1) * phase.K + q * 8;
+            const bf16* w_hi = phase.w + (long)min(row_hi, phase.N - 1) * phase.K + q * 8;
+            const int k_begin = part * s.per_part, k_end = min(phase.K / 32, k_begin + s.per_part);
+            for (int u = 0; u < resident_of(NT) && k_begin + u < k_end; u++) {
+                copy_async_16(sm.wbuf + (2 * u) * THREADS + threadIdx.x, w_lo + (k_begin + u) * 32);
+                copy_async_16(sm.wbuf + (2 * u + 1) * THREADS + threadIdx.x, w_hi + (k_begin + u) * 32);
+            }
+            if (part == 0) {
+                float* bias = sm.bias + (parity * THREADS + threadIdx.x) * 2;
+                if (phase.bias != nullptr) {
+                    if (row_lo < phase.N) copy_async_4(bias, phase.bias + row_lo);
+                    if (row_hi < phase.N) copy_async_4(bias + 1, phase.bias + row_hi);
+                }
+                if (phase.kind == OUT_ADD) {
+#pragma unroll
+                    for (int t = 0; t < NT; t++)
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const int n = (i < 2) ? row_lo : row_hi, m = t * 8 + 2 * q + (i & 1);
+                            if (n < phase.N && m < n_rows)
+                                copy_async_4(sm.old + threadIdx.x * (NT * 4) + t * 4 + i, p.hidden + (long)m * phase.N + n);
+                        }
+                }
+            }
+        }
+        if (phase.gamma != nullptr) {
+            for (int c = threadIdx.x; c < phase.K / 4; c += THREADS) {
+                copy_async_16(sm.gb + c * 4, phase.gamma + c * 4);
+                copy_async_16(sm.gb + phase.K + c * 4, phase.beta + c * 4);
+            }
+        }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+// Stage rows of a bf16 matrix written earlier in this kernel (read through L2).
+template <int MT>
+__device__ void stage_copy(bf16* xs, int K, const bf16* src, long ld_src, int n_rows) {
+    const int ldx = K + XS_PAD, chunks = K / 8, total = MT * chunks;
+    for (int i0 = threadIdx.x; i0 < total; i0 += THREADS * 4) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int i = i0 + u * THREADS;
+            v[u] = make_uint4(0, 0, 0, 0);
+            if (i < total && i / chunks < n_rows)
+                v[u] = __ldcg(reinterpret_cast<const uint4*>(src + (long)(i / chunks) * ld_src + (i % chunks) * 8));
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int i = i0 + u * THREADS;
+            if (i < total) *reinterpret_cast<uint4*>(xs + (i / chunks) * ldx + (i % chunks) * 8) = v[u];
+        }
+    }
+}
+
+// Stage the layer norm of rows of the fp32 hidden state (gathered through `rows`, if given);
+// gain and shift are in shared memory already.  One warp per row; the row is read once.
+template <int MT>
+__device__ void stage_norm(const FusedParams& p, bf16* xs, int K, const float* gb, float eps, const int* rows, int n_rows) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ldx = K + XS_PAD;
+    constexpr int HELD = 8;                        // chunks of four values a lane keeps (rows up to 1024 wide)
+    const int quads = K / 4;
+    const bool held = quads <= 32 * HELD;
+    for (int m = warp; m < MT; m += WARPS) {
+        if (m >= n_rows) {
+            for (int k = lane; k < K; k += 32) xs[m * ldx + k] = __float2bfloat16_rn(0.0f);
+            continue;
+        }
+        const float4* row = reinterpret_cast<const float4*>(p.hidden + (long)(rows ? rows[m] : m) * K);
+        float4 keep[HELD];
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < HELD; i++) {
+            keep[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (held && lane + 32 * i < quads) keep[i] = __ldcg(row + lane + 32 * i);
+            sum += keep[i].x + keep[i].y + keep[i].z + keep[i].w;
+        }
+        if (!held)
+            for (int qd = lane; qd < quads; qd += 32) {
+                const float4 v = __ldcg(row + qd);
+                sum += v.x + v.y + v.z + v.w;
+            }
+        const float mean = warp_sum(sum) / (float)K;
+        float sq = 0.0f;
+        if (held) {
+#pragma unroll
+            for (int i = 0; i < HELD; i++)
+                if (lane + 32 * i < quads) {
+                    const float a = keep[i].x - mean, b = keep[i].y - mean, c = keep[i].z - mean, d = keep[i].w - mean;
+                    sq += a * a + b * b + c * c + d * d;
+                }
+        } else {
+            for (int qd = lane; qd < quads; qd += 32) {
+                const float4 v = __ldcg(row + qd);
+                const float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+                sq += a * a + b * b + c * c + d * d;
+            }
+        }
+        const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)K + eps);
+        auto emit = [&](int qd, const float4& v) {
+            const float4 g = *reinterpret_cast<const float4*>(gb + qd * 4);
+            const float4 b = *reinterpret_cast<const float4*>(gb + K + qd * 4);
+            __nv_bfloat162 lo = __floats2bfloat162_rn((v.x - mean) * inv * g.x + b.x, (v.y - mean) * inv * g.y + b.y);
+            __nv_bfloat162 hi = __floats2bfloat162_rn((v.z - mean) * inv * g.z + b.z, (v.w - mean) * inv * g.w + b.w);
+            *reinterpret_cast<uint2*>(xs + m * ldx + qd * 4) =
+                make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        };
+        if (held) {
+#pragma unroll
+            for (int i = 0; i < HELD; i++)
+                if (lane + 32 * i < quads) emit(lane + 32 * i, keep[i]);
+        } else {
+            for (int qd = lane; qd < quads; qd += 32) emit(qd, __ldcg(row + qd));
+        }
+    }
+}
+
+// One m16n8k16 tensor-core product: D = A (16 x 16, weights) * B (16 x 8, activations) + D.
+__device__ __forceinline__ void mma_16816(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Greedy rules: a NaN beats numbers, the lower index wins ties (engine/src/argmax.cu:8-18).
+__device__ __forceinline__ bool better_candidate(float va, int ia, float vb, int ib) {
+    const bool na = va != va, nb = vb != vb;
+    if (ia < 0) return false;
+    if (ib < 0) return true;
+    if (na != nb) return na;
+    if (na) return ia < ib;
+    if (va != vb) return va > vb;
+    return ia < ib;
+}
+
+// The sampling score of logit v of token m at vocabulary index n: the logit itself (greedy)
+// or logit / T + Gumbel noise from the hash of (seed, counter, n), as in sampling_kernels.cu.
+__device__ __forceinline__ float sampling_score(const FusedParams& p, int m, int n, float v) {
+    const float temp = p.temperature ? p.temperature[m] : 0.0f;
+    if (!(temp > 0.0f)) return v;
+    const unsigned long long seed = p.seeds ? p.seeds[m] : 0ull;
+    const unsigned counter = p.counters ? (unsigned)p.counters[m] : 0u;
+    unsigned long long h = seed ^ ((unsigned long long)counter << 32);
+    h += 0x9E3779B97F4A7C15ull; h = (h ^ (h >> 30)) * 0xBF58476D1CE4E5B9ull;
+    h = (h ^ (h >> 27)) * 0x94D049BB133111EBull; h ^= h >> 31;
+    h ^= (unsigned long long)n;
+    h += 0x9E3779B97F4A7C15ull; h = (h ^ (h >> 30)) * 0xBF58476D1CE4E5B9ull;
+    h = (h ^ (h >> 27)) * 0x94D049BB133111EBull; h ^= h >> 31;
+    const float uni = ((float)(unsigned)(h >> 40) + 0.5f) * (1.0f / 16777216.0f);
+    return v * (1.0f / temp) - logf(-logf(uni));
+}
+
+// One product phase on the tensor cores.  The CTA takes its share of the 16-row blocks of
+// w [N, K]; with fewer blocks than warps, the warps of a block split its K range and their
+// partial tiles meet in shared memory, added in part order.  The first resident_of(NT) K steps of a
+// warp's first block were prefetched into wbuf; the rest stream in from L2 / HBM.
+//
+// A lane (g = lane / 4, q = lane % 4) takes eight consecutive K values of rows g and g + 8
+// (16 bytes each) and the same eight K values of token g (16 bytes from shared memory).
+// Which K value sits in which slot of the instruction does not matter to a sum as long as A
+// and B agree, so the eight values feed two instructions: values 0..3 the first (slots 2q,
+// 2q+1, 2q+8, 2q+9), values 4..7 the second.
+// Once a thread has read its prefetched data it starts the prefetch of `next`.
+template <int NT>
+__device__ void product_phase(const FusedParams& p, const Shared& sm, const Phase& phase, int parity, int ldx, int n_rows,
+                              int activation, const FusedLayer* layer, const Phase& next, float* best_value,
+                              int* best_index) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, q = lane & 3;
+    const int N = phase.N, K = phase.K, kind = phase.kind;
+    const Split sp = split_of(N, K, kind);
+    const int split = sp.split, k_steps = K / 32;
+    const bf16* xs = sm.xs;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");       // this thread's prefetched data has landed
+    for (int b0 = 0; b0 < sp.count || b0 == 0; b0 += sp.blocks_at_a_time) {
+        const int b = b0 + warp / split, part = warp % split;
+        const bool active = b < sp.count;
+        float acc[NT][4];
+#pragma unroll
+        for (int t = 0; t < NT; t++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[t][i] = 0.0f;
+        const int row_lo = (sp.first + b) * 16 + g, row_hi = row_lo + 8;
+        if (active) {
+            // rows past N are read from the last row (their results are never stored)
+            const bf16* w_lo = phase.w + (long)min(row_lo, N - 1) * K + q * 8;
+            const bf16* w_hi = phase.w + (long)min(row_hi, N - 1) * K + q * 8;
+            const bf16* x_lo = xs + g * ldx + q * 8;
+            const int k_begin = part * sp.per_part, k_end = min(k_steps, k_begin + sp.per_part);
+            int ks = k_begin;
+            if (b0 == 0) {
+                for (int u = 0; u < resident_of(NT) && ks < k_end; u++, ks++) {
+                    const uint4 wl = sm.wbuf[(2 * u) * THREADS + threadIdx.x];
+                    const uint4 wh = sm.wbuf[(2 * u + 1) * THREADS + threadIdx.x];
+#pragma unroll
+                    for (int t = 0; t < NT; t++) {
+                        const uint4 xv = *reinterpret_cast<const uint4*>(x_lo + t * 8 * ldx + ks * 32);
+                        mma_16816(acc[t], wl.x, wh.x, wl.y, wh.y, xv.x, xv.y);
+                        mma_16816(acc[t], wl.z, wh.z, wl.w, wh.w, xv.z, xv.w);
+                    }
+                }
+            }
+            for (; ks + 4 <= k_end; ks += 4) {
+                uint4 wl[4], wh[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    wl[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + (ks + u) * 32));
+                    wh[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + (ks + u) * 32));
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+#pragma unroll
+                    for (int t = 0; t < NT; t++) {
+                        const uint4 xv = *reinterpret_cast<const uint4*>(x_lo + t * 8 * ldx + (ks + u) * 32);
+                        mma_16816(acc[t], wl[u].x, wh[u].x, wl[u].y, wh[u].y, xv.x, xv.y);
+                        mma_16816(acc[t], wl[u].z, wh[u].z, wl[u].w, wh[u].w, xv.z, xv.w);
+                    }
+                }
+            }
+            for (; ks < k_end; ks++) {
+                const uint4 wl = __ldg(reinterpret_cast<const uint4*>(w_lo + ks * 32));
+                const uint4 wh = __ldg(reinterpret_cast<const uint4*>(w_hi + ks * 32));
+#pragma unroll
+                for (int t = 0; t < NT; t++) {
+                    const uint4 xv = *reinterpret_cast<const uint4*>(x_lo + t * 8 * ldx + ks * 32);
+                    mma_16816(acc[t], wl.x, wh.x, wl.y, wh.y, xv.x, xv.y);
+                    mma_16816(acc[t], wl.z, wh.z, wl.w, wh.w, xv.z, xv.w);
+                }
+            }
+        }
+        // Biases and the values to add to: prefetched for the warp's first block (read here,
+        // before the next phase's replace them), fetched directly for any further block.
+        float bias_lo = 0.0f, bias_hi = 0.0f, old[NT][4];
+#pragma unroll
+        for (int t = 0; t < NT; t++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) old[t][i] = 0.0f;
+        if (active && part == 0) {
+            if (b0 == 0) {
+                if (phase.bias != nullptr) {
+                    bias_lo = sm.bias[(parity * THREADS + threadIdx.x) * 2];
+                    bias_hi = sm.bias[(parity * THREADS + threadIdx.x) * 2 + 1];
+                }
+                if (kind == OUT_ADD) {
+#pragma unroll
+                    for (int t = 0; t < NT; t++)
+#pragma unroll
+                        for (int i = 0; i < 4; i++) old[t][i] = sm.old[threadIdx.x * (NT * 4) + t * 4 + i];
+                }
+            } else {
+                if (phase.bias != nullptr) {
+                    if (row_lo < N) bias_lo = __ldg(phase.bias + row_lo);
+                    if (row_hi < N) bias_hi = __ldg(phase.bias + row_hi);
+                }
+                if (kind == OUT_ADD) {
+#pragma unroll
+                    for (int t = 0; t < NT; t++)
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const int n = (i < 2) ? row_lo : row_hi, m = t * 8 + 2 * q + (i & 1);
+                            if (n < N && m < n_rows) old[t][i] = __ldcg(p.hidden + (long)m * N + n);
+                        }
+                }
+            }
+        }
+        if (b0 == 0) prefetch_phase<NT>(p, sm, next, parity ^ 1, p.T);
+        if (split > 1) {
+            float* mine = sm.red + (warp * 32 + lane) * (NT * 4);
+#pragma unroll
+            for (int t = 0; t < NT; t++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) mine[t * 4 + i] = acc[t][i];
+            __syncthreads();
+            if (active && part == 0) {
+                for (int s = 1; s < split; s++) {
+                    const float* other = sm.red + ((warp + s) * 32 + lane) * (NT * 4);
+#pragma unroll
+                    for (int t = 0; t < NT; t++)
+#pragma unroll
+                        for (int i = 0; i < 4; i++) acc[t][i] += other[t * 4 + i];
+                }
+            }
+            __syncthreads();
+            if (part != 0) continue;
+        }
+        if (!active) continue;
+        // accumulator i of tile t: row (g or g + 8), token t * 8 + 2q + (i & 1)
+#pragma unroll
+        for (int t = 0; t < NT; t++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int n = (i < 2) ? row_lo : row_hi;
+                const int m = t * 8 + 2 * q + (i & 1);
+                if (n >= N || m >= n_rows) continue;
+                float v = acc[t][i] + ((i < 2) ? bias_lo : bias_hi);
+                if (kind == OUT_ADD) {
+                    p.hidden[(long)m * N + n] = old[t][i] + v;
+                } else if (kind == OUT_BF16) {
+                    if (activation == EPI_GELU_TANH) v = gelu_tanh_f(v);
+                    else if (activation == EPI_GELU_ERF) v = gelu_erf_f(v);
+                    p.up[(long)m * N + n] = __float2bfloat16_rn(v);
+                } else if (kind == OUT_QKV) {
+                    const int q_width = p.H * p.D, kv_width = p.Hkv * p.D;
+                    if (n < q_width) p.q[(long)m * q_width + n] = __float2bfloat16_rn(v);
+                    else if (n < q_width + kv_width) layer->k_pages[sm.kv_base[m] + (n - q_width)] = __float2bfloat16_rn(v);
+                    else layer->v_pages[sm.kv_base[m] + (n - q_width - kv_width)] = __float2bfloat16_rn(v);
+                } else {
+                    p.logits[(long)m * N + n] = v;
+                    if (p.sample != 0) {
+                        const float score = sampling_score(p, m, n, v);
+                        const int slot = t * 2 + (i & 1);
+                        if (better_candidate(score, n, best_value[slot], best_index[slot])) {
+                            best_value[slot] = score;
+                            best_index[slot] = n;
+                        }
+                    }
+                }
+            }
+    }
+}
+
+// Phase 2: one CTA per (token, head); its warps take the keys in turn (four keys and four
+// values in flight per lane), each with an online softmax; the warps' states are merged through
+// shared memory in warp order, so nothing depends on timing.
+template <int D>
+__device__ void attention_phase(const FusedParams& p, const Shared& sm, const FusedLayer& layer) {
+    constexpr int LPK = D / 8, KPW = 32 / LPK, INFLIGHT = 4;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane % LPK, group = lane / LPK;
+    const long kv_width = (long)p.Hkv * D;
+    float* sm_m = sm.att;                     // [WARPS]
+    float* sm_l = sm.att + WARPS;             // [WARPS]
+    float* sm_acc = sm.att + 2 * WARPS;       // [WARPS][D]
+    for (int pair = blockIdx.x; pair < p.T * p.H; pair += gridDim.x) {
+        const int h = pair % p.H, t = pair / p.H;
+        const int pos = sm.pos[t];
+        const int begin = (layer.window > 0 && pos - layer.window + 1 > 0) ? pos - layer.window + 1 : 0;
+        const int* bt = sm.table + t * p.max_blocks;
+        const int hk = h / (p.H / p.Hkv);
+        float qf[8], acc[8];
+        unpack8(__ldcg(reinterpret_cast<const uint4*>(p.q + (long)t * p.H * D + (long)h * D + sub * 8)), qf);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            qf[i] *= layer.score_scale;
+            acc[i] = 0.0f;
+        }
+        float m = -INFINITY, l = 0.0f;
+        for (int jb = begin + warp * INFLIGHT * KPW; jb <= pos; jb += WARPS * INFLIGHT * KPW) {
+            uint4 kv[INFLIGHT], vv[INFLIGHT];
+#pragma unroll
+            for (int s = 0; s < INFLIGHT; s++) {
+                const int j = jb + s * KPW + group;
+                kv[s] = make_uint4(0, 0, 0, 0);
+                vv[s] = make_uint4(0, 0, 0, 0);
+                if (j <= pos) {
+                    const int page = bt[j / p.page_size];
+                    const long base = ((long)page * p.page_size + (j % p.page_size)) * kv_width + (long)hk * D + sub * 8;
+                    kv[s] = __ldcg(reinterpret_cast<const uint4*>(layer.k_pages + base));
+                    vv[s] = __ldcg(reinterpret_cast<const uint4*>(layer.v_pages + base));
+                }
+            }
+#pragma unroll
+            for (int s = 0; s < INFLIGHT; s++) {
+                float kf[8], vf[8];
+                unpack8(kv[s], kf);
+                unpack8(vv[s], vf);
+                float sc = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; i++) sc = fmaf(qf[i], kf[i], sc);
+#pragma unroll
+                for (int o = LPK / 2; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
+                if (jb + s * KPW + group <= pos) {
+                    const float m_new = fmaxf(m, sc);
+                    const float corr = __expf(m - m_new), e = __expf(sc - m_new);
+                    l = l * corr + e;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) acc[i] = acc[i] * corr + e * vf[i];
+                    m = m_new;
+                }
+            }
+        }
+        // merge the key groups of the warp (a butterfly over the group index)
+#pragma unroll
+        for (int o = LPK; o < 32; o <<= 1) {
+            const float m_o = __shfl_xor_sync(0xffffffffu, m, o), l_o = __shfl_xor_sync(0xffffffffu, l, o);
+            const float big = fmaxf(m, m_o);
+            const float wa = (m == -INFINITY) ? 0.0f : __expf(m - big), wb = (m_o == -INFINITY) ? 0.0f : __expf(m_o - big);
+#pragma unroll
+            for (int i = 0; i < 8; i++) acc[i] = acc[i] * wa + __shfl_xor_sync(0xffffffffu, acc[i], o) * wb;
+            l = l * wa + l_o * wb;
+            m = big;
+        }
+        __syncthreads();                      // the scratch may still be read for the previous pair
+        if (group == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) sm_acc[warp * D + sub * 8 + i] = acc[i];
+        }
+        if (lane == 0) {
+            sm_m[warp] = m;
+            sm_l[warp] = l;
+        }
+        __syncthreads();
+        for (int d = threadIdx.x; d < D; d += THREADS) {
+            float top = -INFINITY;
+            for (int w = 0; w < WARPS; w++) top = fmaxf(top, sm_m[w]);
+            float denom = 0.0f, o = 0.0f;
+            for (int w = 0; w < WARPS; w++) {
+                const float weight = (sm_m[w] == -INFINITY) ? 0.0f : __expf(sm_m[w] - top);
+                denom += sm_l[w] * weight;
+                o += sm_acc[w * D + d] * weight;
+            }
+            p.attn[(long)t * p.H * D + (long)h * D + d] = __float2bfloat16_rn(o / denom);
+        }
+    }
+}
+
+__device__ Phase phase_of(const FusedParams& p, int index) {
+    Phase ph{nullptr, nullptr, 16, 32, OUT_BF16, nullptr, nullptr};
+    const int q_width = p.H * p.D, qkv_width = (p.H + 2 * p.Hkv) * p.D;
+    if (index < 4 * p.n_layers) {
+        const FusedLayer& layer = p.layers[index / 4];
+        switch (index % 4) {
+        case 0: ph = Phase{layer.w_qkv, layer.b_qkv, qkv_width, p.E, OUT_QKV, layer.ln1_g, layer.ln1_b}; break;
+        case 1: ph = Phase{layer.w_o, layer.b_o, p.E, q_width, OUT_ADD, nullptr, nullptr}; break;
+        case 2: ph = Phase{layer.w_fc, layer.b_fc, p.I, p.E, OUT_BF16, layer.ln2_g, layer.ln2_b}; break;
+        default: ph = Phase{layer.w_proj, layer.b_proj, p.E, p.I, OUT_ADD, nullptr, nullptr}; break;
+        }
+    } else if (index == 4 * p.n_layers && p.n_want > 0) {
+        ph = Phase{p.w_head, nullptr, p.V, p.E, OUT_LOGITS, p.lnf_g, p.lnf_b};
+    }
+    return ph;
+}
+
+template <int NT>
+__global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedParams p) {
+    constexpr int MT = NT * 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int k_max = max(p.E, max(p.I, p.H * p.D));
+    Shared sm;
+    unsigned char* cursor = smem_raw;
+    sm.xs = reinterpret_cast<bf16*>(cursor);      cursor += (size_t)MT * (k_max + XS_PAD) * 2;
+    sm.red = reinterpret_cast<float*>(cursor);    cursor += (size_t)WARPS * 32 * NT * 4 * 4;
+    sm.att = reinterpret_cast<float*>(cursor);    cursor += (size_t)WARPS * (2 + 256) * 4;
+    sm.wbuf = reinterpret_cast<uint4*>(cursor);   cursor += (size_t)2 * resident_of(NT) * THREADS * 16;
+    sm.bias = reinterpret_cast<float*>(cursor);   cursor += (size_t)2 * THREADS * 2 * 4;
+    sm.old = reinterpret_cast<float*>(cursor);    cursor += (size_t)THREADS * NT * 4 * 4;
+    sm.gb = reinterpret_cast<float*>(cursor);     cursor += (size_t)2 * p.E * 4;
+    sm.kv_base = reinterpret_cast<long*>(cursor); cursor += MAX_TOKENS * 8;
+    sm.pos = reinterpret_cast<int*>(cursor);      cursor += MAX_TOKENS * 4;
+    sm.table = reinterpret_cast<int*>(cursor);
+
+    int stamp = 0;
+    // timeline (may be null): CTA 0 notes the time after every phase, for profiling
+    auto note = [&]() {
+        if (p.timeline != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.timeline[stamp] = now_ns();
+        stamp++;
+    };
+    note();
+    float best_value[NT * 2];
+    int best_index[NT * 2];
+#pragma unroll
+    for (int i = 0; i < NT * 2; i++) {
+        best_value[i] = 0.0f;
+        best_index[i] = -1;
+    }
+
+    // ---- the step's positions, block tables and cache slots, once ----
+    for (int i = threadIdx.x; i < p.T * p.max_blocks; i += THREADS)
+        sm.table[i] = p.block_table[(long)p.token_item[i / p.max_blocks] * p.max_blocks + i % p.max_blocks];
+    if (threadIdx.x < p.T) {
+        const int pos = p.positions[threadIdx.x];
+        const int page = p.block_table[(long)p.token_item[threadIdx.x] * p.max_blocks + pos / p.page_size];
+        sm.pos[threadIdx.x] = pos;
+        sm.kv_base[threadIdx.x] = ((long)page * p.page_size + pos % p.page_size) * ((long)p.Hkv * p.D);
+    }
+    int index = 0;
+    Phase phase = phase_of(p, 0);
+    prefetch_phase<NT>(p, sm, phase, 0, p.T);
+    // ---- embedding: token t is written by CTA t % grid ----
+    for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
+        const long trow = (long)p.token_ids[t] * p.E, prow = p.wpe ? (long)p.positions[t] * p.E : 0;
+        for (int c = threadIdx.x; c < p.E / 4; c += THREADS) {
+            const uint2 tv = __ldg(reinterpret_cast<const uint2*>(p.wte + trow + c * 4));
+            float4 v = make_float4(__uint_as_float(tv.x << 16), __uint_as_float(tv.x & 0xffff0000u),
+                                   __uint_as_float(tv.y << 16), __uint_as_float(tv.y & 0xffff0000u));
+            if (p.wpe) {
+                const uint2 pv = __ldg(reinterpret_cast<const uint2*>(p.wpe + prow + c * 4));
+                v.x += __uint_as_float(pv.x << 16); v.y += __uint_as_float(pv.x & 0xffff0000u);
+                v.z += __uint_as_float(pv.y << 16); v.w += __uint_as_float(pv.y & 0xffff0000u);
+            }
+            reinterpret_cast<float4*>(p.hidden + (long)t * p.E)[c] = v;
+        }
+    }
+    if (!grid_barrier(p)) return;
+    note();
+
+    for (int l = 0; l < p.n_layers; l++) {
+        const FusedLayer& layer = p.layers[l];
+        Phase next = phase_of(p, index + 1);
+        // ---- phase 1 ----
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                  // gain and shift were copied by all threads
+        stage_norm<MT>(p, sm.xs, p.E, sm.gb, layer.eps1, nullptr, p.T);
+        __syncthreads();
+        product_phase<NT>(p, sm, phase, index & 1, p.E + XS_PAD, p.T, EPI_STORE, &layer, next, best_value, best_index);
+        if (!grid_barrier(p)) return;
+        note();
+        // ---- phase 2 ----
+        switch (p.D) {
+        case 16: attention_phase<16>(p, sm, layer); break;
+        case 32: attention_phase<32>(p, sm, layer); break;
+        case 64: attention_phase<64>(p, sm, layer); break;
+        case 128: attention_phase<128>(p, sm, layer); break;
+        default: attention_phase<256>(p, sm, layer); break;
+        }
+        if (!grid_barrier(p)) return;
+        note();
+        // ---- phase 3 ----
+        phase = next; index++; next = phase_of(p, index + 1);
+        stage_copy<MT>(sm.xs, phase.K, p.attn, phase.K, p.T);
+        __syncthreads();
+        product_phase<NT>(p, sm, phase, index & 1, phase.K + XS_PAD, p.T, EPI_STORE, &layer, next, best_value, best_index);
+        if (!grid_barrier(p)) return;
+        note();
+        // ---- phase 4 ----
+        phase = next; index++; next = phase_of(p, index + 1);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        stage_norm<MT>(p, sm.xs, p.E, sm.gb, layer.eps2, nullptr, p.T);
+        __syncthreads();
+        product_phase<NT>(p, sm, phase, index & 1, p.E + XS_PAD, p.T, layer.activation, &layer, next, best_value, best_index);
+        if (!grid_barrier(p)) return;
+        note();
+        // ---- phase 5 ----
+        phase = next; index++; next = phase_of(p, index + 1);
+        stage_copy<MT>(sm.xs, p.I, p.up, p.I, p.T);
+        __syncthreads();
+        product_phase<NT>(p, sm, phase, index & 1, p.I + XS_PAD, p.T, EPI_STORE, &layer, next, best_value, best_index);
+        if (!grid_barrier(p)) return;
+        note();
+        phase = next; index++;
+    }
+    if (p.n_want <= 0) return;
+
+    // ---- final norm, head, sampling candidates ----
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    stage_norm<MT>(p, sm.xs, p.E, sm.gb, p.eps_f, p.want_rows, p.n_want);
+    __syncthreads();
+    product_phase<NT>(p, sm, phase, index & 1, p.E + XS_PAD, p.n_want, EPI_STORE, nullptr, phase_of(p, index + 1),
+                      best_value, best_index);
+    note();
+    if (p.sample == 0) return;
+    // A lane holds candidates for tokens t*8 + 2q + j (slot t*2 + j): the lanes of equal q
+    // compare theirs, then the warps through shared memory, then the CTAs (the CTA that
+    // arrives last does that).
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int i = 0; i < NT * 2; i++)
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best_value[i], o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_index[i], o);
+            if (better_candidate(ov, oi, best_value[i], best_index[i])) {
+                best_value[i] = ov;
+                best_index[i] = oi;
+            }
+        }
+    __shared__ float cta_value[WARPS][MAX_TOKENS];
+    __shared__ int cta_index[WARPS][MAX_TOKENS];
+    __shared__ int is_last;
+    if (lane < 4) {
+#pragma unroll
+        for (int i = 0; i < NT * 2; i++) {
+            const int m = (i / 2) * 8 + 2 * lane + (i & 1);
+            cta_value[warp][m] = best_value[i];
+            cta_index[warp][m] = best_index[i];
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < p.n_want) {
+        float v = 0.0f;
+        int i = -1;
+        for (int w = 0; w < WARPS; w++)
+            if (better_candidate(cta_value[w][threadIdx.x], cta_index[w][threadIdx.x], v, i)) {
+                v = cta_value[w][threadIdx.x];
+                i = cta_index[w][threadIdx.x];
+            }
+        p.cand_value[(long)threadIdx.x * gridDim.x + blockIdx.x] = v;
+        p.cand_index[(long)threadIdx.x * gridDim.x + blockIdx.x] = i;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int ticket = atomicAdd(p.cand_done, 1);
+        is_last = ticket == (int)gridDim.x - 1;
+        if (is_last) *p.cand_done = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (warp < p.n_want) {
+        float v = 0.0f;
+        int i = -1;
+        for (int c = lane; c < (int)gridDim.x; c += 32) {
+            const float cv = __ldcg(p.cand_value + (long)warp * gridDim.x + c);
+            const int ci = __ldcg(p.cand_index + (long)warp * gridDim.x + c);
+            if (better_candidate(cv, ci, v, i)) { v = cv; i = ci; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+            if (better_candidate(ov, oi, v, i)) { v = ov; i = oi; }
+        }
+        if (lane == 0) p.out_tokens[warp] = i;
+    }
+}
+
+int g_sm_count = 0, g_smem_optin = 0;
+
+template <int NT>
+int launch(const FusedParams& p, size_t smem, cudaStream_t s) {
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncAttributes attributes;
+        if (cudaFuncGetAttributes(&attributes, fused_decode_kernel<NT>) != cudaSuccess ||
+            cudaFuncSetAttribute(fused_decode_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 g_smem_optin - (int)attributes.sharedSizeBytes) != cudaSuccess)
+            return fail("fused_decode: cannot raise the shared memory limit");
+        configured = true;
+    }
+    void* args[] = {const_cast<FusedParams*>(&p)};
+    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(fused_decode_kernel<NT>), dim3(g_sm_count),
+                                                dim3(THREADS), args, smem, s);
+    if (e != cudaSuccess) {
+        snprintf(g_error_text, MLLM_ERROR_BUFFER, "fused_decode: cooperative launch failed: %s", cudaGetErrorString(e));
+        cudaGetLastError();
+        return 2;
+    }
+    return check_launch("fused_decode_kernel");
+}
+
+}  // namespace
+
+extern "C" int mllm_fused_layer_bytes(void) { return (int)sizeof(FusedLayer); }
+extern "C" int mllm_fused_params_bytes(void) { return (int)sizeof(FusedParams); }
+
+// Number of CTAs the step runs with (one per SM); sizes the candidate scratch.
+extern "C" int mllm_fused_grid(void) {
+    if (g_sm_count == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, device);
+        cudaDeviceGetAttribute(&g_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+    }
+    return g_sm_count;
+}
+
+// Whether the kernel takes these sizes: up to 16 tokens, widths that are multiples of 32
+// (one tensor-core step), a head size that is a power of two, and everything it keeps in
+// shared memory fitting there.
+extern "C" int mllm_fused_takes(int T, int E, int H, int Hkv, int D, int I, int max_blocks) {
+    mllm_fused_grid();
+    if (T < 1 || T > MAX_TOKENS) return 0;
+    if (E % 32 != 0 || I % 32 != 0 || (H * D) % 32 != 0) return 0;
+    if (!(D == 16 || D == 32 || D == 64 || D == 128 || D == 256)) return 0;
+    if (Hkv <= 0 || H % Hkv != 0 || max_blocks <= 0) return 0;
+    return shared_bytes(T <= 8 ? 1 : 2, E, I, H * D, max_blocks) + 8 * 1024 <= (size_t)g_smem_optin;
+}
+
+extern "C" int mllm_fused_decode_step(const FusedParams* params, void* stream) {
+    const FusedParams& p = *params;
+    if (!mllm_fused_takes(p.T, p.E, p.H, p.Hkv, p.D, p.I, p.max_blocks)) return fail("fused_decode: sizes not taken");
+    if (p.n_want > p.T) return fail("fused_decode: more wanted rows than tokens");
+    const int nt = p.T <= 8 ? 1 : 2;
+    const size_t smem = shared_bytes(nt, p.E, p.I, p.H * p.D, p.max_blocks);
+    cudaStream_t s = (cudaStream_t)stream;
+    return nt == 1 ? launch<1>(p, smem, s) : launch<2>(p, smem, s);
+}

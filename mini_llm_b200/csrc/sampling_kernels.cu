@@ -226,6 +226,17 @@ extern "C" int mllm_sampling_sample_rows_sliced(int* out, const float* logits, l
     return check_launch("sample_rows_sliced_kernel");
 }
 
+// Only the rows with a nucleus cut (temperature > 0 and top_p < 1); every other row of
+// `out` is left as it is.
+extern "C" int mllm_sampling_sample_rows_nucleus(int* out, const float* logits, long ld, int n_rows, int vocab,
+                                                 const float* temperature, const float* top_p,
+                                                 const unsigned long long* seeds, const int* counters, void* stream) {
+    if (n_rows <= 0) return 0;
+    sample_rows_kernel<<<n_rows, 1024, 0, (cudaStream_t)stream>>>(out, logits, ld, vocab, temperature, top_p, seeds,
+                                                                  counters, 1);
+    return check_launch("sample_rows_kernel");
+}
+
 extern "C" int mllm_sampling_sample_rows(int* out, const float* logits, long ld, int n_rows, int vocab,
                                          const float* temperature, const float* top_p,
                                          const unsigned long long* seeds, const int* counters, void* stream) {

@@ -14,6 +14,7 @@ of its input before it launches anything, and a refused step changes nothing.
 
 from __future__ import annotations
 
+import sys
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -23,9 +24,11 @@ from ..cache.manager import CacheManager
 from ..cache.storage import CacheStorage
 from ..config.registry import config_from_folder, describe_model
 from ..kernels import ops
+from ..kernels.lib import KernelError
 from ..kernels.dispatch import Kernels
 from ..sampling import SamplingParams
 from .context import ControlBlock, StepContext, Workspace
+from .fused_decode import FusedDecodePlan
 from .model import Model
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -49,7 +52,8 @@ class StepEntry:
 class Engine:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0", page_size: int = 16,
                  cache_tokens: int | None = None, n_pages: int | None = None, max_requests: int = 64,
-                 max_tokens_per_step: int = 2048, plain_kernels: bool = False, cuda_graphs: bool = True):
+                 max_tokens_per_step: int = 2048, plain_kernels: bool = False, cuda_graphs: bool = True,
+                 fused_decode: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("mini_llm_b200 runs on a CUDA device (sm_100a) only; none is available "
                                "and there is no CPU path")
@@ -86,6 +90,7 @@ class Engine:
         self._sampled = None
         self._graphs = {}
         self._graph_stamp = None
+        self.fused = FusedDecodePlan.build(self) if fused_decode else None
         self._status_checks = 0
 
     # ---- requests ---------------------------------------------------------------------------
@@ -228,6 +233,15 @@ class Engine:
         launch on the host instead of one per kernel.  The reference removes host work per
         step in the same spirit, by keeping sampled tokens on the device
         (engine/src/gpt2_gpu_greedy.cu:80-119)."""
+        if self.fused is not None and self.fused.takes(ctx):
+            block_table = next(v.block_table for v in self.storage.views if v.kind == "paged")
+            try:
+                logits, self._sampled = self.fused.run(ctx, block_table, sample_views, self._any_nucleus)
+                return logits
+            except KernelError as error:
+                # for instance no cooperative launch on this device: say so once, then run the generic path
+                print(f"[mini_llm_b200] fused decode step disabled: {error}", file=sys.stderr, flush=True)
+                self.fused = None
         if not (self.cuda_graphs and ctx.decode_only and self.model.graph_safe):
             return self._forward(ctx, sample_views)
         stamp = (self.workspace.generation, self.control.generation, self.kernels.scratch_generation)

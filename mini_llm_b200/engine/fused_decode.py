@@ -1,0 +1,165 @@
+"""A decode step as ONE kernel, when the model is a plain stack of pre-norm layers.
+
+The generic path runs a step part by part, about five kernels a layer.  For steps of few
+tokens that is bound by launch gaps, not by memory or arithmetic.  If a model's description
+is nothing but ``pre_norm`` layers of ``layer_norm`` / ``causal_self_attention`` /
+``layer_norm`` / ``dense_mlp`` around a ``token_embedding`` (with or without
+``learned_positions``), a final ``layer_norm`` and a ``linear_head``, the same arithmetic is
+compiled into a table of pointers and run by ``csrc/fused_decode.cu``: one persistent kernel
+per step.  Any other model, any step with a prompt portion, and any size the kernel does not
+take go the generic way; nothing outside this file knows the difference.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..kernels import ops
+from ..kernels.lib import Function, KernelError, load
+
+P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+
+
+class _Layer(ctypes.Structure):
+    _fields_ = [("ln1_g", P), ("ln1_b", P), ("w_qkv", P), ("b_qkv", P), ("w_o", P), ("b_o", P), ("ln2_g", P),
+                ("ln2_b", P), ("w_fc", P), ("b_fc", P), ("w_proj", P), ("b_proj", P), ("k_pages", P), ("v_pages", P),
+                ("score_scale", F), ("eps1", F), ("eps2", F), ("activation", I), ("window", I)]
+
+
+class _Params(ctypes.Structure):
+    _fields_ = [("layers", P), ("n_layers", I), ("E", I), ("H", I), ("Hkv", I), ("D", I), ("I", I), ("V", I), ("T", I),
+                ("token_ids", P), ("positions", P), ("token_item", P), ("block_table", P), ("max_blocks", I),
+                ("page_size", I), ("want_rows", P), ("n_want", I), ("wte", P), ("wpe", P), ("lnf_g", P), ("lnf_b", P),
+                ("eps_f", F), ("w_head", P), ("hidden", P), ("q", P), ("attn", P), ("up", P), ("logits", P),
+                ("sample", I),
+                ("temperature", P), ("top_p", P), ("seeds", P), ("counters", P), ("out_tokens", P), ("cand_value", P),
+                ("cand_index", P), ("cand_done", P), ("barrier", P), ("status", P), ("timeline", P)]
+
+
+_step = Function("fused", "mllm_fused_decode_step", [ctypes.POINTER(_Params), P])
+MAX_TOKENS = 16
+_KINDS = {"norm_1": "layer_norm", "mixer": "causal_self_attention", "norm_2": "layer_norm", "feed_forward": "dense_mlp"}
+
+
+def _matches(spec) -> bool:
+    if spec.embedding.kind != "token_embedding" or spec.final_norm.kind != "layer_norm" or spec.head.kind != "linear_head":
+        return False
+    if spec.position is not None and spec.position.kind != "learned_positions":
+        return False
+    for layer in spec.layers:
+        if layer.arrangement != "pre_norm" or {r: p.kind for r, p in layer.parts.items()} != _KINDS:
+            return False
+    return all(entry.cache_of is None for entry in spec.order) and len(spec.order) > 0
+
+
+class FusedDecodePlan:
+    @classmethod
+    def build(cls, engine):
+        """The plan for ``engine``'s model, or None if the model is not of the fused shape."""
+        spec, model = engine.spec, engine.model
+        if engine.dtype != torch.bfloat16 or engine.kernels.plain_only or not _matches(spec):
+            return None
+        mixers = [model.layers[e.layer][1]["mixer"] for e in spec.order]
+        mlps = [model.layers[e.layer][1]["feed_forward"] for e in spec.order]
+        first = mixers[0]
+        same = all((m.width, m.n_heads, m.n_kv_heads, m.head_size) == (first.width, first.n_heads, first.n_kv_heads,
+                                                                        first.head_size) for m in mixers)
+        if not same or any(f.inner != mlps[0].inner for f in mlps) or len({v.group for v in engine.storage.views}) != 1:
+            return None
+        lib = load("fused")
+        if ctypes.sizeof(_Layer) != lib.mllm_fused_layer_bytes() or ctypes.sizeof(_Params) != lib.mllm_fused_params_bytes():
+            raise KernelError("fused_decode: the binding's structures do not match the library's")
+        if not lib.mllm_fused_takes(1, first.width, first.n_heads, first.n_kv_heads, first.head_size, mlps[0].inner,
+                                    engine.cache.groups[0].max_blocks):
+            return None
+        return cls(engine, lib)
+
+    def __init__(self, engine, lib):
+        self.engine = engine
+        self.lib = lib
+        self.grid = lib.mllm_fused_grid()
+        spec, model = engine.spec, engine.model
+        rows = []
+        activations = {"gelu_tanh": ops.EPILOGUES["gelu_tanh"], "gelu_erf": ops.EPILOGUES["gelu_erf"]}
+        for index, entry in enumerate(spec.order):
+            parts = model.layers[entry.layer][1]
+            n1, att, n2, mlp = parts["norm_1"], parts["mixer"], parts["norm_2"], parts["feed_forward"]
+            view = engine.storage.views[index]
+            rows.append(_Layer(
+                n1.w("weight").data_ptr(), n1.w("bias").data_ptr(),
+                att.w(f"{att.qkv_name}.weight").data_ptr(), att.w(f"{att.qkv_name}.bias").data_ptr(),
+                att.w(f"{att.out_name}.weight").data_ptr(), att.w(f"{att.out_name}.bias").data_ptr(),
+                n2.w("weight").data_ptr(), n2.w("bias").data_ptr(),
+                mlp.w(f"{mlp.up_name}.weight").data_ptr(), mlp.w(f"{mlp.up_name}.bias").data_ptr(),
+                mlp.w(f"{mlp.down_name}.weight").data_ptr(), mlp.w(f"{mlp.down_name}.bias").data_ptr(),
+                view.k_pages.data_ptr(), view.v_pages.data_ptr(), att.score_scale, n1.eps, n2.eps,
+                activations[mlp.activation], att.window or 0))
+        table = (_Layer * len(rows))(*rows)
+        raw = torch.frombuffer(bytearray(bytes(table)), dtype=torch.uint8)
+        self.layer_table = raw.to(engine.device)
+        att, mlp = model.layers[spec.order[0].layer][1]["mixer"], model.layers[spec.order[0].layer][1]["feed_forward"]
+        self.sizes = (att.width, att.n_heads, att.n_kv_heads, att.head_size, mlp.inner, spec.vocab_size)
+        device = engine.device
+        self.max_blocks = engine.cache.groups[0].max_blocks
+        self.timeline = None          # set to an int64 tensor of 5 * layers + 3 entries to record phase times
+        self.cand_value = torch.empty(MAX_TOKENS * self.grid, dtype=torch.float32, device=device)
+        self.cand_index = torch.empty(MAX_TOKENS * self.grid, dtype=torch.int32, device=device)
+        self.cand_done = torch.zeros(1, dtype=torch.int32, device=device)
+        self.barrier = torch.zeros(1, dtype=torch.int64, device=device)
+        self.out_tokens = torch.zeros(MAX_TOKENS, dtype=torch.int32, device=device)
+
+    def takes(self, ctx) -> bool:
+        width, heads, kv_heads, head_size, inner, _ = self.sizes
+        return (ctx.decode_only and ctx.n_tokens <= MAX_TOKENS
+                and bool(self.lib.mllm_fused_takes(ctx.n_tokens, width, heads, kv_heads, head_size, inner, self.max_blocks)))
+
+    def run(self, ctx, block_table, sample_views, any_nucleus):
+        """Run the step; returns (logits or None, sampled tokens or None)."""
+        engine = self.engine
+        model = engine.model
+        width, heads, kv_heads, head_size, inner, vocab = self.sizes
+        n = ctx.n_tokens
+        hidden = ctx.buffer("hidden", (n, width), torch.float32)
+        q = ctx.buffer("q", (n, heads * head_size), torch.bfloat16)
+        attn = ctx.buffer("attn_out", (n, heads * head_size), torch.bfloat16)
+        up = ctx.buffer("mlp_up", (n, inner), torch.bfloat16)
+        logits = ctx.buffer("logits", (ctx.n_want, vocab), torch.float32) if ctx.n_want else None
+        params = _Params()
+        params.layers, params.n_layers = self.layer_table.data_ptr(), len(engine.spec.order)
+        params.E, params.H, params.Hkv, params.D, params.I, params.V, params.T = (width, heads, kv_heads, head_size,
+                                                                                    inner, vocab, n)
+        params.token_ids, params.positions = ctx.token_ids.data_ptr(), ctx.positions.data_ptr()
+        params.token_item, params.block_table = ctx.token_item.data_ptr(), block_table.data_ptr()
+        params.max_blocks, params.page_size = block_table.shape[1], engine.page_size
+        params.want_rows, params.n_want = ctx.want_rows.data_ptr(), ctx.n_want
+        params.wte = model.embedding.w(model.embedding.name).data_ptr()
+        params.wpe = model.position.w(model.position.name).data_ptr() if model.position is not None else None
+        params.lnf_g, params.lnf_b = model.final_norm.w("weight").data_ptr(), model.final_norm.w("bias").data_ptr()
+        params.eps_f, params.w_head = model.final_norm.eps, model.head.w(model.head.weight_name).data_ptr()
+        params.hidden, params.q, params.attn, params.up = hidden.data_ptr(), q.data_ptr(), attn.data_ptr(), up.data_ptr()
+        params.logits = logits.data_ptr() if logits is not None else None
+        params.timeline = self.timeline.data_ptr() if self.timeline is not None else None
+        sampled = None
+        if sample_views is not None and ctx.n_want:
+            temperature, top_p, seeds, counters = sample_views
+            params.sample = 1
+            params.temperature, params.top_p = temperature.data_ptr(), top_p.data_ptr()
+            params.seeds, params.counters = seeds.data_ptr(), counters.data_ptr()
+            sampled = self.out_tokens[:ctx.n_want]
+        params.out_tokens = self.out_tokens.data_ptr()
+        params.cand_value, params.cand_index = self.cand_value.data_ptr(), self.cand_index.data_ptr()
+        params.cand_done, params.barrier = self.cand_done.data_ptr(), self.barrier.data_ptr()
+        params.status = engine.kernels.status(engine.device).data_ptr()
+        _step(ctypes.byref(params), torch.cuda.current_stream().cuda_stream)
+        engine.kernels.launches += 1
+        if sampled is not None and any_nucleus:
+            ops.sample_rows_nucleus(sampled, logits, *sample_views)
+            engine.kernels.launches += 1
+        return logits, sampled
+
+    def reset(self) -> None:
+        """After a failed step: the barrier counter and the scratch counters start over."""
+        self.barrier.zero_()
+        self.cand_done.zero_()

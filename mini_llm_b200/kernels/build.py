@@ -40,6 +40,7 @@ LIBRARIES = {
     "decode": "decode_kernels.cu",
     "gemm": "gemm_tcgen05.cu",
     "attention": "attention_tcgen05.cu",
+    "fused": "fused_decode.cu",
 }
 
 _lock = threading.Lock()

@@ -433,3 +433,18 @@ def sample_rows_sliced(out, logits, temperature, top_p, seeds, counters, scratch
                         _ptr(seeds), _ptr(counters), values.data_ptr(), indices.data_ptr(), done.data_ptr(),
                         int(bool(any_nucleus)), _stream())
     return out
+
+
+_sample_rows_nucleus = Function("sampling", "mllm_sampling_sample_rows_nucleus", [P, P, L, I, I, P, P, P, P, P])
+
+
+def sample_rows_nucleus(out, logits, temperature, top_p, seeds, counters):
+    """Draw only the rows with a nucleus cut (temperature > 0, top_p < 1); the rest of ``out`` stays."""
+    _check(out, "sample_rows.out", torch.int32, 1)
+    _check(logits, "sample_rows.logits", torch.float32, 2)
+    _check(temperature, "sample_rows.temperature", torch.float32, 1)
+    _check(top_p, "sample_rows.top_p", torch.float32, 1)
+    r, vocab = logits.shape
+    _sample_rows_nucleus(out.data_ptr(), logits.data_ptr(), logits.stride(0), r, vocab, temperature.data_ptr(),
+                         top_p.data_ptr(), _ptr(seeds), _ptr(counters), _stream())
+    return out

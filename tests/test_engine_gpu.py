@@ -196,3 +196,42 @@ def test_trace_run_program(folders, tmp_path, dtype):
             atol = F32_ATOL if dtype == "float32" else bf16_atol(expected)
             assert np.abs(row - expected[position]).max() <= atol, (step, name, position)
     assert not (out / "77.f32").exists()
+
+
+def test_fused_decode_step_agrees_with_the_part_by_part_path(folders):
+    """Steps of up to 16 single tokens of a plain pre-norm stack run as one persistent kernel.
+    It must be in use for such a model, give the part-by-part path's logits (bfloat16
+    rounding apart), and leave every other step to the generic path."""
+    from mini_llm_b200.engine import Engine, SamplingParams, StepEntry
+    key = "C"                                            # head size 32: the fused kernel takes it
+    vocab = CONFIGS[key]["vocab_size"]
+    fused = Engine(folders[key], dtype="bfloat16", page_size=16, cache_tokens=4096, max_requests=8)
+    plain = Engine(folders[key], dtype="bfloat16", page_size=16, cache_tokens=4096, max_requests=8, fused_decode=False)
+    assert fused.fused is not None and plain.fused is None
+    prompts = [random_tokens(40 + i, n, vocab) for i, n in enumerate((70, 3, 130, 17, 33))]
+    feed = np.random.default_rng(7).integers(0, vocab, (40, len(prompts)))
+    logits = {}
+    for name, engine in (("fused", fused), ("plain", plain)):
+        slots = [engine.open_request() for _ in prompts]
+        engine.step([StepEntry(s, p, []) for s, p in zip(slots, prompts)])
+        rows = []
+        for step in range(40):
+            out = engine.step([StepEntry(s, [int(feed[step, i])], [0]) for i, s in enumerate(slots)],
+                              [SamplingParams(0.7, 1.0, 11 + i, step) for i in range(len(slots))])
+            rows.append((out.cpu().numpy().copy(), engine.sampled_tokens()))
+        engine.check_status()
+        logits[name] = rows
+        assert (engine.fused is not None) == (name == "fused")
+    launches_fused, launches_plain = fused.kernels.launches, plain.kernels.launches
+    assert launches_fused < launches_plain / 3          # one kernel per step instead of dozens
+    agree = 0
+    for (a, ta), (b, tb) in zip(logits["fused"], logits["plain"]):
+        np.testing.assert_allclose(a, b, rtol=0, atol=bf16_atol(b))
+        agree += sum(x == y for x, y in zip(ta, tb))
+    assert agree >= 0.97 * 40 * len(prompts)             # the same draws, near-ties apart
+    # a model the fused kernel does not take (head size 48) runs the generic path silently
+    other = Engine(folders["B"], dtype="bfloat16", page_size=8, cache_tokens=1024, max_requests=4)
+    slot = other.open_request()
+    other.step([StepEntry(slot, random_tokens(1, 9, 1000), [8])])
+    other.step([StepEntry(slot, [5], [0])])
+    assert other.fused is None or not other.fused.takes(other.ctx)
