@@ -6,7 +6,7 @@
 //   producer warp   TMA-loads the block's keys and values page by page (the block table
 //                   names the pages) into shared memory, 128-byte swizzle;
 //   MMA warp        S = Q K^T with tcgen05.mma into tensor memory, later O_blk = P V;
-//   softmax warps   one thread per query row reads its row of S from tensor memory, applies
+//   softmax warps   two threads per query row read their halves of its row of S, apply
 //                   scale, causal (and window) mask and the online softmax in 32-bit, writes
 //                   P as bfloat16 into shared memory for the second product, and folds
 //                   O_blk into its running output row with the usual rescaling.
@@ -14,7 +14,7 @@
 // with the same online softmax (engine/src/attention.cu:71-124); its math is kept, the
 // products move to the tensor cores.
 //
-// Two CTAs fit one SM (256 TMEM columns and ~100 KB of shared memory each): while one waits
+// Two CTAs fit one SM (256 TMEM columns and ~115 KB of shared memory each): while one waits
 // for its softmax the other's products run.  Every mbarrier wait is bounded (tcgen05.cuh).
 #include <mutex>
 #include <unordered_map>
@@ -28,8 +28,15 @@ namespace {
 
 constexpr int TILE = 128;          // queries per CTA = keys per block = TMEM lanes
 constexpr int KV_STAGES = 2;
-constexpr int THREADS = 192;       // warps 0-3 softmax, 4 producer, 5 MMA
+constexpr int THREADS = 320;       // warps 0-7 softmax, 8 producer, 9 MMA
 constexpr int TMEM_COLS = 256;     // S: columns 0..127, O_blk: columns 128..128+D-1
+
+// 2^x with the hardware's approximation (about 2 ulp): its results are rounded to bfloat16.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 struct AttentionParams {
     bf16* out;                     // [T, ld_out]
@@ -45,7 +52,7 @@ struct AttentionParams {
 };
 
 template <int D>
-__global__ void __launch_bounds__(THREADS, 2)
+__global__ void __launch_bounds__(THREADS, D <= 64 ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const AttentionParams p) {
     constexpr int DB = D / 64;                     // 64-column blocks of the head size
@@ -71,6 +78,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     uint64_t* o_ready = p_ready + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + 1);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // the halves' maxima of each row [2][128]; bfloat16 is enough (both halves read the same
+    // rounded values, and the maximum only anchors the exponentials) and all that fits
+    bf16* row_max = reinterpret_cast<bf16*>(tmem_slot + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* tile = p.tiles + 4 * blockIdx.x;
@@ -95,14 +105,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) tmem_alloc(tmem_slot, TMEM_COLS);
+    if (warp == 9) tmem_alloc(tmem_slot, TMEM_COLS);
     tcgen05_before_sync();
     __syncthreads();
     tcgen05_after_sync();
     const uint32_t tmem_s = *tmem_slot;
     const uint32_t tmem_o = tmem_s + 128;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ---- producer ----
         if (lane == 0) {
             mbar_expect_tx(q_full, DB * TILE_BYTES);
@@ -142,7 +152,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     mbar_wait(&kv_full[j % KV_STAGES], (j / KV_STAGES) & 1);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ---- MMA issue ----
         if (lane == 0) {
             const uint32_t idesc_s = make_instr_desc(TILE, TILE);
@@ -186,14 +196,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
         }
     } else {
-        // ---- softmax and output: thread r owns query row r ----
-        const int r = warp * 32 + lane;
+        // ---- softmax and output: two threads per query row, each half of the columns ----
+        // Warp w reads TMEM lanes 32 (w % 4) ..; warps 0-3 take keys 0..63 of a block and the
+        // first half of the head dims, warps 4-7 keys 64..127 and the second half.
+        const int quarter = warp & 3, half = warp >> 2;
+        const int r = quarter * 32 + lane;
         const int my_pos = pos0 + min(r, n_rows - 1);
         const int my_first = (p.window > 0 && my_pos - p.window + 1 > 0) ? my_pos - p.window + 1 : 0;
-        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-        float o[D];
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        constexpr int DH = D / 2;
+        float o[DH];
 #pragma unroll
-        for (int d = 0; d < D; d++) o[d] = 0.0f;
+        for (int d = 0; d < DH; d++) o[d] = 0.0f;
         float m = -INFINITY, l = 0.0f;
         bool ok = true;
         for (int j = 0; j < n_blocks; j++) {
@@ -201,49 +215,58 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tcgen05_after_sync();
-            const int key0 = (block_lo + j) * TILE;
-            const bool needs_mask = key0 + TILE - 1 > pos0 || key0 < my_first || (p.window > 0);
-            // pass 1: the row's maximum
-            float block_max = -INFINITY;
+            const int key0 = (block_lo + j) * TILE + half * 64;
+            // a block whose last key no query of the tile may see needs the mask; so does any window
+            const bool needs_mask = (block_lo + j) * TILE + TILE - 1 > pos0 || p.window > 0;
+            // pass 1: the maximum of this thread's half of the row, then of the whole row
+            float half_max = -INFINITY;
 #pragma unroll 1
-            for (int c = 0; c < TILE; c += 32) {
+            for (int c = 0; c < 64; c += 32) {
                 float v[32];
-                tmem_load_32(tmem_s + lane_addr + c, v);
+                tmem_load_32(tmem_s + lane_addr + half * 64 + c, v);
+                if (needs_mask) {
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    const int key = key0 + c + i;
-                    const bool seen = !needs_mask || (key <= my_pos && key >= my_first);
-                    if (seen) block_max = fmaxf(block_max, v[i]);
+                    for (int i = 0; i < 32; i++) {
+                        const int key = key0 + c + i;
+                        if (key <= my_pos && key >= my_first) half_max = fmaxf(half_max, v[i]);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) half_max = fmaxf(half_max, v[i]);
                 }
             }
+            row_max[half * 128 + r] = __float2bfloat16_rn(half_max);
+            asm volatile("bar.sync 1, 256;" ::: "memory");     // the next write comes after the barrier below
+            const float block_max = fmaxf(__bfloat162float(row_max[half * 128 + r]),
+                                          __bfloat162float(row_max[(half ^ 1) * 128 + r]));
             const float m_new = fmaxf(m, block_max * p.scale_log2);
-            const float corr = (m == -INFINITY) ? 0.0f : exp2f(m - m_new);
+            const float corr = (m == -INFINITY) ? 0.0f : fast_exp2(m - m_new);
             const float base = (m_new == -INFINITY) ? 0.0f : m_new;
-            // pass 2: probabilities, as bfloat16 into shared memory (swizzled like a TMA tile)
+            // pass 2: probabilities, as bfloat16 into shared memory (swizzled like a TMA tile);
+            // this thread's 64 keys are one 128-byte row of key block `half`
             float row_sum = 0.0f;
+            unsigned char* block = p_tile + half * TILE_BYTES + r * 128;
 #pragma unroll 1
-            for (int c = 0; c < TILE; c += 32) {
+            for (int c = 0; c < 64; c += 32) {
                 float v[32];
-                tmem_load_32(tmem_s + lane_addr + c, v);
+                tmem_load_32(tmem_s + lane_addr + half * 64 + c, v);
                 uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float e[2];
-#pragma unroll
-                    for (int u = 0; u < 2; u++) {
-                        const int key = key0 + c + i + u;
-                        const bool seen = !needs_mask || (key <= my_pos && key >= my_first);
-                        e[u] = seen ? exp2f(v[i + u] * p.scale_log2 - base) : 0.0f;
+                    float e0 = fast_exp2(v[i] * p.scale_log2 - base), e1 = fast_exp2(v[i + 1] * p.scale_log2 - base);
+                    if (needs_mask) {
+                        const int key = key0 + c + i;
+                        if (!(key <= my_pos && key >= my_first)) e0 = 0.0f;
+                        if (!(key + 1 <= my_pos && key + 1 >= my_first)) e1 = 0.0f;
                     }
-                    __nv_bfloat162 two = __floats2bfloat162_rn(e[0], e[1]);
+                    __nv_bfloat162 two = __floats2bfloat162_rn(e0, e1);
                     // the sum uses the rounded values the second product will see
                     row_sum += __low2float(two) + __high2float(two);
                     packed[i / 2] = *reinterpret_cast<uint32_t*>(&two);
                 }
-                unsigned char* block = p_tile + (c / 64) * TILE_BYTES + r * 128;
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
-                    const int chunk = ((c % 64) / 8 + q) ^ (r & 7);
+                    const int chunk = (c / 8 + q) ^ (r & 7);
                     *reinterpret_cast<uint4*>(block + chunk * 16) =
                         make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
                 }
@@ -253,17 +276,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             // hand P to the tensor core: writes visible to the async proxy, all 128 rows done
             fence_async_smem();
             tcgen05_before_sync();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, 256;" ::: "memory");
             if (threadIdx.x == 0) mbar_arrive(p_ready);
-            // fold this block's product into the running output
+            // fold this block's product into the running output (this thread's half of the dims)
             if (lane == 0) ok = mbar_wait(o_ready, j & 1) && !*failed;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tcgen05_after_sync();
 #pragma unroll
-            for (int c = 0; c < D; c += 32) {
+            for (int c = 0; c < DH; c += 32) {
                 float v[32];
-                tmem_load_32(tmem_o + lane_addr + c, v);
+                tmem_load_32(tmem_o + lane_addr + half * DH + c, v);
 #pragma unroll
                 for (int i = 0; i < 32; i++) o[c + i] = o[c + i] * corr + v[i];
             }
@@ -274,25 +297,31 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 *failed = 1;
                 atomicExch(p.status, 13);
             }
-        } else if (r < n_rows) {
-            const float inv = 1.0f / l;
-            bf16* dst = p.out + (long)(row0 + r) * p.ld_out + (long)head * D;
+        } else {
+            // the two halves of a row add their sums (through the P tile, free by now)
+            float* sums = reinterpret_cast<float*>(p_tile);
+            sums[half * 128 + r] = l;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const float inv = 1.0f / (l + sums[(half ^ 1) * 128 + r]);
+            if (r < n_rows) {
+                bf16* dst = p.out + (long)(row0 + r) * p.ld_out + (long)head * D + half * DH;
 #pragma unroll
-            for (int d = 0; d < D; d += 8) {
-                uint32_t packed[4];
+                for (int d = 0; d < DH; d += 8) {
+                    uint32_t packed[4];
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    __nv_bfloat162 two = __floats2bfloat162_rn(o[d + 2 * i] * inv, o[d + 2 * i + 1] * inv);
-                    packed[i] = *reinterpret_cast<uint32_t*>(&two);
+                    for (int i = 0; i < 4; i++) {
+                        __nv_bfloat162 two = __floats2bfloat162_rn(o[d + 2 * i] * inv, o[d + 2 * i + 1] * inv);
+                        packed[i] = *reinterpret_cast<uint32_t*>(&two);
+                    }
+                    *reinterpret_cast<uint4*>(dst + d) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                 }
-                *reinterpret_cast<uint4*>(dst + d) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
         }
     }
 
     tcgen05_before_sync();
     __syncthreads();
-    if (warp == 5) tmem_free(tmem_s, TMEM_COLS);
+    if (warp == 9) tmem_free(tmem_s, TMEM_COLS);
 }
 
 // ---- host side -------------------------------------------------------------------------
@@ -372,7 +401,7 @@ template <int D>
 int launch(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v, const AttentionParams& p, int n_tiles,
            cudaStream_t s) {
     constexpr int DB = D / 64;
-    constexpr size_t smem = (size_t)(DB + 2 * KV_STAGES * DB + 2) * TILE * 64 * 2 + (2 * KV_STAGES + 4) * 8 + 16;
+    constexpr size_t smem = (size_t)(DB + 2 * KV_STAGES * DB + 2) * TILE * 64 * 2 + (2 * KV_STAGES + 4) * 8 + 16 + 2 * 128 * 2;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(attention_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=

@@ -45,19 +45,23 @@ struct GemmParams {
     int out_f32;
 };
 
-template <int EPI>
-__device__ __forceinline__ float finish(float v) {
-    return apply_activation<EPI>(v);
+// gelu, tanh form, with the hardware's approximate tanh (relative error about 2^-11): the
+// result is rounded to bfloat16 (2^-9) right after, and an exact tanh for every element of a
+// feed-forward product costs more SM time than the product itself.
+__device__ __forceinline__ float gelu_tanh_fast(float u) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608f * (u + 0.044715f * u * u * u)));
+    return 0.5f * u * (1.0f + t);
 }
 
 __device__ __forceinline__ float activate(float v, int epilogue) {
-    if (epilogue == EPI_GELU_TANH) return gelu_tanh_f(v);
+    if (epilogue == EPI_GELU_TANH) return gelu_tanh_fast(v);
     if (epilogue == EPI_GELU_ERF) return gelu_erf_f(v);
     return v;
 }
 
-template <int BN, int STAGES, bool SWAP>
-__global__ void __launch_bounds__(THREADS, 1)
+template <int BN, int STAGES, bool SWAP, int CTAS_PER_SM>
+__global__ void __launch_bounds__(THREADS, CTAS_PER_SM)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmParams p) {
     // map_a: the operand whose 128 rows fill the tile's rows; map_b: the operand of BN rows.
@@ -163,55 +167,66 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int r = tile_a * BM + warp * 32 + lane;          // row of map_a's operand
             const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
             if (!SWAP) {
-                // r: a row of x (token); columns: output features
-                const bool row_ok = r < p.M;
+                // Lane t of warp w holds row 32w + t of the tile.  To write whole rows with
+                // consecutive lanes on consecutive columns (coalesced, and with the bias and the
+                // old values of a residual sum read the same way), each block of 32 columns is
+                // turned through shared memory: the operand stages are free by now.
+                float* turn = reinterpret_cast<float*>(smem) + warp * (32 * 33);
+                const int row0 = tile_a * BM + warp * 32;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    float v[16];
-                    __syncwarp();                    // the TMEM load is warp-wide: rejoin first
-                    tmem_load_16(lane_base + c0, v);
-                    const int n0 = tile_b * BN + c0;
-                    if (!row_ok || n0 >= p.N) continue;
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    float v[32];
+                    __syncwarp();
+                    tmem_load_32(lane_base + c0, v);
 #pragma unroll
-                    for (int i = 0; i < 16; i++)
-                        if (p.bias != nullptr && n0 + i < p.N) v[i] += p.bias[n0 + i];
-                    const bool whole = n0 + 16 <= p.N;
+                    for (int i = 0; i < 32; i++) turn[lane * 33 + i] = v[i];
+                    __syncwarp();
+                    const int n = tile_b * BN + c0 + lane;
+                    if (tile_b * BN + c0 >= p.N) break;
+                    const bool col_ok = n < p.N;
+                    const float b = (col_ok && p.bias != nullptr) ? p.bias[n] : 0.0f;
                     if (p.epilogue == EPI_ADD) {
-                        float* o = reinterpret_cast<float*>(p.out) + (long)r * p.ldo + n0;
-                        if (whole && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+                        float* o = reinterpret_cast<float*>(p.out) + (long)row0 * p.ldo + n;
+#pragma unroll 1
+                        for (int r0 = 0; r0 < 32; r0 += 8) {
+                            float old[8];
 #pragma unroll
-                            for (int i = 0; i < 16; i += 4) {
-                                float4 old = *reinterpret_cast<float4*>(o + i);
-                                old.x += v[i]; old.y += v[i + 1]; old.z += v[i + 2]; old.w += v[i + 3];
-                                *reinterpret_cast<float4*>(o + i) = old;
-                            }
-                        } else {
-                            for (int i = 0; i < 16 && n0 + i < p.N; i++) o[i] += v[i];
+                            for (int u = 0; u < 8; u++)
+                                old[u] = (col_ok && row0 + r0 + u < p.M) ? o[(long)(r0 + u) * p.ldo] : 0.0f;
+#pragma unroll
+                            for (int u = 0; u < 8; u++)
+                                if (col_ok && row0 + r0 + u < p.M)
+                                    o[(long)(r0 + u) * p.ldo] = old[u] + turn[(r0 + u) * 33 + lane] + b;
                         }
                     } else if (p.out_f32) {
-                        float* o = reinterpret_cast<float*>(p.out) + (long)r * p.ldo + n0;
-                        if (whole && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
-#pragma unroll
-                            for (int i = 0; i < 16; i += 4)
-                                *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                        } else {
-                            for (int i = 0; i < 16 && n0 + i < p.N; i++) o[i] = v[i];
-                        }
+                        float* o = reinterpret_cast<float*>(p.out) + (long)row0 * p.ldo + n;
+#pragma unroll 4
+                        for (int r = 0; r < 32; r++)
+                            if (col_ok && row0 + r < p.M) o[(long)r * p.ldo] = turn[r * 33 + lane] + b;
                     } else {
-                        bf16* o = reinterpret_cast<bf16*>(p.out) + (long)r * p.ldo + n0;
-#pragma unroll
-                        for (int i = 0; i < 16; i++) v[i] = activate(v[i], p.epilogue);
-                        if (whole && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
-                            uint32_t packed[8];
-#pragma unroll
-                            for (int i = 0; i < 8; i++) {
-                                __nv_bfloat162 two = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-                                packed[i] = *reinterpret_cast<uint32_t*>(&two);
-                            }
-                            *reinterpret_cast<uint4*>(o) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                            *reinterpret_cast<uint4*>(o + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        // bfloat16 output: when the block of 32 columns is whole and 4-byte aligned,
+                        // half a warp writes one row (two columns per lane, one 4-byte store), so an
+                        // instruction covers two rows; otherwise one column per lane.
+                        bf16* base = reinterpret_cast<bf16*>(p.out) + (long)row0 * p.ldo + tile_b * BN + c0;
+                        const bool paired = tile_b * BN + c0 + 32 <= p.N && (p.ldo & 1) == 0 &&
+                                            (reinterpret_cast<uintptr_t>(base) & 3) == 0;
+                        if (paired) {
+                            const int half = lane >> 4, c = (lane & 15) * 2;
+                            const float b0 = p.bias != nullptr ? p.bias[tile_b * BN + c0 + c] : 0.0f;
+                            const float b1 = p.bias != nullptr ? p.bias[tile_b * BN + c0 + c + 1] : 0.0f;
+#pragma unroll 4
+                            for (int r = half; r < 32; r += 2)
+                                if (row0 + r < p.M) {
+                                    const __nv_bfloat162 two = __floats2bfloat162_rn(
+                                        activate(turn[r * 33 + c] + b0, p.epilogue), activate(turn[r * 33 + c + 1] + b1, p.epilogue));
+                                    *reinterpret_cast<__nv_bfloat162*>(base + (long)r * p.ldo + c) = two;
+                                }
                         } else {
-                            for (int i = 0; i < 16 && n0 + i < p.N; i++) o[i] = __float2bfloat16_rn(v[i]);
+                            bf16* o = base + lane;
+#pragma unroll 4
+                            for (int r = 0; r < 32; r++)
+                                if (col_ok && row0 + r < p.M)
+                                    o[(long)r * p.ldo] = __float2bfloat16_rn(activate(turn[r * 33 + lane] + b, p.epilogue));
                         }
                     }
                 }
@@ -310,21 +325,29 @@ int tensor_map(const void* base, long rows, long cols, long ld, int box_rows, CU
     return 0;
 }
 
-template <int BN, int STAGES, bool SWAP>
+template <int BN, int STAGES, bool SWAP, int CTAS_PER_SM = 1>
 int launch(const CUtensorMap& a, const CUtensorMap& b, const GemmParams& p, dim3 grid, cudaStream_t s) {
     constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, SWAP>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, SWAP, CTAS_PER_SM>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail("gemm: cannot raise the shared memory limit");
         configured = true;
     }
-    gemm_tcgen05_kernel<BN, STAGES, SWAP><<<grid, THREADS, smem, s>>>(a, b, p);
+    gemm_tcgen05_kernel<BN, STAGES, SWAP, CTAS_PER_SM><<<grid, THREADS, smem, s>>>(a, b, p);
     return check_launch("gemm_tcgen05_kernel");
 }
 
 }  // namespace
+
+// For measurements: force the tile width of the rows orientation (64, 128 or 256; 0: choose).
+static int g_forced_bn = 0;
+extern "C" int mllm_gemm_set_tile(int bn) {
+    if (bn != 0 && bn != 64 && bn != 128 && bn != 256) return fail("gemm: the tile width is 64, 128 or 256");
+    g_forced_bn = bn;
+    return 0;
+}
 
 // Whether the kernel takes a product: K a multiple of 8 (rows of both operands start on
 // 16-byte boundaries) and 16-byte aligned bases and row strides.
@@ -347,14 +370,29 @@ extern "C" int mllm_gemm_bf16(void* out, const void* x, const void* w, const flo
     CUtensorMap map_x, map_w;
     const bool swap = M <= 64;
     int bn = 128;
-    if (swap) bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    if (swap) {
+        bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    } else if (g_forced_bn != 0) {
+        bn = g_forced_bn;
+    } else {
+        // Tile width by how the tiles fill the SMs (measured on the layer shapes of GPT-2 small):
+        // narrow tiles when 128-wide ones would leave SMs idle, 256 columns only for many waves.
+        const long row_tiles = (M + BM - 1) / BM;
+        const long tiles_128 = row_tiles * ((N + 127) / 128), tiles_256 = row_tiles * ((N + 255) / 256);
+        int sms = 148;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+        if (tiles_128 < sms) bn = 64;
+        else if (tiles_256 >= 4 * sms) bn = 256;
+    }
     int rc = tensor_map(x, M, K, ldx, swap ? bn : BM, &map_x);
     if (rc) return rc;
     rc = tensor_map(w, N, K, K, swap ? BM : bn, &map_w);
     if (rc) return rc;
     if (!swap) {
-        dim3 grid((N + 127) / 128, (M + BM - 1) / BM);
-        return launch<128, 6, false>(map_x, map_w, p, grid, s);
+        dim3 grid((N + bn - 1) / bn, (M + BM - 1) / BM);
+        if (bn == 64) return launch<64, 4, false, 2>(map_x, map_w, p, grid, s);
+        if (bn == 256) return launch<256, 4, false, 1>(map_x, map_w, p, grid, s);
+        return launch<128, 3, false, 2>(map_x, map_w, p, grid, s);
     }
     dim3 grid((N + BM - 1) / BM, (M + bn - 1) / bn);
     if (bn == 16) return launch<16, 8, true>(map_w, map_x, p, grid, s);

@@ -49,6 +49,7 @@ class ControlBlock:
         self.device_buffer = None
         self._host = []
         self._events = []
+        self._layouts = {}
         self._turn = 0
         self.generation = 0
 
@@ -76,27 +77,37 @@ class ControlBlock:
         self.capacity = max(size, 2 * self.capacity, 4096)
         self.device_buffer = torch.zeros(self.capacity, dtype=torch.int32, device=self.device)
         self._host = [torch.zeros(self.capacity, dtype=torch.int32).pin_memory() for _ in range(2)]
-        self._events = [None, None]
+        self._host_np = [h.numpy() for h in self._host]
+        self._events = [torch.cuda.Event(), torch.cuda.Event()]
+        self._recorded = [False, False]
+        self._layouts = {}                   # (tokens, entries) -> (offsets, size, device views)
         self.generation += 1
 
     def upload(self, arrays: dict, n_tokens: int, n_items: int):
         """``arrays``: name -> numpy array (int32, or float32/int64 viewed as
         int32).  Returns name -> device view."""
-        offsets, size = self._layout(n_tokens, n_items)
-        self._ensure(size)
+        key = (n_tokens, n_items)
+        held = self._layouts.get(key)
+        if held is None:
+            offsets, size = self._layout(n_tokens, n_items)
+            self._ensure(size)               # may drop every cached layout
+            held = self._layouts[key] = (offsets, size, self._views(offsets, n_tokens, n_items))
+        offsets, size, views = held
         self._turn ^= 1
-        host, event = self._host[self._turn], self._events[self._turn]
-        if event is not None:
-            event.synchronize()              # the copy that last used this host buffer is done
-        host_np = host.numpy()
+        turn = self._turn
+        if self._recorded[turn]:
+            self._events[turn].synchronize()  # the copy that last used this host buffer is done
+        host_np = self._host_np[turn]
         for name, values in arrays.items():
             flat = np.ascontiguousarray(values).reshape(-1).view(np.int32)
             start = offsets[name]
             host_np[start:start + flat.size] = flat
-        self.device_buffer[:size].copy_(host[:size], non_blocking=True)
-        done = torch.cuda.Event()
-        done.record()
-        self._events[self._turn] = done
+        self.device_buffer[:size].copy_(self._host[turn][:size], non_blocking=True)
+        self._events[turn].record()
+        self._recorded[turn] = True
+        return views
+
+    def _views(self, offsets, n_tokens: int, n_items: int):
         views = {}
         buffer = self.device_buffer
         for name, start in offsets.items():

@@ -135,16 +135,18 @@ class Engine:
                     raise StepError(f"entry {index}: wanted place {place} is not among its {n} tokens")
 
     def _reserve(self, entries) -> None:
-        needed = [0] * len(self.cache.groups)
+        cache = self.cache
+        needed = [0] * len(cache.groups)
         for entry in entries:
-            for g, count in enumerate(self.cache.pages_needed(entry.slot, len(entry.tokens))):
+            for g, count in enumerate(cache.pages_needed(entry.slot, len(entry.tokens))):
                 needed[g] += count
-        free = self.cache.pages_free()
-        for g, count in enumerate(needed):
-            if count > free[g]:
-                raise OutOfPages(f"the step needs {count} more pages in cache group {g}, {free[g]} are free")
+        if any(needed):
+            free = cache.pages_free()
+            for g, count in enumerate(needed):
+                if count > free[g]:
+                    raise OutOfPages(f"the step needs {count} more pages in cache group {g}, {free[g]} are free")
         for entry in entries:
-            if not self.cache.reserve(entry.slot, len(entry.tokens)):
+            if not cache.reserve(entry.slot, len(entry.tokens)):
                 raise OutOfPages("page reservation failed after it was checked")   # cannot happen
 
     def step(self, entries, sampling=None):
@@ -227,10 +229,10 @@ class Engine:
         return logits
 
     def _run(self, ctx, sample_views):
-        """Decode-only steps of one shape launch the same kernels with the same arguments
-        (everything that changes lies in the control block on the device), so the second such
-        step is captured into a CUDA graph and later ones replay it: a step then costs one
-        launch on the host instead of one per kernel.  The reference removes host work per
+        """Steps of one shape (tokens, entries, wanted rows, attention tiles) launch the same
+        kernels with the same arguments (everything that changes lies in the control block on
+        the device), so the second such step is captured into a CUDA graph and later ones
+        replay it: a step then costs one launch on the host instead of one per kernel.  The reference removes host work per
         step in the same spirit, by keeping sampled tokens on the device
         (engine/src/gpt2_gpu_greedy.cu:80-119)."""
         if self.fused is not None and self.fused.takes(ctx):
@@ -242,15 +244,17 @@ class Engine:
                 # for instance no cooperative launch on this device: say so once, then run the generic path
                 print(f"[mini_llm_b200] fused decode step disabled: {error}", file=sys.stderr, flush=True)
                 self.fused = None
-        if not (self.cuda_graphs and ctx.decode_only and self.model.graph_safe):
+        if not (self.cuda_graphs and self.model.graph_safe):
             return self._forward(ctx, sample_views)
         stamp = (self.workspace.generation, self.control.generation, self.kernels.scratch_generation)
         if stamp != self._graph_stamp:
             self._graphs.clear()                      # a buffer moved: captured addresses are stale
             self._graph_stamp = stamp
-        key = (ctx.n_tokens, ctx.n_want, sample_views is not None, self._any_nucleus)
+        key = (ctx.n_tokens, ctx.n_items, ctx.n_want, ctx.n_att_tiles, sample_views is not None, self._any_nucleus)
         held = self._graphs.get(key)
         if held is None:
+            if len(self._graphs) >= 48:
+                self._graphs.clear()                  # many shapes came by: start over rather than grow
             self._graphs[key] = "warm"                # run once eagerly: every buffer gets allocated
             return self._forward(ctx, sample_views)
         if held == "warm":

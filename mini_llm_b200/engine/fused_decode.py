@@ -103,6 +103,7 @@ class FusedDecodePlan:
         self.sizes = (att.width, att.n_heads, att.n_kv_heads, att.head_size, mlp.inner, spec.vocab_size)
         device = engine.device
         self.max_blocks = engine.cache.groups[0].max_blocks
+        self._filled = {}             # step shape -> (filled parameters, logits view, sampled view)
         self.timeline = None          # set to an int64 tensor of 5 * layers + 3 entries to record phase times
         self.cand_value = torch.empty(MAX_TOKENS * self.grid, dtype=torch.float32, device=device)
         self.cand_index = torch.empty(MAX_TOKENS * self.grid, dtype=torch.int32, device=device)
@@ -117,6 +118,26 @@ class FusedDecodePlan:
 
     def run(self, ctx, block_table, sample_views, any_nucleus):
         """Run the step; returns (logits or None, sampled tokens or None)."""
+        engine = self.engine
+        sampling = sample_views is not None and ctx.n_want > 0
+        # Steps of one shape find all their arrays at the same addresses (the control block's
+        # layout depends on the step's sizes only): their parameters are filled once.
+        key = (ctx.n_tokens, ctx.n_want, sampling, self.timeline is not None,
+               engine.workspace.generation, engine.control.generation)
+        held = self._filled.get(key)
+        if held is None:
+            if len(self._filled) > 64:
+                self._filled.clear()
+            held = self._filled[key] = self._fill(ctx, block_table, sample_views if sampling else None)
+        params, logits, sampled = held
+        _step(ctypes.byref(params), torch.cuda.current_stream().cuda_stream)
+        engine.kernels.launches += 1
+        if sampled is not None and any_nucleus:
+            ops.sample_rows_nucleus(sampled, logits, *sample_views)
+            engine.kernels.launches += 1
+        return logits, sampled
+
+    def _fill(self, ctx, block_table, sample_views):
         engine = self.engine
         model = engine.model
         width, heads, kv_heads, head_size, inner, vocab = self.sizes
@@ -142,7 +163,7 @@ class FusedDecodePlan:
         params.logits = logits.data_ptr() if logits is not None else None
         params.timeline = self.timeline.data_ptr() if self.timeline is not None else None
         sampled = None
-        if sample_views is not None and ctx.n_want:
+        if sample_views is not None:
             temperature, top_p, seeds, counters = sample_views
             params.sample = 1
             params.temperature, params.top_p = temperature.data_ptr(), top_p.data_ptr()
@@ -152,12 +173,7 @@ class FusedDecodePlan:
         params.cand_value, params.cand_index = self.cand_value.data_ptr(), self.cand_index.data_ptr()
         params.cand_done, params.barrier = self.cand_done.data_ptr(), self.barrier.data_ptr()
         params.status = engine.kernels.status(engine.device).data_ptr()
-        _step(ctypes.byref(params), torch.cuda.current_stream().cuda_stream)
-        engine.kernels.launches += 1
-        if sampled is not None and any_nucleus:
-            ops.sample_rows_nucleus(sampled, logits, *sample_views)
-            engine.kernels.launches += 1
-        return logits, sampled
+        return params, logits, sampled
 
     def reset(self) -> None:
         """After a failed step: the barrier counter and the scratch counters start over."""

@@ -38,7 +38,7 @@ from typing import Callable
 from .engine import SamplingParams, StepEntry
 
 
-@dataclass
+@dataclass(eq=False)
 class Request:
     tokens: list                              # the prompt
     max_new_tokens: int | None = None
@@ -62,7 +62,7 @@ class Request:
         return self.finish_reason is not None or self.error is not None or self.cancelled
 
 
-@dataclass
+@dataclass(eq=False)
 class _Running:
     request: Request
     slot: int
