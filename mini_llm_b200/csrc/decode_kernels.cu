@@ -11,6 +11,8 @@
 //                   layer-norm prologue (the norm never round-trips through
 //                   memory), optional epilogue that scatters key and value
 //                   columns straight into the cache pages.
+//   layernorm       one warp per row, the row read once (the norm of long steps, and of
+//                   steps whose products do not take the norm on the way in).
 //   split_attention one CTA per (token, head, chunk of keys); partial softmax
 //                   states go to scratch memory and the CTA that finishes
 //                   last for its (token, head) merges them in chunk order, so
@@ -377,6 +379,79 @@ extern "C" int mllm_decode_split_attention(void* out, long ld_out, const void* q
 // Whether split_attention takes a head size (the others run the plain kernel).
 extern "C" int mllm_decode_split_attention_takes(int head_size) {
     return head_size == 16 || head_size == 32 || head_size == 64 || head_size == 128 || head_size == 256;
+}
+
+// ---------------------------------------------------------------------------
+// Layer norm, one warp per row, the row read once.  Each lane keeps up to eight chunks of
+// four values in registers (rows up to 1024 wide); a wider row is re-read for each pass.
+// Same arithmetic as the plain kernel: mean, variance of the centred values, then
+// (x - mean) / sqrt(var + eps) * gain + shift, all in 32-bit; the output is bfloat16.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+layernorm_warp_kernel(bf16* __restrict__ out, const float* __restrict__ x, const float* __restrict__ gamma,
+                      const float* __restrict__ beta, const int* __restrict__ rows, int n_rows, int width, float eps) {
+    constexpr int HELD = 8;
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const float4* row = reinterpret_cast<const float4*>(x + (long)(rows ? rows[r] : r) * width);
+    const int quads = width / 4;
+    const bool held = quads <= 32 * HELD;
+    float4 keep[HELD];
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < HELD; i++) {
+        keep[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (held && lane + 32 * i < quads) keep[i] = row[lane + 32 * i];
+        sum += keep[i].x + keep[i].y + keep[i].z + keep[i].w;
+    }
+    if (!held)
+        for (int q = lane; q < quads; q += 32) {
+            const float4 v = row[q];
+            sum += v.x + v.y + v.z + v.w;
+        }
+    const float mean = warp_sum(sum) / (float)width;
+    float sq = 0.0f;
+    if (held) {
+#pragma unroll
+        for (int i = 0; i < HELD; i++)
+            if (lane + 32 * i < quads) {
+                const float a = keep[i].x - mean, b = keep[i].y - mean, c = keep[i].z - mean, d = keep[i].w - mean;
+                sq += a * a + b * b + c * c + d * d;
+            }
+    } else {
+        for (int q = lane; q < quads; q += 32) {
+            const float4 v = row[q];
+            const float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+            sq += a * a + b * b + c * c + d * d;
+        }
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
+    auto emit = [&](int q, const float4& v) {
+        const float4 g = __ldg(reinterpret_cast<const float4*>(gamma) + q);
+        const float4 b = __ldg(reinterpret_cast<const float4*>(beta) + q);
+        __nv_bfloat162 lo = __floats2bfloat162_rn((v.x - mean) * inv * g.x + b.x, (v.y - mean) * inv * g.y + b.y);
+        __nv_bfloat162 hi = __floats2bfloat162_rn((v.z - mean) * inv * g.z + b.z, (v.w - mean) * inv * g.w + b.w);
+        *reinterpret_cast<uint2*>(out + (long)r * width + q * 4) =
+            make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    };
+    if (held) {
+#pragma unroll
+        for (int i = 0; i < HELD; i++)
+            if (lane + 32 * i < quads) emit(lane + 32 * i, keep[i]);
+    } else {
+        for (int q = lane; q < quads; q += 32) emit(q, row[q]);
+    }
+}
+
+// x fp32 [*, width] (width a multiple of 4), out bfloat16 [n_rows, width]; rows: optional gather.
+extern "C" int mllm_decode_layernorm(void* out, const float* x, const float* gamma, const float* beta, const int* rows,
+                                     int n_rows, int width, float eps, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (width <= 0 || width % 4 != 0) return fail("layernorm: the width must be a multiple of 4");
+    layernorm_warp_kernel<<<(n_rows + 7) / 8, 256, 0, (cudaStream_t)stream>>>((bf16*)out, x, gamma, beta, rows, n_rows,
+                                                                              width, eps);
+    return check_launch("layernorm_warp_kernel");
 }
 
 // ---------------------------------------------------------------------------

@@ -123,9 +123,13 @@ class Engine:
             n = len(entry.tokens)
             if n == 0:
                 raise StepError(f"entry {index}: no tokens")
-            for token in entry.tokens:
-                if not 0 <= int(token) < vocab:
-                    raise StepError(f"entry {index}: token id {token} is outside the vocabulary [0, {vocab})")
+            try:
+                ids = np.asarray(entry.tokens, dtype=np.int64)
+            except (TypeError, ValueError, OverflowError):
+                raise StepError(f"entry {index}: token ids must be integers") from None
+            if ids.ndim != 1 or int(ids.min()) < 0 or int(ids.max()) >= vocab:
+                bad = next((t for t in entry.tokens if not 0 <= int(t) < vocab), None)
+                raise StepError(f"entry {index}: token id {bad} is outside the vocabulary [0, {vocab})")
             have = self.cache.length(entry.slot)
             if have + n > self.max_positions:
                 raise StepError(f"entry {index}: {have} cached + {n} new tokens exceed the {self.max_positions} "

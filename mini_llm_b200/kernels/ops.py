@@ -448,3 +448,28 @@ def sample_rows_nucleus(out, logits, temperature, top_p, seeds, counters):
     _sample_rows_nucleus(out.data_ptr(), logits.data_ptr(), logits.stride(0), r, vocab, temperature.data_ptr(),
                          top_p.data_ptr(), _ptr(seeds), _ptr(counters), _stream())
     return out
+
+
+_layernorm_warp = Function("decode", "mllm_decode_layernorm", [P, P, P, P, P, I, I, F, P])
+
+
+def layernorm_warp(out, x, gamma, beta, eps, rows=None):
+    """``layernorm`` into bfloat16 with one warp per row, the row read once (width % 4 == 0)."""
+    _check(out, "layernorm.out", torch.bfloat16, 2)
+    _check(x, "layernorm.x", torch.float32, 2)
+    _check(gamma, "layernorm.gamma", torch.float32, 1)
+    _check(beta, "layernorm.beta", torch.float32, 1)
+    width = x.shape[1]
+    if not x.is_contiguous() or not out.is_contiguous() or width % 4 != 0:
+        raise KernelError("layernorm_warp: x and out must be contiguous, the width a multiple of 4")
+    if out.shape[1] != width or gamma.shape[0] != width or beta.shape[0] != width:
+        raise KernelError("layernorm_warp: widths do not agree")
+    if rows is not None:
+        _check(rows, "layernorm.rows", torch.int32, 1)
+        if rows.shape[0] < out.shape[0]:
+            raise KernelError("layernorm_warp: fewer row indices than output rows")
+    elif x.shape[0] < out.shape[0]:
+        raise KernelError("layernorm_warp: fewer input rows than output rows")
+    _layernorm_warp(out.data_ptr(), x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), _ptr(rows), out.shape[0], width,
+                    float(eps), _stream())
+    return out

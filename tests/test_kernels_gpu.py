@@ -514,3 +514,22 @@ def test_sliced_sampling_draws_what_the_one_block_kernel_draws(vocab):
         assert many.tolist() == one.tolist()
         assert int(scratch[2].sum()) == 0
     assert one.tolist()[3] == 17 and one.tolist()[4] == vocab // 2
+
+
+@pytest.mark.parametrize("width, eps", [(80, 1e-5), (768, 1e-6), (1600, 1e-3), (4100, 1e-5)])
+def test_layernorm_warp(width, eps):
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(width)
+    x = dev(rng.normal(3.0, 5.0, size=(37, width)), torch.float32)
+    gain, shift = dev(rng.uniform(0.5, 1.5, width), torch.float32), dev(rng.normal(0, 0.1, width), torch.float32)
+    out = torch.full((37, width), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.layernorm_warp(out, x, gain, shift, eps)
+    expected = plain.layer_norm(f64(x), f64(gain), f64(shift), eps)
+    np.testing.assert_allclose(f64(out), expected, rtol=0, atol=tol(torch.bfloat16, 4))
+    rows = [36, 0, 7, 7, 20]
+    some = torch.empty(5, width, device="cuda", dtype=torch.bfloat16)
+    ops.layernorm_warp(some, x, gain, shift, eps, dev(rows, torch.int32))
+    np.testing.assert_allclose(f64(some), expected[rows], rtol=0, atol=tol(torch.bfloat16, 4))
+    twin = torch.empty_like(out)
+    ops.layernorm(twin, x, gain, shift, eps)
+    np.testing.assert_allclose(f64(out), f64(twin), rtol=0, atol=tol(torch.bfloat16, 2))
