@@ -47,6 +47,8 @@ def parse_args():
     parser.add_argument("--layers", type=int, default=GPT2_SMALL["n_layer"])
     parser.add_argument("--plain-kernels", action="store_true")
     parser.add_argument("--no-extras", action="store_true", help="skip prefill, batch 1/64 and the end-to-end run")
+    parser.add_argument("--only-prefill", action="store_true",
+                        help="run the 2,048-token prompt step alone and print its own line (for profiling)")
     return parser.parse_args()
 
 
@@ -243,6 +245,11 @@ def run_ours(args):
                         max_tokens_per_step=2048, plain_kernels=args.plain_kernels)
         _, weight_bytes, kv_per_token = model_numbers(config, dtype_bytes)
 
+        if args.only_prefill:
+            prefill_ms = prefill_run(engine, 2, 1024, vocab, repeats=max(1, args.steps))
+            print(json.dumps({"metric": "prefill of 2,048 tokens", "ms": prefill_ms, "n_layer": config["n_layer"],
+                              "value": 2048 / (prefill_ms * 1e-3), "unit": "tokens/s"}))
+            return 0
         sampler = ClockSampler()
         sampler.start()
         ms, launches, mean_cached = decode_run(engine, args.batch, args.steps, args.warmup, context, vocab)
