@@ -47,6 +47,7 @@ def parse_args():
     parser.add_argument("--layers", type=int, default=GPT2_SMALL["n_layer"])
     parser.add_argument("--plain-kernels", action="store_true")
     parser.add_argument("--no-extras", action="store_true", help="skip prefill, batch 1/64 and the end-to-end run")
+    parser.add_argument("--page-size", type=int, default=None, help="tokens per cache page (the engine's default if not given)")
     parser.add_argument("--only-prefill", action="store_true",
                         help="run the 2,048-token prompt step alone and print its own line (for profiling)")
     return parser.parse_args()
@@ -242,7 +243,8 @@ def run_ours(args):
     with tempfile.TemporaryDirectory() as folder:
         make_model_folder(config, folder)
         engine = Engine(folder, dtype=args.dtype, max_requests=64, cache_tokens=64 * context,
-                        max_tokens_per_step=2048, plain_kernels=args.plain_kernels)
+                        max_tokens_per_step=2048, plain_kernels=args.plain_kernels,
+                        **({"page_size": args.page_size} if args.page_size else {}))
         _, weight_bytes, kv_per_token = model_numbers(config, dtype_bytes)
 
         if args.only_prefill:

@@ -50,7 +50,7 @@ class StepEntry:
 
 
 class Engine:
-    def __init__(self, model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0", page_size: int = 16,
+    def __init__(self, model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0", page_size: int = 64,
                  cache_tokens: int | None = None, n_pages: int | None = None, max_requests: int = 64,
                  max_tokens_per_step: int = 2048, plain_kernels: bool = False, cuda_graphs: bool = True,
                  fused_decode: bool = True):

@@ -25,7 +25,7 @@ class EngineOptions:
 
     dtype: str = "bfloat16"               # "bfloat16" or "float32"
     device: str = "cuda:0"
-    page_size: int = 16
+    page_size: int = 64
     cache_tokens: int | None = None       # tokens the page pool holds; default: max_sessions full contexts
     max_sessions: int = 64                # most requests live at a time
     max_tokens_per_step: int = 2048       # token budget of one batch
