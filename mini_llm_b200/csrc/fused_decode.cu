@@ -74,6 +74,9 @@ struct FusedParams {
     const unsigned long long* seeds;
     const int* counters;
     int* out_tokens;
+    int* kept;                  // null, or [n_kept]: the last sampled token of every request slot
+    const int* want_slots;      // [n_want]: the slot a sampled row is kept for, or -1
+    int n_kept;
     float* cand_value;          // [n_want, gridDim.x]
     int* cand_index;
     int* cand_done;             // one zeroed counter
@@ -704,7 +707,12 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
     prefetch_phase<NT>(p, sm, phase, 0, p.T);
     // ---- embedding: token t is written by CTA t % grid ----
     for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
-        const long trow = (long)p.token_ids[t] * p.E, prow = p.wpe ? (long)p.positions[t] * p.E : 0;
+        int token = p.token_ids[t];
+        if (token < 0) {                 // "the token this request sampled last": still on the device
+            const int slot = -1 - token;
+            token = (p.kept != nullptr && slot < p.n_kept) ? __ldcg(p.kept + slot) : 0;
+        }
+        const long trow = (long)token * p.E, prow = p.wpe ? (long)p.positions[t] * p.E : 0;
         for (int c = threadIdx.x; c < p.E / 4; c += THREADS) {
             const uint2 tv = __ldg(reinterpret_cast<const uint2*>(p.wte + trow + c * 4));
             float4 v = make_float4(__uint_as_float(tv.x << 16), __uint_as_float(tv.x & 0xffff0000u),
@@ -839,7 +847,13 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
             const int oi = __shfl_xor_sync(0xffffffffu, i, o);
             if (better_candidate(ov, oi, v, i)) { v = ov; i = oi; }
         }
-        if (lane == 0) p.out_tokens[warp] = i;
+        if (lane == 0) {
+            p.out_tokens[warp] = i;
+            if (p.kept != nullptr) {
+                const int slot = p.want_slots[warp];
+                if (slot >= 0 && slot < p.n_kept) p.kept[slot] = i;
+            }
+        }
     }
 }
 

@@ -246,3 +246,41 @@ extern "C" int mllm_sampling_sample_rows(int* out, const float* logits, long ld,
                                                                   seeds, counters, 0);
     return check_launch("sample_rows_kernel");
 }
+
+// ---------------------------------------------------------------------------
+// Feeding a request its own last sampled token without a trip to the host.
+//   keep_tokens     kept[slots[r]] = tokens[r] for every sampled row r whose slots[r] >= 0
+//   resolve_tokens  ids[t] = kept[-1 - ids[t]] for every id below zero
+// `kept` has one entry per request slot.  The reference keeps the sampled token of its
+// single-sequence greedy loop on the device in the same spirit
+// (engine/src/gpt2_gpu_greedy.cu:80-119).
+// ---------------------------------------------------------------------------
+__global__ void keep_tokens_kernel(int* __restrict__ kept, const int* __restrict__ slots,
+                                   const int* __restrict__ tokens, int n, int n_kept) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n) return;
+    const int slot = slots[r];
+    if (slot >= 0 && slot < n_kept) kept[slot] = tokens[r];
+}
+
+__global__ void resolve_tokens_kernel(int* __restrict__ ids, const int* __restrict__ kept, int n, int n_kept) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n) return;
+    const int id = ids[t];
+    if (id >= 0) return;
+    const int slot = -1 - id;
+    ids[t] = slot < n_kept ? kept[slot] : 0;
+}
+
+extern "C" int mllm_sampling_keep_tokens(int* kept, const int* slots, const int* tokens, int n, int n_kept,
+                                         void* stream) {
+    if (n <= 0) return 0;
+    keep_tokens_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(kept, slots, tokens, n, n_kept);
+    return check_launch("keep_tokens_kernel");
+}
+
+extern "C" int mllm_sampling_resolve_tokens(int* ids, const int* kept, int n, int n_kept, void* stream) {
+    if (n <= 0) return 0;
+    resolve_tokens_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(ids, kept, n, n_kept);
+    return check_launch("resolve_tokens_kernel");
+}

@@ -1,3 +1,3 @@
-from .engine import Engine, OutOfPages, SamplingParams, StepEntry, StepError
+from .engine import PREVIOUS, Engine, OutOfPages, SamplingParams, StepEntry, StepError
 
-__all__ = ["Engine", "OutOfPages", "SamplingParams", "StepEntry", "StepError"]
+__all__ = ["PREVIOUS", "Engine", "OutOfPages", "SamplingParams", "StepEntry", "StepError"]

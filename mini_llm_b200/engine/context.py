@@ -58,7 +58,8 @@ class ControlBlock:
         that steps of equal sizes find their arrays at equal addresses."""
         offsets = {}
         cursor = 0
-        for name in ("token_ids", "positions", "token_item", "want_rows", "counters", "temperature", "top_p"):
+        for name in ("token_ids", "positions", "token_item", "want_rows", "want_slots", "counters", "temperature",
+                     "top_p"):
             offsets[name] = cursor
             cursor += n_tokens
         cursor += cursor & 1                      # 8-byte alignment for the 64-bit seeds
@@ -136,7 +137,8 @@ class StepContext:
         self.n_tokens = 0
         self.n_items = 0
         self.n_want = 0
-        self.token_ids = self.positions = self.token_item = self.want_rows = None
+        self.token_ids = self.positions = self.token_item = self.want_rows = self.want_slots = None
+        self.any_previous = False     # some token id is negative: -1 - slot names that slot's last sampled token
         self.item_slots = []          # host: slot of each entry
         self.item_starts = []         # host: position of each entry's first token
         self.item_counts = []         # host: tokens of each entry

@@ -34,6 +34,11 @@ from .model import Model
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 
 
+# As a token id in ``StepEntry.tokens``: "the token this request sampled in its last sampling
+# step".  It is taken on the device, so the step can be launched before the host has read it.
+PREVIOUS = -1
+
+
 class StepError(ValueError):
     """The step's input is invalid; nothing was run and nothing changed."""
 
@@ -88,6 +93,10 @@ class Engine:
         self.ctx = StepContext(self.kernels, self.workspace, self.dtype, self.device)
         self.steps = 0
         self._sampled = None
+        self.kept_tokens = torch.zeros(self.max_requests, dtype=torch.int32, device=self.device)
+        self._kept_valid = set()              # slots whose entry of kept_tokens is a sampled token
+        self._readback = [None, None]         # per step parity: (pinned host buffer, rows, event)
+        self._turn = 0
         self._graphs = {}
         self._graph_stamp = None
         self.fused = FusedDecodePlan.build(self) if fused_decode else None
@@ -99,11 +108,13 @@ class Engine:
         slot = self.cache.open()
         if slot is not None:
             self.storage.reset_slot(slot)
+            self._kept_valid.discard(slot)
         return slot
 
     def close_request(self, slot: int) -> None:
         """Give back what the request holds."""
         self.cache.close(slot)
+        self._kept_valid.discard(slot)
 
     def cached_tokens(self, slot: int) -> int:
         return self.cache.length(slot)
@@ -127,9 +138,15 @@ class Engine:
                 ids = np.asarray(entry.tokens, dtype=np.int64)
             except (TypeError, ValueError, OverflowError):
                 raise StepError(f"entry {index}: token ids must be integers") from None
-            if ids.ndim != 1 or int(ids.min()) < 0 or int(ids.max()) >= vocab:
+            low = int(ids.min()) if ids.ndim == 1 else -2
+            if low == PREVIOUS and not (ids[1:] == PREVIOUS).any():
+                if entry.slot not in self._kept_valid:
+                    raise StepError(f"entry {index}: slot {entry.slot} has sampled no token that PREVIOUS could name")
+                low = int(ids[1:].min()) if n > 1 else 0
+            if ids.ndim != 1 or low < 0 or int(ids.max()) >= vocab:
                 bad = next((t for t in entry.tokens if not 0 <= int(t) < vocab), None)
-                raise StepError(f"entry {index}: token id {bad} is outside the vocabulary [0, {vocab})")
+                raise StepError(f"entry {index}: token id {bad} is outside the vocabulary [0, {vocab}) "
+                                f"(PREVIOUS may only be an entry's first token)")
             have = self.cache.length(entry.slot)
             if have + n > self.max_positions:
                 raise StepError(f"entry {index}: {have} cached + {n} new tokens exceed the {self.max_positions} "
@@ -171,6 +188,8 @@ class Engine:
         positions = np.empty(n_tokens, dtype=np.int32)
         token_item = np.empty(n_tokens, dtype=np.int32)
         want_rows = np.empty(n_want, dtype=np.int32)
+        want_slots = np.full(n_want, -1, dtype=np.int32)      # the entry's last wanted row is kept for its slot
+        any_previous = False
         ctx = self.ctx
         ctx.item_slots, ctx.item_starts, ctx.item_counts, ctx.item_offsets = [], [], [], []
         row = 0
@@ -179,17 +198,23 @@ class Engine:
             n = len(entry.tokens)
             start = self.cache.length(entry.slot)
             token_ids[row:row + n] = entry.tokens
+            if token_ids[row] == PREVIOUS:
+                token_ids[row] = -1 - entry.slot
+                any_previous = True
             positions[row:row + n] = np.arange(start, start + n, dtype=np.int32)
             token_item[row:row + n] = index
             for place in entry.want:
                 want_rows[w] = row + int(place)
                 w += 1
+            if entry.want:
+                want_slots[w - 1] = entry.slot
             ctx.item_slots.append(entry.slot)
             ctx.item_starts.append(start)
             ctx.item_counts.append(n)
             ctx.item_offsets.append(row)
             row += n
-        arrays = {"token_ids": token_ids, "positions": positions, "token_item": token_item, "want_rows": want_rows}
+        arrays = {"token_ids": token_ids, "positions": positions, "token_item": token_item, "want_rows": want_rows,
+                  "want_slots": want_slots}
         for group in self.cache.groups:
             if group.paged:
                 arrays[("block_table", group.index)] = group.table[ctx.item_slots]
@@ -205,6 +230,8 @@ class Engine:
         ctx.n_tokens, ctx.n_items, ctx.n_want = n_tokens, n_items, n_want
         ctx.token_ids, ctx.positions, ctx.token_item = views["token_ids"], views["positions"], views["token_item"]
         ctx.want_rows = views["want_rows"][:n_want]
+        ctx.want_slots = views["want_slots"][:n_want]
+        ctx.any_previous = any_previous
         ctx.decode_only = all(n == 1 for n in ctx.item_counts)
         ctx.att_tiles, ctx.n_att_tiles = views["att_tiles"], len(tiles)
         for view in self.storage.views:
@@ -220,15 +247,32 @@ class Engine:
         for entry in entries:
             self.cache.commit(entry.slot, len(entry.tokens))
         self.steps += 1
+        self._turn ^= 1
+        if self._sampled is not None:
+            # the sampled ids start for the host right behind the step's kernels
+            held = self._readback[self._turn]
+            if held is None or held[0].shape[0] < n_want:
+                held = (torch.empty(max(n_want, 64), dtype=torch.int32).pin_memory(), 0, torch.cuda.Event())
+            held[0][:n_want].copy_(self._sampled[:n_want], non_blocking=True)
+            held[2].record()
+            self._readback[self._turn] = (held[0], n_want, held[2])
+            for entry in entries:
+                if entry.want:
+                    self._kept_valid.add(entry.slot)
+        elif self._readback[self._turn] is not None:
+            self._readback[self._turn] = (self._readback[self._turn][0], 0, self._readback[self._turn][2])
         return logits
 
     # ---- running the model: eagerly, or as a replayed CUDA graph ---------------------------------
     def _forward(self, ctx, sample_views):
+        if ctx.any_previous:
+            self.kernels.resolve_tokens(ctx.token_ids, self.kept_tokens)
         logits = self.model.forward(ctx, self.storage.views)
         self._sampled = None
         if sample_views is not None and logits is not None:
             out = self.workspace.get("sampled", (ctx.n_want,), torch.int32)
             self.kernels.sample_rows(out, logits, *sample_views, any_nucleus=self._any_nucleus)
+            self.kernels.keep_tokens(self.kept_tokens, ctx.want_slots, out)
             self._sampled = out
         return logits
 
@@ -254,7 +298,8 @@ class Engine:
         if stamp != self._graph_stamp:
             self._graphs.clear()                      # a buffer moved: captured addresses are stale
             self._graph_stamp = stamp
-        key = (ctx.n_tokens, ctx.n_items, ctx.n_want, ctx.n_att_tiles, sample_views is not None, self._any_nucleus)
+        key = (ctx.n_tokens, ctx.n_items, ctx.n_want, ctx.n_att_tiles, sample_views is not None, self._any_nucleus,
+               ctx.any_previous)
         held = self._graphs.get(key)
         if held is None:
             if len(self._graphs) >= 48:
@@ -264,7 +309,9 @@ class Engine:
         if held == "warm":
             before = self.kernels.launches
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            # "relaxed": only this engine's kernels are launched in here, but the collector may
+            # free an older engine's pinned buffers meanwhile, whose allocator then queries events
+            with torch.cuda.graph(graph, capture_error_mode="relaxed"):
                 logits = self._forward(ctx, sample_views)
             if (self.workspace.generation, self.control.generation, self.kernels.scratch_generation) != stamp:
                 raise RuntimeError("a buffer was allocated while a step was captured")
@@ -276,11 +323,17 @@ class Engine:
         self.kernels.launches += launches
         return logits
 
-    def sampled_tokens(self) -> list:
-        """The tokens the last step sampled, on the host (waits for the step)."""
-        if self._sampled is None:
+    def sampled_tokens(self, ago: int = 0) -> list:
+        """The tokens the last step sampled (``ago=0``; waits for that step), or the step
+        before it (``ago=1``: what a caller reads after it has launched the next step, whose
+        entries name their tokens as PREVIOUS).  Older steps are not kept."""
+        if ago not in (0, 1):
+            raise ValueError("only the last two steps' tokens are kept")
+        held = self._readback[self._turn ^ ago]
+        if held is None or held[1] == 0:
             return []
-        tokens = self._sampled.cpu().tolist()
+        held[2].synchronize()
+        tokens = held[0][:held[1]].tolist()
         self._status_checks += 1
         if self._status_checks % 64 == 1:
             self.kernels.check_status()

@@ -34,7 +34,8 @@ class _Params(ctypes.Structure):
                 ("page_size", I), ("want_rows", P), ("n_want", I), ("wte", P), ("wpe", P), ("lnf_g", P), ("lnf_b", P),
                 ("eps_f", F), ("w_head", P), ("hidden", P), ("q", P), ("attn", P), ("up", P), ("logits", P),
                 ("sample", I),
-                ("temperature", P), ("top_p", P), ("seeds", P), ("counters", P), ("out_tokens", P), ("cand_value", P),
+                ("temperature", P), ("top_p", P), ("seeds", P), ("counters", P), ("out_tokens", P), ("kept", P), ("want_slots", P),
+                ("n_kept", I), ("cand_value", P),
                 ("cand_index", P), ("cand_done", P), ("barrier", P), ("status", P), ("timeline", P)]
 
 
@@ -135,6 +136,7 @@ class FusedDecodePlan:
         if sampled is not None and any_nucleus:
             ops.sample_rows_nucleus(sampled, logits, *sample_views)
             engine.kernels.launches += 1
+            engine.kernels.keep_tokens(engine.kept_tokens, ctx.want_slots, sampled)    # the kernel kept its own draw
         return logits, sampled
 
     def _fill(self, ctx, block_table, sample_views):
@@ -170,6 +172,8 @@ class FusedDecodePlan:
             params.seeds, params.counters = seeds.data_ptr(), counters.data_ptr()
             sampled = self.out_tokens[:ctx.n_want]
         params.out_tokens = self.out_tokens.data_ptr()
+        params.kept, params.n_kept = engine.kept_tokens.data_ptr(), engine.kept_tokens.shape[0]
+        params.want_slots = ctx.want_slots.data_ptr()
         params.cand_value, params.cand_index = self.cand_value.data_ptr(), self.cand_index.data_ptr()
         params.cand_done, params.barrier = self.cand_done.data_ptr(), self.barrier.data_ptr()
         params.status = engine.kernels.status(engine.device).data_ptr()

@@ -23,6 +23,16 @@ pages and mixed batches:
 Sampling uses (seed, number of tokens generated so far) per request, so a
 request's tokens depend neither on its batch nor on preemption.
 
+With ``run_ahead`` the scheduler launches a step before it has read the tokens
+of the step before: a decoding request's entry names its token as ``PREVIOUS``
+(the engine takes it on the device), and the host reads the earlier step's
+tokens while the new step runs.  What is known without the tokens decides the
+batch (lengths, "length" and "context" endings); a request that ends on its
+end-of-text token is found one step late, its extra token is dropped.  When
+pages are so short that a decoding request might have to be preempted, the
+step in flight is read first, so that a preempted request always knows all of
+its tokens.
+
 The scheduler needs from its engine: ``open_request``, ``close_request``,
 ``step(entries, sampling)``, ``sampled_tokens()``, ``max_positions`` and
 ``cache`` (a ``CacheManager``).  Tests drive it with a fake engine, as the
@@ -35,7 +45,7 @@ import collections
 from dataclasses import dataclass, field
 from typing import Callable
 
-from .engine import SamplingParams, StepEntry
+from .engine import PREVIOUS, SamplingParams, StepEntry
 
 
 @dataclass(eq=False)
@@ -69,11 +79,12 @@ class _Running:
     pending: list               # tokens not yet run: the rest of the prompt (or of a recomputation), or the last sampled token
     order: int                  # admission counter: the largest was admitted last
     decoding: bool = False      # its prompt is in the cache and it has sampled its first token
+    awaiting: bool = False      # a step that samples for it has been launched and not been read yet
 
 
 class Scheduler:
     def __init__(self, engine, max_tokens_per_step: int = 2048, max_prefill_chunk: int | None = None,
-                 max_batch: int | None = None):
+                 max_batch: int | None = None, run_ahead: bool = False):
         if max_tokens_per_step < 1:
             raise ValueError("max_tokens_per_step must be at least 1")
         self.engine = engine
@@ -84,6 +95,8 @@ class Scheduler:
         self.running: list[_Running] = []
         self._admitted = 0
         self.counters = collections.Counter()
+        self.run_ahead = bool(run_ahead)
+        self._flight = None               # (entries, owners) of the launched step whose tokens are unread
 
     # ---- requests in ------------------------------------------------------------------------
     def submit(self, request: Request) -> None:
@@ -110,46 +123,88 @@ class Scheduler:
     def step(self) -> bool:
         """Build and run one batch.  Returns False if there was nothing to do."""
         self._drop_cancelled()
+        if self._flight is not None and self._pages_are_short():
+            self._collect(0)                  # preemption may be needed: every token must be known
         try:
             entries, owners = self._build_batch()
         except Exception as error:
+            self._flight = None
             self._fail_running(str(error))
             return True
         if not entries:
+            if self._flight is not None:
+                self._collect(0)
+                return True
             return bool(self.running or self.waiting)
         sampling = []
         for running, entry in zip(owners, entries):
             if entry.want:
                 r = running.request
-                sampling.append(SamplingParams(r.temperature, r.top_p, r.seed, len(r.generated)))
+                sampling.append(SamplingParams(r.temperature, r.top_p, r.seed, len(r.generated) + running.awaiting))
         try:
             self.engine.step(entries, sampling)
-            sampled = self.engine.sampled_tokens()
         except Exception as error:          # the engine is shared: every running request is affected
+            self._flight = None
             self._fail_running(str(error))
             return True
         self.counters["steps"] += 1
         self.counters["batch_entries"] += len(entries)
         if any(len(e.tokens) == 1 and e.want for e in entries):
             self.counters["decode_steps"] += 1
-        cursor = 0
+        earlier, self._flight = self._flight, (entries, owners)
         for running, entry in zip(owners, entries):
             n = len(entry.tokens)
-            was_decoding = running.decoding
+            self.counters["decode_tokens" if running.decoding else "prefill_tokens"] += n
             running.pending = running.pending[n:]
-            self.counters["decode_tokens" if was_decoding else "prefill_tokens"] += n
             if entry.want:
-                if not was_decoding:
+                if not running.decoding:
                     self.counters["prefills"] += 1
-                self._deliver(running, int(sampled[cursor]))
-                cursor += 1
+                running.decoding = True
+                running.awaiting = True
+                running.pending = [PREVIOUS]
+        if earlier is not None:
+            self._collect(1, earlier)         # the step before, while the new one runs
+        if not self.run_ahead:
+            self._collect(0)
         self.running = [r for r in self.running if not r.request.done]
         return True
+
+    def _collect(self, ago: int, flight=None) -> None:
+        """Read a launched step's tokens and deliver them."""
+        if flight is None:
+            flight, self._flight = self._flight, None
+        entries, owners = flight
+        try:
+            sampled = self.engine.sampled_tokens(ago) if self.run_ahead else self.engine.sampled_tokens()
+        except Exception as error:
+            self._flight = None
+            self._fail_running(str(error))
+            return
+        cursor = 0
+        for running, entry in zip(owners, entries):
+            if entry.want:
+                token = int(sampled[cursor])
+                cursor += 1
+                running.awaiting = self._in_flight(running)
+                if not running.request.done:       # else: it ended a step ago; this token is dropped
+                    self._deliver(running, token)
+        self.running = [r for r in self.running if not r.request.done]
+
+    def _in_flight(self, running) -> bool:
+        return self._flight is not None and any(o is running and e.want for o, e in zip(self._flight[1], self._flight[0]))
+
+    def _pages_are_short(self) -> bool:
+        """Whether a decoding request could find no page in the next step (each needs at most
+        one new page per group)."""
+        decoding = sum(1 for r in self.running if r.decoding)
+        cache = self.engine.cache
+        free = cache.pages_free()
+        return any(g.paged and free[g.index] < decoding for g in cache.groups)
 
     def run(self, max_steps: int | None = None) -> int:
         """Iterate until nothing runs or waits; returns the number of iterations."""
         steps = 0
-        while (self.running or self.waiting) and (max_steps is None or steps < max_steps):
+        while (self.running or self.waiting or self._flight) and (max_steps is None or steps < max_steps):
             self.step()
             steps += 1
         return steps
@@ -187,6 +242,8 @@ class Scheduler:
                 self._preempt(victim)
                 if victim is running:
                     break
+            if running.awaiting and self._ends_on_count(running.request, 1):
+                continue                      # the token on its way is its last
             if running in self.running and not running.request.done and budget > 0:
                 take(running, 1, True)
                 budget -= 1
@@ -268,6 +325,12 @@ class Scheduler:
         return all(not g.paged or needed[g.index] + held[g.index] <= g.pool.n_pages for g in cache.groups)
 
     # ---- requests out -----------------------------------------------------------------------
+    def _ends_on_count(self, request: Request, more: int) -> bool:
+        """Whether ``more`` further tokens end the request on "context" or "length"."""
+        count = len(request.generated) + more
+        return (len(request.tokens) + count >= self.engine.max_positions or
+                (request.max_new_tokens is not None and count >= request.max_new_tokens))
+
     def _finish_reason(self, request: Request, token: int) -> str | None:
         if request.eos_token_id is not None and token == request.eos_token_id:
             return "stop"
@@ -280,7 +343,8 @@ class Scheduler:
     def _deliver(self, running: _Running, token: int) -> None:
         request = running.request
         request.generated.append(token)
-        running.pending = [token]
+        if not self.run_ahead:
+            running.pending = [token]
         running.decoding = True
         self.counters["tokens"] += 1
         reason = self._finish_reason(request, token)
@@ -323,6 +387,7 @@ class Scheduler:
             self._fail(running.request, message)
 
     def fail_everything(self, message: str) -> None:
+        self._flight = None
         self._fail_running(message)
         while self.waiting:
             self._fail(self.waiting.popleft(), message)

@@ -32,6 +32,7 @@ class EngineOptions:
     max_prefill_chunk: int | None = None  # longest prompt portion in one batch
     plain_kernels: bool = False
     cuda_graphs: bool = True
+    run_ahead: bool = True                # launch a step before the host has read the step before it
 
 
 class LLM:
@@ -47,7 +48,7 @@ class LLM:
                              max_tokens_per_step=options.max_tokens_per_step, plain_kernels=options.plain_kernels,
                              cuda_graphs=options.cuda_graphs)
         self.scheduler = Scheduler(self.engine, options.max_tokens_per_step, options.max_prefill_chunk,
-                                   options.max_sessions)
+                                   options.max_sessions, run_ahead=options.run_ahead)
 
     @property
     def eos_token_id(self):

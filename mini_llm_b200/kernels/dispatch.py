@@ -50,6 +50,14 @@ class Kernels:
         self._status = None          # device word the tensor-core kernels report a timed-out wait in
 
     # ---- operations without a fast variant --------------------------------------------------
+    def keep_tokens(self, kept, slots, tokens):
+        self.launches += 1
+        return ops.keep_tokens(kept, slots, tokens)
+
+    def resolve_tokens(self, token_ids, kept):
+        self.launches += 1
+        return ops.resolve_tokens(token_ids, kept)
+
     def embed(self, out, token_ids, positions, table, position_table=None):
         self.launches += 1
         return ops.embed(out, token_ids, positions, table, position_table)

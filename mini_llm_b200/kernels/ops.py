@@ -473,3 +473,27 @@ def layernorm_warp(out, x, gamma, beta, eps, rows=None):
     _layernorm_warp(out.data_ptr(), x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), _ptr(rows), out.shape[0], width,
                     float(eps), _stream())
     return out
+
+
+_keep_tokens = Function("sampling", "mllm_sampling_keep_tokens", [P, P, P, I, I, P])
+_resolve_tokens = Function("sampling", "mllm_sampling_resolve_tokens", [P, P, I, I, P])
+
+
+def keep_tokens(kept, slots, tokens):
+    """kept[slots[r]] = tokens[r] for every row r with slots[r] >= 0 (all int32, on the device)."""
+    _check(kept, "keep_tokens.kept", torch.int32, 1)
+    _check(slots, "keep_tokens.slots", torch.int32, 1)
+    _check(tokens, "keep_tokens.tokens", torch.int32, 1)
+    n = tokens.shape[0]
+    if slots.shape[0] < n:
+        raise KernelError("keep_tokens: fewer slots than tokens")
+    _keep_tokens(kept.data_ptr(), slots.data_ptr(), tokens.data_ptr(), n, kept.shape[0], _stream())
+    return kept
+
+
+def resolve_tokens(token_ids, kept):
+    """token_ids[t] = kept[-1 - token_ids[t]] wherever token_ids[t] < 0 (in place)."""
+    _check(token_ids, "resolve_tokens.token_ids", torch.int32, 1)
+    _check(kept, "resolve_tokens.kept", torch.int32, 1)
+    _resolve_tokens(token_ids.data_ptr(), kept.data_ptr(), token_ids.shape[0], kept.shape[0], _stream())
+    return token_ids

@@ -235,3 +235,42 @@ def test_fused_decode_step_agrees_with_the_part_by_part_path(folders):
     other.step([StepEntry(slot, random_tokens(1, 9, 1000), [8])])
     other.step([StepEntry(slot, [5], [0])])
     assert other.fused is None or not other.fused.takes(other.ctx)
+
+
+@pytest.mark.parametrize("dtype, key", [("float32", "A"), ("bfloat16", "B"), ("bfloat16", "C")])
+def test_previous_names_the_last_sampled_token_on_the_device(folders, dtype, key):
+    """A request fed PREVIOUS gets exactly what it gets when the host reads the sampled token
+    and feeds it back: through the one-kernel decode step (C), the part-by-part path (A, B),
+    with several requests per step and as the first token of a longer entry."""
+    from mini_llm_b200.engine import PREVIOUS, SamplingParams, StepEntry, StepError
+    engine = engine_of(folders, key, dtype)
+    vocab = CONFIGS[key]["vocab_size"]
+    prompts = [random_tokens(300 + i, n, vocab) for i, n in enumerate((19, 4, 33))]
+    results = {}
+    for mode in ("host", "device"):
+        slots = [engine.open_request() for _ in prompts]
+        with pytest.raises(StepError, match="has sampled no token"):
+            engine.step([StepEntry(slots[0], [PREVIOUS], [0])])
+        engine.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)],
+                    [SamplingParams(0.9, 1.0, 50 + i, 0) for i in range(3)])
+        tokens = engine.sampled_tokens()
+        rows, drawn = [], [tokens]
+        for step in range(1, 6):
+            feed = [[PREVIOUS] if mode == "device" else [t] for t in tokens]
+            if step == 3:                                  # a longer entry that starts with the sampled token
+                feed[1] = feed[1] + [7, 11]
+            out = engine.step([StepEntry(s, f, [len(f) - 1]) for s, f in zip(slots, feed)],
+                              [SamplingParams(0.9, 1.0, 50 + i, step) for i in range(3)])
+            rows.append(out.cpu().numpy().copy())
+            tokens = engine.sampled_tokens()
+            drawn.append(tokens)
+        assert engine.sampled_tokens(ago=1) == drawn[-2]   # the step before stays readable
+        for s in slots:
+            engine.close_request(s)
+        results[mode] = (rows, drawn)
+    engine.check_status()
+    assert results["host"][1] == results["device"][1]
+    for a, b in zip(results["host"][0], results["device"][0]):
+        np.testing.assert_array_equal(a, b)
+    if key == "C":
+        assert engine.fused is not None

@@ -116,3 +116,25 @@ def test_command_line(folders):
     refused = subprocess.run([sys.executable, "-m", "mini_llm_b200.cli", "--model", folders["A"], "--device", "cpu"],
                              capture_output=True, text=True, cwd=root, timeout=600)
     assert refused.returncode != 0 and "no CPU path" in refused.stderr
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_ahead_of_the_host_changes_no_token(folders, dtype):
+    """The scheduler launches a step before it has read the last one's tokens (requests feed
+    themselves on the device).  Tokens, endings and the pages given back are those of the
+    plain loop: with stop tokens found a step late, prompts in portions and sampling."""
+    from mini_llm_b200.generate import LLM
+    prompts = [random_tokens(60 + i, n, 1000) for i, n in enumerate((3, 21, 9, 40, 14, 2))]
+    seeds = [5, 6, 7, 8, 9, 10]
+    runs = {}
+    for ahead in (False, True):
+        llm = LLM(folders["B"], dtype=dtype, page_size=8, max_tokens_per_step=16, max_sessions=4, run_ahead=ahead)
+        first = llm.generate(prompts, max_new_tokens=14, temperature=0.7, top_p=0.9, seed=seeds)
+        eos = first[1][5]                                # a token request 1 really draws: it must stop there
+        requests = llm.generate(prompts, max_new_tokens=14, temperature=0.7, top_p=0.9, seed=seeds, eos_token_id=eos,
+                                return_requests=True)
+        greedy = llm.generate(prompts[:3], max_new_tokens=9)
+        assert llm.engine.cache.pages_in_use() == [0] and llm.scheduler._flight is None
+        runs[ahead] = (first, [(r.generated, r.finish_reason) for r in requests], greedy)
+        assert requests[1].finish_reason == "stop" and requests[1].generated == first[1][:first[1].index(eos) + 1]
+    assert runs[True] == runs[False]

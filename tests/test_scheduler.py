@@ -295,3 +295,129 @@ def test_random_workloads_end_clean_and_batching_never_changes_tokens(seed):
         assert r.error is None and r.finish_reason in ("length", "context")
         assert r.generated == expected_tokens(r.tokens, len(r.generated))
     assert engine.cache.pages_in_use() == [0] and engine.cache.free_slots == engine.cache.max_requests
+
+
+# ---- run-ahead: a step is launched before the tokens of the step before are read -------------
+
+class RunAheadEngine(FakeEngine):
+    """A fake engine that resolves PREVIOUS from what the slot sampled last, keeps the last two
+    steps' tokens and notes the order of launches and reads."""
+
+    def __init__(self, **kwargs):
+        super().__init__(**kwargs)
+        self.kept = {}
+        self.history = [[], []]
+        self.calls = []
+
+    def open_request(self):
+        slot = super().open_request()
+        self.kept.pop(slot, None)
+        return slot
+
+    def step(self, entries, sampling=None):
+        from mini_llm_b200.engine.engine import PREVIOUS, StepEntry
+        resolved = []
+        for e in entries:
+            tokens = list(e.tokens)
+            if tokens[0] == PREVIOUS:
+                assert e.slot in self.kept, "PREVIOUS for a slot that has sampled nothing"
+                tokens[0] = self.kept[e.slot]
+            assert PREVIOUS not in tokens
+            resolved.append(StepEntry(e.slot, tokens, e.want))
+        super().step(resolved, sampling)
+        cursor = 0
+        for e in resolved:
+            if e.want:
+                self.kept[e.slot] = self._sampled[cursor]
+                cursor += 1
+        self.history = [list(self._sampled), self.history[0]]
+        self.calls.append("step")
+
+    def sampled_tokens(self, ago=0):
+        self.calls.append(f"read{ago}")
+        return self.history[ago]
+
+
+def test_run_ahead_launches_the_next_step_before_it_reads_the_last():
+    engine = RunAheadEngine()
+    s = Scheduler(engine, max_tokens_per_step=64, run_ahead=True)
+    a, b = Request(prompt(100, 5), max_new_tokens=6), Request(prompt(101, 9), max_new_tokens=4)
+    s.submit(a)
+    s.submit(b)
+    s.run()
+    assert a.generated == expected_tokens(a.tokens, 6) and b.generated == expected_tokens(b.tokens, 4)
+    assert a.finish_reason == b.finish_reason == "length"
+    # prompt step, then five decode steps each launched before the step before is read, then the last read
+    assert engine.calls == ["step"] + ["step", "read1"] * 5 + ["read0"]
+    assert engine.batches[3] == [(0, 1, True), (1, 1, True)] and engine.batches[4] == [(0, 1, True)]   # b's 4th token was its last
+    assert [(p.seed, p.counter) for p in engine.sampling] == [(0, 5)]
+    assert engine.cache.pages_in_use() == [0] and engine.cache.free_slots == 4
+
+
+def test_run_ahead_finds_the_stop_token_one_step_late_and_drops_the_extra_token():
+    engine = RunAheadEngine()
+    s = Scheduler(engine, max_tokens_per_step=64, run_ahead=True)
+    p = prompt(110, 6)
+    eos = expected_tokens(p, 3)[2]
+    seen = []
+    stops = Request(p, max_new_tokens=10, eos_token_id=eos, emit=lambda token, reason: seen.append((token, reason)))
+    other = Request(prompt(111, 4), max_new_tokens=8)
+    late = Request(prompt(112, 7), max_new_tokens=3)
+    s.submit(stops)
+    s.submit(other)
+    for _ in range(3):
+        s.step()
+    s.submit(late)                         # takes the slot the stopped request gives back
+    s.run()
+    assert stops.finish_reason == "stop" and stops.generated == expected_tokens(p, 3)
+    assert seen[-1] == (eos, "stop") and len(seen) == 3
+    assert other.generated == expected_tokens(other.tokens, 8)
+    assert late.generated == expected_tokens(late.tokens, 3)
+    assert sum(1 for b in engine.batches for slot, n, want in b if slot == 0 and n == 1) >= 3   # one step more than it needed
+    assert engine.cache.pages_in_use() == [0] and engine.cache.free_slots == 4
+
+
+def test_run_ahead_reads_first_when_pages_are_short_so_that_preemption_knows_every_token():
+    engine = RunAheadEngine(n_pages=6, page_size=4, max_requests=3)
+    s = Scheduler(engine, max_tokens_per_step=64, run_ahead=True)
+    first = Request(prompt(40, 7), max_new_tokens=12)
+    last = Request(prompt(41, 8), max_new_tokens=9)
+    s.submit(first)
+    s.submit(last)
+    s.run()
+    assert s.stats()["preemptions"] >= 1 and last.preemptions >= 1 and first.preemptions == 0
+    assert first.generated == expected_tokens(first.tokens, 12)
+    assert last.generated == expected_tokens(last.tokens, 9)
+    assert "read0" in engine.calls[:-1]
+    assert engine.cache.pages_in_use() == [0]
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_run_ahead_random_workloads_give_the_same_tokens(seed):
+    rng = random.Random(1000 + seed)
+    engine = RunAheadEngine(n_pages=rng.choice([10, 14, 24]), page_size=4, max_requests=rng.choice([2, 3, 5]),
+                            max_positions=40)
+    s = Scheduler(engine, max_tokens_per_step=rng.choice([5, 9, 32]), max_prefill_chunk=rng.choice([None, 3, 8]),
+                  run_ahead=True)
+    requests = []
+    for i in range(14):
+        p = prompt(seed * 100 + i, rng.randrange(1, 24))
+        limit = rng.randrange(1, 12)
+        eos = expected_tokens(p, limit)[rng.randrange(limit)] if rng.random() < 0.4 else None
+        requests.append(Request(p, max_new_tokens=limit, eos_token_id=eos))
+    pending = list(requests)
+    for _ in range(2000):
+        if pending and rng.random() < 0.3:
+            s.submit(pending.pop(0))
+        if not s.step() and not pending:
+            break
+        engine.cache.check()
+    assert not pending and not s.running and not s.waiting and s._flight is None
+    for r in requests:
+        assert r.error is None and r.finish_reason in ("length", "context", "stop")
+        assert r.generated == expected_tokens(r.tokens, len(r.generated))
+        if r.finish_reason == "stop":
+            assert r.generated[-1] == r.eos_token_id and r.eos_token_id not in r.generated[:-1]
+        elif r.eos_token_id is not None:
+            assert r.eos_token_id not in r.generated
+    assert engine.cache.pages_in_use() == [0] and engine.cache.free_slots == engine.cache.max_requests
