@@ -194,12 +194,16 @@ class Scheduler:
         return self._flight is not None and any(o is running and e.want for o, e in zip(self._flight[1], self._flight[0]))
 
     def _pages_are_short(self) -> bool:
-        """Whether a decoding request could find no page in the next step (each needs at most
-        one new page per group)."""
-        decoding = sum(1 for r in self.running if r.decoding)
+        """Whether the decoding requests' next tokens need more pages than are free (lengths
+        are known without the tokens: a launched step has already been committed)."""
         cache = self.engine.cache
         free = cache.pages_free()
-        return any(g.paged and free[g.index] < decoding for g in cache.groups)
+        need = [0] * len(free)
+        for running in self.running:
+            if running.decoding:
+                for g, count in enumerate(cache.pages_needed(running.slot, 1)):
+                    need[g] += count
+        return any(n > f for n, f in zip(need, free))
 
     def run(self, max_steps: int | None = None) -> int:
         """Iterate until nothing runs or waits; returns the number of iterations."""
