@@ -20,6 +20,7 @@
 // frees its tensor memory and returns.
 #include <cuda.h>
 
+#include <algorithm>
 #include <mutex>
 #include <unordered_map>
 
@@ -43,6 +44,9 @@ struct GemmParams {
     long ldo;
     int epilogue;
     int out_f32;
+    int splits;               // swapped orientation only: CTAs along K per tile (blockIdx.z)
+    float* partial;           // [tiles, splits, BN, 128] partial sums when splits > 1
+    int* counters;            // [tiles], zero between launches
 };
 
 // gelu, tanh form, with the hardware's approximate tanh (relative error about 2^-11): the
@@ -81,7 +85,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_a = SWAP ? blockIdx.x : blockIdx.y;      // which block of 128 rows of map_a
     const int tile_b = SWAP ? blockIdx.y : blockIdx.x;      // which block of BN rows of map_b
-    const int num_k = (p.K + BK - 1) / BK;
+    // k blocks of this CTA: all of them, or its share when the tile is split along K
+    const int all_k = (p.K + BK - 1) / BK;
+    const int per_split = (all_k + p.splits - 1) / p.splits;
+    const int kb_first = SWAP ? (int)blockIdx.z * per_split : 0;
+    const int num_k = SWAP ? max(0, min(all_k, kb_first + per_split) - kb_first) : all_k;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -116,8 +124,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     break;
                 }
                 mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-                tma_load_2d(stage_a + s * A_BYTES, &map_a, &full[s], kb * BK, tile_a * BM);
-                tma_load_2d(stage_b + s * B_BYTES, &map_b, &full[s], kb * BK, tile_b * BN);
+                tma_load_2d(stage_a + s * A_BYTES, &map_a, &full[s], (kb_first + kb) * BK, tile_a * BM);
+                tma_load_2d(stage_b + s * B_BYTES, &map_b, &full[s], (kb_first + kb) * BK, tile_b * BN);
                 issued = kb + 1;
             }
             if (*failed) {
@@ -157,6 +165,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         bool ok = true;
         if (lane == 0) ok = mbar_wait(accumulator_ready, 0);
         ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (SWAP && p.splits > 1) {
+            // the four warps meet at barriers below: they go on only if all of them may
+            int mine = ok && !*failed, all;
+            asm volatile("{\n\t.reg .pred q, r;\n\tsetp.ne.b32 q, %1, 0;\n\tbar.red.and.pred r, 1, 128, q;\n\t"
+                         "selp.b32 %0, 1, 0, r;\n\t}" : "=r"(all) : "r"(mine) : "memory");
+            if (!all && ok && !*failed) ok = false;
+        }
         if (!ok || *failed) {
             if (lane == 0 && !*failed) {
                 *failed = STATUS_TIMEOUT_EPILOGUE;
@@ -235,21 +250,107 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 // features of one token: coalesced.
                 const bool row_ok = r < p.N;
                 const float b = (row_ok && p.bias != nullptr) ? p.bias[r] : 0.0f;
+                auto finish = [&](int t, float x) {
+                    const long at = (long)t * p.ldo + r;
+                    if (p.epilogue == EPI_ADD) reinterpret_cast<float*>(p.out)[at] += x;
+                    else if (p.out_f32) reinterpret_cast<float*>(p.out)[at] = x;
+                    else reinterpret_cast<bf16*>(p.out)[at] = __float2bfloat16_rn(activate(x, p.epilogue));
+                };
+                if (p.splits <= 1) {
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    float v[16];
-                    __syncwarp();
-                    tmem_load_16(lane_base + c0, v);
-                    if (!row_ok) continue;
+                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                        float v[16];
+                        __syncwarp();
+                        tmem_load_16(lane_base + c0, v);
+                        if (!row_ok) continue;
+                        if (p.epilogue == EPI_ADD) {
+                            // all old values first: sixteen loads in flight instead of one at a time
+                            float* o = reinterpret_cast<float*>(p.out) + (long)(tile_b * BN + c0) * p.ldo + r;
+                            const int left = p.M - (tile_b * BN + c0);
+                            float old[16];
 #pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        const int t = tile_b * BN + c0 + i;
-                        if (t >= p.M) break;
-                        const float x = v[i] + b;
-                        const long at = (long)t * p.ldo + r;
-                        if (p.epilogue == EPI_ADD) reinterpret_cast<float*>(p.out)[at] += x;
-                        else if (p.out_f32) reinterpret_cast<float*>(p.out)[at] = x;
-                        else reinterpret_cast<bf16*>(p.out)[at] = __float2bfloat16_rn(activate(x, p.epilogue));
+                            for (int i = 0; i < 16; i++) old[i] = i < left ? o[(long)i * p.ldo] : 0.0f;
+#pragma unroll
+                            for (int i = 0; i < 16; i++)
+                                if (i < left) o[(long)i * p.ldo] = old[i] + v[i] + b;
+                            continue;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 16; i++) {
+                            const int t = tile_b * BN + c0 + i;
+                            if (t >= p.M) break;
+                            finish(t, v[i] + b);
+                        }
+                    }
+                } else {
+                    // The tile is split along K: every CTA leaves its partial sums in global
+                    // memory; the CTA that arrives last adds them in the order of the splits
+                    // (so the result does not depend on which one that is) and finishes the tile.
+                    // (the four warps agree first: one that gave up alone must not leave the others at a barrier)
+                    const int tile = tile_b * gridDim.x + tile_a;
+                    float* mine = p.partial + ((long)tile * p.splits + blockIdx.z) * (BN * BM) + warp * 32 + lane;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                        float v[16];
+                        __syncwarp();
+                        tmem_load_16(lane_base + c0, v);
+                        if (num_k == 0) {
+#pragma unroll
+                            for (int i = 0; i < 16; i++) v[i] = 0.0f;       // a split past the last k block
+                        }
+#pragma unroll
+                        for (int i = 0; i < 16; i++) __stcg(mine + (long)(c0 + i) * BM, v[i]);
+                    }
+                    __threadfence();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    int* ticket = const_cast<int*>(failed) + 1;
+                    if (threadIdx.x == 0) *ticket = atomicAdd(p.counters + tile, 1);
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (*ticket == p.splits - 1) {
+                        __threadfence();
+                        // Thread t adds four neighbouring features of tokens t/32, t/32 + 4, ...:
+                        // 16-byte loads, those of all splits and of two tokens in flight at once.
+                        const float* all = p.partial + (long)tile * p.splits * (BN * BM);
+                        const int tokens = min(BN, p.M - tile_b * BN);
+                        const int f = (threadIdx.x & 31) * 4, feature = tile_a * BM + f;
+#pragma unroll 1
+                        for (int c = threadIdx.x >> 5; c < tokens; c += 8) {
+                            float4 part[2][8];
+#pragma unroll
+                            for (int h = 0; h < 2; h++)
+#pragma unroll
+                                for (int z = 0; z < 8; z++)
+                                    part[h][z] = (z < p.splits && c + 4 * h < tokens)
+                                        ? __ldcg(reinterpret_cast<const float4*>(all + ((long)z * BN + c + 4 * h) * BM + f))
+                                        : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                            for (int h = 0; h < 2; h++) {
+                                if (c + 4 * h >= tokens) break;
+                                float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                                for (int z = 0; z < 8; z++) {
+                                    sum[0] += part[h][z].x; sum[1] += part[h][z].y;
+                                    sum[2] += part[h][z].z; sum[3] += part[h][z].w;
+                                }
+                                const int t = tile_b * BN + c + 4 * h;
+                                float old[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                                if (p.epilogue == EPI_ADD) {
+#pragma unroll
+                                    for (int u = 0; u < 4; u++)
+                                        if (feature + u < p.N)
+                                            old[u] = reinterpret_cast<const float*>(p.out)[(long)t * p.ldo + feature + u];
+                                }
+#pragma unroll
+                                for (int u = 0; u < 4; u++) {
+                                    if (feature + u >= p.N) break;
+                                    const float x = sum[u] + (p.bias != nullptr ? p.bias[feature + u] : 0.0f);
+                                    const long at = (long)t * p.ldo + feature + u;
+                                    if (p.epilogue == EPI_ADD || p.out_f32) reinterpret_cast<float*>(p.out)[at] = old[u] + x;
+                                    else reinterpret_cast<bf16*>(p.out)[at] = __float2bfloat16_rn(activate(x, p.epilogue));
+                                }
+                            }
+                        }
+                        if (threadIdx.x == 0) p.counters[tile] = 0;      // ready for the next launch
                     }
                 }
             }
@@ -327,7 +428,7 @@ int tensor_map(const void* base, long rows, long cols, long ld, int box_rows, CU
 
 template <int BN, int STAGES, bool SWAP, int CTAS_PER_SM = 1>
 int launch(const CUtensorMap& a, const CUtensorMap& b, const GemmParams& p, dim3 grid, cudaStream_t s) {
-    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;   // barriers, TMEM slot, flag, ticket
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, SWAP, CTAS_PER_SM>,
@@ -359,14 +460,18 @@ extern "C" int mllm_gemm_takes(long K, long ldx, const void* x, const void* w) {
 // out[M, N] = epilogue(x[M, K] w[N, K]^T + bias).  x, w bf16 (K contiguous; x with row stride
 // ldx); out bf16, or fp32 with out_f32 or the residual epilogue.  status: a device int that
 // must be zero; a non-zero value afterwards means a bounded wait inside the kernel ran out.
+// scratch / counters (may be null): fp32 room for partial sums and zeroed ints (one per tile;
+// the kernel leaves them zero) that let a product of few tokens be split along K; a tile
+// needs splits x 64 x 128 floats, and as many tiles are split as fit.
 extern "C" int mllm_gemm_bf16(void* out, const void* x, const void* w, const float* bias, int M, int N, int K,
-                              long ldx, long ldo, int epilogue, int out_f32, int* status, void* stream) {
+                              long ldx, long ldo, int epilogue, int out_f32, int* status, float* scratch,
+                              long scratch_floats, int* counters, int n_counters, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (!mllm_gemm_takes(K, ldx, x, w)) return fail("gemm: K and the row stride of x must be multiples of 8, bases 16-byte aligned");
     if (epilogue == EPI_ADD && !out_f32) return fail("gemm: the residual sum is kept in 32-bit");
     if (status == nullptr) return fail("gemm: a status word is required");
     cudaStream_t s = (cudaStream_t)stream;
-    GemmParams p{out, bias, status, M, N, K, ldo, epilogue, out_f32};
+    GemmParams p{out, bias, status, M, N, K, ldo, epilogue, out_f32, 1, scratch, counters};
     CUtensorMap map_x, map_w;
     const bool swap = M <= 64;
     int bn = 128;
@@ -395,6 +500,23 @@ extern "C" int mllm_gemm_bf16(void* out, const void* x, const void* w, const flo
         return launch<128, 3, false, 2>(map_x, map_w, p, grid, s);
     }
     dim3 grid((N + BM - 1) / BM, (M + bn - 1) / bn);
+    {
+        // Few tiles: split them along K so that more SMs stream the weights (at least two k
+        // blocks per CTA, at most eight CTAs per tile: the last one adds all partial sums).
+        int sms = 148;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+        const int tiles = grid.x * grid.y, all_k = (K + BK - 1) / BK;
+        int splits = std::min(std::min(sms / tiles, all_k / 2), 8);
+        // measured: the sum at the end costs more than the split saves unless the tiles are few,
+        // K is long and the tile narrow
+        if (tiles * 16 > sms || all_k < 24 || bn > 32) splits = 1;
+        if (splits >= 2 && scratch != nullptr && counters != nullptr && tiles <= n_counters &&
+            (long)tiles * splits * bn * BM <= scratch_floats) {
+            const int per = (all_k + splits - 1) / splits;
+            p.splits = (all_k + per - 1) / per;
+            grid.z = p.splits;
+        }
+    }
     if (bn == 16) return launch<16, 8, true>(map_w, map_x, p, grid, s);
     if (bn == 32) return launch<32, 8, true>(map_w, map_x, p, grid, s);
     return launch<64, 8, true>(map_w, map_x, p, grid, s);
