@@ -207,6 +207,11 @@ extern "C" int mllm_decode_skinny_linear(const SkinnyParams* params, void* strea
     return launch_skinny<16>(p, s);
 }
 
+__device__ __forceinline__ void cp_async_16(void* smem, const void* global) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(global)
+                 : "memory");
+}
+
 // ---------------------------------------------------------------------------
 // split_attention
 // ---------------------------------------------------------------------------
@@ -238,51 +243,75 @@ split_attention_kernel(bf16* __restrict__ out, long ld_out, const bf16* __restri
 
     float qf[8], acc[8];
     unpack8(*reinterpret_cast<const uint4*>(q + (long)t * ld_q + (long)h * D + sub * 8), qf);
+    // scores are kept in units of log2(e): exp(x) = 2^(x log2 e) costs one instruction then
+    const float scale_log2 = scale * 1.4426950408889634f;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        qf[i] *= scale;
+        qf[i] *= scale_log2;
         acc[i] = 0.0f;
     }
-    float m = -INFINITY, l = 0.0f;
+    float m = -INFINITY, l = 0.0f;       // m in log2 units
     // Every lane of the warp runs the same trips (the shuffles need all of them); a lane
-    // whose key lies past the end loads nothing and skips the update.  Two keys per lane are
-    // in flight per trip.
-    for (int jb = begin + warp * KPW; jb <= end; jb += 8 * KPW) {
-        int j[2] = {jb + group, jb + group + 4 * KPW};
-        bool valid[2] = {j[0] <= end, j[1] <= end};
-        uint4 kv[2], vv[2];
+    // whose key lies past the end copies nothing and skips the update.  A trip brings two
+    // keys and values per lane; RING trips are in flight per warp (cp.async into a ring in
+    // shared memory that each lane reads back itself), so that a trip's latency (block table,
+    // then the page) is paid once per chunk and not once per trip.
+    constexpr int RING = 4;
+    __shared__ uint4 ring[RING][2][2][128];       // [trip in flight][key of the lane][K, V][thread]
+    const int first_key = begin + warp * KPW + group;
+    const int trips = (end - (begin + warp * KPW)) / (8 * KPW) + 1;      // <= 0: nothing for this warp
+    // pages of a power of two are the rule: shift and mask instead of a division per key
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
+    const long head_offset = (long)hk * D + sub * 8;
+    auto issue = [&](int trip) {
+        if (trip < trips) {
 #pragma unroll
-        for (int u = 0; u < 2; u++) {
-            kv[u] = make_uint4(0, 0, 0, 0);
-            vv[u] = make_uint4(0, 0, 0, 0);
-            if (valid[u]) {
-                int page = bt[j[u] / page_size];
-                long base = ((long)page * page_size + (j[u] % page_size)) * kv_width + (long)hk * D + sub * 8;
-                kv[u] = __ldg(reinterpret_cast<const uint4*>(k_pages + base));
-                vv[u] = __ldg(reinterpret_cast<const uint4*>(v_pages + base));
+            for (int u = 0; u < 2; u++) {
+                const int j = first_key + trip * 8 * KPW + u * 4 * KPW;
+                if (j <= end) {
+                    const int block = page_shift >= 0 ? j >> page_shift : j / page_size;
+                    const int within = page_shift >= 0 ? j & (page_size - 1) : j % page_size;
+                    const long base = ((long)bt[block] * page_size + within) * kv_width + head_offset;
+                    cp_async_16(&ring[trip % RING][u][0][threadIdx.x], k_pages + base);
+                    cp_async_16(&ring[trip % RING][u][1][threadIdx.x], v_pages + base);
+                }
             }
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    for (int i = 0; i < RING - 1; i++) issue(i);
+    for (int trip = 0; trip < trips; trip++) {
+        issue(trip + RING - 1);
+        asm volatile("cp.async.wait_group %0;" ::"n"(RING - 1) : "memory");
+        // the two keys of the trip share one rescaling of the running sums
+        float sc[2], vf[2][8];
 #pragma unroll
         for (int u = 0; u < 2; u++) {
-            float kf[8], vf[8];
-            unpack8(kv[u], kf);
-            unpack8(vv[u], vf);
-            float s = 0.0f;
+            const bool valid = first_key + trip * 8 * KPW + u * 4 * KPW <= end;
+            float kf[8];
+            unpack8(ring[trip % RING][u][0][threadIdx.x], kf);
+            unpack8(ring[trip % RING][u][1][threadIdx.x], vf[u]);
+            float dot = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 8; i++) s = fmaf(qf[i], kf[i], s);
+            for (int i = 0; i < 8; i++) dot = fmaf(qf[i], kf[i], dot);
 #pragma unroll
-            for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            if (valid[u]) {
-                float m_new = fmaxf(m, s);
-                float corr = __expf(m - m_new);
-                float e = __expf(s - m_new);
-                l = l * corr + e;
+            for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            sc[u] = valid ? dot : -INFINITY;          // what an absent key left in the ring is never used
+            if (!valid) {
 #pragma unroll
-                for (int i = 0; i < 8; i++) acc[i] = acc[i] * corr + e * vf[i];
-                m = m_new;
+                for (int i = 0; i < 8; i++) vf[u][i] = 0.0f;
             }
+        }
+        const float m_new = fmaxf(m, fmaxf(sc[0], sc[1]));
+        if (m_new != -INFINITY) {
+            const float corr = exp2f(m - m_new), e0 = exp2f(sc[0] - m_new), e1 = exp2f(sc[1] - m_new);
+            l = fmaf(l, corr, e0 + e1);
+#pragma unroll
+            for (int i = 0; i < 8; i++) acc[i] = fmaf(acc[i], corr, fmaf(e0, vf[0][i], e1 * vf[1][i]));
+            m = m_new;
         }
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 
     // merge the key groups of a warp, then the four warps, always in the same order
     __shared__ float sm_m[4][KPW];
@@ -304,7 +333,7 @@ split_attention_kernel(bf16* __restrict__ out, long ld_out, const bf16* __restri
         for (int w = 0; w < 4; w++)
             for (int g = 0; g < KPW; g++) {
                 float mg = sm_m[w][g];
-                if (mg != -INFINITY) o += sm_acc[w][g][d] * __expf(mg - big);
+                if (mg != -INFINITY) o += sm_acc[w][g][d] * exp2f(mg - big);
             }
         part_acc[cell * D + d] = o;
     }
@@ -313,7 +342,7 @@ split_attention_kernel(bf16* __restrict__ out, long ld_out, const bf16* __restri
         for (int w = 0; w < 4; w++)
             for (int g = 0; g < KPW; g++) {
                 float mg = sm_m[w][g];
-                if (mg != -INFINITY) total += sm_l[w][g] * __expf(mg - big);
+                if (mg != -INFINITY) total += sm_l[w][g] * exp2f(mg - big);
             }
         part_ml[cell * 2] = big;
         part_ml[cell * 2 + 1] = total;
@@ -336,11 +365,11 @@ split_attention_kernel(bf16* __restrict__ out, long ld_out, const bf16* __restri
     for (int cc = c_first; cc <= c_last; cc++) top = fmaxf(top, __ldcg(part_ml + (first + cc) * 2));
     float denom = 0.0f;
     for (int cc = c_first; cc <= c_last; cc++)
-        denom += __ldcg(part_ml + (first + cc) * 2 + 1) * __expf(__ldcg(part_ml + (first + cc) * 2) - top);
+        denom += __ldcg(part_ml + (first + cc) * 2 + 1) * exp2f(__ldcg(part_ml + (first + cc) * 2) - top);
     for (int d = threadIdx.x; d < D; d += 128) {
         float o = 0.0f;
         for (int cc = c_first; cc <= c_last; cc++)
-            o += __ldcg(part_acc + (first + cc) * D + d) * __expf(__ldcg(part_ml + (first + cc) * 2) - top);
+            o += __ldcg(part_acc + (first + cc) * D + d) * exp2f(__ldcg(part_ml + (first + cc) * 2) - top);
         out[(long)t * ld_out + (long)h * D + d] = __float2bfloat16_rn(o / denom);
     }
 }

@@ -33,7 +33,7 @@ namespace {
 
 constexpr int BM = 128;             // tile rows = TMEM lanes
 constexpr int BK = 64;              // 64 bf16 = 128 bytes = one swizzle row
-constexpr int THREADS = 192;        // warps 0-3 epilogue, 4 producer, 5 MMA
+constexpr int THREADS = 320;        // warps 0-7 epilogue, 8 producer, 9 MMA
 enum { STATUS_OK = 0, STATUS_TIMEOUT_PRODUCER = 1, STATUS_TIMEOUT_MMA = 2, STATUS_TIMEOUT_EPILOGUE = 3 };
 
 struct GemmParams {
@@ -47,6 +47,15 @@ struct GemmParams {
     int splits;               // swapped orientation only: CTAs along K per tile (blockIdx.z)
     float* partial;           // [tiles, splits, BN, 128] partial sums when splits > 1
     int* counters;            // [tiles], zero between launches
+    // Optional scatter of a fused query/key/value product: output features below q_width go
+    // to out [M, q_width], the next kv_width to the key pages, the rest to the value pages,
+    // each token at the cache slot its position and block table name (k_pages null: off).
+    bf16* k_pages;
+    bf16* v_pages;
+    const int* positions;
+    const int* token_item;
+    const int* block_table;
+    int max_blocks, page_size, q_width, kv_width;
 };
 
 // gelu, tanh form, with the hardware's approximate tanh (relative error about 2^-11): the
@@ -62,6 +71,47 @@ __device__ __forceinline__ float activate(float v, int epilogue) {
     if (epilogue == EPI_GELU_TANH) return gelu_tanh_fast(v);
     if (epilogue == EPI_GELU_ERF) return gelu_erf_f(v);
     return v;
+}
+
+// One block of 32 rows x 32 columns, turned through shared memory (turn[r * 33 + c]), stored
+// as bfloat16 with bias and activation; row r goes to base + row_offset(r).  When the block
+// is whole and 4-byte aligned (paired), half a warp writes one row (two columns per lane, one
+// 4-byte store), so an instruction covers two rows; otherwise one column per lane.
+template <int EPI> __device__ __forceinline__ float activate_as(float v) {
+    if (EPI == EPI_GELU_TANH) return gelu_tanh_fast(v);
+    if (EPI == EPI_GELU_ERF) return gelu_erf_f(v);
+    return v;
+}
+
+template <int EPI, typename RowOffset>
+__device__ __forceinline__ void store_rows_bf16_as(const float* turn, bf16* base, RowOffset row_offset, bool paired,
+                                                   bool col_ok, int lane, int rows_left, const float* bias) {
+    if (paired) {
+        const int half = lane >> 4, c = (lane & 15) * 2;
+        const float b0 = bias != nullptr ? bias[c] : 0.0f, b1 = bias != nullptr ? bias[c + 1] : 0.0f;
+#pragma unroll 4
+        for (int r = half; r < 32; r += 2)
+            if (r < rows_left) {
+                const __nv_bfloat162 two = __floats2bfloat162_rn(activate_as<EPI>(turn[r * 33 + c] + b0),
+                                                                 activate_as<EPI>(turn[r * 33 + c + 1] + b1));
+                *reinterpret_cast<__nv_bfloat162*>(base + row_offset(r) + c) = two;
+            }
+    } else {
+        const float b = (col_ok && bias != nullptr) ? bias[lane] : 0.0f;
+#pragma unroll 4
+        for (int r = 0; r < 32; r++)
+            if (col_ok && r < rows_left)
+                base[row_offset(r) + lane] = __float2bfloat16_rn(activate_as<EPI>(turn[r * 33 + lane] + b));
+    }
+}
+
+// The activation is chosen outside the loops over the rows.
+template <typename RowOffset>
+__device__ __forceinline__ void store_rows_bf16(const float* turn, bf16* base, RowOffset row_offset, bool paired,
+                                                bool col_ok, int lane, int rows_left, const float* bias, int epilogue) {
+    if (epilogue == EPI_GELU_TANH) store_rows_bf16_as<EPI_GELU_TANH>(turn, base, row_offset, paired, col_ok, lane, rows_left, bias);
+    else if (epilogue == EPI_GELU_ERF) store_rows_bf16_as<EPI_GELU_ERF>(turn, base, row_offset, paired, col_ok, lane, rows_left, bias);
+    else store_rows_bf16_as<EPI_STORE>(turn, base, row_offset, paired, col_ok, lane, rows_left, bias);
 }
 
 template <int BN, int STAGES, bool SWAP, int CTAS_PER_SM>
@@ -81,6 +131,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint64_t* accumulator_ready = empty + STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accumulator_ready + 1);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // element offset of each of the tile's tokens in the cache pages (scatter only)
+    long* kv_off = reinterpret_cast<long*>(smem + STAGES * (A_BYTES + B_BYTES) + (2 * STAGES + 1) * 8 + 16);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_a = SWAP ? blockIdx.x : blockIdx.y;      // which block of 128 rows of map_a
@@ -100,7 +152,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {
+    if (warp == 9) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                      "r"(TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
@@ -110,7 +162,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ---- producer ----
         if (lane == 0) {
             int issued = 0;
@@ -135,7 +187,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     mbar_wait(&full[kb % STAGES], (kb / STAGES) & 1);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ---- MMA issue ----
         if (lane == 0) {
             const uint32_t idesc = make_instr_desc(BM, BN);
@@ -161,14 +213,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             umma_commit(accumulator_ready);      // arrives when every MMA above has finished
         }
     } else {
-        // ---- epilogue: warp w owns TMEM lanes 32w .. 32w+31 ----
+        // ---- epilogue: warps w and w + 4 own TMEM lanes 32w .. 32w+31 and split the columns ----
+        const int quarter = warp & 3, col_half = warp >> 2;
+        if (p.k_pages != nullptr) {
+            const int t = (SWAP ? tile_b * BN : tile_a * BM) + threadIdx.x;
+            if (t < p.M && threadIdx.x < (SWAP ? BN : BM)) {
+                const int pos = p.positions[t];
+                const int page = p.block_table[(long)p.token_item[t] * p.max_blocks + pos / p.page_size];
+                kv_off[threadIdx.x] = ((long)page * p.page_size + pos % p.page_size) * p.kv_width;
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+        }
         bool ok = true;
         if (lane == 0) ok = mbar_wait(accumulator_ready, 0);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (SWAP && p.splits > 1) {
             // the four warps meet at barriers below: they go on only if all of them may
             int mine = ok && !*failed, all;
-            asm volatile("{\n\t.reg .pred q, r;\n\tsetp.ne.b32 q, %1, 0;\n\tbar.red.and.pred r, 1, 128, q;\n\t"
+            asm volatile("{\n\t.reg .pred q, r;\n\tsetp.ne.b32 q, %1, 0;\n\tbar.red.and.pred r, 1, 256, q;\n\t"
                          "selp.b32 %0, 1, 0, r;\n\t}" : "=r"(all) : "r"(mine) : "memory");
             if (!all && ok && !*failed) ok = false;
         }
@@ -179,17 +241,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
         } else {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int r = tile_a * BM + warp * 32 + lane;          // row of map_a's operand
-            const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+            const int r = tile_a * BM + quarter * 32 + lane;       // row of map_a's operand
+            const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            // columns of this warp: one half of the tile (all of a tile narrower than 32)
+            constexpr int SPAN = BN >= 32 ? BN / 2 : BN;
+            const int c_first = BN >= 32 ? col_half * SPAN : 0;
+            const bool has_columns = BN >= 32 || col_half == 0;
             if (!SWAP) {
                 // Lane t of warp w holds row 32w + t of the tile.  To write whole rows with
                 // consecutive lanes on consecutive columns (coalesced, and with the bias and the
                 // old values of a residual sum read the same way), each block of 32 columns is
                 // turned through shared memory: the operand stages are free by now.
                 float* turn = reinterpret_cast<float*>(smem) + warp * (32 * 33);
-                const int row0 = tile_a * BM + warp * 32;
+                const int row0 = tile_a * BM + quarter * 32;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32) {
+                for (int c0 = c_first; c0 < c_first + SPAN; c0 += 32) {
                     float v[32];
                     __syncwarp();
                     tmem_load_32(lane_base + c0, v);
@@ -219,30 +285,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         for (int r = 0; r < 32; r++)
                             if (col_ok && row0 + r < p.M) o[(long)r * p.ldo] = turn[r * 33 + lane] + b;
                     } else {
-                        // bfloat16 output: when the block of 32 columns is whole and 4-byte aligned,
-                        // half a warp writes one row (two columns per lane, one 4-byte store), so an
-                        // instruction covers two rows; otherwise one column per lane.
-                        bf16* base = reinterpret_cast<bf16*>(p.out) + (long)row0 * p.ldo + tile_b * BN + c0;
-                        const bool paired = tile_b * BN + c0 + 32 <= p.N && (p.ldo & 1) == 0 &&
-                                            (reinterpret_cast<uintptr_t>(base) & 3) == 0;
-                        if (paired) {
-                            const int half = lane >> 4, c = (lane & 15) * 2;
-                            const float b0 = p.bias != nullptr ? p.bias[tile_b * BN + c0 + c] : 0.0f;
-                            const float b1 = p.bias != nullptr ? p.bias[tile_b * BN + c0 + c + 1] : 0.0f;
-#pragma unroll 4
-                            for (int r = half; r < 32; r += 2)
-                                if (row0 + r < p.M) {
-                                    const __nv_bfloat162 two = __floats2bfloat162_rn(
-                                        activate(turn[r * 33 + c] + b0, p.epilogue), activate(turn[r * 33 + c + 1] + b1, p.epilogue));
-                                    *reinterpret_cast<__nv_bfloat162*>(base + (long)r * p.ldo + c) = two;
-                                }
-                        } else {
-                            bf16* o = base + lane;
-#pragma unroll 4
-                            for (int r = 0; r < 32; r++)
-                                if (col_ok && row0 + r < p.M)
-                                    o[(long)r * p.ldo] = __float2bfloat16_rn(activate(turn[r * 33 + lane] + b, p.epilogue));
-                        }
+                        // bfloat16 output.  Where row r of this block of 32 columns goes: the output, or (scatter) a cache page
+                        const int n0 = tile_b * BN + c0;
+                        const int region = p.k_pages == nullptr || n0 < p.q_width ? 0 : (n0 < p.q_width + p.kv_width ? 1 : 2);
+                        bf16* const region_base = region == 0 ? reinterpret_cast<bf16*>(p.out) + (long)row0 * p.ldo + n0
+                                                  : (region == 1 ? p.k_pages + (n0 - p.q_width)
+                                                                 : p.v_pages + (n0 - p.q_width - p.kv_width));
+                        const bool paired = n0 + 32 <= p.N && (p.ldo & 1) == 0 && (p.kv_width & 1) == 0 &&
+                                            (reinterpret_cast<uintptr_t>(region_base) & 3) == 0;
+                        // the loop over the 32 rows is compiled twice: rows of the output (a fixed
+                        // stride), and cache slots (offsets from shared memory)
+                        const long ldo = p.ldo;
+                        const long* slots = kv_off + quarter * 32;
+                        if (region == 0)
+                            store_rows_bf16(turn, region_base, [ldo](int r) { return (long)r * ldo; }, paired, col_ok, lane,
+                                            p.M - row0, p.bias != nullptr ? p.bias + n0 : nullptr, p.epilogue);
+                        else
+                            store_rows_bf16(turn, region_base, [slots](int r) { return slots[r]; }, paired, col_ok, lane,
+                                            p.M - row0, p.bias != nullptr ? p.bias + n0 : nullptr, p.epilogue);
                     }
                 }
             } else {
@@ -251,6 +311,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const bool row_ok = r < p.N;
                 const float b = (row_ok && p.bias != nullptr) ? p.bias[r] : 0.0f;
                 auto finish = [&](int t, float x) {
+                    if (p.k_pages != nullptr && r >= p.q_width) {
+                        const long slot = kv_off[t - tile_b * BN];
+                        if (r < p.q_width + p.kv_width) p.k_pages[slot + r - p.q_width] = __float2bfloat16_rn(x);
+                        else p.v_pages[slot + r - p.q_width - p.kv_width] = __float2bfloat16_rn(x);
+                        return;
+                    }
                     const long at = (long)t * p.ldo + r;
                     if (p.epilogue == EPI_ADD) reinterpret_cast<float*>(p.out)[at] += x;
                     else if (p.out_f32) reinterpret_cast<float*>(p.out)[at] = x;
@@ -258,7 +324,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 };
                 if (p.splits <= 1) {
 #pragma unroll 1
-                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                    for (int c0 = c_first; has_columns && c0 < c_first + SPAN; c0 += 16) {
                         float v[16];
                         __syncwarp();
                         tmem_load_16(lane_base + c0, v);
@@ -288,9 +354,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     // (so the result does not depend on which one that is) and finishes the tile.
                     // (the four warps agree first: one that gave up alone must not leave the others at a barrier)
                     const int tile = tile_b * gridDim.x + tile_a;
-                    float* mine = p.partial + ((long)tile * p.splits + blockIdx.z) * (BN * BM) + warp * 32 + lane;
+                    float* mine = p.partial + ((long)tile * p.splits + blockIdx.z) * (BN * BM) + quarter * 32 + lane;
 #pragma unroll 1
-                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                    for (int c0 = c_first; has_columns && c0 < c_first + SPAN; c0 += 16) {
                         float v[16];
                         __syncwarp();
                         tmem_load_16(lane_base + c0, v);
@@ -302,11 +368,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         for (int i = 0; i < 16; i++) __stcg(mine + (long)(c0 + i) * BM, v[i]);
                     }
                     __threadfence();
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
                     int* ticket = const_cast<int*>(failed) + 1;
                     if (threadIdx.x == 0) *ticket = atomicAdd(p.counters + tile, 1);
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                    if (*ticket == p.splits - 1) {
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
+                    if (*ticket == p.splits - 1 && threadIdx.x < 128) {
                         __threadfence();
                         // Thread t adds four neighbouring features of tokens t/32, t/32 + 4, ...:
                         // 16-byte loads, those of all splits and of two tokens in flight at once.
@@ -359,7 +425,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
     }
 }
@@ -428,7 +494,7 @@ int tensor_map(const void* base, long rows, long cols, long ld, int box_rows, CU
 
 template <int BN, int STAGES, bool SWAP, int CTAS_PER_SM = 1>
 int launch(const CUtensorMap& a, const CUtensorMap& b, const GemmParams& p, dim3 grid, cudaStream_t s) {
-    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;   // barriers, TMEM slot, flag, ticket
+    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + BM * 8 + 1024;   // barriers, TMEM slot, flag, ticket, cache offsets
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, SWAP, CTAS_PER_SM>,
@@ -463,15 +529,41 @@ extern "C" int mllm_gemm_takes(long K, long ldx, const void* x, const void* w) {
 // scratch / counters (may be null): fp32 room for partial sums and zeroed ints (one per tile;
 // the kernel leaves them zero) that let a product of few tokens be split along K; a tile
 // needs splits x 64 x 128 floats, and as many tiles are split as fit.
-extern "C" int mllm_gemm_bf16(void* out, const void* x, const void* w, const float* bias, int M, int N, int K,
-                              long ldx, long ldo, int epilogue, int out_f32, int* status, float* scratch,
-                              long scratch_floats, int* counters, int n_counters, void* stream) {
+struct GemmScatter {
+    void* k_pages;
+    void* v_pages;
+    const int* positions;
+    const int* token_item;
+    const int* block_table;
+    int max_blocks, page_size, q_width, kv_width;
+};
+
+static int gemm_bf16(void* out, const void* x, const void* w, const float* bias, int M, int N, int K, long ldx, long ldo,
+                     int epilogue, int out_f32, int* status, float* scratch, long scratch_floats, int* counters,
+                     int n_counters, const GemmScatter* scatter, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (!mllm_gemm_takes(K, ldx, x, w)) return fail("gemm: K and the row stride of x must be multiples of 8, bases 16-byte aligned");
     if (epilogue == EPI_ADD && !out_f32) return fail("gemm: the residual sum is kept in 32-bit");
     if (status == nullptr) return fail("gemm: a status word is required");
     cudaStream_t s = (cudaStream_t)stream;
-    GemmParams p{out, bias, status, M, N, K, ldo, epilogue, out_f32, 1, scratch, counters};
+    GemmParams p{out, bias, status, M, N, K, ldo, epilogue, out_f32, 1, scratch, counters,
+                 nullptr, nullptr, nullptr, nullptr, nullptr, 0, 1, 0, 0};
+    if (scatter != nullptr) {
+        if (out_f32 || epilogue != EPI_STORE) return fail("gemm: the scatter goes with a plain bfloat16 store");
+        if (scatter->q_width % 32 != 0 || scatter->kv_width % 32 != 0 || scatter->q_width + 2 * scatter->kv_width != N ||
+            scatter->page_size <= 0)
+            return fail("gemm: the scatter needs query and key/value widths that are multiples of 32 and add up to N");
+        p.k_pages = (bf16*)scatter->k_pages;
+        p.v_pages = (bf16*)scatter->v_pages;
+        p.positions = scatter->positions;
+        p.token_item = scatter->token_item;
+        p.block_table = scatter->block_table;
+        p.max_blocks = scatter->max_blocks;
+        p.page_size = scatter->page_size;
+        p.q_width = scatter->q_width;
+        p.kv_width = scatter->kv_width;
+        scratch = nullptr;                     // a scattered product is never split along K
+    }
     CUtensorMap map_x, map_w;
     const bool swap = M <= 64;
     int bn = 128;
@@ -520,4 +612,22 @@ extern "C" int mllm_gemm_bf16(void* out, const void* x, const void* w, const flo
     if (bn == 16) return launch<16, 8, true>(map_w, map_x, p, grid, s);
     if (bn == 32) return launch<32, 8, true>(map_w, map_x, p, grid, s);
     return launch<64, 8, true>(map_w, map_x, p, grid, s);
+}
+
+extern "C" int mllm_gemm_bf16(void* out, const void* x, const void* w, const float* bias, int M, int N, int K,
+                              long ldx, long ldo, int epilogue, int out_f32, int* status, float* scratch,
+                              long scratch_floats, int* counters, int n_counters, void* stream) {
+    return gemm_bf16(out, x, w, bias, M, N, K, ldx, ldo, epilogue, out_f32, status, scratch, scratch_floats, counters,
+                     n_counters, nullptr, stream);
+}
+
+// The fused query/key/value product of a layer: out [M, q_width] gets the queries; keys and
+// values go straight to the slots of the cache pages [n_pages, page_size, kv_width] that each
+// token's position and its request's row of the block table name.
+extern "C" int mllm_gemm_bf16_qkv(void* out, const void* x, const void* w, const float* bias, int M, int N, int K,
+                                  long ldx, long ldo, int* status, void* k_pages, void* v_pages, const int* positions,
+                                  const int* token_item, const int* block_table, int max_blocks, int page_size,
+                                  int q_width, int kv_width, void* stream) {
+    GemmScatter scatter{k_pages, v_pages, positions, token_item, block_table, max_blocks, page_size, q_width, kv_width};
+    return gemm_bf16(out, x, w, bias, M, N, K, ldx, ldo, EPI_STORE, 0, status, nullptr, 0, nullptr, 0, &scatter, stream);
 }

@@ -150,6 +150,15 @@ class Kernels:
             else:
                 ops.skinny_linear(q, a, w, bias, "store", scatter=scatter)
             return q
+        if isinstance(a, DeferredNorm):
+            self.launches += 1
+            a = a.materialize(ctx)
+        if cache.writes and not self.plain_only and ops.gemm_qkv_takes(a, w, q_width, kv_width):
+            q = ctx.buffer("q", (m, q_width), ctx.act_dtype)
+            self.launches += 1
+            return ops.gemm_bf16_qkv(q, a, w, bias, self.status(ctx.device), cache.k_pages, cache.v_pages,
+                                     ctx.positions, ctx.token_item, cache.block_table, cache.page_size, q_width,
+                                     kv_width)
         qkv = ctx.buffer("qkv", (m, q_width + 2 * kv_width), ctx.act_dtype)
         self.linear(ctx, qkv, a, w, bias)
         if cache.writes:
@@ -166,7 +175,7 @@ class Kernels:
             # chunk of keys per CTA: small when there are few (token, head) pairs, so that the
             # chunks still fill the GPU
             pairs = n * n_heads
-            chunk = 64 if pairs < 64 else (128 if pairs < 256 else 256)
+            chunk = 64 if pairs < 64 else (128 if pairs < 256 else 512)
             reach = cache.block_table.shape[1] * cache.page_size
             max_chunks = -(-reach // chunk)
             acc, ml, counters = self._scratch(ctx, SPLIT_ATTENTION_MAX_ROWS * n_heads, -(-reach // 64), head_size)

@@ -365,6 +365,49 @@ def gemm_bf16(out, a, w, bias, epilogue, status, scratch=None):
     return out
 
 
+_gemm_bf16_qkv = Function("gemm", "mllm_gemm_bf16_qkv", [P, P, P, P, I, I, I, L, L, P, P, P, P, P, P, I, I, I, I, P])
+
+
+def gemm_qkv_takes(a, w, q_width, kv_width) -> bool:
+    """Whether ``gemm_bf16_qkv`` takes the product (what ``gemm_takes`` asks, and query and
+    key/value widths that are multiples of 32)."""
+    return gemm_takes(a, w) and q_width % 32 == 0 and kv_width % 32 == 0 and w.shape[0] == q_width + 2 * kv_width
+
+
+def gemm_bf16_qkv(q_out, a, w, bias, status, k_pages, v_pages, positions, token_item, block_table, page_size,
+                  q_width, kv_width):
+    """The fused query/key/value product on the tensor cores: queries into ``q_out``
+    [M, q_width]; keys and values into the cache pages, each token at the slot its position
+    and its request's block table row name (the epilogue of ``gemm_bf16`` with a scatter)."""
+    _check(a, "gemm_qkv.a", torch.bfloat16, 2)
+    _check(w, "gemm_qkv.w", torch.bfloat16, 2)
+    _check(q_out, "gemm_qkv.q_out", torch.bfloat16, 2)
+    _check(k_pages, "gemm_qkv.k_pages", torch.bfloat16)
+    _check(v_pages, "gemm_qkv.v_pages", torch.bfloat16)
+    _check(positions, "gemm_qkv.positions", torch.int32, 1)
+    _check(token_item, "gemm_qkv.token_item", torch.int32, 1)
+    _check(block_table, "gemm_qkv.block_table", torch.int32, 2)
+    _check(status, "gemm_qkv.status", torch.int32)
+    m, k = a.shape
+    n = w.shape[0]
+    if not gemm_qkv_takes(a, w, q_width, kv_width) or w.shape[1] != k:
+        raise KernelError("gemm_qkv: operands are not laid out for the tensor-core kernel with a scatter")
+    if q_out.shape[0] != m or q_out.shape[1] != q_width or q_out.stride(1) != 1:
+        raise KernelError("gemm_qkv: q_out must be [M, q_width]")
+    if not (k_pages.is_contiguous() and v_pages.is_contiguous() and block_table.is_contiguous()):
+        raise KernelError("gemm_qkv: pages and block table must be contiguous")
+    if positions.shape[0] < m or token_item.shape[0] < m:
+        raise KernelError("gemm_qkv: fewer positions than rows")
+    if bias is not None:
+        _check(bias, "gemm_qkv.bias", torch.float32, 1)
+        if bias.shape[0] != n:
+            raise KernelError("gemm_qkv: bias has another length")
+    _gemm_bf16_qkv(q_out.data_ptr(), a.data_ptr(), w.data_ptr(), _ptr(bias), m, n, k, a.stride(0), q_out.stride(0),
+                   status.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), positions.data_ptr(), token_item.data_ptr(),
+                   block_table.data_ptr(), block_table.shape[1], page_size, q_width, kv_width, _stream())
+    return q_out
+
+
 # ---- tensor-core attention for prompt portions (bfloat16) ----------------------------------------
 
 _attention_prefill = Function("attention", "mllm_attention_prefill",

@@ -570,3 +570,44 @@ def test_gemm_tcgen05_split_along_k(m, n, k, epilogue):
     assert int(status.item()) == 0 and int(scratch[1].abs().sum().item()) == 0
     np.testing.assert_array_equal(runs[0], runs[1])
     assert not np.isnan(f64(scratch[0][:16 * 128])).any()                # the split path did run
+
+
+@pytest.mark.parametrize("m, q_width, kv_width, k, page", [(300, 768, 768, 256, 16), (40, 256, 64, 128, 8),
+                                                           (130, 96, 32, 64, 64), (64, 128, 128, 512, 4),
+                                                           (17, 64, 32, 96, 16)])
+def test_gemm_tcgen05_scatters_keys_and_values_into_the_pages(m, q_width, kv_width, k, page):
+    """The fused query/key/value product: queries to their buffer, keys and values straight to
+    the cache slots that positions and block tables name; nothing else in the pages changes."""
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(m + k)
+    n = q_width + 2 * kv_width
+    a, w = dev(rng.normal(size=(m, k)), torch.bfloat16), dev(rng.normal(size=(n, k)) / math.sqrt(k), torch.bfloat16)
+    bias = dev(rng.normal(size=n), torch.float32)
+    # three requests with different starts; pages handed out in a shuffled order
+    counts = [m // 2, m // 3, m - m // 2 - m // 3]
+    starts = [5, 0, 3 * page + 1]
+    max_blocks = max(-(-(s + c) // page) for s, c in zip(starts, counts)) + 1
+    n_pages = 3 * max_blocks + 2
+    order = rng.permutation(n_pages)
+    table = np.full((3, max_blocks), -1, dtype=np.int32)
+    for item in range(3):
+        table[item] = order[item * max_blocks:(item + 1) * max_blocks]
+    positions = np.concatenate([np.arange(s, s + c) for s, c in zip(starts, counts)]).astype(np.int32)
+    token_item = np.concatenate([np.full(c, i) for i, c in enumerate(counts)]).astype(np.int32)
+    k_pages = torch.full((n_pages, page, kv_width), 7.0, device="cuda", dtype=torch.bfloat16)
+    v_pages = torch.full((n_pages, page, kv_width), -7.0, device="cuda", dtype=torch.bfloat16)
+    q = torch.full((m, q_width), float("nan"), device="cuda", dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.gemm_bf16_qkv(q, a, w, bias, status, k_pages, v_pages, dev(positions, torch.int32), dev(token_item, torch.int32),
+                      dev(table, torch.int32), page, q_width, kv_width)
+    assert int(status.item()) == 0
+    expected = f64(a) @ f64(w).T + f64(bias)
+    atol = tol(torch.bfloat16, 4)
+    np.testing.assert_allclose(f64(q), expected[:, :q_width], rtol=0, atol=atol)
+    want_k, want_v = np.full((n_pages, page, kv_width), 7.0), np.full((n_pages, page, kv_width), -7.0)
+    for t in range(m):
+        pg = table[token_item[t], positions[t] // page]
+        want_k[pg, positions[t] % page] = expected[t, q_width:q_width + kv_width]
+        want_v[pg, positions[t] % page] = expected[t, q_width + kv_width:]
+    np.testing.assert_allclose(f64(k_pages), want_k, rtol=0, atol=atol)
+    np.testing.assert_allclose(f64(v_pages), want_v, rtol=0, atol=atol)
