@@ -14,8 +14,23 @@
 // with the same online softmax (engine/src/attention.cu:71-124); its math is kept, the
 // products move to the tensor cores.
 //
-// Two CTAs fit one SM (256 TMEM columns and ~115 KB of shared memory each): while one waits
-// for its softmax the other's products run.  Every mbarrier wait is bounded (tcgen05.cuh).
+// S has two buffers in tensor memory: S of block j+1 is computed while the softmax warps work
+// on block j.  The block's output O_blk = P V is written over the S buffer that was just
+// read, and folded into the running output one block later (behind the next block's row
+// maxima), so that neither product is waited for.  Keys and values have barriers of their
+// own: the keys of block j+2 are loaded as soon as S of block j is done.
+//
+// A tile with many key blocks may be given to several CTAs ("parts"), each taking a share of
+// the blocks: the work list names part and number of parts.  A part leaves its un-normalised
+// output, maximum and sum in scratch memory; the part that arrives last adds them in the order
+// of the parts and writes the tile.  The longest CTA then has a few blocks, not all of them.
+//
+// The CTAs are persistent: two per SM (256 TMEM columns and ~115 KB of shared memory each;
+// while one waits for its softmax the other's products run), each taking the next record of
+// the work list from a counter until the list is done.  The list is sorted by falling number
+// of key blocks, so that the long tiles start first and the short ones fill the gaps; tensor
+// memory is allocated once per CTA.  Every mbarrier wait is bounded (tcgen05.cuh).
+#include <algorithm>
 #include <mutex>
 #include <unordered_map>
 
@@ -29,7 +44,7 @@ namespace {
 constexpr int TILE = 128;          // queries per CTA = keys per block = TMEM lanes
 constexpr int KV_STAGES = 2;
 constexpr int THREADS = 320;       // warps 0-7 softmax, 8 producer, 9 MMA
-constexpr int TMEM_COLS = 256;     // S: columns 0..127, O_blk: columns 128..128+D-1
+constexpr int TMEM_COLS = 256;     // two S buffers of 128 columns; O_blk of block j overwrites S of block j
 
 // 2^x with the hardware's approximation (about 2 ulp): its results are rounded to bfloat16.
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -41,7 +56,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
 struct AttentionParams {
     bf16* out;                     // [T, ld_out]
     long ld_out;
-    const int* tiles;              // per tile: item, first row, rows, position of the first row
+    const int* tiles;              // per CTA: item, first row, rows, position of the first row, part,
+                                   // parts, number of the tile among the split ones, unused
+    float* partial;                // [split tiles, heads, max_parts, 128, D + 4]: a part's output, maximum, sum, padding
+    int* counters;                 // [split tiles, heads], zero between launches
+    int max_parts;
+    int n_tiles;                   // records of the work list
+    int* work;                     // [2] zero between launches: next (record, head) to take; CTAs that are done
     const int* block_table;        // [items, max_blocks]
     int max_blocks;
     int n_heads, n_kv_heads;
@@ -71,46 +92,69 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     unsigned char* p_tile = v_stage + KV_STAGES * DB * TILE_BYTES;  // 2 blocks: keys 0..63, 64..127
     uint64_t* bars = reinterpret_cast<uint64_t*>(p_tile + 2 * TILE_BYTES);
     uint64_t* q_full = bars;
-    uint64_t* kv_full = bars + 1;                  // [KV_STAGES]
-    uint64_t* kv_empty = kv_full + KV_STAGES;      // [KV_STAGES]
-    uint64_t* s_ready = kv_empty + KV_STAGES;
-    uint64_t* p_ready = s_ready + 1;
-    uint64_t* o_ready = p_ready + 1;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + 1);
+    uint64_t* k_full = bars + 1;                   // [KV_STAGES]
+    uint64_t* k_empty = k_full + KV_STAGES;        // [KV_STAGES]
+    uint64_t* v_full = k_empty + KV_STAGES;        // [KV_STAGES]
+    uint64_t* v_empty = v_full + KV_STAGES;        // [KV_STAGES]
+    uint64_t* s_ready = v_empty + KV_STAGES;       // [2]: S of an even / odd block is in tensor memory
+    uint64_t* o_ready = s_ready + 2;               // [2]: O_blk of an even / odd block is in tensor memory
+    uint64_t* o_folded = o_ready + 2;              // [2]: every softmax warp has read that O_blk
+    uint64_t* p_ready = o_folded + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_ready + 1);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
     // the halves' maxima of each row [2][128]; bfloat16 is enough (both halves read the same
     // rounded values, and the maximum only anchors the exponentials) and all that fits
     bf16* row_max = reinterpret_cast<bf16*>(tmem_slot + 2);
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int* tile = p.tiles + 4 * blockIdx.x;
-    const int item = tile[0], row0 = tile[1], n_rows = tile[2], pos0 = tile[3];
-    const int head = blockIdx.y;
-    const int kv_head = head / (p.n_heads / p.n_kv_heads);
-    const int last_pos = pos0 + n_rows - 1;
-    const int first_key = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
-    const int block_lo = first_key / TILE, block_hi = last_pos / TILE;       // inclusive
-    const int n_blocks = block_hi - block_lo + 1;
-    const int pages_per_block = TILE / p.page_size;
+    int* next_work = reinterpret_cast<int*>(row_max + 2 * 128);
 
-    if (threadIdx.x == 0) {
-        mbar_init(q_full, 1);
-        for (int s = 0; s < KV_STAGES; s++) {
-            mbar_init(&kv_full[s], 1);
-            mbar_init(&kv_empty[s], 1);
-        }
-        mbar_init(s_ready, 1);
-        mbar_init(p_ready, 1);
-        mbar_init(o_ready, 1);
-        *failed = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pages_per_block = TILE / p.page_size;
+    if (threadIdx.x == 0) *failed = 0;
     if (warp == 9) tmem_alloc(tmem_slot, TMEM_COLS);
     tcgen05_before_sync();
     __syncthreads();
     tcgen05_after_sync();
-    const uint32_t tmem_s = *tmem_slot;
-    const uint32_t tmem_o = tmem_s + 128;
+    const uint32_t tmem_base = *tmem_slot;         // buffer b: columns 128 b ..
+    const int total_work = p.n_tiles * p.n_heads;
+
+  for (int round = 0;; round++) {
+    // ---- the next (record, head); fresh barriers for it ----
+    if (threadIdx.x == 0) {
+        *next_work = atomicAdd(p.work, 1);
+        if (round > 0)
+            for (int b = 0; b < 4 * KV_STAGES + 8; b++) mbar_inval(&bars[b]);
+        mbar_init(q_full, 1);
+        for (int s = 0; s < KV_STAGES; s++) {
+            mbar_init(&k_full[s], 1);
+            mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1);
+            mbar_init(&v_empty[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&s_ready[b], 1);
+            mbar_init(&o_ready[b], 1);
+            mbar_init(&o_folded[b], 8);            // one arrival per softmax warp
+        }
+        mbar_init(p_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const int work = *next_work;
+    if (work >= total_work || *failed) break;
+    const int* tile = p.tiles + 8 * (work / p.n_heads);
+    const int item = tile[0], row0 = tile[1], n_rows = tile[2], pos0 = tile[3];
+    const int part = tile[4], n_parts = tile[5], split_id = tile[6];
+    const int head = work % p.n_heads;
+    const int kv_head = head / (p.n_heads / p.n_kv_heads);
+    const int last_pos = pos0 + n_rows - 1;
+    const int first_key = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
+    // the key blocks of the tile, and this part's share of them (none, if a window left fewer
+    // blocks than parts)
+    const int tile_lo = first_key / TILE, tile_blocks = last_pos / TILE - tile_lo + 1;
+    const int per_part = (tile_blocks + n_parts - 1) / n_parts;
+    const int block_lo = tile_lo + part * per_part;
+    const int n_blocks = max(0, min(per_part, tile_blocks - part * per_part));
 
     if (warp == 8) {
         // ---- producer ----
@@ -119,37 +163,41 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (int db = 0; db < DB; db++)
                 tma_load_2d(q_tile + db * TILE_BYTES, &map_q, q_full, head * D + db * 64, row0);
             const int* bt = p.block_table + (long)item * p.max_blocks;
-            int issued = 0;
+            int issued_k = 0, issued_v = 0;
             for (int j = 0; j < n_blocks; j++) {
                 const int s = j % KV_STAGES;
-                if (!mbar_wait(&kv_empty[s], ((j / KV_STAGES) & 1) ^ 1) || *failed) {
-                    if (!*failed) {
-                        *failed = 1;
-                        atomicExch(p.status, 11);
-                    }
-                    break;
-                }
-                mbar_expect_tx(&kv_full[s], 2 * DB * TILE_BYTES);
+                const uint32_t parity = ((j / KV_STAGES) & 1) ^ 1;
                 const int first_page = (block_lo + j) * pages_per_block;
-                for (int g = 0; g < pages_per_block; g++) {
-                    const int index = first_page + g;
-                    // A page past the request's last one is read outside the pool: zeros.
-                    int page = (index < p.max_blocks && index * p.page_size <= last_pos) ? bt[index] : -1;
-                    if (page < 0) page = p.n_pages;
-                    const int offset = g * p.page_size * 128;           // rows of 128 bytes
-                    for (int db = 0; db < DB; db++) {
-                        tma_load_4d(k_stage + (s * DB + db) * TILE_BYTES + offset, &map_k, &kv_full[s], db * 64,
-                                    kv_head, 0, page);
-                        tma_load_4d(v_stage + (s * DB + db) * TILE_BYTES + offset, &map_v, &kv_full[s], db * 64,
-                                    kv_head, 0, page);
+                auto load = [&](unsigned char* stage, const CUtensorMap* map, uint64_t* full) {
+                    mbar_expect_tx(full, DB * TILE_BYTES);
+                    for (int g = 0; g < pages_per_block; g++) {
+                        const int index = first_page + g;
+                        // A page past the request's last one is read outside the pool: zeros.
+                        int page = (index < p.max_blocks && index * p.page_size <= last_pos) ? bt[index] : -1;
+                        if (page < 0) page = p.n_pages;
+                        const int offset = g * p.page_size * 128;           // rows of 128 bytes
+                        for (int db = 0; db < DB; db++)
+                            tma_load_4d(stage + (s * DB + db) * TILE_BYTES + offset, map, full, db * 64, kv_head, 0, page);
                     }
-                }
-                issued = j + 1;
+                };
+                if (!mbar_wait_idle(&k_empty[s], parity) || *failed) break;
+                load(k_stage, &map_k, &k_full[s]);
+                issued_k = j + 1;
+                if (!mbar_wait_idle(&v_empty[s], parity) || *failed) break;
+                load(v_stage, &map_v, &v_full[s]);
+                issued_v = j + 1;
+            }
+            if (issued_v < n_blocks && !*failed) {
+                *failed = 1;
+                atomicExch(p.status, 11);
             }
             if (*failed) {
+                // copies that were issued still land in shared memory: none may be in flight at the end
                 mbar_wait(q_full, 0);
-                for (int j = max(0, issued - KV_STAGES); j < issued; j++)
-                    mbar_wait(&kv_full[j % KV_STAGES], (j / KV_STAGES) & 1);
+                for (int j = max(0, issued_k - KV_STAGES); j < issued_k; j++)
+                    mbar_wait(&k_full[j % KV_STAGES], (j / KV_STAGES) & 1);
+                for (int j = max(0, issued_v - KV_STAGES); j < issued_v; j++)
+                    mbar_wait(&v_full[j % KV_STAGES], (j / KV_STAGES) & 1);
             }
         }
     } else if (warp == 9) {
@@ -165,15 +213,25 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 for (int kk = 0; kk < D / UMMA_K; kk++) {
                     const uint64_t a = make_smem_desc(smem_u32(q_tile + (kk / 4) * TILE_BYTES)) + 2 * (kk % 4);
                     const uint64_t b = make_smem_desc(smem_u32(k_stage + (s * DB + kk / 4) * TILE_BYTES)) + 2 * (kk % 4);
-                    umma(tmem_s, a, b, idesc_s, kk > 0 ? 1u : 0u);
+                    umma(tmem_base + 128 * (j & 1), a, b, idesc_s, kk > 0 ? 1u : 0u);
                 }
-                umma_commit(s_ready);
+                umma_commit(&s_ready[j & 1]);
+                umma_commit(&k_empty[s]);
             };
-            if (ok && n_blocks > 0) ok = mbar_wait(&kv_full[0], 0);
-            if (ok) issue_s(0);
+            if (ok && n_blocks > 0) ok = mbar_wait(&k_full[0], 0);
+            if (ok && n_blocks > 0) issue_s(0);
             for (int j = 0; ok && j < n_blocks; j++) {
                 const int s = j % KV_STAGES;
-                ok = mbar_wait(p_ready, j & 1) && !*failed;       // P is in shared memory, S has been read
+                if (j + 1 < n_blocks) {
+                    // S of the next block, while the softmax warps work on this one; its buffer
+                    // held O_blk of block j-1, which every softmax warp must have read
+                    ok = mbar_wait(&k_full[(j + 1) % KV_STAGES], ((j + 1) / KV_STAGES) & 1) && !*failed;
+                    if (ok && j >= 1) ok = mbar_wait_idle(&o_folded[(j - 1) & 1], ((j - 1) >> 1) & 1) && !*failed;
+                    if (!ok) break;
+                    issue_s(j + 1);
+                }
+                // P is in shared memory and S of this block has been read: O_blk goes over S
+                ok = mbar_wait_idle(p_ready, j & 1) && mbar_wait(&v_full[s], (j / KV_STAGES) & 1) && !*failed;
                 if (!ok) break;
                 tcgen05_after_sync();
 #pragma unroll
@@ -181,15 +239,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     const uint64_t a = make_smem_desc(smem_u32(p_tile + (kk / 4) * TILE_BYTES)) + 2 * (kk % 4);
                     // 16 keys = two 8-row groups of the value tile; head dims beyond 64 lie one tile further
                     const uint64_t b = make_smem_desc_mn(smem_u32(v_stage + s * DB * TILE_BYTES + kk * 2048), TILE_BYTES);
-                    umma(tmem_o, a, b, idesc_o, kk > 0 ? 1u : 0u);
+                    umma(tmem_base + 128 * (j & 1), a, b, idesc_o, kk > 0 ? 1u : 0u);
                 }
-                umma_commit(o_ready);
-                umma_commit(&kv_empty[s]);
-                if (j + 1 < n_blocks) {
-                    ok = mbar_wait(&kv_full[(j + 1) % KV_STAGES], ((j + 1) / KV_STAGES) & 1) && !*failed;
-                    if (ok) issue_s(j + 1);
-                }
+                umma_commit(&o_ready[j & 1]);
+                umma_commit(&v_empty[s]);
             }
+            // the commits that free the last stages have arrived before the barriers are set up again
+            for (int j = max(0, n_blocks - KV_STAGES); ok && j < n_blocks; j++)
+                ok = mbar_wait(&k_empty[j % KV_STAGES], (j / KV_STAGES) & 1) &&
+                     mbar_wait(&v_empty[j % KV_STAGES], (j / KV_STAGES) & 1);
             if (!ok && !*failed) {
                 *failed = 1;
                 atomicExch(p.status, 12);
@@ -209,9 +267,30 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
         for (int d = 0; d < DH; d++) o[d] = 0.0f;
         float m = -INFINITY, l = 0.0f;
+        float corr_prev = 0.0f;                       // the rescaling that goes with the block not yet folded
         bool ok = true;
+        // o = o * corr + O_blk of block j (tensor memory buffer j & 1); then the buffer is free
+        auto fold = [&](int j, float corr) -> bool {
+            bool done = true;
+            if (lane == 0) done = mbar_wait(&o_ready[j & 1], (j >> 1) & 1) && !*failed;
+            done = __shfl_sync(0xffffffffu, done, 0);
+            if (!done) return false;
+            tcgen05_after_sync();
+#pragma unroll
+            for (int c = 0; c < DH; c += 32) {
+                float v[32];
+                tmem_load_32(tmem_base + 128 * (j & 1) + lane_addr + half * DH + c, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) o[c + i] = o[c + i] * corr + v[i];
+            }
+            tcgen05_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&o_folded[j & 1]);
+            return true;
+        };
         for (int j = 0; j < n_blocks; j++) {
-            if (lane == 0) ok = mbar_wait(s_ready, j & 1) && !*failed;
+            const uint32_t tmem_s = tmem_base + 128 * (j & 1);
+            if (lane == 0) ok = mbar_wait(&s_ready[j & 1], (j >> 1) & 1) && !*failed;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tcgen05_after_sync();
@@ -242,6 +321,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const float m_new = fmaxf(m, block_max * p.scale_log2);
             const float corr = (m == -INFINITY) ? 0.0f : fast_exp2(m - m_new);
             const float base = (m_new == -INFINITY) ? 0.0f : m_new;
+            // the block before: its product has had the first pass to finish, and the P tile
+            // it read is written again below
+            if (j > 0) {
+                ok = fold(j - 1, corr_prev);
+                if (!ok) break;
+            }
+            corr_prev = corr;
             // pass 2: probabilities, as bfloat16 into shared memory (swizzled like a TMA tile);
             // this thread's 64 keys are one 128-byte row of key block `half`
             float row_sum = 0.0f;
@@ -273,25 +359,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
             l = l * corr + row_sum;
             m = m_new;
-            // hand P to the tensor core: writes visible to the async proxy, all 128 rows done
+            // hand P to the tensor core: writes visible to the async proxy, all 128 rows done,
+            // and S of this block read by everyone (its buffer takes O_blk next)
             fence_async_smem();
             tcgen05_before_sync();
             asm volatile("bar.sync 1, 256;" ::: "memory");
             if (threadIdx.x == 0) mbar_arrive(p_ready);
-            // fold this block's product into the running output (this thread's half of the dims)
-            if (lane == 0) ok = mbar_wait(o_ready, j & 1) && !*failed;
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
-            tcgen05_after_sync();
-#pragma unroll
-            for (int c = 0; c < DH; c += 32) {
-                float v[32];
-                tmem_load_32(tmem_o + lane_addr + half * DH + c, v);
-#pragma unroll
-                for (int i = 0; i < 32; i++) o[c + i] = o[c + i] * corr + v[i];
-            }
-            tcgen05_before_sync();
         }
+        if (ok && n_blocks > 0) ok = fold(n_blocks - 1, corr_prev);
         if (!ok) {
             if (lane == 0 && !*failed) {
                 *failed = 1;
@@ -302,8 +377,49 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             float* sums = reinterpret_cast<float*>(p_tile);
             sums[half * 128 + r] = l;
             asm volatile("bar.sync 1, 256;" ::: "memory");
-            const float inv = 1.0f / (l + sums[(half ^ 1) * 128 + r]);
-            if (r < n_rows) {
+            float total = l + sums[(half ^ 1) * 128 + r];
+            bool writes = true;
+            if (n_parts > 1) {
+                // leave this part's state; the part that arrives last merges all of them
+                constexpr int ROW = D + 4;              // rows stay 16-byte aligned for the float4 accesses
+                float* mine = p.partial + (((long)split_id * p.n_heads + head) * p.max_parts + part) * (TILE * ROW) + r * ROW;
+#pragma unroll
+                for (int d = 0; d < DH; d += 4)
+                    __stcg(reinterpret_cast<float4*>(mine + half * DH + d), make_float4(o[d], o[d + 1], o[d + 2], o[d + 3]));
+                if (half == 0) {
+                    __stcg(mine + D, m);
+                    __stcg(mine + D + 1, total);
+                }
+                __threadfence();
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                int* ticket = reinterpret_cast<int*>(p_tile) + 512;          // behind the 256 sums
+                if (threadIdx.x == 0) *ticket = atomicAdd(p.counters + split_id * p.n_heads + head, 1);
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                writes = *ticket == n_parts - 1;
+                if (writes) {
+                    __threadfence();
+                    const float* all = p.partial + ((long)split_id * p.n_heads + head) * p.max_parts * (TILE * ROW) + r * ROW;
+                    float top = -INFINITY;
+                    for (int q = 0; q < n_parts; q++) top = fmaxf(top, __ldcg(all + (long)q * TILE * ROW + D));
+                    total = 0.0f;
+#pragma unroll
+                    for (int d = 0; d < DH; d++) o[d] = 0.0f;
+                    for (int q = 0; q < n_parts; q++) {
+                        const float* theirs = all + (long)q * TILE * ROW;
+                        const float mq = __ldcg(theirs + D);
+                        const float weight = (mq == -INFINITY) ? 0.0f : fast_exp2(mq - top);
+                        total += __ldcg(theirs + D + 1) * weight;
+#pragma unroll
+                        for (int d = 0; d < DH; d += 4) {
+                            const float4 v = __ldcg(reinterpret_cast<const float4*>(theirs + half * DH + d));
+                            o[d] += v.x * weight; o[d + 1] += v.y * weight; o[d + 2] += v.z * weight; o[d + 3] += v.w * weight;
+                        }
+                    }
+                    if (threadIdx.x == 0) p.counters[split_id * p.n_heads + head] = 0;     // ready for the next launch
+                }
+            }
+            const float inv = 1.0f / total;
+            if (writes && r < n_rows) {
                 bf16* dst = p.out + (long)(row0 + r) * p.ld_out + (long)head * D + half * DH;
 #pragma unroll
                 for (int d = 0; d < DH; d += 8) {
@@ -319,9 +435,23 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
     }
 
+    // everyone is done with this record's barriers, tiles and tensor memory
     tcgen05_before_sync();
     __syncthreads();
-    if (warp == 9) tmem_free(tmem_s, TMEM_COLS);
+    tcgen05_after_sync();
+  }
+
+    // the CTA that leaves last puts the counters back for the next launch
+    if (threadIdx.x == 0) {
+        const int left = atomicAdd(p.work + 1, 1);
+        if (left == (int)gridDim.x - 1) {
+            p.work[0] = 0;
+            p.work[1] = 0;
+        }
+    }
+    tcgen05_before_sync();
+    __syncthreads();
+    if (warp == 9) tmem_free(tmem_base, TMEM_COLS);
 }
 
 // ---- host side -------------------------------------------------------------------------
@@ -401,7 +531,7 @@ template <int D>
 int launch(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v, const AttentionParams& p, int n_tiles,
            cudaStream_t s) {
     constexpr int DB = D / 64;
-    constexpr size_t smem = (size_t)(DB + 2 * KV_STAGES * DB + 2) * TILE * 64 * 2 + (2 * KV_STAGES + 4) * 8 + 16 + 2 * 128 * 2;
+    constexpr size_t smem = (size_t)(DB + 2 * KV_STAGES * DB + 2) * TILE * 64 * 2 + (4 * KV_STAGES + 8) * 8 + 16 + 2 * 128 * 2 + 16;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(attention_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
@@ -409,8 +539,10 @@ int launch(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v, con
             return fail("attention: cannot raise the shared memory limit");
         configured = true;
     }
-    dim3 grid(n_tiles, p.n_heads);
-    attention_tcgen05_kernel<D><<<grid, THREADS, smem, s>>>(q, k, v, p);
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+    const long total = (long)n_tiles * p.n_heads, resident = (long)sms * (D <= 64 ? 2 : 1);
+    attention_tcgen05_kernel<D><<<(unsigned)std::min(total, resident), THREADS, smem, s>>>(q, k, v, p);
     return check_launch("attention_tcgen05_kernel");
 }
 
@@ -424,15 +556,25 @@ extern "C" int mllm_attention_takes(int head_size, int page_size, long ld_q, con
            (reinterpret_cast<uintptr_t>(q) & 15) == 0;
 }
 
-// tiles: device int32 [n_tiles, 4] = (entry of the step, first row among the step's tokens,
-// rows (1..128), position of the first row); rows of one tile belong to one request and
-// are consecutive.  status: zeroed device word, see the matrix-product kernel.
+// tiles: device int32 [n_tiles, 8], one record per CTA = (entry of the step, first row among
+// the step's tokens, rows (1..128), position of the first row, part, parts, number of the tile
+// among the split ones, 0); rows of one tile belong to one request and are consecutive; a
+// tile of several parts has one record per part.  partial / counters (may be null if no tile
+// has parts): fp32 [split tiles, heads, max_parts, 128, head_size + 4] and zeroed int32
+// [split tiles, heads] (the kernel leaves them zero).  work: two zeroed ints (left zero).
+// The records should be sorted by falling number of key blocks.  status: zeroed device word,
+// see the matrix-product kernel.
 extern "C" int mllm_attention_prefill(void* out, long ld_out, const void* q, long q_rows, long q_cols, long ld_q,
                                       const void* k_pages, const void* v_pages, int n_pages, int page_size,
                                       const int* block_table, int max_blocks, const int* tiles, int n_tiles,
                                       int n_heads, int n_kv_heads, int head_size, float scale, int window,
-                                      int* status, void* stream) {
+                                      int* status, float* partial, int* counters, int max_parts, int* work,
+                                      void* stream) {
     if (n_tiles <= 0) return 0;
+    if (work == nullptr) return fail("attention: the work counter is required");
+    if (max_parts < 1 || (max_parts > 1 && (partial == nullptr || counters == nullptr)))
+        return fail("attention: tiles in parts need scratch memory");
+    if ((reinterpret_cast<uintptr_t>(partial) & 15) != 0) return fail("attention: the scratch must be 16-byte aligned");
     if (!mllm_attention_takes(head_size, page_size, ld_q, q))
         return fail("attention: head size must be 64 or 128, the page size a power of two in 8..128, q 16-byte aligned");
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_heads > 65535)
@@ -452,7 +594,7 @@ extern "C" int mllm_attention_prefill(void* out, long ld_out, const void* q, lon
         rc = page_map(v_pages, n_pages, page_size, n_kv_heads, head_size, &map_v);
         if (rc) return rc;
     }
-    AttentionParams p{(bf16*)out, ld_out, tiles, block_table, max_blocks, n_heads, n_kv_heads, page_size, n_pages,
+    AttentionParams p{(bf16*)out, ld_out, tiles, partial, counters, max_parts, n_tiles, work, block_table, max_blocks, n_heads, n_kv_heads, page_size, n_pages,
                       scale * 1.4426950408889634f, window, status};
     cudaStream_t s = (cudaStream_t)stream;
     if (head_size == 64) return launch<64>(map_q, map_k, map_v, p, n_tiles, s);

@@ -37,6 +37,11 @@ __device__ __forceinline__ unsigned long long now_ns() {
     return t;
 }
 
+// Before a barrier's memory is initialised again.
+__device__ __forceinline__ void mbar_inval(uint64_t* bar) {
+    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 // Wait for the phase with `parity` to complete; false if the time limit passed first.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -45,6 +50,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 #pragma unroll 1
         for (int i = 0; i < 256; i++)
             if (mbar_try_wait(bar, parity)) return true;
+        if (now_ns() - start > WAIT_LIMIT_NS) return false;
+    }
+}
+
+// The same for a thread that expects to wait long (a producer or an MMA issuer between blocks):
+// it sleeps between looks, so that its polling does not take issue slots from working warps.
+__device__ __forceinline__ bool mbar_wait_idle(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long start = now_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; i++) {
+            if (mbar_try_wait(bar, parity)) return true;
+            __nanosleep(40);
+        }
         if (now_ns() - start > WAIT_LIMIT_NS) return false;
     }
 }

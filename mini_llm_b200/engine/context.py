@@ -53,6 +53,12 @@ class ControlBlock:
         self._turn = 0
         self.generation = 0
 
+    @staticmethod
+    def tile_ints(n_tokens: int, n_items: int) -> int:
+        """Room for the attention work list: at most n_tokens // 128 + n_items tiles, each in
+        at most 8 parts, 8 int32 per record."""
+        return 8 * 8 * (n_tokens // 128 + n_items)
+
     def _layout(self, n_tokens: int, n_items: int):
         """Offsets (in int32 units) as a function of the step's sizes only, so
         that steps of equal sizes find their arrays at equal addresses."""
@@ -66,7 +72,7 @@ class ControlBlock:
         offsets["seeds"] = cursor
         cursor += 2 * n_tokens
         offsets["att_tiles"] = cursor             # work list of the prompt-attention kernel
-        cursor += 4 * (n_tokens // 128 + n_items)
+        cursor += self.tile_ints(n_tokens, n_items)
         for index, max_blocks in self.groups:
             offsets[("block_table", index)] = cursor
             cursor += n_items * max_blocks
@@ -117,7 +123,7 @@ class ControlBlock:
             elif name in ("temperature", "top_p"):
                 views[name] = buffer[start:start + n_tokens].view(torch.float32)
             elif name == "att_tiles":
-                views[name] = buffer[start:start + 4 * (n_tokens // 128 + n_items)]
+                views[name] = buffer[start:start + self.tile_ints(n_tokens, n_items)]
             elif isinstance(name, tuple):
                 max_blocks = dict(self.groups)[name[1]]
                 views[name] = buffer[start:start + n_items * max_blocks].view(n_items, max_blocks)
@@ -145,7 +151,9 @@ class StepContext:
         self.item_offsets = []        # host: row of each entry's first token
         self.decode_only = False      # every entry brings exactly one token
         self.att_tiles = None         # device work list (tiles of up to 128 tokens of one entry), or None
-        self.n_att_tiles = 0
+        self.n_att_tiles = 0          # records (CTAs) of the work list
+        self.n_split_tiles = 0        # tiles among them that come in several parts
+        self.att_parts = 1            # most parts of a tile
 
     def buffer(self, tag: str, shape, dtype):
         return self.workspace.get(tag, shape, dtype)

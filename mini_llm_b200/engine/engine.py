@@ -218,7 +218,7 @@ class Engine:
         for group in self.cache.groups:
             if group.paged:
                 arrays[("block_table", group.index)] = group.table[ctx.item_slots]
-        tiles = ops.attention_tiles(ctx.item_offsets, ctx.item_counts, ctx.item_starts)
+        tiles, n_split, most_parts = ops.attention_tiles(ctx.item_offsets, ctx.item_counts, ctx.item_starts)
         arrays["att_tiles"] = np.array(tiles, dtype=np.int32)
         if sampling is not None:
             arrays["temperature"] = np.array([s.temperature for s in sampling], dtype=np.float32)
@@ -234,6 +234,7 @@ class Engine:
         ctx.any_previous = any_previous
         ctx.decode_only = all(n == 1 for n in ctx.item_counts)
         ctx.att_tiles, ctx.n_att_tiles = views["att_tiles"], len(tiles)
+        ctx.n_split_tiles, ctx.att_parts = n_split, most_parts
         for view in self.storage.views:
             if view.kind == "paged":
                 view.block_table = views[("block_table", view.group)]
@@ -298,8 +299,8 @@ class Engine:
         if stamp != self._graph_stamp:
             self._graphs.clear()                      # a buffer moved: captured addresses are stale
             self._graph_stamp = stamp
-        key = (ctx.n_tokens, ctx.n_items, ctx.n_want, ctx.n_att_tiles, sample_views is not None, self._any_nucleus,
-               ctx.any_previous)
+        key = (ctx.n_tokens, ctx.n_items, ctx.n_want, ctx.n_att_tiles, ctx.att_parts, sample_views is not None,
+               self._any_nucleus, ctx.any_previous)
         held = self._graphs.get(key)
         if held is None:
             if len(self._graphs) >= 48:

@@ -48,6 +48,8 @@ class Kernels:
         self._sample_scratch = None
         self.scratch_generation = 0  # grows when scratch moves (captured graphs are then stale)
         self._status = None
+        self._att_scratch = None
+        self._att_work = None
         self._gemm_scratch = None          # device word the tensor-core kernels report a timed-out wait in
 
     # ---- operations without a fast variant --------------------------------------------------
@@ -132,8 +134,11 @@ class Kernels:
             code = int(self._status.item())
             if code != 0:
                 self._status.zero_()
-                if self._gemm_scratch is not None:
-                    self._gemm_scratch[1].zero_()     # a tile that was given up left its counter
+                for held in (self._gemm_scratch, self._att_scratch):
+                    if held is not None:
+                        held[1].zero_()               # a tile that was given up left its counter
+                if self._att_work is not None:
+                    self._att_work.zero_()
                 raise ops.KernelError(f"a tensor-core kernel gave up waiting (code {code}): its result is invalid")
 
     def qkv_projection(self, ctx, a, w, bias, cache, q_width, kv_width):
@@ -184,11 +189,35 @@ class Kernels:
                                        window, chunk, max_chunks, acc, ml, counters)
         if (not self.plain_only and ctx.att_tiles is not None
                 and ops.attention_prefill_takes(q, head_size, cache.page_size)):
+            scratch = None
+            if ctx.att_parts > 1:
+                scratch = self._attention_scratch(ctx.device, ctx.n_split_tiles * n_heads, ops.ATTENTION_MAX_PARTS
+                                                  * ops.ATTENTION_TILE * (head_size + 4))
             return ops.attention_prefill(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.att_tiles,
                                          ctx.n_att_tiles, n_heads, n_kv_heads, head_size, cache.page_size, scale,
-                                         window, self.status(ctx.device))
+                                         window, self.status(ctx.device), self.attention_work(ctx.device), scratch,
+                                         ctx.n_split_tiles,
+                                         ops.ATTENTION_MAX_PARTS if ctx.att_parts > 1 else 1)
         return ops.attention_plain(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
                                    ctx.token_item, n_heads, n_kv_heads, head_size, cache.page_size, scale, window)
+
+    def attention_work(self, device):
+        """The work counter of the persistent prompt-attention kernel (zero between launches)."""
+        if self._att_work is None:
+            self._att_work = torch.zeros(2, dtype=torch.int32, device=device)
+            self.scratch_generation += 1
+        return self._att_work
+
+    def _attention_scratch(self, device, cells, floats_per_cell):
+        """Partial states and counters of prompt attention tiles that come in parts; grows
+        (doubling) when a step has more split tiles than any before."""
+        held = self._att_scratch
+        if held is None or held[1].shape[0] < cells or held[0].shape[0] < cells * floats_per_cell:
+            cells = max(cells, 2 * held[1].shape[0] if held is not None else 256)
+            self._att_scratch = held = (torch.empty(cells * floats_per_cell, dtype=torch.float32, device=device),
+                                        torch.zeros(cells, dtype=torch.int32, device=device))
+            self.scratch_generation += 1
+        return held
 
     def _scratch(self, ctx, pairs, chunks, head_size):
         """Scratch of split_attention, sized for the largest step it takes; allocated once

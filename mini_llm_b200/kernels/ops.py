@@ -411,7 +411,7 @@ def gemm_bf16_qkv(q_out, a, w, bias, status, k_pages, v_pages, positions, token_
 # ---- tensor-core attention for prompt portions (bfloat16) ----------------------------------------
 
 _attention_prefill = Function("attention", "mllm_attention_prefill",
-                              [P, L, P, L, L, L, P, P, I, I, P, I, P, I, I, I, I, F, I, P, P])
+                              [P, L, P, L, L, L, P, P, I, I, P, I, P, I, I, I, I, F, I, P, P, P, I, P, P])
 
 PREFILL_ATTENTION_HEAD_SIZES = (64, 128)
 PREFILL_ATTENTION_PAGE_SIZES = (8, 16, 32, 64, 128)
@@ -423,20 +423,49 @@ def attention_prefill_takes(q, head_size, page_size) -> bool:
             and page_size in PREFILL_ATTENTION_PAGE_SIZES and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
 
 
-def attention_tiles(item_offsets, item_counts, item_starts):
+ATTENTION_TILE_RECORD = 8           # int32 per CTA of attention_prefill
+ATTENTION_BLOCKS_PER_PART = 4       # a tile with more key blocks than this is shared among several CTAs
+ATTENTION_MAX_PARTS = 8
+
+
+def attention_tiles(item_offsets, item_counts, item_starts, split=None):
     """The work list of attention_prefill: tiles of up to 128 consecutive tokens of one
-    entry, as rows (entry, first row, rows, position of the first row)."""
-    tiles = []
+    entry, one record per unit of work: (entry, first row, rows, position of the first row,
+    part, parts, number of the tile among the split ones, key blocks of the part), sorted by
+    falling number of key blocks.  A tile that reaches over more than
+    four blocks of 128 keys can be given to several CTAs (parts), so that the longest CTA of a
+    step stays short.  That pays only while the step has few tiles (measured: two CTAs on one
+    SM run no faster than one after the other), so by default tiles are split when there are
+    at most eight of them; ``split=True`` / ``False`` forces it (whole tiles need no scratch).
+    Returns (records, number of split tiles, most parts of a tile)."""
+    records, n_split, most = [], 0, 1
+    if split is None:
+        split = sum(-(-count // ATTENTION_TILE) for count in item_counts) <= 8
     for item, (offset, count, start) in enumerate(zip(item_offsets, item_counts, item_starts)):
         for first in range(0, count, ATTENTION_TILE):
-            tiles.append((item, offset + first, min(ATTENTION_TILE, count - first), start + first))
-    return tiles
+            rows = min(ATTENTION_TILE, count - first)
+            blocks = (start + first + rows - 1) // ATTENTION_TILE + 1
+            parts = min(ATTENTION_MAX_PARTS, -(-blocks // ATTENTION_BLOCKS_PER_PART)) if split else 1
+            share = -(-blocks // parts)
+            for part in range(parts):
+                records.append((item, offset + first, rows, start + first, part, parts, n_split if parts > 1 else 0,
+                                min(share, blocks - part * share)))
+            if parts > 1:
+                n_split += 1
+                most = max(most, parts)
+    # the kernel's CTAs take records in this order: the longest first
+    records.sort(key=lambda record: -record[7])
+    return records, n_split, most
 
 
 def attention_prefill(out, q, k_pages, v_pages, block_table, tiles, n_tiles, n_heads, n_kv_heads, head_size,
-                      page_size, scale, window, status):
+                      page_size, scale, window, status, work, scratch=None, n_split=0, max_parts=1):
     """Causal attention over the paged cache on the tensor cores (tcgen05): one CTA per
-    (tile of 128 queries, head).  ``tiles``: device int32 [>= n_tiles, 4] from ``attention_tiles``."""
+    (record of the work list, head).  ``tiles``: device int32 [>= n_tiles, 8] from
+    ``attention_tiles``.  ``work``: two zeroed int32 (the kernel's work counter; left zero).
+    ``scratch``: (fp32 partial states, zeroed int32 counters) when tiles
+    come in parts: n_split * heads * max_parts * 128 * (head_size + 4) floats and
+    n_split * heads counters."""
     _check(out, "attention_prefill.out", torch.bfloat16, 2)
     _check(q, "attention_prefill.q", torch.bfloat16, 2)
     _check(k_pages, "attention_prefill.k_pages", torch.bfloat16, 4)
@@ -444,6 +473,9 @@ def attention_prefill(out, q, k_pages, v_pages, block_table, tiles, n_tiles, n_h
     _check(block_table, "attention_prefill.block_table", torch.int32, 2)
     _check(tiles, "attention_prefill.tiles", torch.int32)
     _check(status, "attention_prefill.status", torch.int32)
+    _check(work, "attention_prefill.work", torch.int32, 1)
+    if work.shape[0] < 2:
+        raise KernelError("attention_prefill: the work counter has two entries")
     if not attention_prefill_takes(q, head_size, page_size):
         raise KernelError(f"attention_prefill does not take head size {head_size} with pages of {page_size}")
     n_pages = k_pages.shape[0]
@@ -451,12 +483,23 @@ def attention_prefill(out, q, k_pages, v_pages, block_table, tiles, n_tiles, n_h
         raise KernelError("attention_prefill: pages must be [n_pages, page_size, kv_heads, head_size]")
     if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous():
         raise KernelError("attention_prefill: pages and block table must be contiguous")
-    if q.shape[1] != n_heads * head_size or out.shape != q.shape or tiles.numel() < 4 * n_tiles:
+    if q.shape[1] != n_heads * head_size or out.shape != q.shape or tiles.numel() < ATTENTION_TILE_RECORD * n_tiles:
         raise KernelError("attention_prefill: q / out / tiles do not fit")
+    partial = counters = None
+    if max_parts > 1:
+        if scratch is None:
+            raise KernelError("attention_prefill: tiles in parts need scratch")
+        partial, counters = scratch
+        _check(partial, "attention_prefill.scratch", torch.float32, 1)
+        _check(counters, "attention_prefill.scratch", torch.int32, 1)
+        if (partial.shape[0] < n_split * n_heads * max_parts * ATTENTION_TILE * (head_size + 4)
+                or counters.shape[0] < n_split * n_heads):
+            raise KernelError("attention_prefill: scratch too small")
     _attention_prefill(out.data_ptr(), out.stride(0), q.data_ptr(), q.shape[0], q.shape[1], q.stride(0),
                        k_pages.data_ptr(), v_pages.data_ptr(), n_pages, page_size, block_table.data_ptr(),
                        block_table.shape[1], tiles.data_ptr(), n_tiles, n_heads, n_kv_heads, head_size, float(scale),
-                       int(window or 0), status.data_ptr(), _stream())
+                       int(window or 0), status.data_ptr(), _ptr(partial), _ptr(counters), int(max_parts),
+                       work.data_ptr(), _stream())
     return out
 
 

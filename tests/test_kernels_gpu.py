@@ -453,16 +453,30 @@ def test_attention_prefill_over_pages(n_heads, n_kv_heads, head, page, window):
     out = torch.full_like(q, float("nan"))
     offsets = np.concatenate([[0], np.cumsum(n_new)[:-1]]).tolist()
     starts = [l - m for l, m in zip(lengths, n_new)]
-    tiles = ops.attention_tiles(offsets, n_new, starts)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     scale = 1.0 / math.sqrt(head)
-    ops.attention_prefill(out, q, k_pages.view(kv_shape), v_pages.view(kv_shape), table,
-                          dev(np.array(tiles, dtype=np.int32)), len(tiles), n_heads, n_kv_heads, head, page, scale,
-                          window, status)
-    assert int(status.item()) == 0
     expected = attention_expected(f64(q), dense, f64(positions).astype(int), f64(items).astype(int), n_heads,
                                   n_kv_heads, head, scale, window)
+    work = torch.zeros(2, dtype=torch.int32, device="cuda")
+    # every tile by one CTA, then the long tiles in parts (twice: the counters must be back at zero)
+    whole, n_split, most = ops.attention_tiles(offsets, n_new, starts, split=False)
+    assert n_split == 0 and most == 1
+    ops.attention_prefill(out, q, k_pages.view(kv_shape), v_pages.view(kv_shape), table,
+                          dev(np.array(whole, dtype=np.int32)), len(whole), n_heads, n_kv_heads, head, page, scale,
+                          window, status, work)
     np.testing.assert_allclose(f64(out), expected, rtol=0, atol=tol(torch.bfloat16, 2))
+    parts, n_split, most = ops.attention_tiles(offsets, n_new, starts, split=True)
+    assert n_split == 2 and most == 2 and len(parts) == len(whole) + 2          # the tiles that end past key 512
+    scratch = (torch.full((n_split * n_heads * 8 * 128 * (head + 4),), float("nan"), device="cuda"),
+               torch.zeros(n_split * n_heads, dtype=torch.int32, device="cuda"))
+    for _ in range(2):
+        out.fill_(float("nan"))
+        ops.attention_prefill(out, q, k_pages.view(kv_shape), v_pages.view(kv_shape), table,
+                              dev(np.array(parts, dtype=np.int32)), len(parts), n_heads, n_kv_heads, head, page, scale,
+                              window, status, work, scratch, n_split, 8)
+        np.testing.assert_allclose(f64(out), expected, rtol=0, atol=tol(torch.bfloat16, 2))
+    assert int(status.item()) == 0 and int(scratch[1].abs().sum().item()) == 0 and int(work.abs().sum().item()) == 0
+    assert [r[7] for r in parts] == sorted((r[7] for r in parts), reverse=True)     # the longest units first
 
 
 def test_attention_prefill_finds_one_far_key_and_respects_the_windows_edge():
@@ -481,10 +495,15 @@ def test_attention_prefill_finds_one_far_key_and_respects_the_windows_edge():
     kv_shape = (k_pages.shape[0], page, 1, head)
     qd = dev(q, torch.bfloat16)
     out = torch.empty_like(qd)
-    tiles = dev(np.array(ops.attention_tiles([0], [new], [length - new]), dtype=np.int32))
+    records, n_split, most = ops.attention_tiles([0], [new], [length - new])      # two tiles: split by default
+    assert n_split == 2 and most == 2 and len(records) == 4
+    tiles = dev(np.array(records, dtype=np.int32))
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    scratch = (torch.empty(n_split * 8 * 128 * (head + 4), device="cuda"), torch.zeros(n_split, dtype=torch.int32, device="cuda"))
+    work = torch.zeros(2, dtype=torch.int32, device="cuda")
     run = lambda window: ops.attention_prefill(out, qd, k_pages.view(kv_shape), v_pages.view(kv_shape), table, tiles,
-                                               2, 1, 1, head, page, 1.0 / math.sqrt(head), window, status)
+                                               4, 1, 1, head, page, 1.0 / math.sqrt(head), window, status, work,
+                                               scratch, n_split, 8)
     run(0)
     np.testing.assert_allclose(f64(out)[-1], f64(dev(v[far], torch.bfloat16)), rtol=2e-2, atol=0.5)
     run(length - 1 - far)
