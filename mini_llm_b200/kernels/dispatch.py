@@ -16,7 +16,8 @@ import torch
 
 from . import ops
 
-SKINNY_MAX_ROWS = 16          # up to here a product streams the weights once through the SIMT kernel
+SKINNY_MAX_ROWS = 8           # up to here a product streams the weights once through the SIMT kernel (measured:
+                              # from 9 rows on the tensor-core kernel with swapped operands is faster)
 SPLIT_ATTENTION_MAX_ROWS = 64 # up to here attention runs one CTA per (token, head, chunk of keys)
 
 
