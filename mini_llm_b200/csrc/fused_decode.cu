@@ -83,6 +83,9 @@ struct FusedParams {
     unsigned long long* barrier;    // monotonically increasing arrival counter
     int* status;
     unsigned long long* timeline;   // null, or room for 5 * layers + 3 time stamps
+    int att_parts;                  // CTAs that share the keys of one (token, head): 1 .. 16
+    float* att_partial;             // [T * H, att_parts, D + 2]: a part's output, maximum, sum
+    int* att_counters;              // [T * H], zero between launches
 };
 
 namespace {
@@ -548,9 +551,13 @@ __device__ void product_phase(const FusedParams& p, const Shared& sm, const Phas
     }
 }
 
-// Phase 2: one CTA per (token, head); its warps take the keys in turn (four keys and four
-// values in flight per lane), each with an online softmax; the warps' states are merged through
-// shared memory in warp order, so nothing depends on timing.
+// Phase 2: one CTA per (token, head) pair, or, when the pairs are so few that SMs would stay
+// idle, p.att_parts CTAs per pair, each with a share of the keys.  A CTA's warps take its
+// keys in turn (four keys and four values in flight per lane), each with an online softmax;
+// the warps' states are merged through shared memory in warp order.  A pair in several parts
+// is finished by the CTA that arrives last, which adds the parts in their order: nothing
+// depends on timing.  (Measured: a part costs about 3 us for the hand-over, so parts pay only
+// while every CTA has at most one.)
 template <int D>
 __device__ void attention_phase(const FusedParams& p, const Shared& sm, const FusedLayer& layer) {
     constexpr int LPK = D / 8, KPW = 32 / LPK, INFLIGHT = 4;
@@ -560,10 +567,16 @@ __device__ void attention_phase(const FusedParams& p, const Shared& sm, const Fu
     float* sm_m = sm.att;                     // [WARPS]
     float* sm_l = sm.att + WARPS;             // [WARPS]
     float* sm_acc = sm.att + 2 * WARPS;       // [WARPS][D]
-    for (int pair = blockIdx.x; pair < p.T * p.H; pair += gridDim.x) {
+    __shared__ int last_part;
+    const int parts = p.att_parts;
+    for (int unit = blockIdx.x; unit < p.T * p.H * parts; unit += gridDim.x) {
+        const int pair = unit / parts, part = unit % parts;
         const int h = pair % p.H, t = pair / p.H;
         const int pos = sm.pos[t];
         const int begin = (layer.window > 0 && pos - layer.window + 1 > 0) ? pos - layer.window + 1 : 0;
+        // this part's keys: an equal share, in whole steps of a warp
+        const int share = ((pos - begin + parts) / parts + KPW - 1) / KPW * KPW;
+        const int first = begin + part * share, last = min(pos, first + share - 1);
         const int* bt = sm.table + t * p.max_blocks;
         const int hk = h / (p.H / p.Hkv);
         float qf[8], acc[8];
@@ -574,14 +587,14 @@ __device__ void attention_phase(const FusedParams& p, const Shared& sm, const Fu
             acc[i] = 0.0f;
         }
         float m = -INFINITY, l = 0.0f;
-        for (int jb = begin + warp * INFLIGHT * KPW; jb <= pos; jb += WARPS * INFLIGHT * KPW) {
+        for (int jb = first + warp * INFLIGHT * KPW; jb <= last; jb += WARPS * INFLIGHT * KPW) {
             uint4 kv[INFLIGHT], vv[INFLIGHT];
 #pragma unroll
             for (int s = 0; s < INFLIGHT; s++) {
                 const int j = jb + s * KPW + group;
                 kv[s] = make_uint4(0, 0, 0, 0);
                 vv[s] = make_uint4(0, 0, 0, 0);
-                if (j <= pos) {
+                if (j <= last) {
                     const int page = bt[j / p.page_size];
                     const long base = ((long)page * p.page_size + (j % p.page_size)) * kv_width + (long)hk * D + sub * 8;
                     kv[s] = __ldcg(reinterpret_cast<const uint4*>(layer.k_pages + base));
@@ -598,7 +611,7 @@ __device__ void attention_phase(const FusedParams& p, const Shared& sm, const Fu
                 for (int i = 0; i < 8; i++) sc = fmaf(qf[i], kf[i], sc);
 #pragma unroll
                 for (int o = LPK / 2; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
-                if (jb + s * KPW + group <= pos) {
+                if (jb + s * KPW + group <= last) {
                     const float m_new = fmaxf(m, sc);
                     const float corr = __expf(m - m_new), e = __expf(sc - m_new);
                     l = l * corr + e;
@@ -619,7 +632,7 @@ __device__ void attention_phase(const FusedParams& p, const Shared& sm, const Fu
             l = l * wa + l_o * wb;
             m = big;
         }
-        __syncthreads();                      // the scratch may still be read for the previous pair
+        __syncthreads();                      // the scratch may still be read for the previous unit
         if (group == 0) {
 #pragma unroll
             for (int i = 0; i < 8; i++) sm_acc[warp * D + sub * 8 + i] = acc[i];
@@ -629,16 +642,48 @@ __device__ void attention_phase(const FusedParams& p, const Shared& sm, const Fu
             sm_l[warp] = l;
         }
         __syncthreads();
-        for (int d = threadIdx.x; d < D; d += THREADS) {
-            float top = -INFINITY;
+        float top = -INFINITY, denom = 0.0f, o = 0.0f;
+        if (threadIdx.x < D) {
+            const int d = threadIdx.x;
             for (int w = 0; w < WARPS; w++) top = fmaxf(top, sm_m[w]);
-            float denom = 0.0f, o = 0.0f;
             for (int w = 0; w < WARPS; w++) {
                 const float weight = (sm_m[w] == -INFINITY) ? 0.0f : __expf(sm_m[w] - top);
                 denom += sm_l[w] * weight;
                 o += sm_acc[w * D + d] * weight;
             }
-            p.attn[(long)t * p.H * D + (long)h * D + d] = __float2bfloat16_rn(o / denom);
+        }
+        bf16* out = p.attn + (long)t * p.H * D + (long)h * D;
+        if (parts == 1) {
+            if (threadIdx.x < D) out[threadIdx.x] = __float2bfloat16_rn(o / denom);
+            continue;
+        }
+        // leave this part's state; the part that arrives last finishes the pair
+        float* mine = p.att_partial + ((long)pair * parts + part) * (D + 2);
+        if (threadIdx.x < D) {
+            __stcg(mine + threadIdx.x, o);
+            if (threadIdx.x == 0) {
+                __stcg(mine + D, top);
+                __stcg(mine + D + 1, denom);
+            }
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) last_part = atomicAdd(p.att_counters + pair, 1) == parts - 1;
+        __syncthreads();
+        if (last_part && threadIdx.x < D) {
+            __threadfence();
+            const float* all = p.att_partial + (long)pair * parts * (D + 2);
+            float big = -INFINITY;
+            for (int q = 0; q < parts; q++) big = fmaxf(big, __ldcg(all + q * (D + 2) + D));
+            float sum = 0.0f, total = 0.0f;
+            for (int q = 0; q < parts; q++) {
+                const float mq = __ldcg(all + q * (D + 2) + D);
+                const float weight = (mq == -INFINITY) ? 0.0f : __expf(mq - big);
+                sum += __ldcg(all + q * (D + 2) + threadIdx.x) * weight;
+                total += __ldcg(all + q * (D + 2) + D + 1) * weight;
+            }
+            out[threadIdx.x] = __float2bfloat16_rn(sum / total);
+            if (threadIdx.x == 0) p.att_counters[pair] = 0;      // ready for the next layer and launch
         }
     }
 }

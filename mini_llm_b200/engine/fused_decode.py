@@ -36,11 +36,13 @@ class _Params(ctypes.Structure):
                 ("sample", I),
                 ("temperature", P), ("top_p", P), ("seeds", P), ("counters", P), ("out_tokens", P), ("kept", P), ("want_slots", P),
                 ("n_kept", I), ("cand_value", P),
-                ("cand_index", P), ("cand_done", P), ("barrier", P), ("status", P), ("timeline", P)]
+                ("cand_index", P), ("cand_done", P), ("barrier", P), ("status", P), ("timeline", P),
+                ("att_parts", I), ("att_partial", P), ("att_counters", P)]
 
 
 _step = Function("fused", "mllm_fused_decode_step", [ctypes.POINTER(_Params), P])
 MAX_TOKENS = 16
+MAX_ATTENTION_PARTS = 16
 _KINDS = {"norm_1": "layer_norm", "mixer": "causal_self_attention", "norm_2": "layer_norm", "feed_forward": "dense_mlp"}
 
 
@@ -111,11 +113,23 @@ class FusedDecodePlan:
         self.cand_done = torch.zeros(1, dtype=torch.int32, device=device)
         self.barrier = torch.zeros(1, dtype=torch.int64, device=device)
         self.out_tokens = torch.zeros(MAX_TOKENS, dtype=torch.int32, device=device)
+        heads, head_size = self.sizes[1], self.sizes[3]
+        self.att_partial = torch.empty(MAX_TOKENS * heads * MAX_ATTENTION_PARTS * (head_size + 2), dtype=torch.float32,
+                                       device=device)
+        self.att_counters = torch.zeros(MAX_TOKENS * heads, dtype=torch.int32, device=device)
 
     def takes(self, ctx) -> bool:
         width, heads, kv_heads, head_size, inner, _ = self.sizes
         return (ctx.decode_only and ctx.n_tokens <= MAX_TOKENS
                 and bool(self.lib.mllm_fused_takes(ctx.n_tokens, width, heads, kv_heads, head_size, inner, self.max_blocks)))
+
+    def attention_parts(self, ctx) -> int:
+        """How many CTAs share the keys of one (token, head) pair: as many as leave every CTA at
+        most one part (a part's hand-over costs more than a second part would save), with at
+        least 64 keys each."""
+        pairs = ctx.n_tokens * self.sizes[1]
+        longest = max(ctx.item_starts) + 1
+        return max(1, min(MAX_ATTENTION_PARTS, self.grid // pairs, longest // 64))
 
     def run(self, ctx, block_table, sample_views, any_nucleus):
         """Run the step; returns (logits or None, sampled tokens or None)."""
@@ -123,13 +137,14 @@ class FusedDecodePlan:
         sampling = sample_views is not None and ctx.n_want > 0
         # Steps of one shape find all their arrays at the same addresses (the control block's
         # layout depends on the step's sizes only): their parameters are filled once.
-        key = (ctx.n_tokens, ctx.n_want, sampling, self.timeline is not None,
+        parts = self.attention_parts(ctx)
+        key = (ctx.n_tokens, ctx.n_want, sampling, self.timeline is not None, parts,
                engine.workspace.generation, engine.control.generation)
         held = self._filled.get(key)
         if held is None:
             if len(self._filled) > 64:
                 self._filled.clear()
-            held = self._filled[key] = self._fill(ctx, block_table, sample_views if sampling else None)
+            held = self._filled[key] = self._fill(ctx, block_table, sample_views if sampling else None, parts)
         params, logits, sampled = held
         _step(ctypes.byref(params), torch.cuda.current_stream().cuda_stream)
         engine.kernels.launches += 1
@@ -139,7 +154,7 @@ class FusedDecodePlan:
             engine.kernels.keep_tokens(engine.kept_tokens, ctx.want_slots, sampled)    # the kernel kept its own draw
         return logits, sampled
 
-    def _fill(self, ctx, block_table, sample_views):
+    def _fill(self, ctx, block_table, sample_views, parts):
         engine = self.engine
         model = engine.model
         width, heads, kv_heads, head_size, inner, vocab = self.sizes
@@ -177,9 +192,12 @@ class FusedDecodePlan:
         params.cand_value, params.cand_index = self.cand_value.data_ptr(), self.cand_index.data_ptr()
         params.cand_done, params.barrier = self.cand_done.data_ptr(), self.barrier.data_ptr()
         params.status = engine.kernels.status(engine.device).data_ptr()
+        params.att_parts = parts
+        params.att_partial, params.att_counters = self.att_partial.data_ptr(), self.att_counters.data_ptr()
         return params, logits, sampled
 
     def reset(self) -> None:
         """After a failed step: the barrier counter and the scratch counters start over."""
         self.barrier.zero_()
         self.cand_done.zero_()
+        self.att_counters.zero_()

@@ -229,6 +229,20 @@ def test_fused_decode_step_agrees_with_the_part_by_part_path(folders):
         np.testing.assert_allclose(a, b, rtol=0, atol=bf16_atol(b))
         agree += sum(x == y for x, y in zip(ta, tb))
     assert agree >= 0.97 * 40 * len(prompts)             # the same draws, near-ties apart
+    # one long request: few (token, head) pairs, so several CTAs share each pair's keys
+    long_prompt = random_tokens(77, 600, vocab)
+    rows = {}
+    for name, engine in (("fused", fused), ("plain", plain)):
+        slot = engine.open_request()
+        engine.step([StepEntry(slot, long_prompt, [])])
+        rows[name] = [engine.step([StepEntry(slot, [int(feed[step, 0])], [0])]).cpu().numpy().copy() for step in range(12)]
+        engine.close_request(slot)
+    class _One:
+        n_tokens, item_starts = 1, [600]
+    assert fused.fused.attention_parts(_One) >= 4
+    for a, b in zip(rows["fused"], rows["plain"]):
+        np.testing.assert_allclose(a, b, rtol=0, atol=bf16_atol(b))
+    fused.check_status()
     # a model the fused kernel does not take (head size 48) runs the generic path silently
     other = Engine(folders["B"], dtype="bfloat16", page_size=8, cache_tokens=1024, max_requests=4)
     slot = other.open_request()
