@@ -411,6 +411,271 @@ extern "C" int mllm_decode_split_attention_takes(int head_size) {
 }
 
 // ---------------------------------------------------------------------------
+// group_attention: the same split-key attention with the products on mma.sync tiles.
+//
+// One CTA per (token, key/value head, chunk of keys); its four warps take tiles of 16 keys in
+// turn.  The query heads that share the key/value head (1 to 8) are the rows of the tiles:
+//   S[heads x 8 keys]  = Q[heads x dims] K^T      m16n8k16, A = Q (kept in registers), B = K
+//   O[heads x 8 dims] += P[heads x 16 keys] V     A = P (the registers S came in), B = V
+// Keys and values stream through a cp.async ring in shared memory (a warp's own slots); the
+// key rows are read back as 16-byte chunks, the value tiles with ldmatrix.trans.  The dims of
+// a row are taken in a permuted order that is the same for Q and K, so that a lane reads whole
+// 16-byte chunks; both tiles are swizzled so that the reads have no bank conflicts.  The
+// softmax is the online one of split_attention, per 16 keys, in 32-bit, in exp2 units; the
+// partial states and their merge by the last CTA of a pair use split_attention's scratch
+// layout.  Against one key per eight lanes this needs about a tenth of the instructions.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void mma_bf16_16816(float& c0, float& c1, float& c2, float& c3, uint32_t a0, uint32_t a1,
+                                               uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+                 "{%0, %1, %2, %3};"
+                 : "+f"(c0), "+f"(c1), "+f"(c2), "+f"(c3)
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 two = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&two);
+}
+
+template <int D>       // head size: 64 or 128
+__global__ void __launch_bounds__(128)
+group_attention_kernel(bf16* __restrict__ out, long ld_out, const bf16* __restrict__ q, long ld_q,
+                       const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+                       const int* __restrict__ block_table, int max_blocks, const int* __restrict__ positions,
+                       const int* __restrict__ token_item, int n_heads, int n_kv_heads, int page_size, float scale,
+                       int window, int chunk, int max_chunks, float* __restrict__ part_acc,
+                       float* __restrict__ part_ml, int* __restrict__ counters) {
+    constexpr int CH = D / 8;              // 16-byte chunks of a key or value row
+    constexpr int PAIRS = D / 32;          // chunks a lane reads of a key row (each serves two k steps)
+    constexpr int NT = D / 8;              // 8-dim tiles of the output
+    constexpr int RING = 256 / D;          // tiles of 16 keys in flight per warp: 4 (D = 64) or 2
+    constexpr int TILE_BYTES = 16 * D * 2; // one tile of keys (or values)
+    extern __shared__ __align__(16) unsigned char ga_smem[];
+    const int t = blockIdx.x, hk = blockIdx.y, c = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, tq = lane & 3;
+    const int heads = n_heads / n_kv_heads;            // 1..8: rows of the tiles
+    const int p = positions[t];
+    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int c_first = lo / chunk, c_last = p / chunk;
+    if (c < c_first || c > c_last) return;
+    const int begin = max(lo, c * chunk), end = min(p, c * chunk + chunk - 1);     // inclusive
+    const int* bt = block_table + (long)token_item[t] * max_blocks;
+    const long kv_width = (long)n_kv_heads * D;
+    const float scale_log2 = scale * 1.4426950408889634f;
+    unsigned char* ring_k = ga_smem + (size_t)warp * RING * 2 * TILE_BYTES;
+    unsigned char* ring_v = ring_k + RING * TILE_BYTES;
+
+    // the queries of this lane's row: chunk 4u + tq serves k steps 2u (words 0, 1) and 2u + 1 (words 2, 3)
+    uint32_t qa[PAIRS][4];
+#pragma unroll
+    for (int u = 0; u < PAIRS; u++) {
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (g < heads) v = *reinterpret_cast<const uint4*>(q + (long)t * ld_q + (long)(hk * heads + g) * D + (4 * u + tq) * 8);
+        qa[u][0] = v.x; qa[u][1] = v.y; qa[u][2] = v.z; qa[u][3] = v.w;
+    }
+    float o[NT][2];
+#pragma unroll
+    for (int j = 0; j < NT; j++) o[j][0] = o[j][1] = 0.0f;
+    float m = -INFINITY, l = 0.0f;         // of row g; l is this lane's share of the sum
+
+    const int n_tiles = (end - begin) / 16 + 1;                         // of the chunk
+    const int my_tiles = n_tiles > warp ? (n_tiles - warp + 3) / 4 : 0; // tiles warp, warp + 4, ...
+    auto issue = [&](int i) {
+        if (i < my_tiles) {
+            const int first = begin + (warp + 4 * i) * 16;
+            unsigned char* tk = ring_k + (i % RING) * TILE_BYTES;
+            unsigned char* tv = ring_v + (i % RING) * TILE_BYTES;
+#pragma unroll
+            for (int r = 0; r < CH / 2; r++) {
+                const int idx = lane + 32 * r, key = idx / CH, ch = idx % CH;
+                const int j = first + key;
+                // keys: chunk position xor 4 on odd rows; values: xor the row's low three bits
+                unsigned char* dk = tk + key * (D * 2) + ((ch & ~7) | ((ch ^ ((key & 1) << 2)) & 7)) * 16;
+                unsigned char* dv = tv + key * (D * 2) + ((ch & ~7) | ((ch ^ key) & 7)) * 16;
+                if (j <= end) {
+                    const long base = ((long)bt[j / page_size] * page_size + (j % page_size)) * kv_width + (long)hk * D + ch * 8;
+                    cp_async_16(dk, k_pages + base);
+                    cp_async_16(dv, v_pages + base);
+                } else {
+                    *reinterpret_cast<uint4*>(dv) = make_uint4(0, 0, 0, 0);     // a value that is never weighted must not be NaN
+                    *reinterpret_cast<uint4*>(dk) = make_uint4(0, 0, 0, 0);
+                }
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    for (int i = 0; i < RING - 1; i++) issue(i);
+    for (int i = 0; i < my_tiles; i++) {
+        issue(i + RING - 1);
+        asm volatile("cp.async.wait_group %0;" ::"n"(RING - 1) : "memory");
+        __syncwarp();                                   // every lane's copies of this tile have landed
+        const int first = begin + (warp + 4 * i) * 16;
+        const unsigned char* tk = ring_k + (i % RING) * TILE_BYTES;
+        const uint32_t tv = (uint32_t)__cvta_generic_to_shared(ring_v + (i % RING) * TILE_BYTES);
+        // scores of row g against keys 2 tq, 2 tq + 1 of both halves of the tile
+        float s[2][4];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            s[h][0] = s[h][1] = s[h][2] = s[h][3] = 0.0f;
+            const int key = 8 * h + g;
+#pragma unroll
+            for (int u = 0; u < PAIRS; u++) {
+                const int ch = 4 * u + tq;
+                const uint4 kb = *reinterpret_cast<const uint4*>(tk + key * (D * 2) + ((ch & ~7) | ((ch ^ ((key & 1) << 2)) & 7)) * 16);
+                mma_bf16_16816(s[h][0], s[h][1], s[h][2], s[h][3], qa[u][0], 0u, qa[u][1], 0u, kb.x, kb.y);
+                mma_bf16_16816(s[h][0], s[h][1], s[h][2], s[h][3], qa[u][2], 0u, qa[u][3], 0u, kb.z, kb.w);
+            }
+        }
+        float tile_max = -INFINITY;
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int j = first + 8 * h + 2 * tq + e;
+                s[h][e] = j <= end ? s[h][e] * scale_log2 : -INFINITY;
+                tile_max = fmaxf(tile_max, s[h][e]);
+            }
+        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
+        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
+        const float m_new = fmaxf(m, tile_max);           // finite: the tile's first key is never past the end
+        const float corr = exp2f(m - m_new);
+        const float p00 = exp2f(s[0][0] - m_new), p01 = exp2f(s[0][1] - m_new);
+        const float p10 = exp2f(s[1][0] - m_new), p11 = exp2f(s[1][1] - m_new);
+        const uint32_t pa0 = pack_bf16(p00, p01), pa1 = pack_bf16(p10, p11);
+        // the sum uses the rounded weights the product below sees
+        const __nv_bfloat162 r0 = *reinterpret_cast<const __nv_bfloat162*>(&pa0), r1 = *reinterpret_cast<const __nv_bfloat162*>(&pa1);
+        l = l * corr + (__low2float(r0) + __high2float(r0)) + (__low2float(r1) + __high2float(r1));
+        m = m_new;
+        float unused0 = 0.0f, unused1 = 0.0f;             // rows 8..15 of the tiles
+#pragma unroll
+        for (int j = 0; j < NT; j += 2) {
+            // four 8 x 8 blocks of the value tile, transposed: (keys 0-7 | 8-15) x (dims 8j.. | 8(j+1)..)
+            const int key = (lane & 7) + ((lane >> 3) & 1) * 8, ch = j + (lane >> 4);
+            uint32_t b0, b1, b2, b3;
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                         : "r"(tv + key * (D * 2) + ((ch & ~7) | ((ch ^ key) & 7)) * 16));
+            o[j][0] *= corr; o[j][1] *= corr; o[j + 1][0] *= corr; o[j + 1][1] *= corr;
+            mma_bf16_16816(o[j][0], o[j][1], unused0, unused1, pa0, 0u, pa1, 0u, b0, b1);
+            mma_bf16_16816(o[j + 1][0], o[j + 1][1], unused0, unused1, pa0, 0u, pa1, 0u, b2, b3);
+        }
+        __syncwarp();                                   // the slot is copied into again two issues from now
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+
+    // merge the four warps (through the ring, free by now), always in the same order
+    __syncthreads();
+    float* sm_m = reinterpret_cast<float*>(ga_smem);           // [4][8]
+    float* sm_l = sm_m + 32;                                   // [4][8]
+    float* sm_acc = sm_l + 32;                                 // [4][8][D]
+    if (tq == 0) {
+        sm_m[warp * 8 + g] = m;
+        sm_l[warp * 8 + g] = l;
+    }
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+        sm_acc[(warp * 8 + g) * D + 8 * j + 2 * tq] = o[j][0];
+        sm_acc[(warp * 8 + g) * D + 8 * j + 2 * tq + 1] = o[j][1];
+    }
+    __syncthreads();
+    __shared__ int is_last[8];
+    for (int row = 0; row < heads; row++) {
+        const int h = hk * heads + row;
+        float big = -INFINITY;
+        for (int w = 0; w < 4; w++) big = fmaxf(big, sm_m[w * 8 + row]);
+        const long cell = (((long)t * n_heads + h) * max_chunks + c);
+        for (int d = threadIdx.x; d < D; d += 128) {
+            float acc = 0.0f;
+            for (int w = 0; w < 4; w++) {
+                const float mw = sm_m[w * 8 + row];
+                if (mw != -INFINITY) acc += sm_acc[(w * 8 + row) * D + d] * exp2f(mw - big);
+            }
+            part_acc[cell * D + d] = acc;
+        }
+        if (threadIdx.x == 0) {
+            float total = 0.0f;
+            for (int w = 0; w < 4; w++) {
+                const float mw = sm_m[w * 8 + row];
+                if (mw != -INFINITY) total += sm_l[w * 8 + row] * exp2f(mw - big);
+            }
+            part_ml[cell * 2] = big;
+            part_ml[cell * 2 + 1] = total;
+        }
+    }
+    // the CTA that arrives last for a (token, head) merges the chunks
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x < heads) {
+        const int h = hk * heads + threadIdx.x;
+        const int ticket = atomicAdd(&counters[t * n_heads + h], 1);
+        is_last[threadIdx.x] = (ticket == c_last - c_first);
+        if (is_last[threadIdx.x]) counters[t * n_heads + h] = 0;      // ready for the next launch
+    }
+    __syncthreads();
+    for (int row = 0; row < heads; row++) {
+        if (!is_last[row]) continue;
+        __threadfence();
+        const int h = hk * heads + row;
+        const long first_cell = ((long)t * n_heads + h) * max_chunks;
+        float top = -INFINITY;
+        for (int cc = c_first; cc <= c_last; cc++) top = fmaxf(top, __ldcg(part_ml + (first_cell + cc) * 2));
+        float denom = 0.0f;
+        for (int cc = c_first; cc <= c_last; cc++)
+            denom += __ldcg(part_ml + (first_cell + cc) * 2 + 1) * exp2f(__ldcg(part_ml + (first_cell + cc) * 2) - top);
+        for (int d = threadIdx.x; d < D; d += 128) {
+            float acc = 0.0f;
+            for (int cc = c_first; cc <= c_last; cc++)
+                acc += __ldcg(part_acc + (first_cell + cc) * D + d) * exp2f(__ldcg(part_ml + (first_cell + cc) * 2) - top);
+            out[(long)t * ld_out + (long)h * D + d] = __float2bfloat16_rn(acc / denom);
+        }
+    }
+}
+
+// Whether group_attention takes a layout: head size 64 or 128, at most eight query heads per
+// key/value head, rows of q on 16-byte boundaries.
+extern "C" int mllm_decode_group_attention_takes(int head_size, int n_heads, int n_kv_heads, long ld_q, const void* q) {
+    return (head_size == 64 || head_size == 128) && n_kv_heads > 0 && n_heads % n_kv_heads == 0 &&
+           n_heads / n_kv_heads <= 8 && ld_q % 8 == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0;
+}
+
+// Same arguments and scratch as mllm_decode_split_attention; chunk must be a multiple of 16.
+extern "C" int mllm_decode_group_attention(void* out, long ld_out, const void* q, long ld_q, const void* k_pages,
+                                           const void* v_pages, const int* block_table, int max_blocks,
+                                           const int* positions, const int* token_item, int n_tokens, int n_heads,
+                                           int n_kv_heads, int head_size, int page_size, float scale, int window,
+                                           int chunk, int max_chunks, float* part_acc, float* part_ml, int* counters,
+                                           void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (!mllm_decode_group_attention_takes(head_size, n_heads, n_kv_heads, ld_q, q))
+        return fail("group_attention: head size 64 or 128, at most 8 query heads per key/value head, q 16-byte aligned");
+    if (chunk <= 0 || chunk % 16 != 0 || max_chunks <= 0 || max_chunks > 65535 || n_kv_heads > 65535)
+        return fail("group_attention: bad chunking");
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(n_tokens, n_kv_heads, max_chunks);
+    const size_t smem = (size_t)4 * (256 / head_size) * 2 * 16 * head_size * 2;       // 64 KB
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(group_attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+            cudaFuncSetAttribute(group_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return fail("group_attention: cannot raise the shared memory limit");
+        configured = true;
+    }
+#define LAUNCH_GROUP(D)                                                                                              \
+    group_attention_kernel<D><<<grid, 128, smem, s>>>((bf16*)out, ld_out, (const bf16*)q, ld_q, (const bf16*)k_pages, \
+                                                      (const bf16*)v_pages, block_table, max_blocks, positions,      \
+                                                      token_item, n_heads, n_kv_heads, page_size, scale, window,     \
+                                                      chunk, max_chunks, part_acc, part_ml, counters)
+    if (head_size == 64) LAUNCH_GROUP(64);
+    else LAUNCH_GROUP(128);
+#undef LAUNCH_GROUP
+    return check_launch("group_attention_kernel");
+}
+
+// ---------------------------------------------------------------------------
 // Layer norm, one warp per row, the row read once.  Each lane keeps up to eight chunks of
 // four values in registers (rows up to 1024 wide); a wider row is re-read for each pass.
 // Same arithmetic as the plain kernel: mean, variance of the centred values, then

@@ -310,6 +310,49 @@ def split_attention(out, q, k_pages, v_pages, block_table, positions, token_item
     return out
 
 
+_group_attention = Function("decode", "mllm_decode_group_attention",
+                            [P, L, P, L, P, P, P, I, P, P, I, I, I, I, I, F, I, I, I, P, P, P, P])
+GROUP_ATTENTION_HEAD_SIZES = (64, 128)
+
+
+def group_attention_takes(q, n_heads, n_kv_heads, head_size) -> bool:
+    """Whether ``group_attention`` takes the layout: bfloat16, head size 64 or 128, at most
+    eight query heads per key/value head, rows of q on 16-byte boundaries."""
+    return (q.dtype == torch.bfloat16 and head_size in GROUP_ATTENTION_HEAD_SIZES and n_kv_heads > 0
+            and n_heads % n_kv_heads == 0 and n_heads // n_kv_heads <= 8 and q.stride(0) % 8 == 0
+            and q.data_ptr() % 16 == 0)
+
+
+def group_attention(out, q, k_pages, v_pages, block_table, positions, token_item, n_heads, n_kv_heads, head_size,
+                    page_size, scale, window, chunk, max_chunks, part_acc, part_ml, counters):
+    """``split_attention`` with the products on mma.sync tiles: one CTA per (token, key/value
+    head, chunk of keys), the query heads of the group as the rows of the tiles.  Same
+    arguments and scratch; ``chunk`` must be a multiple of 16."""
+    _check(out, "group_attention.out", torch.bfloat16, 2)
+    _check(q, "group_attention.q", torch.bfloat16, 2)
+    _check(k_pages, "group_attention.k_pages", torch.bfloat16)
+    _check(v_pages, "group_attention.v_pages", torch.bfloat16)
+    _check(block_table, "group_attention.block_table", torch.int32, 2)
+    _check(part_acc, "group_attention.part_acc", torch.float32)
+    _check(part_ml, "group_attention.part_ml", torch.float32)
+    _check(counters, "group_attention.counters", torch.int32)
+    n = q.shape[0]
+    cells = n * n_heads * max_chunks
+    if not group_attention_takes(q, n_heads, n_kv_heads, head_size) or chunk % 16 != 0:
+        raise KernelError(f"group_attention does not take head size {head_size} with {n_heads}/{n_kv_heads} heads")
+    if q.shape[1] != n_heads * head_size or out.shape != q.shape:
+        raise KernelError("group_attention: q / out do not have heads * head_size columns")
+    if part_acc.numel() < cells * head_size or part_ml.numel() < cells * 2 or counters.numel() < n * n_heads:
+        raise KernelError("group_attention: scratch too small")
+    if max_chunks * chunk < page_size * block_table.shape[1]:
+        raise KernelError("group_attention: the chunks do not cover the longest block table")
+    _group_attention(out.data_ptr(), out.stride(0), q.data_ptr(), q.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
+                     block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), token_item.data_ptr(), n,
+                     n_heads, n_kv_heads, head_size, page_size, float(scale), int(window or 0), int(chunk),
+                     int(max_chunks), part_acc.data_ptr(), part_ml.data_ptr(), counters.data_ptr(), _stream())
+    return out
+
+
 # ---- tensor-core matrix product (bfloat16) -------------------------------------------------------
 
 _gemm_bf16 = Function("gemm", "mllm_gemm_bf16", [P, P, P, P, I, I, I, L, L, I, I, P, P, L, P, I, P])

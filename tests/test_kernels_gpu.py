@@ -354,6 +354,64 @@ def test_split_attention_over_pages(n_heads, n_kv_heads, head, page, window, chu
         out.fill_(float("nan"))
 
 
+@pytest.mark.parametrize("n_heads, n_kv_heads, head, page, window", [
+    (6, 2, 64, 16, 0), (12, 12, 64, 64, 0), (8, 1, 64, 8, 0), (2, 2, 128, 8, 0), (4, 1, 128, 32, 0),
+    (2, 2, 64, 16, 16), (6, 3, 64, 4, 150), (25, 25, 64, 16, 0)])
+@pytest.mark.parametrize("chunk", [64, 128, 512])
+def test_group_attention_over_pages(n_heads, n_kv_heads, head, page, window, chunk):
+    """The mma.sync variant of split_attention: groups of 1 to 8 query heads per key/value
+    head, lengths that end inside a tile of 16 keys, twice on the same scratch."""
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(n_heads * head + page + chunk)
+    lengths, n_new = [37, 1, 300, 64, 17, 129, 700], [37, 1, 1, 9, 2, 1, 3]
+    k_pages, v_pages, table, positions, items, dense = paged_case(rng, lengths, n_new, n_heads, n_kv_heads, head,
+                                                                  page, torch.bfloat16)
+    dense = [(f64(dev(k, torch.bfloat16)), f64(dev(v, torch.bfloat16))) for k, v in dense]
+    n = len(f64(positions))
+    q = dev(rng.normal(size=(n, n_heads * head)), torch.bfloat16)
+    out = torch.full_like(q, float("nan"))
+    scale = 1.0 / math.sqrt(head)
+    max_chunks = -(-(table.shape[1] * page) // chunk)
+    acc, ml, counters = split_scratch(n, n_heads, max_chunks, head)
+    assert ops.group_attention_takes(q, n_heads, n_kv_heads, head)
+    expected = attention_expected(f64(q), dense, f64(positions).astype(int), f64(items).astype(int), n_heads,
+                                  n_kv_heads, head, scale, window)
+    for _ in range(2):
+        ops.group_attention(out, q, k_pages, v_pages, table, positions, items, n_heads, n_kv_heads, head, page,
+                            scale, window, chunk, max_chunks, acc, ml, counters)
+        np.testing.assert_allclose(f64(out), expected, rtol=0, atol=tol(torch.bfloat16, 2))
+        assert int(counters.abs().sum()) == 0
+        out.fill_(float("nan"))
+
+
+def test_group_attention_finds_one_far_key_and_respects_the_windows_edge():
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(5)
+    head, page, length, chunk = 64, 16, 500, 64
+    far = 3 * page + 5
+    k_pages, v_pages, table, positions, items, dense = paged_case(rng, [length], [1], 1, 1, head, page, torch.bfloat16)
+    k, v = dense[0]
+    q = rng.normal(size=(1, head))
+    k[far] = q[0] * 4.0
+    v[far] = 100.0 + np.arange(head)
+    block, offset = int(f64(table)[0, far // page]), far % page
+    k_pages[block, offset] = dev(k[far], torch.bfloat16)
+    v_pages[block, offset] = dev(v[far], torch.bfloat16)
+    qd = dev(q, torch.bfloat16)
+    out = torch.empty_like(qd)
+    scale = 1.0 / math.sqrt(head)
+    max_chunks = -(-(table.shape[1] * page) // chunk)
+    scratch = split_scratch(1, 1, max_chunks, head)
+    run = lambda window: ops.group_attention(out, qd, k_pages, v_pages, table, positions, items, 1, 1, head, page,
+                                             scale, window, chunk, max_chunks, *scratch)
+    run(0)
+    np.testing.assert_allclose(f64(out)[0], f64(dev(v[far], torch.bfloat16)), rtol=2e-2, atol=0.5)
+    run(length - 1 - far)
+    assert float(out.float().abs().max()) < 10.0
+    run(length - far)
+    np.testing.assert_allclose(f64(out)[0], f64(dev(v[far], torch.bfloat16)), rtol=2e-2, atol=0.5)
+
+
 def test_split_attention_finds_one_far_key_and_respects_the_windows_edge():
     from mini_llm_b200.kernels import ops
     rng = np.random.default_rng(5)

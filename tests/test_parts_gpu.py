@@ -97,7 +97,8 @@ def test_norm_feed_forward_embedding_head(dtype, plain_only):
 
 
 @pytest.mark.parametrize("dtype, plain_only", MODES)
-@pytest.mark.parametrize("n_heads, n_kv_heads, head, window", [(3, 3, 32, None), (4, 2, 16, None), (2, 2, 48, 5)])
+@pytest.mark.parametrize("n_heads, n_kv_heads, head, window", [(3, 3, 32, None), (4, 2, 16, None), (2, 2, 48, 5),
+                                                              (6, 2, 64, None), (8, 1, 64, 9)])
 def test_attention_part_with_its_cache(dtype, plain_only, n_heads, n_kv_heads, head, window):
     """Two requests; the first comes in two steps, so the second step reads keys the first
     stored.  Compared with plain attention over the whole sequences."""
