@@ -226,7 +226,7 @@ def e2e_run(folder, args, context: int, vocab: int):
     out = llm.generate(prompts, max_new_tokens=steps + warmup, temperature=0.0, on_token=on_token)
     assert all(len(tokens) == steps + warmup for tokens in out)
     seconds = stamps[-1] - stamps[warmup - 1]              # K steps after the warm-up steps
-    control_bytes = 4 * (7 * batch + (batch & 1) + 2 * batch + batch * llm.engine.cache.groups[0].max_blocks)
+    control_bytes = llm.engine.control.last_upload_bytes        # the control block of a decode step, as copied
     return {"value": batch * steps / seconds, "unit": "tokens/s", "h2d_bytes_per_step": control_bytes,
             "d2h_bytes_per_step": 4 * batch, "ms_per_step": 1000.0 * seconds / steps}
 

@@ -39,19 +39,27 @@ class Workspace:
 
 
 class ControlBlock:
-    """One int32 device buffer with the step's token arrays and block tables,
-    filled through pinned host memory with a single copy."""
+    """The step's token arrays and block tables in one int32 device buffer, written with a
+    single copy from pinned host memory.
+
+    There are two device buffers.  Steps that ask for it (``alternate``) use them in turn and
+    copy on a stream of their own: the arrays of step k+1 are on the device while the kernels
+    of step k still read theirs, so no copy stands between two steps' kernels; a step's kernels
+    wait for their copy, and a copy waits for the kernels that read the buffer it overwrites
+    (``consumed`` records them).  Other steps keep to the first buffer (their kernels are
+    replayed from graphs with fixed addresses) and copy in the order of the compute stream."""
 
     def __init__(self, device, groups):
         self.device = device
         self.groups = [(g.index, g.max_blocks) for g in groups if g.paged]
         self.capacity = 0
-        self.device_buffer = None
+        self.device_buffers = [None, None]
+        self.copy_stream = torch.cuda.Stream(device=device)
         self._host = []
-        self._events = []
         self._layouts = {}
-        self._turn = 0
+        self.parity = 0
         self.generation = 0
+        self.last_upload_bytes = 0            # bytes of the last step's host-to-device copy
 
     @staticmethod
     def tile_ints(n_tokens: int, n_items: int) -> int:
@@ -81,42 +89,68 @@ class ControlBlock:
     def _ensure(self, size: int):
         if size <= self.capacity:
             return
+        torch.cuda.synchronize(self.device)      # nothing may still read or fill the old buffers
         self.capacity = max(size, 2 * self.capacity, 4096)
-        self.device_buffer = torch.zeros(self.capacity, dtype=torch.int32, device=self.device)
+        self.device_buffers = [torch.zeros(self.capacity, dtype=torch.int32, device=self.device) for _ in range(2)]
         self._host = [torch.zeros(self.capacity, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._host_np = [h.numpy() for h in self._host]
-        self._events = [torch.cuda.Event(), torch.cuda.Event()]
-        self._recorded = [False, False]
-        self._layouts = {}                   # (tokens, entries) -> (offsets, size, device views)
+        self._copied = [torch.cuda.Event(), torch.cuda.Event()]       # the copy out of host buffer t is done
+        self._copied_once = [False, False]
+        self._host_turn = 0
+        self._consumed = [torch.cuda.Event(), torch.cuda.Event()]     # the kernels that read device buffer p are done
+        self._in_use = [False, False]
+        self._layouts = {}                   # (parity, tokens, entries) -> (offsets, size, device views)
         self.generation += 1
 
-    def upload(self, arrays: dict, n_tokens: int, n_items: int):
+    def upload(self, arrays: dict, n_tokens: int, n_items: int, alternate: bool = True):
         """``arrays``: name -> numpy array (int32, or float32/int64 viewed as
-        int32).  Returns name -> device view."""
-        key = (n_tokens, n_items)
+        int32).  Returns name -> device view (of this step's buffer).  ``alternate=False``
+        keeps to the first buffer: steps whose kernels are replayed from a captured graph
+        (fixed addresses) use that, and wait for the step before them."""
+        self.parity = (self.parity ^ 1) if alternate else 0
+        parity = self.parity
+        key = (parity, n_tokens, n_items)
         held = self._layouts.get(key)
         if held is None:
             offsets, size = self._layout(n_tokens, n_items)
             self._ensure(size)               # may drop every cached layout
-            held = self._layouts[key] = (offsets, size, self._views(offsets, n_tokens, n_items))
+            held = self._layouts[key] = (offsets, size, self._views(self.device_buffers[parity], offsets, n_tokens, n_items))
         offsets, size, views = held
-        self._turn ^= 1
-        turn = self._turn
-        if self._recorded[turn]:
-            self._events[turn].synchronize()  # the copy that last used this host buffer is done
+        self.last_upload_bytes = 4 * size
+        # host side: two pinned buffers in turn; the copy that last read this one must be done
+        self._host_turn ^= 1
+        turn = self._host_turn
+        if self._copied_once[turn]:
+            self._copied[turn].synchronize()
         host_np = self._host_np[turn]
         for name, values in arrays.items():
             flat = np.ascontiguousarray(values).reshape(-1).view(np.int32)
             start = offsets[name]
             host_np[start:start + flat.size] = flat
-        self.device_buffer[:size].copy_(self._host[turn][:size], non_blocking=True)
-        self._events[turn].record()
-        self._recorded[turn] = True
+        compute = torch.cuda.current_stream(self.device)
+        if alternate:
+            # beside the kernels of the step before; behind the kernels that last read this buffer
+            with torch.cuda.stream(self.copy_stream):
+                if self._in_use[parity]:
+                    self.copy_stream.wait_event(self._consumed[parity])
+                self.device_buffers[parity][:size].copy_(self._host[turn][:size], non_blocking=True)
+                self._copied[turn].record(self.copy_stream)
+            compute.wait_event(self._copied[turn])
+        else:
+            # in the order of the compute stream: behind everything that read the buffer
+            self.device_buffers[parity][:size].copy_(self._host[turn][:size], non_blocking=True)
+            self._copied[turn].record(compute)
+        self._copied_once[turn] = True
         return views
 
-    def _views(self, offsets, n_tokens: int, n_items: int):
+    def consumed(self) -> None:
+        """Call after the step's kernels are enqueued: its buffer may be overwritten once they
+        are done."""
+        self._consumed[self.parity].record(torch.cuda.current_stream(self.device))
+        self._in_use[self.parity] = True
+
+    def _views(self, buffer, offsets, n_tokens: int, n_items: int):
         views = {}
-        buffer = self.device_buffer
         for name, start in offsets.items():
             if name == "seeds":
                 views[name] = buffer[start:start + 2 * n_tokens].view(torch.int64)

@@ -97,6 +97,9 @@ class Engine:
         self._kept_valid = set()              # slots whose entry of kept_tokens is a sampled token
         self._readback = [None, None]         # per step parity: (pinned host buffer, rows, event)
         self._turn = 0
+        self._alternated = False              # whether the last step took its arrays from the alternating buffers
+        self._readback_stream = torch.cuda.Stream(device=self.device)    # sampled ids go to the host beside the next step
+        self._sampled_events = [torch.cuda.Event(), torch.cuda.Event()]  # a step's sampling is done
         self._graphs = {}
         self._graph_stamp = None
         self.fused = FusedDecodePlan.build(self) if fused_decode else None
@@ -225,7 +228,10 @@ class Engine:
             arrays["top_p"] = np.array([s.top_p for s in sampling], dtype=np.float32)
             arrays["seeds"] = np.array([s.seed & 0xFFFFFFFFFFFFFFFF for s in sampling], dtype=np.uint64)
             arrays["counters"] = np.array([s.counter for s in sampling], dtype=np.int32)
-        views = self.control.upload(arrays, n_tokens, n_items)
+        # the one-kernel decode step takes its arrays from alternating buffers, so that the next
+        # step's copy runs beside it; captured graphs have their addresses fixed
+        alternate = self.fused is not None and self.fused.takes_sizes(n_tokens, all(n == 1 for n in ctx.item_counts))
+        views = self.control.upload(arrays, n_tokens, n_items, alternate)
 
         ctx.n_tokens, ctx.n_items, ctx.n_want = n_tokens, n_items, n_want
         ctx.token_ids, ctx.positions, ctx.token_item = views["token_ids"], views["positions"], views["token_item"]
@@ -244,18 +250,38 @@ class Engine:
         if sampling is not None and n_want > 0:
             sample_views = (views["temperature"][:n_want], views["top_p"][:n_want], views["seeds"][:n_want],
                             views["counters"][:n_want])
+        self._turn ^= 1                       # the slot of the readback ring this step fills
+        compute = torch.cuda.current_stream(self.device)
+        # This step's kernels write their sampled ids where an earlier step left its own: that
+        # step's copy to the host must be done.  Two steps that alternate use different buffers,
+        # so the second need not wait for the first one's copy (it runs beside it).
+        for slot in (self._turn, self._turn ^ 1):
+            beside = slot != self._turn and alternate and self._alternated
+            if self._readback[slot] is not None and not beside:
+                compute.wait_event(self._readback[slot][2])
+        self._alternated = alternate
         logits = self._run(ctx, sample_views)
+        self.control.consumed()
         for entry in entries:
             self.cache.commit(entry.slot, len(entry.tokens))
         self.steps += 1
-        self._turn ^= 1
         if self._sampled is not None:
-            # the sampled ids start for the host right behind the step's kernels
+            # the sampled ids start for the host right behind the step's kernels; for the steps
+            # that alternate on a stream of their own, so that the next step's kernels do not
+            # queue behind the copy
             held = self._readback[self._turn]
             if held is None or held[0].shape[0] < n_want:
                 held = (torch.empty(max(n_want, 64), dtype=torch.int32).pin_memory(), 0, torch.cuda.Event())
-            held[0][:n_want].copy_(self._sampled[:n_want], non_blocking=True)
-            held[2].record()
+            if alternate:
+                done = self._sampled_events[self._turn]
+                done.record(compute)
+                with torch.cuda.stream(self._readback_stream):
+                    self._readback_stream.wait_event(done)
+                    held[0][:n_want].copy_(self._sampled[:n_want], non_blocking=True)
+                    held[2].record(self._readback_stream)
+            else:
+                held[0][:n_want].copy_(self._sampled[:n_want], non_blocking=True)
+                held[2].record(compute)
             self._readback[self._turn] = (held[0], n_want, held[2])
             for entry in entries:
                 if entry.want:
@@ -271,7 +297,7 @@ class Engine:
         logits = self.model.forward(ctx, self.storage.views)
         self._sampled = None
         if sample_views is not None and logits is not None:
-            out = self.workspace.get("sampled", (ctx.n_want,), torch.int32)
+            out = self.workspace.get(f"sampled{self.control.parity}", (ctx.n_want,), torch.int32)
             self.kernels.sample_rows(out, logits, *sample_views, any_nucleus=self._any_nucleus)
             self.kernels.keep_tokens(self.kept_tokens, ctx.want_slots, out)
             self._sampled = out
@@ -300,7 +326,7 @@ class Engine:
             self._graphs.clear()                      # a buffer moved: captured addresses are stale
             self._graph_stamp = stamp
         key = (ctx.n_tokens, ctx.n_items, ctx.n_want, ctx.n_att_tiles, ctx.att_parts, sample_views is not None,
-               self._any_nucleus, ctx.any_previous)
+               self._any_nucleus, ctx.any_previous, self.control.parity)
         held = self._graphs.get(key)
         if held is None:
             if len(self._graphs) >= 48:

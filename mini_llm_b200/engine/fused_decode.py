@@ -112,16 +112,19 @@ class FusedDecodePlan:
         self.cand_index = torch.empty(MAX_TOKENS * self.grid, dtype=torch.int32, device=device)
         self.cand_done = torch.zeros(1, dtype=torch.int32, device=device)
         self.barrier = torch.zeros(1, dtype=torch.int64, device=device)
-        self.out_tokens = torch.zeros(MAX_TOKENS, dtype=torch.int32, device=device)
+        self.out_tokens = torch.zeros(2, MAX_TOKENS, dtype=torch.int32, device=device)     # by the step's parity
         heads, head_size = self.sizes[1], self.sizes[3]
         self.att_partial = torch.empty(MAX_TOKENS * heads * MAX_ATTENTION_PARTS * (head_size + 2), dtype=torch.float32,
                                        device=device)
         self.att_counters = torch.zeros(MAX_TOKENS * heads, dtype=torch.int32, device=device)
 
     def takes(self, ctx) -> bool:
+        return self.takes_sizes(ctx.n_tokens, ctx.decode_only)
+
+    def takes_sizes(self, n_tokens: int, decode_only: bool) -> bool:
         width, heads, kv_heads, head_size, inner, _ = self.sizes
-        return (ctx.decode_only and ctx.n_tokens <= MAX_TOKENS
-                and bool(self.lib.mllm_fused_takes(ctx.n_tokens, width, heads, kv_heads, head_size, inner, self.max_blocks)))
+        return (decode_only and n_tokens <= MAX_TOKENS
+                and bool(self.lib.mllm_fused_takes(n_tokens, width, heads, kv_heads, head_size, inner, self.max_blocks)))
 
     def attention_parts(self, ctx) -> int:
         """How many CTAs share the keys of one (token, head) pair: as many as leave every CTA at
@@ -138,7 +141,7 @@ class FusedDecodePlan:
         # Steps of one shape find all their arrays at the same addresses (the control block's
         # layout depends on the step's sizes only): their parameters are filled once.
         parts = self.attention_parts(ctx)
-        key = (ctx.n_tokens, ctx.n_want, sampling, self.timeline is not None, parts,
+        key = (ctx.n_tokens, ctx.n_want, sampling, self.timeline is not None, parts, engine.control.parity,
                engine.workspace.generation, engine.control.generation)
         held = self._filled.get(key)
         if held is None:
@@ -185,8 +188,8 @@ class FusedDecodePlan:
             params.sample = 1
             params.temperature, params.top_p = temperature.data_ptr(), top_p.data_ptr()
             params.seeds, params.counters = seeds.data_ptr(), counters.data_ptr()
-            sampled = self.out_tokens[:ctx.n_want]
-        params.out_tokens = self.out_tokens.data_ptr()
+            sampled = self.out_tokens[engine.control.parity, :ctx.n_want]
+        params.out_tokens = self.out_tokens[engine.control.parity].data_ptr()
         params.kept, params.n_kept = engine.kept_tokens.data_ptr(), engine.kept_tokens.shape[0]
         params.want_slots = ctx.want_slots.data_ptr()
         params.cand_value, params.cand_index = self.cand_value.data_ptr(), self.cand_index.data_ptr()
