@@ -292,6 +292,10 @@ class Engine:
 
     # ---- running the model: eagerly, or as a replayed CUDA graph ---------------------------------
     def _forward(self, ctx, sample_views):
+        with ops.launches_on_current_stream():
+            return self._forward_on_stream(ctx, sample_views)
+
+    def _forward_on_stream(self, ctx, sample_views):
         if ctx.any_previous:
             self.kernels.resolve_tokens(ctx.token_ids, self.kept_tokens)
         logits = self.model.forward(ctx, self.storage.views)

@@ -27,8 +27,29 @@ def dtype_code(dtype: torch.dtype) -> int:
         raise KernelError(f"unsupported element type {dtype}") from None
 
 
+_pinned_stream = None
+
+
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """The stream launches go to: the current stream, looked up per launch, or the one a
+    caller pinned for a run of launches (the lookup costs more than a launch's own checks)."""
+    return _pinned_stream if _pinned_stream is not None else torch.cuda.current_stream().cuda_stream
+
+
+class launches_on_current_stream:
+    """Within the block every launch of this module goes to the stream that is current at
+    entry (do not switch streams inside)."""
+
+    def __enter__(self):
+        global _pinned_stream
+        self.before = _pinned_stream
+        _pinned_stream = torch.cuda.current_stream().cuda_stream
+        return self
+
+    def __exit__(self, *exc):
+        global _pinned_stream
+        _pinned_stream = self.before
+        return False
 
 
 def _check(t: torch.Tensor, name: str, dtype=None, dims=None) -> None:
