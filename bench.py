@@ -189,7 +189,7 @@ def prefill_run(engine, n_prompts: int, length: int, vocab: int, repeats: int = 
     rng = np.random.default_rng(99)
     prompts = [rng.integers(0, vocab, length).tolist() for _ in range(n_prompts)]
     times = []
-    for repeat in range(repeats + 2):
+    for repeat in range(repeats + 5):                    # the first runs are eager, then one captures a graph
         slots = [engine.open_request() for _ in range(n_prompts)]
         torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -197,7 +197,7 @@ def prefill_run(engine, n_prompts: int, length: int, vocab: int, repeats: int = 
         engine.step([StepEntry(slot, prompt, [length - 1]) for slot, prompt in zip(slots, prompts)])
         stop.record()
         torch.cuda.synchronize()
-        if repeat >= 2:
+        if repeat >= 5:
             times.append(start.elapsed_time(stop))
         for slot in slots:
             engine.close_request(slot)
@@ -214,19 +214,21 @@ def e2e_run(folder, args, context: int, vocab: int):
     rng = np.random.default_rng(4321)
     prompt_len = context - steps - warmup
     prompts = [rng.integers(0, vocab, prompt_len).tolist() for _ in range(batch)]
+    # every prompt is admitted in the first step, so that all requests decode side by side to the end
     llm = LLM(folder, dtype=args.dtype, max_sessions=batch, cache_tokens=batch * context,
-              max_tokens_per_step=max(2048, batch), plain_kernels=args.plain_kernels)
-    stamps = []
+              max_tokens_per_step=batch * context, plain_kernels=args.plain_kernels)
+    stamps, uploads = [], []
 
     def on_token(index, token, reason):
         if index == batch - 1:
             stamps.append(time.perf_counter())
+            uploads.append(llm.engine.control.last_upload_bytes)
 
     launches_before = llm.engine.kernels.launches
     out = llm.generate(prompts, max_new_tokens=steps + warmup, temperature=0.0, on_token=on_token)
     assert all(len(tokens) == steps + warmup for tokens in out)
     seconds = stamps[-1] - stamps[warmup - 1]              # K steps after the warm-up steps
-    control_bytes = llm.engine.control.last_upload_bytes        # the control block of a decode step, as copied
+    control_bytes = uploads[len(uploads) // 2]                  # the control block of a decode step, as copied
     return {"value": batch * steps / seconds, "unit": "tokens/s", "h2d_bytes_per_step": control_bytes,
             "d2h_bytes_per_step": 4 * batch, "ms_per_step": 1000.0 * seconds / steps}
 

@@ -332,12 +332,15 @@ class Engine:
         key = (ctx.n_tokens, ctx.n_items, ctx.n_want, ctx.n_att_tiles, ctx.att_parts, sample_views is not None,
                self._any_nucleus, ctx.any_previous, self.control.parity)
         held = self._graphs.get(key)
-        if held is None:
-            if len(self._graphs) >= 48:
+        # A capture costs as much as about twenty eager steps: a decode shape comes back at once
+        # and is captured the second time it is seen, a shape with prompt portions the fourth.
+        wait = 1 if ctx.decode_only else 3
+        if held is None or (isinstance(held, int) and held < wait):
+            if held is None and len(self._graphs) >= 48:
                 self._graphs.clear()                  # many shapes came by: start over rather than grow
-            self._graphs[key] = "warm"                # run once eagerly: every buffer gets allocated
+            self._graphs[key] = (held or 0) + 1       # run eagerly: every buffer gets allocated
             return self._forward(ctx, sample_views)
-        if held == "warm":
+        if isinstance(held, int):
             before = self.kernels.launches
             graph = torch.cuda.CUDAGraph()
             # "relaxed": only this engine's kernels are launched in here, but the collector may
