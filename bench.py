@@ -33,6 +33,10 @@ sys.path.insert(0, ROOT)
 GPT2_SMALL = {"architectures": ["GPT2LMHeadModel"], "model_type": "gpt2", "n_layer": 12, "n_embd": 768, "n_head": 12,
               "n_inner": 3072, "vocab_size": 50257, "n_positions": 1024, "activation_function": "gelu_new",
               "layer_norm_epsilon": 1e-5, "tie_word_embeddings": True}
+# The other GPT-2 sizes, for runs beside the headline one (--model).
+SIZES = {"small": {}, "medium": {"n_layer": 24, "n_embd": 1024, "n_head": 16, "n_inner": 4096},
+         "large": {"n_layer": 36, "n_embd": 1280, "n_head": 20, "n_inner": 5120},
+         "xl": {"n_layer": 48, "n_embd": 1600, "n_head": 25, "n_inner": 6400}}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -44,7 +48,8 @@ def parse_args():
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--dtype", default="bfloat16", choices=("bfloat16", "float32"))
-    parser.add_argument("--layers", type=int, default=GPT2_SMALL["n_layer"])
+    parser.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in the line)")
+    parser.add_argument("--model", default="small", choices=sorted(SIZES), help="GPT-2 size; the headline run is small")
     parser.add_argument("--plain-kernels", action="store_true")
     parser.add_argument("--no-extras", action="store_true", help="skip prefill, batch 1/64 and the end-to-end run")
     parser.add_argument("--page-size", type=int, default=None, help="tokens per cache page (the engine's default if not given)")
@@ -237,8 +242,10 @@ def run_ours(args):
     import torch
     from mini_llm_b200.engine import Engine
 
-    config = dict(GPT2_SMALL)
-    config["n_layer"] = args.layers
+    config = dict(GPT2_SMALL, **SIZES[args.model])
+    layers_of_model = config["n_layer"]
+    if args.layers is not None:
+        config["n_layer"] = args.layers
     context, vocab = config["n_positions"], config["vocab_size"]
     dtype_bytes = 2 if args.dtype == "bfloat16" else 4
     peak = peaks()
@@ -261,11 +268,11 @@ def run_ours(args):
         step_bytes = weight_bytes + args.batch * mean_cached * kv_per_token
         achieved = step_bytes / (ms * 1e-3) / 1e9
         line = {
-            "metric": "decode tokens/s, GPT-2 small, batch 8, context 1024", "value": args.batch / (ms * 1e-3),
+            "metric": f"decode tokens/s, GPT-2 {args.model}, batch {args.batch}, context {context}", "value": args.batch / (ms * 1e-3),
             "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if dtype_bytes == 2 else "fp32",
             "data": "synthetic: seeded random weights (N(0, 0.02)) and uniform random token ids", "impl": "ours",
-            "config": {"model": "gpt2-small", "n_layer": config["n_layer"], "n_layer_of_model": GPT2_SMALL["n_layer"],
+            "config": {"model": f"gpt2-{args.model}", "n_layer": config["n_layer"], "n_layer_of_model": layers_of_model,
                        "n_embd": config["n_embd"], "n_head": config["n_head"], "n_inner": config["n_inner"],
                        "vocab_size": vocab, "n_positions": context, "global_batch": args.batch, "seq_len": context,
                        "prompt_tokens": context - args.steps - args.warmup, "page_size": engine.page_size,
@@ -387,7 +394,7 @@ def run_reference(args):
     ms = start.elapsed_time(stop) / steps
     for cache in caches:
         engine.release_cache(cache)
-    line = {"metric": "decode tokens/s, GPT-2 small, batch 8, context 1024", "value": batch / (ms * 1e-3),
+    line = {"metric": f"decode tokens/s, GPT-2 {args.model}, batch {args.batch}, context {context}", "value": batch / (ms * 1e-3),
             "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16 weights, fp32 arithmetic",
             "data": "synthetic: seeded random weights (N(0, 0.02)) and uniform random token ids", "impl": "reference",
