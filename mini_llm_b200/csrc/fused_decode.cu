@@ -94,9 +94,10 @@ constexpr int THREADS = 512;
 constexpr int WARPS = THREADS / 32;
 constexpr int MAX_TOKENS = 16;
 constexpr int XS_PAD = 32;           // bf16 elements between the rows staged in shared memory
-// K steps of weights a warp prefetches into shared memory per phase: with one token tile
-// there is room for every step of the widest product of GPT-2 small, with two for fewer.
-__host__ __device__ constexpr int resident_of(int nt) { return nt == 1 ? 6 : 4; }
+// RES (a template parameter of the kernel): K steps of weights a warp prefetches into shared
+// memory per phase, 6, 4 or 2; the launcher takes the largest that leaves room for the staged
+// activations (with one token tile of GPT-2 small there is room for every step of its widest
+// product).
 constexpr unsigned long long BARRIER_LIMIT_NS = 2000000000ull;
 enum { OUT_BF16 = 0, OUT_ADD = 1, OUT_QKV = 2, OUT_LOGITS = 3 };
 
@@ -113,7 +114,7 @@ struct Shared {
     bf16* xs;                  // staged activations [NT * 8][k_max + XS_PAD]
     float* red;                // partial tiles [WARPS][32][NT * 4]
     float* att;                // attention merge [WARPS][2 + 256]
-    uint4* wbuf;               // prefetched weight fragments [2 * resident_of(NT)][THREADS]
+    uint4* wbuf;               // prefetched weight fragments [2 * RES][THREADS]
     float* bias;               // [2][THREADS][2], by phase parity
     float* old;                // [THREADS][NT * 4]
     float* gb;                 // norm gain and shift [2][E]
@@ -122,10 +123,10 @@ struct Shared {
     int* table;                // [T][max_blocks]
 };
 
-__host__ __device__ inline size_t shared_bytes(int nt, int E, int I, int HD, int max_blocks) {
+__host__ __device__ inline size_t shared_bytes(int nt, int res, int E, int I, int HD, int max_blocks) {
     const int k_max = E > I ? (E > HD ? E : HD) : (I > HD ? I : HD);
     return (size_t)nt * 8 * (k_max + XS_PAD) * 2 + (size_t)WARPS * 32 * nt * 4 * 4 + (size_t)WARPS * (2 + 256) * 4 +
-           (size_t)2 * resident_of(nt) * THREADS * 16 + (size_t)2 * THREADS * 2 * 4 + (size_t)THREADS * nt * 4 * 4 +
+           (size_t)2 * res * THREADS * 16 + (size_t)2 * THREADS * 2 * 4 + (size_t)THREADS * nt * 4 * 4 +
            (size_t)2 * E * 4 + MAX_TOKENS * 8 + MAX_TOKENS * 4 + (size_t)MAX_TOKENS * max_blocks * 4 + 64;
 }
 
@@ -216,7 +217,7 @@ __device__ __forceinline__ Split split_of(int N, int K, int kind) {
 // Start copying what `phase` needs and what is final already: this thread's first weight
 // fragments (its private slots of wbuf), the biases of its rows, the values its results are
 // added to, and (all threads together) the gain and shift of the phase's input norm.
-template <int NT>
+template <int NT, int RES>
 __device__ void prefetch_phase(const FusedParams& p, const Shared& sm, const Phase& phase, int parity, int n_rows) {
     if (phase.w != nullptr) {
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -228,7 +229,7 @@ __device__ void prefetch_phase(const FusedParams& p, const Shared& sm, const Pha
             const bf16* w_lo = phase.w + (long)min(row_lo, phase.N - 1) * phase.K + q * 8;
             const bf16* w_hi = phase.w + (long)min(row_hi, phase.N - 1) * phase.K + q * 8;
             const int k_begin = part * s.per_part, k_end = min(phase.K / 32, k_begin + s.per_part);
-            for (int u = 0; u < resident_of(NT) && k_begin + u < k_end; u++) {
+            for (int u = 0; u < RES && k_begin + u < k_end; u++) {
                 copy_async_16(sm.wbuf + (2 * u) * THREADS + threadIdx.x, w_lo + (k_begin + u) * 32);
                 copy_async_16(sm.wbuf + (2 * u + 1) * THREADS + threadIdx.x, w_hi + (k_begin + u) * 32);
             }
@@ -384,7 +385,7 @@ __device__ __forceinline__ float sampling_score(const FusedParams& p, int m, int
 
 // One product phase on the tensor cores.  The CTA takes its share of the 16-row blocks of
 // w [N, K]; with fewer blocks than warps, the warps of a block split its K range and their
-// partial tiles meet in shared memory, added in part order.  The first resident_of(NT) K steps of a
+// partial tiles meet in shared memory, added in part order.  The first RES K steps of a
 // warp's first block were prefetched into wbuf; the rest stream in from L2 / HBM.
 //
 // A lane (g = lane / 4, q = lane % 4) takes eight consecutive K values of rows g and g + 8
@@ -393,7 +394,7 @@ __device__ __forceinline__ float sampling_score(const FusedParams& p, int m, int
 // and B agree, so the eight values feed two instructions: values 0..3 the first (slots 2q,
 // 2q+1, 2q+8, 2q+9), values 4..7 the second.
 // Once a thread has read its prefetched data it starts the prefetch of `next`.
-template <int NT>
+template <int NT, int RES>
 __device__ void product_phase(const FusedParams& p, const Shared& sm, const Phase& phase, int parity, int ldx, int n_rows,
                               int activation, const FusedLayer* layer, const Phase& next, float* best_value,
                               int* best_index) {
@@ -421,7 +422,7 @@ __device__ void product_phase(const FusedParams& p, const Shared& sm, const Phas
             const int k_begin = part * sp.per_part, k_end = min(k_steps, k_begin + sp.per_part);
             int ks = k_begin;
             if (b0 == 0) {
-                for (int u = 0; u < resident_of(NT) && ks < k_end; u++, ks++) {
+                for (int u = 0; u < RES && ks < k_end; u++, ks++) {
                     const uint4 wl = sm.wbuf[(2 * u) * THREADS + threadIdx.x];
                     const uint4 wh = sm.wbuf[(2 * u + 1) * THREADS + threadIdx.x];
 #pragma unroll
@@ -495,7 +496,7 @@ __device__ void product_phase(const FusedParams& p, const Shared& sm, const Phas
                 }
             }
         }
-        if (b0 == 0) prefetch_phase<NT>(p, sm, next, parity ^ 1, p.T);
+        if (b0 == 0) prefetch_phase<NT, RES>(p, sm, next, parity ^ 1, p.T);
         if (split > 1) {
             float* mine = sm.red + (warp * 32 + lane) * (NT * 4);
 #pragma unroll
@@ -705,7 +706,7 @@ __device__ Phase phase_of(const FusedParams& p, int index) {
     return ph;
 }
 
-template <int NT>
+template <int NT, int RES>
 __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedParams p) {
     constexpr int MT = NT * 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -715,7 +716,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
     sm.xs = reinterpret_cast<bf16*>(cursor);      cursor += (size_t)MT * (k_max + XS_PAD) * 2;
     sm.red = reinterpret_cast<float*>(cursor);    cursor += (size_t)WARPS * 32 * NT * 4 * 4;
     sm.att = reinterpret_cast<float*>(cursor);    cursor += (size_t)WARPS * (2 + 256) * 4;
-    sm.wbuf = reinterpret_cast<uint4*>(cursor);   cursor += (size_t)2 * resident_of(NT) * THREADS * 16;
+    sm.wbuf = reinterpret_cast<uint4*>(cursor);   cursor += (size_t)2 * RES * THREADS * 16;
     sm.bias = reinterpret_cast<float*>(cursor);   cursor += (size_t)2 * THREADS * 2 * 4;
     sm.old = reinterpret_cast<float*>(cursor);    cursor += (size_t)THREADS * NT * 4 * 4;
     sm.gb = reinterpret_cast<float*>(cursor);     cursor += (size_t)2 * p.E * 4;
@@ -749,7 +750,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
     }
     int index = 0;
     Phase phase = phase_of(p, 0);
-    prefetch_phase<NT>(p, sm, phase, 0, p.T);
+    prefetch_phase<NT, RES>(p, sm, phase, 0, p.T);
     // ---- embedding: token t is written by CTA t % grid ----
     for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
         int token = p.token_ids[t];
@@ -781,7 +782,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
         __syncthreads();                                  // gain and shift were copied by all threads
         stage_norm<MT>(p, sm.xs, p.E, sm.gb, layer.eps1, nullptr, p.T);
         __syncthreads();
-        product_phase<NT>(p, sm, phase, index & 1, p.E + XS_PAD, p.T, EPI_STORE, &layer, next, best_value, best_index);
+        product_phase<NT, RES>(p, sm, phase, index & 1, p.E + XS_PAD, p.T, EPI_STORE, &layer, next, best_value, best_index);
         if (!grid_barrier(p)) return;
         note();
         // ---- phase 2 ----
@@ -798,7 +799,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
         phase = next; index++; next = phase_of(p, index + 1);
         stage_copy<MT>(sm.xs, phase.K, p.attn, phase.K, p.T);
         __syncthreads();
-        product_phase<NT>(p, sm, phase, index & 1, phase.K + XS_PAD, p.T, EPI_STORE, &layer, next, best_value, best_index);
+        product_phase<NT, RES>(p, sm, phase, index & 1, phase.K + XS_PAD, p.T, EPI_STORE, &layer, next, best_value, best_index);
         if (!grid_barrier(p)) return;
         note();
         // ---- phase 4 ----
@@ -807,14 +808,14 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
         __syncthreads();
         stage_norm<MT>(p, sm.xs, p.E, sm.gb, layer.eps2, nullptr, p.T);
         __syncthreads();
-        product_phase<NT>(p, sm, phase, index & 1, p.E + XS_PAD, p.T, layer.activation, &layer, next, best_value, best_index);
+        product_phase<NT, RES>(p, sm, phase, index & 1, p.E + XS_PAD, p.T, layer.activation, &layer, next, best_value, best_index);
         if (!grid_barrier(p)) return;
         note();
         // ---- phase 5 ----
         phase = next; index++; next = phase_of(p, index + 1);
         stage_copy<MT>(sm.xs, p.I, p.up, p.I, p.T);
         __syncthreads();
-        product_phase<NT>(p, sm, phase, index & 1, p.I + XS_PAD, p.T, EPI_STORE, &layer, next, best_value, best_index);
+        product_phase<NT, RES>(p, sm, phase, index & 1, p.I + XS_PAD, p.T, EPI_STORE, &layer, next, best_value, best_index);
         if (!grid_barrier(p)) return;
         note();
         phase = next; index++;
@@ -826,7 +827,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
     __syncthreads();
     stage_norm<MT>(p, sm.xs, p.E, sm.gb, p.eps_f, p.want_rows, p.n_want);
     __syncthreads();
-    product_phase<NT>(p, sm, phase, index & 1, p.E + XS_PAD, p.n_want, EPI_STORE, nullptr, phase_of(p, index + 1),
+    product_phase<NT, RES>(p, sm, phase, index & 1, p.E + XS_PAD, p.n_want, EPI_STORE, nullptr, phase_of(p, index + 1),
                       best_value, best_index);
     note();
     if (p.sample == 0) return;
@@ -904,19 +905,19 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
 
 int g_sm_count = 0, g_smem_optin = 0;
 
-template <int NT>
+template <int NT, int RES>
 int launch(const FusedParams& p, size_t smem, cudaStream_t s) {
     static bool configured = false;
     if (!configured) {
         cudaFuncAttributes attributes;
-        if (cudaFuncGetAttributes(&attributes, fused_decode_kernel<NT>) != cudaSuccess ||
-            cudaFuncSetAttribute(fused_decode_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncGetAttributes(&attributes, fused_decode_kernel<NT, RES>) != cudaSuccess ||
+            cudaFuncSetAttribute(fused_decode_kernel<NT, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  g_smem_optin - (int)attributes.sharedSizeBytes) != cudaSuccess)
             return fail("fused_decode: cannot raise the shared memory limit");
         configured = true;
     }
     void* args[] = {const_cast<FusedParams*>(&p)};
-    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(fused_decode_kernel<NT>), dim3(g_sm_count),
+    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(fused_decode_kernel<NT, RES>), dim3(g_sm_count),
                                                 dim3(THREADS), args, smem, s);
     if (e != cudaSuccess) {
         snprintf(g_error_text, MLLM_ERROR_BUFFER, "fused_decode: cooperative launch failed: %s", cudaGetErrorString(e));
@@ -942,6 +943,15 @@ extern "C" int mllm_fused_grid(void) {
     return g_sm_count;
 }
 
+// The K steps of weights kept in shared memory: the most that fits beside everything else
+// (0: nothing fits).
+static int resident_steps(int T, int E, int I, int HD, int max_blocks) {
+    const int nt = T <= 8 ? 1 : 2;
+    for (int res = nt == 1 ? 6 : 4; res >= 2; res -= 2)
+        if (shared_bytes(nt, res, E, I, HD, max_blocks) + 8 * 1024 <= (size_t)g_smem_optin) return res;
+    return 0;
+}
+
 // Whether the kernel takes these sizes: up to 16 tokens, widths that are multiples of 32
 // (one tensor-core step), a head size that is a power of two, and everything it keeps in
 // shared memory fitting there.
@@ -951,15 +961,16 @@ extern "C" int mllm_fused_takes(int T, int E, int H, int Hkv, int D, int I, int 
     if (E % 32 != 0 || I % 32 != 0 || (H * D) % 32 != 0) return 0;
     if (!(D == 16 || D == 32 || D == 64 || D == 128 || D == 256)) return 0;
     if (Hkv <= 0 || H % Hkv != 0 || max_blocks <= 0) return 0;
-    return shared_bytes(T <= 8 ? 1 : 2, E, I, H * D, max_blocks) + 8 * 1024 <= (size_t)g_smem_optin;
+    return resident_steps(T, E, I, H * D, max_blocks) > 0;
 }
 
 extern "C" int mllm_fused_decode_step(const FusedParams* params, void* stream) {
     const FusedParams& p = *params;
     if (!mllm_fused_takes(p.T, p.E, p.H, p.Hkv, p.D, p.I, p.max_blocks)) return fail("fused_decode: sizes not taken");
     if (p.n_want > p.T) return fail("fused_decode: more wanted rows than tokens");
-    const int nt = p.T <= 8 ? 1 : 2;
-    const size_t smem = shared_bytes(nt, p.E, p.I, p.H * p.D, p.max_blocks);
+    const int nt = p.T <= 8 ? 1 : 2, res = resident_steps(p.T, p.E, p.I, p.H * p.D, p.max_blocks);
+    const size_t smem = shared_bytes(nt, res, p.E, p.I, p.H * p.D, p.max_blocks);
     cudaStream_t s = (cudaStream_t)stream;
-    return nt == 1 ? launch<1>(p, smem, s) : launch<2>(p, smem, s);
+    if (nt == 1) return res == 6 ? launch<1, 6>(p, smem, s) : (res == 4 ? launch<1, 4>(p, smem, s) : launch<1, 2>(p, smem, s));
+    return res == 4 ? launch<2, 4>(p, smem, s) : launch<2, 2>(p, smem, s);
 }
