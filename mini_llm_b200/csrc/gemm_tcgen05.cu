@@ -13,7 +13,8 @@
 // Two orientations:
 //   rows    the 128 tile rows are rows of x (tokens), the BN tile columns rows of W.
 //   swapped the 128 tile rows are rows of W (outputs), the BN columns are tokens: for steps
-//           of few tokens, where a 128-row token tile would be mostly padding.
+//           of few tokens, where a 128-row token tile would be mostly padding.  When such a
+//           product has few tiles, each is shared along K by a cluster of CTAs.
 //
 // Every wait on an mbarrier is bounded: when the bound is hit the kernel writes a code to
 // its status word, stops issuing work, waits (bounded again) for its own copies in flight,
@@ -44,9 +45,7 @@ struct GemmParams {
     long ldo;
     int epilogue;
     int out_f32;
-    int splits;               // swapped orientation only: CTAs along K per tile (blockIdx.z)
-    float* partial;           // [tiles, splits, BN, 128] partial sums when splits > 1
-    int* counters;            // [tiles], zero between launches
+    int splits;               // swapped orientation only: the CTAs of a cluster share a tile along K (blockIdx.z)
     // Optional scatter of a fused query/key/value product: output features below q_width go
     // to out [M, q_width], the next kv_width to the key pages, the rest to the value pages,
     // each token at the cache slot its position and block table name (k_pages null: off).
@@ -77,6 +76,24 @@ __device__ __forceinline__ float activate(float v, int epilogue) {
 // as bfloat16 with bias and activation; row r goes to base + row_offset(r).  When the block
 // is whole and 4-byte aligned (paired), half a warp writes one row (two columns per lane, one
 // 4-byte store), so an instruction covers two rows; otherwise one column per lane.
+// Thread block clusters: the CTAs that share a tile along K add their partial sums through
+// each other's shared memory.
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {       // by every thread of every CTA of the cluster
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float load_from_rank(const float* mine, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(mine)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
 template <int EPI> __device__ __forceinline__ float activate_as(float v) {
     if (EPI == EPI_GELU_TANH) return gelu_tanh_fast(v);
     if (EPI == EPI_GELU_ERF) return gelu_erf_f(v);
@@ -227,13 +244,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         bool ok = true;
         if (lane == 0) ok = mbar_wait(accumulator_ready, 0);
         ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (SWAP && p.splits > 1) {
-            // the four warps meet at barriers below: they go on only if all of them may
-            int mine = ok && !*failed, all;
-            asm volatile("{\n\t.reg .pred q, r;\n\tsetp.ne.b32 q, %1, 0;\n\tbar.red.and.pred r, 1, 256, q;\n\t"
-                         "selp.b32 %0, 1, 0, r;\n\t}" : "=r"(all) : "r"(mine) : "memory");
-            if (!all && ok && !*failed) ok = false;
-        }
         if (!ok || *failed) {
             if (lane == 0 && !*failed) {
                 *failed = STATUS_TIMEOUT_EPILOGUE;
@@ -349,78 +359,51 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                     }
                 } else {
-                    // The tile is split along K: every CTA leaves its partial sums in global
-                    // memory; the CTA that arrives last adds them in the order of the splits
-                    // (so the result does not depend on which one that is) and finishes the tile.
-                    // (the four warps agree first: one that gave up alone must not leave the others at a barrier)
-                    const int tile = tile_b * gridDim.x + tile_a;
-                    float* mine = p.partial + ((long)tile * p.splits + blockIdx.z) * (BN * BM) + quarter * 32 + lane;
+                    // The tile is split along K over the CTAs of a cluster: every CTA leaves its
+                    // partial sums in its own shared memory (the operand stages are free by
+                    // now), [token][128 features]; they are added below, behind a cluster barrier.
+                    float* part = reinterpret_cast<float*>(smem) + quarter * 32 + lane;
 #pragma unroll 1
                     for (int c0 = c_first; has_columns && c0 < c_first + SPAN; c0 += 16) {
                         float v[16];
                         __syncwarp();
                         tmem_load_16(lane_base + c0, v);
-                        if (num_k == 0) {
 #pragma unroll
-                            for (int i = 0; i < 16; i++) v[i] = 0.0f;       // a split past the last k block
-                        }
-#pragma unroll
-                        for (int i = 0; i < 16; i++) __stcg(mine + (long)(c0 + i) * BM, v[i]);
-                    }
-                    __threadfence();
-                    asm volatile("bar.sync 1, 256;" ::: "memory");
-                    int* ticket = const_cast<int*>(failed) + 1;
-                    if (threadIdx.x == 0) *ticket = atomicAdd(p.counters + tile, 1);
-                    asm volatile("bar.sync 1, 256;" ::: "memory");
-                    if (*ticket == p.splits - 1 && threadIdx.x < 128) {
-                        __threadfence();
-                        // Thread t adds four neighbouring features of tokens t/32, t/32 + 4, ...:
-                        // 16-byte loads, those of all splits and of two tokens in flight at once.
-                        const float* all = p.partial + (long)tile * p.splits * (BN * BM);
-                        const int tokens = min(BN, p.M - tile_b * BN);
-                        const int f = (threadIdx.x & 31) * 4, feature = tile_a * BM + f;
-#pragma unroll 1
-                        for (int c = threadIdx.x >> 5; c < tokens; c += 8) {
-                            float4 part[2][8];
-#pragma unroll
-                            for (int h = 0; h < 2; h++)
-#pragma unroll
-                                for (int z = 0; z < 8; z++)
-                                    part[h][z] = (z < p.splits && c + 4 * h < tokens)
-                                        ? __ldcg(reinterpret_cast<const float4*>(all + ((long)z * BN + c + 4 * h) * BM + f))
-                                        : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-#pragma unroll
-                            for (int h = 0; h < 2; h++) {
-                                if (c + 4 * h >= tokens) break;
-                                float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-                                for (int z = 0; z < 8; z++) {
-                                    sum[0] += part[h][z].x; sum[1] += part[h][z].y;
-                                    sum[2] += part[h][z].z; sum[3] += part[h][z].w;
-                                }
-                                const int t = tile_b * BN + c + 4 * h;
-                                float old[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                                if (p.epilogue == EPI_ADD) {
-#pragma unroll
-                                    for (int u = 0; u < 4; u++)
-                                        if (feature + u < p.N)
-                                            old[u] = reinterpret_cast<const float*>(p.out)[(long)t * p.ldo + feature + u];
-                                }
-#pragma unroll
-                                for (int u = 0; u < 4; u++) {
-                                    if (feature + u >= p.N) break;
-                                    const float x = sum[u] + (p.bias != nullptr ? p.bias[feature + u] : 0.0f);
-                                    const long at = (long)t * p.ldo + feature + u;
-                                    if (p.epilogue == EPI_ADD || p.out_f32) reinterpret_cast<float*>(p.out)[at] = old[u] + x;
-                                    else reinterpret_cast<bf16*>(p.out)[at] = __float2bfloat16_rn(activate(x, p.epilogue));
-                                }
-                            }
-                        }
-                        if (threadIdx.x == 0) p.counters[tile] = 0;      // ready for the next launch
+                        for (int i = 0; i < 16; i++) part[(c0 + i) * BM] = num_k > 0 ? v[i] : 0.0f;
                     }
                 }
             }
         }
+    }
+
+    if (SWAP && p.splits > 1) {
+        // Every thread of every CTA of the cluster comes by here, whatever happened above.
+        __syncthreads();
+        __syncwarp();
+        cluster_sync();
+        if (warp < 8 && !*failed) {
+            // CTA `rank` finishes the tokens rank, rank + splits, ...: it adds the partial sums
+            // of all CTAs in their order, so the result does not depend on timing.  Thread t
+            // keeps feature t % 128 (the row it read from tensor memory) and every other token.
+            const int quarter = warp & 3;
+            const int r = tile_a * BM + quarter * 32 + lane;
+            const bool row_ok = r < p.N;
+            const float b = (row_ok && p.bias != nullptr) ? p.bias[r] : 0.0f;
+            const float* part = reinterpret_cast<const float*>(smem) + quarter * 32 + lane;
+            const int tokens = min(BN, p.M - tile_b * BN), rank = (int)cluster_rank();
+            for (int c = rank + p.splits * (warp >> 2); row_ok && c < tokens; c += 2 * p.splits) {
+                float sum = 0.0f;
+                for (int z = 0; z < p.splits; z++) sum += load_from_rank(part + c * BM, (uint32_t)z);
+                const float x = sum + b;
+                const int t = tile_b * BN + c;
+                const long at = (long)t * p.ldo + r;
+                if (p.epilogue == EPI_ADD) reinterpret_cast<float*>(p.out)[at] += x;
+                else if (p.out_f32) reinterpret_cast<float*>(p.out)[at] = x;
+                else reinterpret_cast<bf16*>(p.out)[at] = __float2bfloat16_rn(activate(x, p.epilogue));
+            }
+        }
+        __syncwarp();
+        cluster_sync();        // nobody leaves while its shared memory may still be read
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -502,6 +485,27 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const GemmParams& p, dim3
         if (e != cudaSuccess) return fail("gemm: cannot raise the shared memory limit");
         configured = true;
     }
+    if (grid.z > 1) {
+        // the CTAs that share a tile along K form a cluster (they read each other's shared memory)
+        cudaLaunchConfig_t config = {};
+        config.gridDim = grid;
+        config.blockDim = dim3(THREADS);
+        config.dynamicSmemBytes = smem;
+        config.stream = s;
+        cudaLaunchAttribute attribute;
+        attribute.id = cudaLaunchAttributeClusterDimension;
+        attribute.val.clusterDim.x = 1;
+        attribute.val.clusterDim.y = 1;
+        attribute.val.clusterDim.z = grid.z;
+        config.attrs = &attribute;
+        config.numAttrs = 1;
+        cudaError_t e = cudaLaunchKernelEx(&config, gemm_tcgen05_kernel<BN, STAGES, SWAP, CTAS_PER_SM>, a, b, p);
+        if (e != cudaSuccess) {
+            snprintf(g_error_text, MLLM_ERROR_BUFFER, "gemm_tcgen05_kernel (cluster of %u): %s", grid.z, cudaGetErrorString(e));
+            return 2;
+        }
+        return 0;
+    }
     gemm_tcgen05_kernel<BN, STAGES, SWAP, CTAS_PER_SM><<<grid, THREADS, smem, s>>>(a, b, p);
     return check_launch("gemm_tcgen05_kernel");
 }
@@ -526,9 +530,8 @@ extern "C" int mllm_gemm_takes(long K, long ldx, const void* x, const void* w) {
 // out[M, N] = epilogue(x[M, K] w[N, K]^T + bias).  x, w bf16 (K contiguous; x with row stride
 // ldx); out bf16, or fp32 with out_f32 or the residual epilogue.  status: a device int that
 // must be zero; a non-zero value afterwards means a bounded wait inside the kernel ran out.
-// scratch / counters (may be null): fp32 room for partial sums and zeroed ints (one per tile;
-// the kernel leaves them zero) that let a product of few tokens be split along K; a tile
-// needs splits x 64 x 128 floats, and as many tiles are split as fit.
+// A product of few tokens and few tiles is split along K over the CTAs of a cluster, which add
+// their partial sums through each other's shared memory in a fixed order.
 struct GemmScatter {
     void* k_pages;
     void* v_pages;
@@ -539,14 +542,13 @@ struct GemmScatter {
 };
 
 static int gemm_bf16(void* out, const void* x, const void* w, const float* bias, int M, int N, int K, long ldx, long ldo,
-                     int epilogue, int out_f32, int* status, float* scratch, long scratch_floats, int* counters,
-                     int n_counters, const GemmScatter* scatter, void* stream) {
+                     int epilogue, int out_f32, int* status, const GemmScatter* scatter, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (!mllm_gemm_takes(K, ldx, x, w)) return fail("gemm: K and the row stride of x must be multiples of 8, bases 16-byte aligned");
     if (epilogue == EPI_ADD && !out_f32) return fail("gemm: the residual sum is kept in 32-bit");
     if (status == nullptr) return fail("gemm: a status word is required");
     cudaStream_t s = (cudaStream_t)stream;
-    GemmParams p{out, bias, status, M, N, K, ldo, epilogue, out_f32, 1, scratch, counters,
+    GemmParams p{out, bias, status, M, N, K, ldo, epilogue, out_f32, 1,
                  nullptr, nullptr, nullptr, nullptr, nullptr, 0, 1, 0, 0};
     if (scatter != nullptr) {
         if (out_f32 || epilogue != EPI_STORE) return fail("gemm: the scatter goes with a plain bfloat16 store");
@@ -562,7 +564,6 @@ static int gemm_bf16(void* out, const void* x, const void* w, const float* bias,
         p.page_size = scatter->page_size;
         p.q_width = scatter->q_width;
         p.kv_width = scatter->kv_width;
-        scratch = nullptr;                     // a scattered product is never split along K
     }
     CUtensorMap map_x, map_w;
     const bool swap = M <= 64;
@@ -593,21 +594,18 @@ static int gemm_bf16(void* out, const void* x, const void* w, const float* bias,
     }
     dim3 grid((N + BM - 1) / BM, (M + bn - 1) / bn);
     {
-        // Few tiles: split them along K so that more SMs stream the weights (at least two k
-        // blocks per CTA, at most eight CTAs per tile: the last one adds all partial sums).
+        // Few tiles: share each among a cluster of 8, 4 or 2 CTAs along K, so that more SMs
+        // stream the weights (at least two k blocks per CTA; not with the cache scatter)
         int sms = 148;
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
         const int tiles = grid.x * grid.y, all_k = (K + BK - 1) / BK;
-        int splits = std::min(std::min(sms / tiles, all_k / 2), 8);
-        // measured: the sum at the end costs more than the split saves unless the tiles are few,
-        // K is long and the tile narrow
-        if (tiles * 16 > sms || all_k < 24 || bn > 32) splits = 1;
-        if (splits >= 2 && scratch != nullptr && counters != nullptr && tiles <= n_counters &&
-            (long)tiles * splits * bn * BM <= scratch_floats) {
-            const int per = (all_k + splits - 1) / splits;
-            p.splits = (all_k + per - 1) / per;
-            grid.z = p.splits;
-        }
+        if (scatter == nullptr)
+            for (int splits = 8; splits >= 2; splits /= 2)
+                if (tiles * splits <= sms && all_k / splits >= 2) {
+                    p.splits = splits;
+                    grid.z = splits;
+                    break;
+                }
     }
     if (bn == 16) return launch<16, 8, true>(map_w, map_x, p, grid, s);
     if (bn == 32) return launch<32, 8, true>(map_w, map_x, p, grid, s);
@@ -615,10 +613,8 @@ static int gemm_bf16(void* out, const void* x, const void* w, const float* bias,
 }
 
 extern "C" int mllm_gemm_bf16(void* out, const void* x, const void* w, const float* bias, int M, int N, int K,
-                              long ldx, long ldo, int epilogue, int out_f32, int* status, float* scratch,
-                              long scratch_floats, int* counters, int n_counters, void* stream) {
-    return gemm_bf16(out, x, w, bias, M, N, K, ldx, ldo, epilogue, out_f32, status, scratch, scratch_floats, counters,
-                     n_counters, nullptr, stream);
+                              long ldx, long ldo, int epilogue, int out_f32, int* status, void* stream) {
+    return gemm_bf16(out, x, w, bias, M, N, K, ldx, ldo, epilogue, out_f32, status, nullptr, stream);
 }
 
 // The fused query/key/value product of a layer: out [M, q_width] gets the queries; keys and
@@ -629,5 +625,5 @@ extern "C" int mllm_gemm_bf16_qkv(void* out, const void* x, const void* w, const
                                   const int* token_item, const int* block_table, int max_blocks, int page_size,
                                   int q_width, int kv_width, void* stream) {
     GemmScatter scatter{k_pages, v_pages, positions, token_item, block_table, max_blocks, page_size, q_width, kv_width};
-    return gemm_bf16(out, x, w, bias, M, N, K, ldx, ldo, EPI_STORE, 0, status, nullptr, 0, nullptr, 0, &scatter, stream);
+    return gemm_bf16(out, x, w, bias, M, N, K, ldx, ldo, EPI_STORE, 0, status, &scatter, stream);
 }

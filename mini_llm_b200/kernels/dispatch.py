@@ -48,10 +48,9 @@ class Kernels:
         self._split_scratch = None
         self._sample_scratch = None
         self.scratch_generation = 0  # grows when scratch moves (captured graphs are then stale)
-        self._status = None
+        self._status = None          # device word the tensor-core kernels report a timed-out wait in
         self._att_scratch = None
         self._att_work = None
-        self._gemm_scratch = None          # device word the tensor-core kernels report a timed-out wait in
 
     # ---- operations without a fast variant --------------------------------------------------
     def keep_tokens(self, kept, slots, tokens):
@@ -113,7 +112,7 @@ class Kernels:
             self.launches += 1
             a = a.materialize(ctx)
         if not self.plain_only and ops.gemm_takes(a, w):
-            return ops.gemm_bf16(out, a, w, bias, epilogue, self.status(ctx.device), self.gemm_scratch(ctx.device))
+            return ops.gemm_bf16(out, a, w, bias, epilogue, self.status(ctx.device))
         return ops.linear_plain(out, a, w, bias, epilogue)
 
     def status(self, device):
@@ -121,23 +120,14 @@ class Kernels:
             self._status = torch.zeros(1, dtype=torch.int32, device=device)
         return self._status
 
-    def gemm_scratch(self, device):
-        """Partial sums and tile counters for matrix products that are split along K."""
-        if self._gemm_scratch is None:
-            self._gemm_scratch = (torch.empty(ops.GEMM_SCRATCH_FLOATS, dtype=torch.float32, device=device),
-                                  torch.zeros(ops.GEMM_SCRATCH_COUNTERS, dtype=torch.int32, device=device))
-            self.scratch_generation += 1
-        return self._gemm_scratch
-
     def check_status(self) -> None:
         """Raise if a kernel reported that one of its bounded waits ran out (synchronises)."""
         if self._status is not None:
             code = int(self._status.item())
             if code != 0:
                 self._status.zero_()
-                for held in (self._gemm_scratch, self._att_scratch):
-                    if held is not None:
-                        held[1].zero_()               # a tile that was given up left its counter
+                if self._att_scratch is not None:
+                    self._att_scratch[1].zero_()      # a tile that was given up left its counter
                 if self._att_work is not None:
                     self._att_work.zero_()
                 raise ops.KernelError(f"a tensor-core kernel gave up waiting (code {code}): its result is invalid")

@@ -376,11 +376,7 @@ def group_attention(out, q, k_pages, v_pages, block_table, positions, token_item
 
 # ---- tensor-core matrix product (bfloat16) -------------------------------------------------------
 
-_gemm_bf16 = Function("gemm", "mllm_gemm_bf16", [P, P, P, P, I, I, I, L, L, I, I, P, P, L, P, I, P])
-# Scratch that lets products of few tokens be split along K: partial sums (fp32) for up to one
-# CTA per SM of 64 tokens x 128 features, and one counter per tile.
-GEMM_SCRATCH_FLOATS = 148 * 64 * 128
-GEMM_SCRATCH_COUNTERS = 148
+_gemm_bf16 = Function("gemm", "mllm_gemm_bf16", [P, P, P, P, I, I, I, L, L, I, I, P, P])
 
 
 def gemm_takes(a, w) -> bool:
@@ -393,13 +389,12 @@ def gemm_takes(a, w) -> bool:
             and w.is_contiguous() and w.data_ptr() % 16 == 0)
 
 
-def gemm_bf16(out, a, w, bias, epilogue, status, scratch=None):
+def gemm_bf16(out, a, w, bias, epilogue, status):
     """out = epilogue(a @ w.T + bias) on the tensor cores (tcgen05, TMEM accumulators, TMA).
 
     a [M, K] and w [N, K] bf16; out bf16, or fp32 for logits and for the residual epilogue
     "add".  ``status``: a zeroed int32 device word the kernel writes a code to if one of its
-    bounded waits runs out.  ``scratch``: (fp32 tensor, zeroed int32 tensor) for products that
-    are split along K, or None."""
+    bounded waits runs out."""
     _check(a, "gemm.a", torch.bfloat16, 2)
     _check(w, "gemm.w", torch.bfloat16, 2)
     _check(out, "gemm.out", None, 2)
@@ -418,14 +413,8 @@ def gemm_bf16(out, a, w, bias, epilogue, status, scratch=None):
         _check(bias, "gemm.bias", torch.float32, 1)
         if bias.shape[0] != n:
             raise KernelError("gemm: bias has another length")
-    partial, counters = scratch if scratch is not None else (None, None)
-    if partial is not None:
-        _check(partial, "gemm.scratch", torch.float32, 1)
-        _check(counters, "gemm.scratch", torch.int32, 1)
     _gemm_bf16(out.data_ptr(), a.data_ptr(), w.data_ptr(), _ptr(bias), m, n, k, a.stride(0), out.stride(0),
-               EPILOGUES[epilogue], int(out.dtype == torch.float32), status.data_ptr(), _ptr(partial),
-               partial.shape[0] if partial is not None else 0, _ptr(counters),
-               counters.shape[0] if counters is not None else 0, _stream())
+               EPILOGUES[epilogue], int(out.dtype == torch.float32), status.data_ptr(), _stream())
     return out
 
 
