@@ -288,3 +288,35 @@ def test_previous_names_the_last_sampled_token_on_the_device(folders, dtype, key
         np.testing.assert_array_equal(a, b)
     if key == "C":
         assert engine.fused is not None
+
+
+def test_fused_decode_step_with_products_that_stream(tmp_path):
+    """Sizes at which the one-kernel step's products do not fit their prefetch: a vocabulary of
+    40,000 (17 blocks of rows per CTA, each longer than the prefetch) and an inner size of 4096
+    (a warp's share of K longer than the prefetch).  Against the part-by-part path."""
+    from mini_llm_b200.engine import Engine, SamplingParams, StepEntry
+    raw = {"architectures": ["GPT2LMHeadModel"], "model_type": "gpt2", "n_layer": 2, "n_embd": 512, "n_head": 8,
+           "n_inner": 4096, "vocab_size": 40000, "n_positions": 256, "activation_function": "gelu_new",
+           "layer_norm_epsilon": 1e-5, "tie_word_embeddings": True}
+    folder = make_model(str(tmp_path / "wide"), raw, "varied", 3)
+    fused = Engine(folder, dtype="bfloat16", page_size=16, cache_tokens=2048, max_requests=8)
+    plain = Engine(folder, dtype="bfloat16", page_size=16, cache_tokens=2048, max_requests=8, fused_decode=False)
+    assert fused.fused is not None
+    prompts = [random_tokens(90 + i, n, 40000) for i, n in enumerate((60, 7, 150))]
+    feed = np.random.default_rng(9).integers(0, 40000, (6, len(prompts)))
+    rows = {}
+    for name, engine in (("fused", fused), ("plain", plain)):
+        slots = [engine.open_request() for _ in prompts]
+        engine.step([StepEntry(s, p, []) for s, p in zip(slots, prompts)])
+        rows[name] = []
+        for step in range(6):
+            out = engine.step([StepEntry(s, [int(feed[step, i])], [0]) for i, s in enumerate(slots)],
+                              [SamplingParams(0.0, 1.0, 0, step) for _ in slots])
+            rows[name].append((out.cpu().numpy().copy(), engine.sampled_tokens()))
+        engine.check_status()
+    assert fused.fused is not None and fused.kernels.launches < plain.kernels.launches / 3
+    agree = 0
+    for (a, ta), (b, tb) in zip(rows["fused"], rows["plain"]):
+        np.testing.assert_allclose(a, b, rtol=0, atol=bf16_atol(b))
+        agree += sum(x == y for x, y in zip(ta, tb))
+    assert agree >= 16                                   # greedy choices agree, near-ties apart
