@@ -61,13 +61,15 @@ def test_layernorm(dtype, width, eps):
     np.testing.assert_allclose(f64(some), expected[rows], rtol=0, atol=tol(dtype, 4))
 
 
+# every size with a plain store; the other epilogues at the smaller sizes
+LINEAR_PLAIN_CASES = [(m, n, k, e) for m, n, k in [(1, 50, 96), (7, 1000, 160), (65, 129, 33), (130, 768, 3072), (2, 50257, 64)]
+                      for e in ("store", "gelu_tanh", "gelu_erf", "add") if e == "store" or n <= 2000]
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("m, n, k", [(1, 50, 96), (7, 1000, 160), (65, 129, 33), (130, 768, 3072), (2, 50257, 64)])
-@pytest.mark.parametrize("epilogue", ["store", "gelu_tanh", "gelu_erf", "add"])
+@pytest.mark.parametrize("m, n, k, epilogue", LINEAR_PLAIN_CASES)
 def test_linear_plain(dtype, m, n, k, epilogue):
     from mini_llm_b200.kernels import ops
-    if epilogue != "store" and n > 2000:
-        pytest.skip("epilogues are covered at the smaller sizes")
     rng = np.random.default_rng(m * n + k)
     a, w = dev(rng.normal(size=(m, k)), dtype), dev(rng.normal(size=(n, k)) / math.sqrt(k), dtype)
     bias = dev(rng.normal(size=n), torch.float32)
@@ -252,13 +254,16 @@ def test_sampling_temperature_and_nucleus_match_the_plain_sampler(vocab):
 
 # ---- kernels for steps of few tokens --------------------------------------------------------
 
-@pytest.mark.parametrize("m", [1, 2, 3, 5, 8, 13, 16, 37, 64])
-@pytest.mark.parametrize("n, k", [(768, 768), (100, 96), (1000, 160), (2304, 768), (777, 3072), (50257, 64)])
-@pytest.mark.parametrize("epilogue", ["store", "gelu_tanh", "gelu_erf", "add"])
+# every row count and size with a plain store; the other epilogues at fewer of them
+SKINNY_CASES = [(m, n, k, e) for m in (1, 2, 3, 5, 8, 13, 16, 37, 64)
+                for n, k in [(768, 768), (100, 96), (1000, 160), (2304, 768), (777, 3072), (50257, 64)]
+                for e in ("store", "gelu_tanh", "gelu_erf", "add")
+                if e == "store" or (n <= 3000 and m in (1, 5, 16, 37))]
+
+
+@pytest.mark.parametrize("m, n, k, epilogue", SKINNY_CASES)
 def test_skinny_linear(m, n, k, epilogue):
     from mini_llm_b200.kernels import ops
-    if (epilogue != "store" and n > 3000) or (m not in (1, 5, 16, 37) and epilogue != "store"):
-        pytest.skip("epilogues are covered at fewer sizes")
     rng = np.random.default_rng(m * 7 + n + k)
     a, w = dev(rng.normal(size=(m, k + 8)), torch.bfloat16)[:, :k], dev(rng.normal(size=(n, k)) / math.sqrt(k), torch.bfloat16)
     bias = dev(rng.normal(size=n), torch.float32)
@@ -442,16 +447,19 @@ def test_split_attention_finds_one_far_key_and_respects_the_windows_edge():
 
 # ---- tensor-core matrix product --------------------------------------------------------------
 
-@pytest.mark.parametrize("m, n, k", [
+# every size with a plain store; the other epilogues at six of them
+GEMM_CASES = [(m, n, k, e) for m, n, k in [
     (128, 128, 64), (128, 128, 256), (256, 384, 768), (300, 1000, 160), (2048, 768, 768), (1, 256, 64),
     (8, 2304, 768), (17, 777, 96), (40, 768, 3072), (64, 1000, 160), (65, 136, 72), (5, 50257, 64),
-    (1024, 3072, 768), (513, 768, 3072)])
-@pytest.mark.parametrize("epilogue", ["store", "gelu_tanh", "gelu_erf", "add", "logits"])
+    (1024, 3072, 768), (513, 768, 3072)]
+    for e in ("store", "gelu_tanh", "gelu_erf", "add", "logits")
+    if e == "store" or (m, n, k) in [(128, 128, 256), (300, 1000, 160), (17, 777, 96), (64, 1000, 160),
+                                     (513, 768, 3072), (5, 50257, 64)]]
+
+
+@pytest.mark.parametrize("m, n, k, epilogue", GEMM_CASES)
 def test_gemm_tcgen05(m, n, k, epilogue):
     from mini_llm_b200.kernels import ops
-    if epilogue != "store" and (m, n, k) not in [(128, 128, 256), (300, 1000, 160), (17, 777, 96), (64, 1000, 160),
-                                                 (513, 768, 3072), (5, 50257, 64)]:
-        pytest.skip("epilogues are covered at fewer sizes")
     rng = np.random.default_rng(m + n + k)
     a, w = dev(rng.normal(size=(m, k)), torch.bfloat16), dev(rng.normal(size=(n, k)) / math.sqrt(k), torch.bfloat16)
     bias = dev(rng.normal(size=n), torch.float32)
