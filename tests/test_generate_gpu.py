@@ -137,4 +137,38 @@ def test_running_ahead_of_the_host_changes_no_token(folders, dtype):
         assert llm.engine.cache.pages_in_use() == [0] and llm.scheduler._flight is None
         runs[ahead] = (first, [(r.generated, r.finish_reason) for r in requests], greedy)
         assert requests[1].finish_reason == "stop" and requests[1].generated == first[1][:first[1].index(eos) + 1]
-    assert runs[True] == runs[False]
+    if dtype == "float32":
+        assert runs[True] == runs[False]
+    else:
+        # The two modes admit a request a step apart, so a token may meet another batch (and
+        # another kernel's rounding) in one than in the other: each mode's tokens are those of
+        # the plain sampler, near-ties apart.
+        for ahead in (False, True):
+            undecided = sum(follow(folders["B"], dtype, p, t, 0.7, 0.9, s) for p, t, s in zip(prompts, runs[ahead][0], seeds))
+            undecided += sum(follow(folders["B"], dtype, p, t) for p, t in zip(prompts[:3], runs[ahead][2]))
+            assert undecided <= 4
+
+
+
+def test_many_requests_through_the_scheduler_in_32_bit(folders):
+    """Twenty requests of mixed lengths through four slots, prompts in portions of 16 tokens
+    beside decoding requests, sampled: running ahead of the host or not, every request draws
+    the same tokens (in 32-bit nothing depends on what a token was batched with), and every page
+    and slot comes back."""
+    from mini_llm_b200.generate import LLM
+    rng = np.random.default_rng(21)
+    prompts = [random_tokens(200 + i, int(rng.integers(1, 60)), 1000) for i in range(20)]
+    seeds = list(range(300, 320))
+    outs = {}
+    for ahead in (True, False):
+        llm = LLM(folders["B"], dtype="float32", page_size=8, cache_tokens=480, max_tokens_per_step=24,
+                  max_prefill_chunk=16, max_sessions=4, run_ahead=ahead)
+        requests = llm.generate(prompts, max_new_tokens=18, temperature=0.9, top_p=0.95, seed=seeds, return_requests=True)
+        assert all(r.error is None and len(r.generated) == 18 for r in requests)
+        stats = llm.scheduler.stats()
+        assert stats["tokens"] == 20 * 18 and stats["running"] == 0 and stats["waiting"] == 0
+        assert llm.engine.cache.pages_in_use() == [0] and llm.engine.cache.free_slots == 4
+        llm.engine.check_status()
+        outs[ahead] = [list(r.generated) for r in requests]
+    assert outs[True] == outs[False]
+    assert follow(folders["B"], "float32", prompts[7], outs[True][7], 0.9, 0.95, seeds[7]) == 0
