@@ -145,6 +145,12 @@ __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
     }
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ void copy_async_16(void* smem_dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src)
                  : "memory");
@@ -564,7 +570,8 @@ __device__ void attention_phase(const FusedParams& p, const Shared& sm, const Fu
     constexpr int LPK = D / 8, KPW = 32 / LPK, INFLIGHT = 4;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane % LPK, group = lane / LPK;
-    const long kv_width = (long)p.Hkv * D;
+    const int kv_width = p.Hkv * D;
+    const int page_shift = (p.page_size & (p.page_size - 1)) == 0 ? 31 - __clz(p.page_size) : -1;
     float* sm_m = sm.att;                     // [WARPS]
     float* sm_l = sm.att + WARPS;             // [WARPS]
     float* sm_acc = sm.att + 2 * WARPS;       // [WARPS][D]
@@ -580,41 +587,53 @@ __device__ void attention_phase(const FusedParams& p, const Shared& sm, const Fu
         const int first = begin + part * share, last = min(pos, first + share - 1);
         const int* bt = sm.table + t * p.max_blocks;
         const int hk = h / (p.H / p.Hkv);
+        const uint4 q_raw = __ldcg(reinterpret_cast<const uint4*>(p.q + (long)t * p.H * D + (long)h * D + sub * 8));
+        float m = -INFINITY, l = 0.0f;          // m in units of log2(e): an exponential is one instruction
+        // The warp's keys in turn n = 0, 1, ...: key first + (n * WARPS + warp) * KPW + group.  A lane
+        // keeps INFLIGHT keys and values on their way, one per slot; it takes the oldest, asks
+        // for the key INFLIGHT turns later into the same slot and goes on to the next slot, so
+        // loads, address arithmetic and the softmax update of different keys overlap.
+        const int head_offset = hk * D + sub * 8;
+        const int my_key = first + warp * KPW + group;
+        uint4 kv[INFLIGHT], vv[INFLIGHT];
+        // A turn past the end asks for the last key again (valid memory, never used): no lane
+        // branches around its loads.
+        const long v_from_k = layer.v_pages - layer.k_pages;
+        auto ask = [&](uint4& k_slot, uint4& v_slot, int j) {
+            j = min(j, last);
+            // pages of a power of two are the rule: shift and mask instead of a division per key
+            const int block = page_shift >= 0 ? j >> page_shift : j / p.page_size;
+            const int within = page_shift >= 0 ? j & (p.page_size - 1) : j % p.page_size;
+            const bf16* k_at = layer.k_pages + (((long)bt[block] * p.page_size + within) * kv_width + head_offset);
+            k_slot = __ldcg(reinterpret_cast<const uint4*>(k_at));
+            v_slot = __ldcg(reinterpret_cast<const uint4*>(k_at + v_from_k));
+        };
+#pragma unroll
+        for (int s = 0; s < INFLIGHT; s++) ask(kv[s], vv[s], my_key + s * (WARPS * KPW));
+        // the query is unpacked after the first keys are asked for: nothing waits for it before
         float qf[8], acc[8];
-        unpack8(__ldcg(reinterpret_cast<const uint4*>(p.q + (long)t * p.H * D + (long)h * D + sub * 8)), qf);
+        unpack8(q_raw, qf);
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            qf[i] *= layer.score_scale;
+            qf[i] *= layer.score_scale * 1.4426950408889634f;
             acc[i] = 0.0f;
         }
-        float m = -INFINITY, l = 0.0f;
-        for (int jb = first + warp * INFLIGHT * KPW; jb <= last; jb += WARPS * INFLIGHT * KPW) {
-            uint4 kv[INFLIGHT], vv[INFLIGHT];
+        for (int j0 = my_key; j0 - group <= last; j0 += INFLIGHT * WARPS * KPW) {
 #pragma unroll
             for (int s = 0; s < INFLIGHT; s++) {
-                const int j = jb + s * KPW + group;
-                kv[s] = make_uint4(0, 0, 0, 0);
-                vv[s] = make_uint4(0, 0, 0, 0);
-                if (j <= last) {
-                    const int page = bt[j / p.page_size];
-                    const long base = ((long)page * p.page_size + (j % p.page_size)) * kv_width + (long)hk * D + sub * 8;
-                    kv[s] = __ldcg(reinterpret_cast<const uint4*>(layer.k_pages + base));
-                    vv[s] = __ldcg(reinterpret_cast<const uint4*>(layer.v_pages + base));
-                }
-            }
-#pragma unroll
-            for (int s = 0; s < INFLIGHT; s++) {
+                const int j = j0 + s * (WARPS * KPW);
                 float kf[8], vf[8];
                 unpack8(kv[s], kf);
                 unpack8(vv[s], vf);
+                ask(kv[s], vv[s], j + INFLIGHT * (WARPS * KPW));
                 float sc = 0.0f;
 #pragma unroll
                 for (int i = 0; i < 8; i++) sc = fmaf(qf[i], kf[i], sc);
 #pragma unroll
                 for (int o = LPK / 2; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
-                if (jb + s * KPW + group <= last) {
+                if (j <= last) {
                     const float m_new = fmaxf(m, sc);
-                    const float corr = __expf(m - m_new), e = __expf(sc - m_new);
+                    const float corr = fast_exp2(m - m_new), e = fast_exp2(sc - m_new);
                     l = l * corr + e;
 #pragma unroll
                     for (int i = 0; i < 8; i++) acc[i] = acc[i] * corr + e * vf[i];
@@ -627,7 +646,7 @@ __device__ void attention_phase(const FusedParams& p, const Shared& sm, const Fu
         for (int o = LPK; o < 32; o <<= 1) {
             const float m_o = __shfl_xor_sync(0xffffffffu, m, o), l_o = __shfl_xor_sync(0xffffffffu, l, o);
             const float big = fmaxf(m, m_o);
-            const float wa = (m == -INFINITY) ? 0.0f : __expf(m - big), wb = (m_o == -INFINITY) ? 0.0f : __expf(m_o - big);
+            const float wa = (m == -INFINITY) ? 0.0f : fast_exp2(m - big), wb = (m_o == -INFINITY) ? 0.0f : fast_exp2(m_o - big);
 #pragma unroll
             for (int i = 0; i < 8; i++) acc[i] = acc[i] * wa + __shfl_xor_sync(0xffffffffu, acc[i], o) * wb;
             l = l * wa + l_o * wb;
@@ -643,25 +662,36 @@ __device__ void attention_phase(const FusedParams& p, const Shared& sm, const Fu
             sm_l[warp] = l;
         }
         __syncthreads();
+        // R threads per output value, each over WARPS / R warps, then the R in a fixed order
+        constexpr int R = (THREADS / D >= 4) ? 4 : THREADS / D;
         float top = -INFINITY, denom = 0.0f, o = 0.0f;
-        if (threadIdx.x < D) {
-            const int d = threadIdx.x;
-            for (int w = 0; w < WARPS; w++) top = fmaxf(top, sm_m[w]);
-            for (int w = 0; w < WARPS; w++) {
-                const float weight = (sm_m[w] == -INFINITY) ? 0.0f : __expf(sm_m[w] - top);
+        if (threadIdx.x < R * D) {
+            const int d = threadIdx.x / R, r = threadIdx.x % R;
+            for (int w = r * (WARPS / R); w < (r + 1) * (WARPS / R); w++) top = fmaxf(top, sm_m[w]);
+#pragma unroll
+            for (int x = 1; x < R; x <<= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, x, R));
+            for (int w = r * (WARPS / R); w < (r + 1) * (WARPS / R); w++) {
+                const float weight = (sm_m[w] == -INFINITY) ? 0.0f : fast_exp2(sm_m[w] - top);
                 denom += sm_l[w] * weight;
                 o += sm_acc[w * D + d] * weight;
             }
+#pragma unroll
+            for (int x = 1; x < R; x <<= 1) {
+                denom += __shfl_xor_sync(0xffffffffu, denom, x, R);
+                o += __shfl_xor_sync(0xffffffffu, o, x, R);
+            }
         }
+        const bool writes = threadIdx.x < R * D && threadIdx.x % R == 0;
+        const int out_d = threadIdx.x / R;
         bf16* out = p.attn + (long)t * p.H * D + (long)h * D;
         if (parts == 1) {
-            if (threadIdx.x < D) out[threadIdx.x] = __float2bfloat16_rn(o / denom);
+            if (writes) out[out_d] = __float2bfloat16_rn(o / denom);
             continue;
         }
         // leave this part's state; the part that arrives last finishes the pair
         float* mine = p.att_partial + ((long)pair * parts + part) * (D + 2);
-        if (threadIdx.x < D) {
-            __stcg(mine + threadIdx.x, o);
+        if (writes) {
+            __stcg(mine + out_d, o);
             if (threadIdx.x == 0) {
                 __stcg(mine + D, top);
                 __stcg(mine + D + 1, denom);
@@ -679,7 +709,7 @@ __device__ void attention_phase(const FusedParams& p, const Shared& sm, const Fu
             float sum = 0.0f, total = 0.0f;
             for (int q = 0; q < parts; q++) {
                 const float mq = __ldcg(all + q * (D + 2) + D);
-                const float weight = (mq == -INFINITY) ? 0.0f : __expf(mq - big);
+                const float weight = (mq == -INFINITY) ? 0.0f : fast_exp2(mq - big);
                 sum += __ldcg(all + q * (D + 2) + threadIdx.x) * weight;
                 total += __ldcg(all + q * (D + 2) + D + 1) * weight;
             }
