@@ -439,31 +439,36 @@ __device__ void product_phase(const FusedParams& p, const Shared& sm, const Phas
                     }
                 }
             }
-            for (; ks + 4 <= k_end; ks += 4) {
-                uint4 wl[4], wh[4];
+            // The steps that were not prefetched stream in through a ring of four register
+            // slots: a slot is used and asked for the step four further on at once, so that the
+            // latency of a load is paid once per block and not once per four steps.
+            uint4 wl[4], wh[4];
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
+            for (int u = 0; u < 4; u++) {
+                wl[u] = make_uint4(0, 0, 0, 0);
+                wh[u] = make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (ks + u < k_end) {
                     wl[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + (ks + u) * 32));
                     wh[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + (ks + u) * 32));
                 }
+            for (; ks < k_end; ks += 4) {
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
+                    if (ks + u < k_end) {
 #pragma unroll
-                    for (int t = 0; t < NT; t++) {
-                        const uint4 xv = *reinterpret_cast<const uint4*>(x_lo + t * 8 * ldx + (ks + u) * 32);
-                        mma_16816(acc[t], wl[u].x, wh[u].x, wl[u].y, wh[u].y, xv.x, xv.y);
-                        mma_16816(acc[t], wl[u].z, wh[u].z, wl[u].w, wh[u].w, xv.z, xv.w);
+                        for (int t = 0; t < NT; t++) {
+                            const uint4 xv = *reinterpret_cast<const uint4*>(x_lo + t * 8 * ldx + (ks + u) * 32);
+                            mma_16816(acc[t], wl[u].x, wh[u].x, wl[u].y, wh[u].y, xv.x, xv.y);
+                            mma_16816(acc[t], wl[u].z, wh[u].z, wl[u].w, wh[u].w, xv.z, xv.w);
+                        }
                     }
-                }
-            }
-            for (; ks < k_end; ks++) {
-                const uint4 wl = __ldg(reinterpret_cast<const uint4*>(w_lo + ks * 32));
-                const uint4 wh = __ldg(reinterpret_cast<const uint4*>(w_hi + ks * 32));
-#pragma unroll
-                for (int t = 0; t < NT; t++) {
-                    const uint4 xv = *reinterpret_cast<const uint4*>(x_lo + t * 8 * ldx + ks * 32);
-                    mma_16816(acc[t], wl.x, wh.x, wl.y, wh.y, xv.x, xv.y);
-                    mma_16816(acc[t], wl.z, wh.z, wl.w, wh.w, xv.z, xv.w);
+                    if (ks + u + 4 < k_end) {
+                        wl[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + (ks + u + 4) * 32));
+                        wh[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + (ks + u + 4) * 32));
+                    }
                 }
             }
         }
