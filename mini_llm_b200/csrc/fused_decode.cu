@@ -107,7 +107,10 @@ struct Phase {
     const float* bias;
     int N, K, kind;
     const float *gamma, *beta; // norm applied to the phase's input, or null
+    int which;                 // 0 .. 3: the layer's products in their order, 4: the output head
 };
+
+struct Split;
 
 // Regions of the dynamic shared memory.
 struct Shared {
@@ -121,6 +124,7 @@ struct Shared {
     long* kv_base;             // [MAX_TOKENS] element offset of each token's slot in the pages
     int* pos;                  // [MAX_TOKENS]
     int* table;                // [T][max_blocks]
+    const Split* splits;       // [5]: how each kind of product phase is split (the same in every layer)
 };
 
 __host__ __device__ inline size_t shared_bytes(int nt, int res, int E, int I, int HD, int max_blocks) {
@@ -203,6 +207,7 @@ struct Split {
     int split;                 // warps per block
     int blocks_at_a_time;      // blocks the CTA works on at a time
     int per_part;              // K steps (of 32) per warp
+    int split_shift;           // log2(split)
 };
 
 __device__ __forceinline__ Split split_of(int N, int K, int kind) {
@@ -217,6 +222,7 @@ __device__ __forceinline__ Split split_of(int N, int K, int kind) {
         s.blocks_at_a_time = pow2;
     }
     s.per_part = (K / 32 + s.split - 1) / s.split;
+    s.split_shift = 31 - __clz(s.split);
     return s;
 }
 
@@ -228,8 +234,8 @@ __device__ void prefetch_phase(const FusedParams& p, const Shared& sm, const Pha
     if (phase.w != nullptr) {
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         const int g = lane >> 2, q = lane & 3;
-        const Split s = split_of(phase.N, phase.K, phase.kind);
-        const int b = warp / s.split, part = warp % s.split;
+        const Split s = sm.splits[phase.which];
+        const int b = warp >> s.split_shift, part = warp & (s.split - 1);
         if (b < s.count) {
             const int row_lo = (s.first + b) * 16 + g, row_hi = row_lo + 8;
             const bf16* w_lo = phase.w + (long)min(row_lo, phase.N - 1) * phase.K + q * 8;
@@ -407,12 +413,12 @@ __device__ void product_phase(const FusedParams& p, const Shared& sm, const Phas
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
     const int N = phase.N, K = phase.K, kind = phase.kind;
-    const Split sp = split_of(N, K, kind);
+    const Split sp = sm.splits[phase.which];
     const int split = sp.split, k_steps = K / 32;
     const bf16* xs = sm.xs;
     asm volatile("cp.async.wait_group 0;" ::: "memory");       // this thread's prefetched data has landed
     for (int b0 = 0; b0 < sp.count || b0 == 0; b0 += sp.blocks_at_a_time) {
-        const int b = b0 + warp / split, part = warp % split;
+        const int b = b0 + (warp >> sp.split_shift), part = warp & (split - 1);
         const bool active = b < sp.count;
         float acc[NT][4];
 #pragma unroll
@@ -725,18 +731,18 @@ __device__ void attention_phase(const FusedParams& p, const Shared& sm, const Fu
 }
 
 __device__ Phase phase_of(const FusedParams& p, int index) {
-    Phase ph{nullptr, nullptr, 16, 32, OUT_BF16, nullptr, nullptr};
+    Phase ph{nullptr, nullptr, 16, 32, OUT_BF16, nullptr, nullptr, 0};
     const int q_width = p.H * p.D, qkv_width = (p.H + 2 * p.Hkv) * p.D;
     if (index < 4 * p.n_layers) {
         const FusedLayer& layer = p.layers[index / 4];
         switch (index % 4) {
-        case 0: ph = Phase{layer.w_qkv, layer.b_qkv, qkv_width, p.E, OUT_QKV, layer.ln1_g, layer.ln1_b}; break;
-        case 1: ph = Phase{layer.w_o, layer.b_o, p.E, q_width, OUT_ADD, nullptr, nullptr}; break;
-        case 2: ph = Phase{layer.w_fc, layer.b_fc, p.I, p.E, OUT_BF16, layer.ln2_g, layer.ln2_b}; break;
-        default: ph = Phase{layer.w_proj, layer.b_proj, p.E, p.I, OUT_ADD, nullptr, nullptr}; break;
+        case 0: ph = Phase{layer.w_qkv, layer.b_qkv, qkv_width, p.E, OUT_QKV, layer.ln1_g, layer.ln1_b, 0}; break;
+        case 1: ph = Phase{layer.w_o, layer.b_o, p.E, q_width, OUT_ADD, nullptr, nullptr, 1}; break;
+        case 2: ph = Phase{layer.w_fc, layer.b_fc, p.I, p.E, OUT_BF16, layer.ln2_g, layer.ln2_b, 2}; break;
+        default: ph = Phase{layer.w_proj, layer.b_proj, p.E, p.I, OUT_ADD, nullptr, nullptr, 3}; break;
         }
     } else if (index == 4 * p.n_layers && p.n_want > 0) {
-        ph = Phase{p.w_head, nullptr, p.V, p.E, OUT_LOGITS, p.lnf_g, p.lnf_b};
+        ph = Phase{p.w_head, nullptr, p.V, p.E, OUT_LOGITS, p.lnf_g, p.lnf_b, 4};
     }
     return ph;
 }
@@ -758,6 +764,14 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
     sm.kv_base = reinterpret_cast<long*>(cursor); cursor += MAX_TOKENS * 8;
     sm.pos = reinterpret_cast<int*>(cursor);      cursor += MAX_TOKENS * 4;
     sm.table = reinterpret_cast<int*>(cursor);
+    // How each kind of phase is split over CTAs and warps: worked out once (it takes divisions).
+    __shared__ Split splits[5];
+    sm.splits = splits;
+    if (threadIdx.x < 5) {
+        const Phase ph = phase_of(p, threadIdx.x < 4 ? threadIdx.x : 4 * p.n_layers);
+        splits[threadIdx.x] = split_of(ph.N, ph.K, ph.kind);
+    }
+    __syncthreads();
 
     int stamp = 0;
     // timeline (may be null): CTA 0 notes the time after every phase, for profiling
