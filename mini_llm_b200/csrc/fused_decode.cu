@@ -165,15 +165,17 @@ __device__ __forceinline__ void copy_async_4(void* smem_dst, const void* src) {
 }
 
 // Grid-wide barrier: release-add, then poll with acquire loads.  Returns false if the step
-// has failed (limit hit here or elsewhere).
-__device__ bool grid_barrier(const FusedParams& p) {
+// has failed (limit hit here or elsewhere).  The counter only grows, by the grid's size per
+// barrier; `target` (thread 0's, 0 before the first barrier) is the count that ends this
+// barrier: the first one takes it from its ticket with a division, the others add to it.
+__device__ bool grid_barrier(const FusedParams& p, unsigned long long& target) {
     __shared__ int ok;
     __syncthreads();
     if (threadIdx.x == 0) {
         ok = 1;
         unsigned long long ticket;
         asm volatile("atom.add.release.gpu.global.u64 %0, [%1], 1;" : "=l"(ticket) : "l"(p.barrier) : "memory");
-        const unsigned long long target = (ticket / gridDim.x + 1) * gridDim.x;
+        target = target == 0 ? (ticket / gridDim.x + 1) * gridDim.x : target + gridDim.x;
         unsigned long long start = 0;
         for (unsigned spins = 0;; spins++) {
             unsigned long long seen;
@@ -273,23 +275,23 @@ __device__ void prefetch_phase(const FusedParams& p, const Shared& sm, const Pha
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
-// Stage rows of a bf16 matrix written earlier in this kernel (read through L2).
+// Stage rows of a bf16 matrix written earlier in this kernel (read through L2).  A thread
+// takes the same 16 bytes of eight rows at a time: eight loads on their way and no division
+// (an index taken apart by a run-time row length costs more than the copy).
 template <int MT>
 __device__ void stage_copy(bf16* xs, int K, const bf16* src, long ld_src, int n_rows) {
-    const int ldx = K + XS_PAD, chunks = K / 8, total = MT * chunks;
-    for (int i0 = threadIdx.x; i0 < total; i0 += THREADS * 4) {
-        uint4 v[4];
+    const int ldx = K + XS_PAD, chunks = K / 8;
+    for (int c = threadIdx.x; c < chunks; c += THREADS) {
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
-            const int i = i0 + u * THREADS;
-            v[u] = make_uint4(0, 0, 0, 0);
-            if (i < total && i / chunks < n_rows)
-                v[u] = __ldcg(reinterpret_cast<const uint4*>(src + (long)(i / chunks) * ld_src + (i % chunks) * 8));
-        }
+        for (int m0 = 0; m0 < MT; m0 += 8) {
+            uint4 v[8];
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
-            const int i = i0 + u * THREADS;
-            if (i < total) *reinterpret_cast<uint4*>(xs + (i / chunks) * ldx + (i % chunks) * 8) = v[u];
+            for (int u = 0; u < 8; u++) {
+                v[u] = make_uint4(0, 0, 0, 0);
+                if (m0 + u < n_rows) v[u] = __ldcg(reinterpret_cast<const uint4*>(src + (long)(m0 + u) * ld_src + c * 8));
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) *reinterpret_cast<uint4*>(xs + (m0 + u) * ldx + c * 8) = v[u];
         }
     }
 }
@@ -774,6 +776,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
     __syncthreads();
 
     int stamp = 0;
+    unsigned long long barrier_target = 0;
     // timeline (may be null): CTA 0 notes the time after every phase, for profiling
     auto note = [&]() {
         if (p.timeline != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.timeline[stamp] = now_ns();
@@ -820,7 +823,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
             reinterpret_cast<float4*>(p.hidden + (long)t * p.E)[c] = v;
         }
     }
-    if (!grid_barrier(p)) return;
+    if (!grid_barrier(p, barrier_target)) return;
     note();
 
     for (int l = 0; l < p.n_layers; l++) {
@@ -832,7 +835,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
         stage_norm<MT>(p, sm.xs, p.E, sm.gb, layer.eps1, nullptr, p.T);
         __syncthreads();
         product_phase<NT, RES>(p, sm, phase, index & 1, p.E + XS_PAD, p.T, EPI_STORE, &layer, next, best_value, best_index);
-        if (!grid_barrier(p)) return;
+        if (!grid_barrier(p, barrier_target)) return;
         note();
         // ---- phase 2 ----
         switch (p.D) {
@@ -842,14 +845,14 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
         case 128: attention_phase<128>(p, sm, layer); break;
         default: attention_phase<256>(p, sm, layer); break;
         }
-        if (!grid_barrier(p)) return;
+        if (!grid_barrier(p, barrier_target)) return;
         note();
         // ---- phase 3 ----
         phase = next; index++; next = phase_of(p, index + 1);
         stage_copy<MT>(sm.xs, phase.K, p.attn, phase.K, p.T);
         __syncthreads();
         product_phase<NT, RES>(p, sm, phase, index & 1, phase.K + XS_PAD, p.T, EPI_STORE, &layer, next, best_value, best_index);
-        if (!grid_barrier(p)) return;
+        if (!grid_barrier(p, barrier_target)) return;
         note();
         // ---- phase 4 ----
         phase = next; index++; next = phase_of(p, index + 1);
@@ -858,14 +861,14 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
         stage_norm<MT>(p, sm.xs, p.E, sm.gb, layer.eps2, nullptr, p.T);
         __syncthreads();
         product_phase<NT, RES>(p, sm, phase, index & 1, p.E + XS_PAD, p.T, layer.activation, &layer, next, best_value, best_index);
-        if (!grid_barrier(p)) return;
+        if (!grid_barrier(p, barrier_target)) return;
         note();
         // ---- phase 5 ----
         phase = next; index++; next = phase_of(p, index + 1);
         stage_copy<MT>(sm.xs, p.I, p.up, p.I, p.T);
         __syncthreads();
         product_phase<NT, RES>(p, sm, phase, index & 1, p.I + XS_PAD, p.T, EPI_STORE, &layer, next, best_value, best_index);
-        if (!grid_barrier(p)) return;
+        if (!grid_barrier(p, barrier_target)) return;
         note();
         phase = next; index++;
     }
