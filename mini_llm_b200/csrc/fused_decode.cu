@@ -548,7 +548,7 @@ __device__ void product_phase(const FusedParams& p, const Shared& sm, const Phas
                 if (kind == OUT_ADD) {
                     p.hidden[(long)m * N + n] = old[t][i] + v;
                 } else if (kind == OUT_BF16) {
-                    if (activation == EPI_GELU_TANH) v = gelu_tanh_f(v);
+                    if (activation == EPI_GELU_TANH) v = gelu_tanh_fast(v);
                     else if (activation == EPI_GELU_ERF) v = gelu_erf_f(v);
                     p.up[(long)m * N + n] = __float2bfloat16_rn(v);
                 } else if (kind == OUT_QKV) {

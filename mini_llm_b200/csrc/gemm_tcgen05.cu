@@ -57,15 +57,6 @@ struct GemmParams {
     int max_blocks, page_size, q_width, kv_width;
 };
 
-// gelu, tanh form, with the hardware's approximate tanh (relative error about 2^-11): the
-// result is rounded to bfloat16 (2^-9) right after, and an exact tanh for every element of a
-// feed-forward product costs more SM time than the product itself.
-__device__ __forceinline__ float gelu_tanh_fast(float u) {
-    float t;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608f * (u + 0.044715f * u * u * u)));
-    return 0.5f * u * (1.0f + t);
-}
-
 __device__ __forceinline__ float activate(float v, int epilogue) {
     if (epilogue == EPI_GELU_TANH) return gelu_tanh_fast(v);
     if (epilogue == EPI_GELU_ERF) return gelu_erf_f(v);
