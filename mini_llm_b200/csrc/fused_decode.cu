@@ -231,7 +231,7 @@ __device__ __forceinline__ Split split_of(int N, int K, int kind) {
 // Start copying what `phase` needs and what is final already: this thread's first weight
 // fragments (its private slots of wbuf), the biases of its rows, the values its results are
 // added to, and (all threads together) the gain and shift of the phase's input norm.
-template <int NT, int RES>
+template <int NT, int RES, bool ADDS, bool NORMED>       // of `phase`: its results are added to hidden; its input is normed
 __device__ void prefetch_phase(const FusedParams& p, const Shared& sm, const Phase& phase, int parity, int n_rows) {
     if (phase.w != nullptr) {
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -253,7 +253,7 @@ __device__ void prefetch_phase(const FusedParams& p, const Shared& sm, const Pha
                     if (row_lo < phase.N) copy_async_4(bias, phase.bias + row_lo);
                     if (row_hi < phase.N) copy_async_4(bias + 1, phase.bias + row_hi);
                 }
-                if (phase.kind == OUT_ADD) {
+                if (ADDS) {
 #pragma unroll
                     for (int t = 0; t < NT; t++)
 #pragma unroll
@@ -265,7 +265,7 @@ __device__ void prefetch_phase(const FusedParams& p, const Shared& sm, const Pha
                 }
             }
         }
-        if (phase.gamma != nullptr) {
+        if (NORMED) {
             for (int c = threadIdx.x; c < phase.K / 4; c += THREADS) {
                 copy_async_16(sm.gb + c * 4, phase.gamma + c * 4);
                 copy_async_16(sm.gb + phase.K + c * 4, phase.beta + c * 4);
@@ -408,13 +408,16 @@ __device__ __forceinline__ float sampling_score(const FusedParams& p, int m, int
 // and B agree, so the eight values feed two instructions: values 0..3 the first (slots 2q,
 // 2q+1, 2q+8, 2q+9), values 4..7 the second.
 // Once a thread has read its prefetched data it starts the prefetch of `next`.
-template <int NT, int RES>
+// KIND is the phase's kind, NEXT_ADDS and NEXT_NORMED describe `next` (see prefetch_phase): known
+// where the phase is called, so that each copy of this code holds one epilogue and one prefetch.
+template <int NT, int RES, int KIND, bool NEXT_ADDS, bool NEXT_NORMED>
 __device__ void product_phase(const FusedParams& p, const Shared& sm, const Phase& phase, int parity, int ldx, int n_rows,
                               int activation, const FusedLayer* layer, const Phase& next, float* best_value,
                               int* best_index) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
-    const int N = phase.N, K = phase.K, kind = phase.kind;
+    const int N = phase.N, K = phase.K;
+    constexpr int kind = KIND;
     const Split sp = sm.splits[phase.which];
     const int split = sp.split, k_steps = K / 32;
     const bf16* xs = sm.xs;
@@ -515,7 +518,7 @@ __device__ void product_phase(const FusedParams& p, const Shared& sm, const Phas
                 }
             }
         }
-        if (b0 == 0) prefetch_phase<NT, RES>(p, sm, next, parity ^ 1, p.T);
+        if (b0 == 0) prefetch_phase<NT, RES, NEXT_ADDS, NEXT_NORMED>(p, sm, next, parity ^ 1, p.T);
         if (split > 1) {
             float* mine = sm.red + (warp * 32 + lane) * (NT * 4);
 #pragma unroll
@@ -802,7 +805,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
     }
     int index = 0;
     Phase phase = phase_of(p, 0);
-    prefetch_phase<NT, RES>(p, sm, phase, 0, p.T);
+    prefetch_phase<NT, RES, false, true>(p, sm, phase, 0, p.T);
     // ---- embedding: token t is written by CTA t % grid ----
     for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
         int token = p.token_ids[t];
@@ -834,7 +837,8 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
         __syncthreads();                                  // gain and shift were copied by all threads
         stage_norm<MT>(p, sm.xs, p.E, sm.gb, layer.eps1, nullptr, p.T);
         __syncthreads();
-        product_phase<NT, RES>(p, sm, phase, index & 1, p.E + XS_PAD, p.T, EPI_STORE, &layer, next, best_value, best_index);
+        product_phase<NT, RES, OUT_QKV, true, false>(p, sm, phase, index & 1, p.E + XS_PAD, p.T, EPI_STORE, &layer, next, best_value,
+                                                     best_index);
         if (!grid_barrier(p, barrier_target)) return;
         note();
         // ---- phase 2 ----
@@ -851,7 +855,8 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
         phase = next; index++; next = phase_of(p, index + 1);
         stage_copy<MT>(sm.xs, phase.K, p.attn, phase.K, p.T);
         __syncthreads();
-        product_phase<NT, RES>(p, sm, phase, index & 1, phase.K + XS_PAD, p.T, EPI_STORE, &layer, next, best_value, best_index);
+        product_phase<NT, RES, OUT_ADD, false, true>(p, sm, phase, index & 1, phase.K + XS_PAD, p.T, EPI_STORE, &layer, next,
+                                                     best_value, best_index);
         if (!grid_barrier(p, barrier_target)) return;
         note();
         // ---- phase 4 ----
@@ -860,14 +865,16 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
         __syncthreads();
         stage_norm<MT>(p, sm.xs, p.E, sm.gb, layer.eps2, nullptr, p.T);
         __syncthreads();
-        product_phase<NT, RES>(p, sm, phase, index & 1, p.E + XS_PAD, p.T, layer.activation, &layer, next, best_value, best_index);
+        product_phase<NT, RES, OUT_BF16, true, false>(p, sm, phase, index & 1, p.E + XS_PAD, p.T, layer.activation, &layer, next,
+                                                      best_value, best_index);
         if (!grid_barrier(p, barrier_target)) return;
         note();
         // ---- phase 5 ----
         phase = next; index++; next = phase_of(p, index + 1);
         stage_copy<MT>(sm.xs, p.I, p.up, p.I, p.T);
         __syncthreads();
-        product_phase<NT, RES>(p, sm, phase, index & 1, p.I + XS_PAD, p.T, EPI_STORE, &layer, next, best_value, best_index);
+        product_phase<NT, RES, OUT_ADD, false, true>(p, sm, phase, index & 1, p.I + XS_PAD, p.T, EPI_STORE, &layer, next, best_value,
+                                                     best_index);
         if (!grid_barrier(p, barrier_target)) return;
         note();
         phase = next; index++;
@@ -879,8 +886,8 @@ __global__ void __launch_bounds__(THREADS, 1) fused_decode_kernel(const FusedPar
     __syncthreads();
     stage_norm<MT>(p, sm.xs, p.E, sm.gb, p.eps_f, p.want_rows, p.n_want);
     __syncthreads();
-    product_phase<NT, RES>(p, sm, phase, index & 1, p.E + XS_PAD, p.n_want, EPI_STORE, nullptr, phase_of(p, index + 1),
-                      best_value, best_index);
+    product_phase<NT, RES, OUT_LOGITS, false, false>(p, sm, phase, index & 1, p.E + XS_PAD, p.n_want, EPI_STORE, nullptr,
+                                                     phase_of(p, index + 1), best_value, best_index);
     note();
     if (p.sample == 0) return;
     // A lane holds candidates for tokens t*8 + 2q + j (slot t*2 + j): the lanes of equal q
