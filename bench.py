@@ -28,7 +28,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: GPT-2 small.  Layers may be reduced with --layers where time or
+# The headline configuration: GPT-2 small.  Layers may be reduced with --layers where time or
 # memory needs it; the line then names both numbers.
 GPT2_SMALL = {"architectures": ["GPT2LMHeadModel"], "model_type": "gpt2", "n_layer": 12, "n_embd": 768, "n_head": 12,
               "n_inner": 3072, "vocab_size": 50257, "n_positions": 1024, "activation_function": "gelu_new",
