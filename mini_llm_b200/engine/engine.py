@@ -25,7 +25,7 @@ from ..cache.storage import CacheStorage
 from ..config.registry import config_from_folder, describe_model
 from ..kernels import ops
 from ..kernels.lib import KernelError
-from ..kernels.dispatch import Kernels
+from ..kernels.dispatch import SPLIT_ATTENTION_MAX_ROWS, Kernels
 from ..sampling import SamplingParams
 from .context import ControlBlock, StepContext, Workspace
 from .fused_decode import FusedDecodePlan
@@ -137,19 +137,29 @@ class Engine:
             n = len(entry.tokens)
             if n == 0:
                 raise StepError(f"entry {index}: no tokens")
-            try:
-                ids = np.asarray(entry.tokens, dtype=np.int64)
-            except (TypeError, ValueError, OverflowError):
-                raise StepError(f"entry {index}: token ids must be integers") from None
-            low = int(ids.min()) if ids.ndim == 1 else -2
-            if low == PREVIOUS and not (ids[1:] == PREVIOUS).any():
-                if entry.slot not in self._kept_valid:
-                    raise StepError(f"entry {index}: slot {entry.slot} has sampled no token that PREVIOUS could name")
-                low = int(ids[1:].min()) if n > 1 else 0
-            if ids.ndim != 1 or low < 0 or int(ids.max()) >= vocab:
-                bad = next((t for t in entry.tokens if not 0 <= int(t) < vocab), None)
-                raise StepError(f"entry {index}: token id {bad} is outside the vocabulary [0, {vocab}) "
-                                f"(PREVIOUS may only be an entry's first token)")
+            first = entry.tokens[0]
+            if n == 1 and type(first) is int:
+                # a decoding request's one token: the common case, checked without an array
+                if first == PREVIOUS:
+                    if entry.slot not in self._kept_valid:
+                        raise StepError(f"entry {index}: slot {entry.slot} has sampled no token that PREVIOUS could name")
+                elif not 0 <= first < vocab:
+                    raise StepError(f"entry {index}: token id {first} is outside the vocabulary [0, {vocab}) "
+                                    f"(PREVIOUS may only be an entry's first token)")
+            else:
+                try:
+                    ids = np.asarray(entry.tokens, dtype=np.int64)
+                except (TypeError, ValueError, OverflowError):
+                    raise StepError(f"entry {index}: token ids must be integers") from None
+                low = int(ids.min()) if ids.ndim == 1 else -2
+                if low == PREVIOUS and not (ids[1:] == PREVIOUS).any():
+                    if entry.slot not in self._kept_valid:
+                        raise StepError(f"entry {index}: slot {entry.slot} has sampled no token that PREVIOUS could name")
+                    low = int(ids[1:].min()) if n > 1 else 0
+                if ids.ndim != 1 or low < 0 or int(ids.max()) >= vocab:
+                    bad = next((t for t in entry.tokens if not 0 <= int(t) < vocab), None)
+                    raise StepError(f"entry {index}: token id {bad} is outside the vocabulary [0, {vocab}) "
+                                    f"(PREVIOUS may only be an entry's first token)")
             have = self.cache.length(entry.slot)
             if have + n > self.max_positions:
                 raise StepError(f"entry {index}: {have} cached + {n} new tokens exceed the {self.max_positions} "
@@ -221,7 +231,13 @@ class Engine:
         for group in self.cache.groups:
             if group.paged:
                 arrays[("block_table", group.index)] = group.table[ctx.item_slots]
-        tiles, n_split, most_parts = ops.attention_tiles(ctx.item_offsets, ctx.item_counts, ctx.item_starts)
+        # A step of single tokens of few requests goes to the decode attention, which takes no
+        # work list: none is made for it.
+        decode_only = n_tokens == n_items
+        if decode_only and n_items <= SPLIT_ATTENTION_MAX_ROWS:
+            tiles, n_split, most_parts = [], 0, 1
+        else:
+            tiles, n_split, most_parts = ops.attention_tiles(ctx.item_offsets, ctx.item_counts, ctx.item_starts)
         arrays["att_tiles"] = np.array(tiles, dtype=np.int32)
         if sampling is not None:
             arrays["temperature"] = np.array([s.temperature for s in sampling], dtype=np.float32)
@@ -239,7 +255,7 @@ class Engine:
         ctx.want_slots = views["want_slots"][:n_want]
         ctx.any_previous = any_previous
         ctx.decode_only = all(n == 1 for n in ctx.item_counts)
-        ctx.att_tiles, ctx.n_att_tiles = views["att_tiles"], len(tiles)
+        ctx.att_tiles, ctx.n_att_tiles = (views["att_tiles"] if tiles else None), len(tiles)
         ctx.n_split_tiles, ctx.att_parts = n_split, most_parts
         for view in self.storage.views:
             if view.kind == "paged":
