@@ -145,14 +145,16 @@ class CacheManager:
                 return False
         return self._take(slot).length + n_new <= self.max_tokens_per_request
 
-    def reserve(self, slot: int, n_new: int) -> bool:
-        """Make room for ``n_new`` more tokens in every group, or change nothing and return False."""
+    def reserve(self, slot: int, n_new: int, needed: list | None = None) -> bool:
+        """Make room for ``n_new`` more tokens in every group, or change nothing and return False.
+        ``needed``: what ``pages_needed(slot, n_new)`` just returned, if the caller has it."""
         request = self._take(slot)
         if n_new < 0:
             raise ValueError("cannot reserve a negative number of tokens")
         if request.length + n_new > self.max_tokens_per_request:
             return False
-        needed = self.pages_needed(slot, n_new)
+        if needed is None:
+            needed = self.pages_needed(slot, n_new)
         for group, count in zip(self.groups, needed):
             if group.paged and count > group.pool.available:
                 return False

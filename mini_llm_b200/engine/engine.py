@@ -171,16 +171,19 @@ class Engine:
     def _reserve(self, entries) -> None:
         cache = self.cache
         needed = [0] * len(cache.groups)
+        per_entry = []
         for entry in entries:
-            for g, count in enumerate(cache.pages_needed(entry.slot, len(entry.tokens))):
+            mine = cache.pages_needed(entry.slot, len(entry.tokens))
+            per_entry.append(mine)
+            for g, count in enumerate(mine):
                 needed[g] += count
         if any(needed):
             free = cache.pages_free()
             for g, count in enumerate(needed):
                 if count > free[g]:
                     raise OutOfPages(f"the step needs {count} more pages in cache group {g}, {free[g]} are free")
-        for entry in entries:
-            if not cache.reserve(entry.slot, len(entry.tokens)):
+        for entry, mine in zip(entries, per_entry):
+            if not cache.reserve(entry.slot, len(entry.tokens), mine):
                 raise OutOfPages("page reservation failed after it was checked")   # cannot happen
 
     def step(self, entries, sampling=None):
