@@ -86,6 +86,7 @@ class CacheManager:
                 self.entry_group[entry] = (index, position)
         self._free_slots = list(range(self.max_requests - 1, -1, -1))
         self._requests: dict[int, _Request] = {}
+        self._paged = [(g.index, g.paged) for g in self.groups]     # what pages_needed walks
         self.freed_by_window = 0
 
     # ---- slots ------------------------------------------------------------------------------
@@ -134,16 +135,22 @@ class CacheManager:
     def pages_needed(self, slot: int, n_new: int) -> list:
         """Pages each paged group must add so the request can hold ``n_new`` more tokens."""
         request = self._take(slot)
-        target = self._blocks_for(request.length + n_new)
-        return [max(0, target - request.n_blocks[g.index]) if g.paged else 0 for g in self.groups]
+        target = -(-(request.length + n_new) // self.page_size)
+        held = request.n_blocks
+        return [(target - held[g] if target > held[g] else 0) if paged else 0 for g, paged in self._paged]
+
+    def room_for(self, slot: int, n_new: int, spare: list | None = None) -> list | None:
+        """``pages_needed(slot, n_new)`` if ``reserve`` would succeed, else None.  ``spare[g]``
+        pages of group g count as already taken."""
+        needed = self.pages_needed(slot, n_new)
+        for group, count in zip(self.groups, needed):
+            if count > 0 and count > group.pool.available - (spare[group.index] if spare else 0):
+                return None
+        return needed if self._take(slot).length + n_new <= self.max_tokens_per_request else None
 
     def can_reserve(self, slot: int, n_new: int, spare: list | None = None) -> bool:
         """Would ``reserve`` succeed?  ``spare[g]`` pages of group g count as already taken."""
-        needed = self.pages_needed(slot, n_new)
-        for group, count in zip(self.groups, needed):
-            if group.paged and count > group.pool.available - (spare[group.index] if spare else 0):
-                return False
-        return self._take(slot).length + n_new <= self.max_tokens_per_request
+        return self.room_for(slot, n_new, spare) is not None
 
     def reserve(self, slot: int, n_new: int, needed: list | None = None) -> bool:
         """Make room for ``n_new`` more tokens in every group, or change nothing and return False.

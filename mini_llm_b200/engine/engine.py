@@ -200,35 +200,53 @@ class Engine:
 
         n_tokens = sum(len(e.tokens) for e in entries)
         n_items = len(entries)
-        token_ids = np.empty(n_tokens, dtype=np.int32)
-        positions = np.empty(n_tokens, dtype=np.int32)
-        token_item = np.empty(n_tokens, dtype=np.int32)
-        want_rows = np.empty(n_want, dtype=np.int32)
-        want_slots = np.full(n_want, -1, dtype=np.int32)      # the entry's last wanted row is kept for its slot
         any_previous = False
         ctx = self.ctx
-        ctx.item_slots, ctx.item_starts, ctx.item_counts, ctx.item_offsets = [], [], [], []
-        row = 0
-        w = 0
-        for index, entry in enumerate(entries):
-            n = len(entry.tokens)
-            start = self.cache.length(entry.slot)
-            token_ids[row:row + n] = entry.tokens
-            if token_ids[row] == PREVIOUS:
-                token_ids[row] = -1 - entry.slot
-                any_previous = True
-            positions[row:row + n] = np.arange(start, start + n, dtype=np.int32)
-            token_item[row:row + n] = index
-            for place in entry.want:
-                want_rows[w] = row + int(place)
-                w += 1
-            if entry.want:
-                want_slots[w - 1] = entry.slot
-            ctx.item_slots.append(entry.slot)
-            ctx.item_starts.append(start)
-            ctx.item_counts.append(n)
-            ctx.item_offsets.append(row)
-            row += n
+        cache_length = self.cache.length
+        if n_tokens == n_items and all(type(e.tokens[0]) is int and len(e.want) <= 1 for e in entries):
+            # single tokens only (a decode step): the arrays straight from lists, no slices per entry
+            slots = [e.slot for e in entries]
+            starts = [cache_length(slot) for slot in slots]
+            firsts = [e.tokens[0] for e in entries]
+            any_previous = PREVIOUS in firsts
+            if any_previous:
+                firsts = [-1 - slot if t == PREVIOUS else t for t, slot in zip(firsts, slots)]
+            token_ids = np.array(firsts, dtype=np.int32)
+            positions = np.array(starts, dtype=np.int32)
+            token_item = np.arange(n_items, dtype=np.int32)
+            wanted = [(index, e.slot) for index, e in enumerate(entries) if e.want]
+            want_rows = np.array([index for index, _ in wanted], dtype=np.int32)
+            want_slots = np.array([slot for _, slot in wanted], dtype=np.int32)
+            ctx.item_slots, ctx.item_starts = slots, starts
+            ctx.item_counts, ctx.item_offsets = [1] * n_items, list(range(n_items))
+        else:
+            token_ids = np.empty(n_tokens, dtype=np.int32)
+            positions = np.empty(n_tokens, dtype=np.int32)
+            token_item = np.empty(n_tokens, dtype=np.int32)
+            want_rows = np.empty(n_want, dtype=np.int32)
+            want_slots = np.full(n_want, -1, dtype=np.int32)      # the entry's last wanted row is kept for its slot
+            ctx.item_slots, ctx.item_starts, ctx.item_counts, ctx.item_offsets = [], [], [], []
+            row = 0
+            w = 0
+            for index, entry in enumerate(entries):
+                n = len(entry.tokens)
+                start = cache_length(entry.slot)
+                token_ids[row:row + n] = entry.tokens
+                if token_ids[row] == PREVIOUS:
+                    token_ids[row] = -1 - entry.slot
+                    any_previous = True
+                positions[row:row + n] = np.arange(start, start + n, dtype=np.int32)
+                token_item[row:row + n] = index
+                for place in entry.want:
+                    want_rows[w] = row + int(place)
+                    w += 1
+                if entry.want:
+                    want_slots[w - 1] = entry.slot
+                ctx.item_slots.append(entry.slot)
+                ctx.item_starts.append(start)
+                ctx.item_counts.append(n)
+                ctx.item_offsets.append(row)
+                row += n
         arrays = {"token_ids": token_ids, "positions": positions, "token_item": token_item, "want_rows": want_rows,
                   "want_slots": want_slots}
         for group in self.cache.groups:
@@ -249,7 +267,7 @@ class Engine:
             arrays["counters"] = np.array([s.counter for s in sampling], dtype=np.int32)
         # the one-kernel decode step takes its arrays from alternating buffers, so that the next
         # step's copy runs beside it; captured graphs have their addresses fixed
-        alternate = self.fused is not None and self.fused.takes_sizes(n_tokens, all(n == 1 for n in ctx.item_counts))
+        alternate = self.fused is not None and self.fused.takes_sizes(n_tokens, decode_only)
         views = self.control.upload(arrays, n_tokens, n_items, alternate)
 
         ctx.n_tokens, ctx.n_items, ctx.n_want = n_tokens, n_items, n_want
@@ -257,7 +275,7 @@ class Engine:
         ctx.want_rows = views["want_rows"][:n_want]
         ctx.want_slots = views["want_slots"][:n_want]
         ctx.any_previous = any_previous
-        ctx.decode_only = all(n == 1 for n in ctx.item_counts)
+        ctx.decode_only = decode_only
         ctx.att_tiles, ctx.n_att_tiles = (views["att_tiles"] if tiles else None), len(tiles)
         ctx.n_split_tiles, ctx.att_parts = n_split, most_parts
         for view in self.storage.views:

@@ -96,7 +96,7 @@ class Scheduler:
         self._admitted = 0
         self.counters = collections.Counter()
         self.run_ahead = bool(run_ahead)
-        self._flight = None               # (entries, owners) of the launched step whose tokens are unread
+        self._flight = None               # (entries, owners, ids of the owners it samples for) of the launched step whose tokens are unread
 
     # ---- requests in ------------------------------------------------------------------------
     def submit(self, request: Request) -> None:
@@ -151,7 +151,7 @@ class Scheduler:
         self.counters["batch_entries"] += len(entries)
         if any(len(e.tokens) == 1 and e.want for e in entries):
             self.counters["decode_steps"] += 1
-        earlier, self._flight = self._flight, (entries, owners)
+        earlier, self._flight = self._flight, (entries, owners, {id(o) for o, e in zip(owners, entries) if e.want})
         for running, entry in zip(owners, entries):
             n = len(entry.tokens)
             self.counters["decode_tokens" if running.decoding else "prefill_tokens"] += n
@@ -173,7 +173,7 @@ class Scheduler:
         """Read a launched step's tokens and deliver them."""
         if flight is None:
             flight, self._flight = self._flight, None
-        entries, owners = flight
+        entries, owners, _ = flight
         try:
             sampled = self.engine.sampled_tokens(ago) if self.run_ahead else self.engine.sampled_tokens()
         except Exception as error:
@@ -191,13 +191,16 @@ class Scheduler:
         self.running = [r for r in self.running if not r.request.done]
 
     def _in_flight(self, running) -> bool:
-        return self._flight is not None and any(o is running and e.want for o, e in zip(self._flight[1], self._flight[0]))
+        return self._flight is not None and id(running) in self._flight[2]
 
     def _pages_are_short(self) -> bool:
         """Whether the decoding requests' next tokens need more pages than are free (lengths
         are known without the tokens: a launched step has already been committed)."""
         cache = self.engine.cache
         free = cache.pages_free()
+        decoding = sum(1 for running in self.running if running.decoding)
+        if all(f >= decoding for f in free):
+            return False                      # one more token takes at most one page per group
         need = [0] * len(free)
         for running in self.running:
             if running.decoding:
@@ -220,8 +223,9 @@ class Scheduler:
         entries, owners = [], []
         budget = self.budget
 
-        def take(running, n, want):
-            needed = cache.pages_needed(running.slot, n)
+        def take(running, n, want, needed=None):
+            if needed is None:
+                needed = cache.pages_needed(running.slot, n)
             for g, count in enumerate(needed):
                 spare[g] += count
             entries.append(StepEntry(running.slot, running.pending[:n], [n - 1] if want else []))
@@ -231,7 +235,7 @@ class Scheduler:
         for running in [r for r in self.running if r.decoding]:
             if running not in self.running:
                 continue                      # preempted below
-            while not cache.can_reserve(running.slot, 1, spare):
+            while (needed := cache.room_for(running.slot, 1, spare)) is None:
                 victim = max(self.running, key=lambda r: r.order)
                 if victim is running and len(self.running) == 1:
                     self._close(running)
@@ -249,7 +253,7 @@ class Scheduler:
             if running.awaiting and self._ends_on_count(running.request, 1):
                 continue                      # the token on its way is its last
             if running in self.running and not running.request.done and budget > 0:
-                take(running, 1, True)
+                take(running, 1, True, needed)
                 budget -= 1
 
         # 2. portions of prompts: continued ones first, then new requests in arrival order
