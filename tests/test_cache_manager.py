@@ -57,6 +57,21 @@ def test_block_tables_grow_and_are_given_back():
     m.check()
 
 
+def test_room_for_gives_the_need_or_none():
+    """``room_for`` answers like ``can_reserve`` and hands back what ``pages_needed`` would;
+    ``reserve`` given that need does what it does without it; pages set aside count as taken."""
+    m = CacheManager([FULL, STATE, WINDOW], page_size=8, n_pages=[4, 0, 3], max_requests=2, max_tokens_per_request=40)
+    a = m.open()
+    assert m.room_for(a, 9) == m.pages_needed(a, 9) == [2, 0, 2]
+    assert m.room_for(a, 25) is None and not m.can_reserve(a, 25)          # the second pool has 3 pages
+    assert m.room_for(a, 41) is None                                      # more than a request may hold
+    assert m.room_for(a, 9, spare=[2, 0, 1]) == [2, 0, 2] and m.room_for(a, 9, spare=[3, 0, 0]) is None
+    need = m.room_for(a, 9)
+    assert m.reserve(a, 9, need) and m.pages_held(a) == [2, 0, 2] and m.room_for(a, 0) == [0, 0, 0]
+    m.commit(a, 9)
+    m.check()
+
+
 def test_request_cannot_outgrow_its_positions():
     m = CacheManager([FULL], page_size=4, n_pages=100, max_requests=1, max_tokens_per_request=10)
     s = m.open()
