@@ -88,6 +88,9 @@ class CacheManager:
         self._requests: dict[int, _Request] = {}
         self._paged = [(g.index, g.paged) for g in self.groups]     # what pages_needed walks
         self.freed_by_window = 0
+        # Called with (group index, page ids) whenever pages go back to a pool: the device side
+        # of a debugging engine overwrites them, so that a stale block-table row shows.
+        self.on_free = None
 
     # ---- slots ------------------------------------------------------------------------------
     @property
@@ -112,6 +115,7 @@ class CacheManager:
             row = group.table[slot]
             held = [int(p) for p in row[request.first_block[group.index]:request.n_blocks[group.index]] if p != NO_PAGE]
             group.pool.free(held, slot)
+            self._freed(group, held)
             row[:] = NO_PAGE
         del self._requests[slot]
         self._free_slots.append(slot)
@@ -175,6 +179,28 @@ class CacheManager:
         request.reserved = max(request.reserved, request.length + n_new)
         return True
 
+    def unreserve(self, slot: int) -> None:
+        """Give back the pages that were reserved beyond the committed length (a step that
+        reserved them did not run to its end): the request is as it was before ``reserve``."""
+        request = self._take(slot)
+        keep = self._blocks_for(request.length)
+        for group in self.groups:
+            if not group.paged:
+                continue
+            held = request.n_blocks[group.index]
+            if held > keep:
+                row = group.table[slot]
+                extra = [int(p) for p in row[keep:held] if p != NO_PAGE]
+                group.pool.free(extra, slot)
+                self._freed(group, extra)
+                row[keep:held] = NO_PAGE
+                request.n_blocks[group.index] = keep
+        request.reserved = request.length
+
+    def _freed(self, group, pages) -> None:
+        if self.on_free is not None and pages:
+            self.on_free(group.index, pages)
+
     def commit(self, slot: int, n_new: int) -> None:
         """``n_new`` tokens were stored.  Pages a window has passed are given back."""
         request = self._take(slot)
@@ -192,6 +218,7 @@ class CacheManager:
                 row = group.table[slot]
                 passed = [int(p) for p in row[first:keep_from]]
                 group.pool.free(passed, slot)
+                self._freed(group, passed)
                 row[first:keep_from] = NO_PAGE
                 request.first_block[group.index] = keep_from
                 self.freed_by_window += len(passed)

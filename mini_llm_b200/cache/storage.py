@@ -50,18 +50,24 @@ class StateLayerCache(LayerCache):
 
 
 class CacheStorage:
-    def __init__(self, manager, order, dtype: torch.dtype, device, max_items: int):
+    def __init__(self, manager, order, dtype: torch.dtype, device, max_items: int, poison: float | None = None):
+        """``poison``: a debugging value.  Every page slot holds it until a token is stored
+        there, and a page holds it again from the moment it is given back: a kernel that
+        reads a slot past a request's length, or through a stale block-table row, then
+        reads ``poison`` instead of another request's plausible keys."""
         self.manager = manager
         self.device = device
         self.max_items = int(max_items)
+        self.poison = poison
         self.keys, self.values, self.states, self.block_tables = {}, {}, {}, {}
         for group in manager.groups:
             n_entries = len(group.entries)
             if isinstance(group.need, PagedKV):
                 shape = (n_entries, max(group.pool.n_pages, 1), manager.page_size, group.need.n_kv_heads,
                          group.need.head_size)
-                self.keys[group.index] = torch.zeros(shape, dtype=dtype, device=device)
-                self.values[group.index] = torch.zeros(shape, dtype=dtype, device=device)
+                fill = 0.0 if poison is None else poison
+                self.keys[group.index] = torch.full(shape, fill, dtype=dtype, device=device)
+                self.values[group.index] = torch.full(shape, fill, dtype=dtype, device=device)
                 self.block_tables[group.index] = torch.zeros((self.max_items, group.max_blocks), dtype=torch.int32,
                                                              device=device)
             elif isinstance(group.need, FixedState):
@@ -81,6 +87,32 @@ class CacheStorage:
                                                   self.block_tables[g], manager.page_size, writes))
             else:
                 self.views.append(StateLayerCache(g, self.states[g][position], writes))
+
+        if poison is not None:
+            manager.on_free = self.poison_pages
+
+    def poison_pages(self, group_index: int, pages) -> None:
+        """Overwrite pages that went back to their pool (debugging engines only)."""
+        index = torch.tensor(list(pages), dtype=torch.int64, device=self.device)
+        for store in (self.keys, self.values):
+            store[group_index].index_fill_(1, index, self.poison)
+
+    def read_tokens(self, view_index: int, slot: int, first: int, count: int):
+        """Keys and values of tokens ``first .. first + count - 1`` of the request in ``slot``
+        as run entry ``view_index`` holds them: two tensors [count, kv_heads, head_size],
+        gathered through the block table (the reference's test hook copies a layer's rows
+        out of its contiguous cache, engine/src/gpt2_gpu.cu:185-195)."""
+        view = self.views[view_index]
+        if view.kind != "paged":
+            raise ValueError(f"run entry {view_index} keeps no paged keys and values")
+        page_size = self.manager.page_size
+        row = self.manager.block_table_row(view.group, slot)
+        positions = torch.arange(first, first + count, dtype=torch.int64)
+        pages = torch.from_numpy(row.astype("int64"))[positions // page_size]
+        if count and int(pages.min()) < 0:
+            raise ValueError(f"slot {slot} holds no page for some of tokens {first}..{first + count - 1}")
+        pages, within = pages.to(self.device), (positions % page_size).to(self.device)
+        return view.k_pages[pages, within].clone(), view.v_pages[pages, within].clone()
 
     def reset_slot(self, slot: int) -> None:
         """Fixed-size state starts at zero for a new request."""

@@ -12,6 +12,10 @@ line of numbers), and text only if the model folder holds a ``tokenizer.json``
 and the ``tokenizers`` package is installed.
 
     python -m mini_llm_b200.cli --model DIR --prompt-ids 464,3290,318 --temperature 0
+    python -m mini_llm_b200.cli --random config.json --weights-seed 0 --prompt-ids 1,2,3
+
+The second form needs no weights file: it writes a model folder with seeded random weights
+for the given ``config.json`` into a temporary folder first.
 """
 
 from __future__ import annotations
@@ -36,7 +40,28 @@ def parse_args(argv=None) -> argparse.Namespace:
     parser.add_argument("--page-size", type=int, default=16)
     parser.add_argument("--max-tokens-per-step", type=int, default=2048)
     parser.add_argument("--plain-kernels", action="store_true")
+    parser.add_argument("--random", metavar="CONFIG.json",
+                        help="instead of --model: write a model folder with random weights for this config.json "
+                             "into a temporary folder and complete with it")
+    parser.add_argument("--weights-seed", type=int, default=0, help="seed of --random's weights")
+    parser.add_argument("--recipe", default="gpt2", choices=("gpt2", "varied"), help="how --random fills the tensors")
     return parser.parse_args(argv)
+
+
+def random_model_folder(args) -> str:
+    """A temporary model folder (config.json, model.safetensors) for ``--random``."""
+    import atexit
+    import json
+    import shutil
+    import tempfile
+    from .config import config_from_dict
+    from .weights import write_random_model
+    with open(args.random) as handle:
+        raw = json.load(handle)
+    folder = tempfile.mkdtemp(prefix="mini_llm_b200-random-")
+    atexit.register(shutil.rmtree, folder, ignore_errors=True)
+    write_random_model(config_from_dict(raw), args.weights_seed, folder, recipe=args.recipe)
+    return folder
 
 
 def choose_device(requested: str) -> str:
@@ -82,6 +107,8 @@ def main(argv=None) -> int:
     args = parse_args(argv)
     device = choose_device(args.device)
     from .generate import LLM
+    if args.random:
+        args.model = random_model_folder(args)
     llm = LLM(args.model, dtype=args.dtype, device=device, page_size=args.page_size,
               max_tokens_per_step=args.max_tokens_per_step, plain_kernels=args.plain_kernels)
     tokenizer = load_tokenizer(args.model)

@@ -539,8 +539,10 @@ int launch(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v, con
             return fail("attention: cannot raise the shared memory limit");
         configured = true;
     }
-    int sms = 148;
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+    int device = 0, sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
+        sms = 148;
     const long total = (long)n_tiles * p.n_heads, resident = (long)sms * (D <= 64 ? 2 : 1);
     attention_tcgen05_kernel<D><<<(unsigned)std::min(total, resident), THREADS, smem, s>>>(q, k, v, p);
     return check_launch("attention_tcgen05_kernel");

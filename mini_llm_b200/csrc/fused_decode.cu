@@ -86,6 +86,8 @@ struct FusedParams {
     int att_parts;                  // CTAs that share the keys of one (token, head): 1 .. 16
     float* att_partial;             // [T * H, att_parts, D + 2]: a part's output, maximum, sum
     int* att_counters;              // [T * H], zero between launches
+    unsigned long long barrier_limit_ns;    // 0: the default limit of a barrier wait
+    int skip_arrival;               // tests of the limit: CTA 0 does not arrive at the first barrier, so no CTA passes it
 };
 
 namespace {
@@ -174,8 +176,12 @@ __device__ bool grid_barrier(const FusedParams& p, unsigned long long& target) {
     if (threadIdx.x == 0) {
         ok = 1;
         unsigned long long ticket;
-        asm volatile("atom.add.release.gpu.global.u64 %0, [%1], 1;" : "=l"(ticket) : "l"(p.barrier) : "memory");
+        if (p.skip_arrival != 0 && blockIdx.x == 0 && target == 0)
+            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(ticket) : "l"(p.barrier) : "memory");
+        else
+            asm volatile("atom.add.release.gpu.global.u64 %0, [%1], 1;" : "=l"(ticket) : "l"(p.barrier) : "memory");
         target = target == 0 ? (ticket / gridDim.x + 1) * gridDim.x : target + gridDim.x;
+        const unsigned long long limit = p.barrier_limit_ns != 0 ? p.barrier_limit_ns : BARRIER_LIMIT_NS;
         unsigned long long start = 0;
         for (unsigned spins = 0;; spins++) {
             unsigned long long seen;
@@ -185,7 +191,7 @@ __device__ bool grid_barrier(const FusedParams& p, unsigned long long& target) {
                 if (start == 0) start = now_ns();
                 int failed;
                 asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(failed) : "l"(p.status) : "memory");
-                if (failed != 0 || now_ns() - start > BARRIER_LIMIT_NS) {
+                if (failed != 0 || now_ns() - start > limit) {
                     if (failed == 0) atomicExch(p.status, 21);
                     ok = 0;
                     break;

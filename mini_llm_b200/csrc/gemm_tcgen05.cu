@@ -63,10 +63,6 @@ __device__ __forceinline__ float activate(float v, int epilogue) {
     return v;
 }
 
-// One block of 32 rows x 32 columns, turned through shared memory (turn[r * 33 + c]), stored
-// as bfloat16 with bias and activation; row r goes to base + row_offset(r).  When the block
-// is whole and 4-byte aligned (paired), half a warp writes one row (two columns per lane, one
-// 4-byte store), so an instruction covers two rows; otherwise one column per lane.
 // Thread block clusters: the CTAs that share a tile along K add their partial sums through
 // each other's shared memory.
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -91,6 +87,10 @@ template <int EPI> __device__ __forceinline__ float activate_as(float v) {
     return v;
 }
 
+// One block of 32 rows x 32 columns, turned through shared memory (turn[r * 33 + c]), stored
+// as bfloat16 with bias and activation; row r goes to base + row_offset(r).  When the block
+// is whole and 4-byte aligned (paired), half a warp writes one row (two columns per lane, one
+// 4-byte store), so an instruction covers two rows; otherwise one column per lane.
 template <int EPI, typename RowOffset>
 __device__ __forceinline__ void store_rows_bf16_as(const float* turn, bf16* base, RowOffset row_offset, bool paired,
                                                    bool col_ok, int lane, int rows_left, const float* bias) {
@@ -503,12 +503,17 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const GemmParams& p, dim3
 
 }  // namespace
 
-// For measurements: force the tile width of the rows orientation (64, 128 or 256; 0: choose).
-static int g_forced_bn = 0;
-extern "C" int mllm_gemm_set_tile(int bn) {
-    if (bn != 0 && bn != 64 && bn != 128 && bn != 256) return fail("gemm: the tile width is 64, 128 or 256");
-    g_forced_bn = bn;
-    return 0;
+// The SM count of the current device (asked once per device).
+static int sm_count() {
+    static int counts[64] = {0};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 148;
+    if (counts[device] == 0) {
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
+        counts[device] = sms;
+    }
+    return counts[device];
 }
 
 // Whether the kernel takes a product: K a multiple of 8 (rows of both operands start on
@@ -561,15 +566,12 @@ static int gemm_bf16(void* out, const void* x, const void* w, const float* bias,
     int bn = 128;
     if (swap) {
         bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-    } else if (g_forced_bn != 0) {
-        bn = g_forced_bn;
     } else {
         // Tile width by how the tiles fill the SMs (measured on the layer shapes of GPT-2 small):
         // narrow tiles when 128-wide ones would leave SMs idle, 256 columns only for many waves.
         const long row_tiles = (M + BM - 1) / BM;
         const long tiles_128 = row_tiles * ((N + 127) / 128), tiles_256 = row_tiles * ((N + 255) / 256);
-        int sms = 148;
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+        const int sms = sm_count();
         if (tiles_128 < sms) bn = 64;
         else if (tiles_256 >= 4 * sms) bn = 256;
     }
@@ -587,8 +589,7 @@ static int gemm_bf16(void* out, const void* x, const void* w, const float* bias,
     {
         // Few tiles: share each among a cluster of 8, 4 or 2 CTAs along K, so that more SMs
         // stream the weights (at least two k blocks per CTA; not with the cache scatter)
-        int sms = 148;
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+        const int sms = sm_count();
         const int tiles = grid.x * grid.y, all_k = (K + BK - 1) / BK;
         if (scatter == nullptr)
             for (int splits = 8; splits >= 2; splits /= 2)

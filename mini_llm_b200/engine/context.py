@@ -184,6 +184,8 @@ class StepContext:
         self.item_counts = []         # host: tokens of each entry
         self.item_offsets = []        # host: row of each entry's first token
         self.decode_only = False      # every entry brings exactly one token
+        self.fused = False            # the step goes to the one-kernel decode step
+        self.dump = None              # a list: the model appends the residual stream after every run entry
         self.att_tiles = None         # device work list (tiles of up to 128 tokens of one entry), or None
         self.n_att_tiles = 0          # records (CTAs) of the work list
         self.n_split_tiles = 0        # tiles among them that come in several parts

@@ -58,7 +58,12 @@ class Engine:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", device: str = "cuda:0", page_size: int = 64,
                  cache_tokens: int | None = None, n_pages: int | None = None, max_requests: int = 64,
                  max_tokens_per_step: int = 2048, plain_kernels: bool = False, cuda_graphs: bool = True,
-                 fused_decode: bool = True):
+                 fused_decode: bool = True, debug_poison: bool = False):
+        """``debug_poison``: every cache slot that holds no live token holds a poison value
+        (NaN on the 32-bit path; 1e30 on the bfloat16 path, whose tensor-core attention
+        multiplies what lies in a masked slot by a weight of zero), so that a read past a
+        request's length or through a stale block-table row ruins the logits instead of
+        passing for another request's keys."""
         if not torch.cuda.is_available():
             raise RuntimeError("mini_llm_b200 runs on a CUDA device (sm_100a) only; none is available "
                                "and there is no CPU path")
@@ -87,7 +92,10 @@ class Engine:
             per_request = n_pages * self.page_size
         self.max_positions = per_request
         self.cache = CacheManager(needs, self.page_size, int(n_pages), self.max_requests, per_request)
-        self.storage = CacheStorage(self.cache, self.spec.order, self.dtype, self.device, self.max_requests)
+        poison = None
+        if debug_poison:
+            poison = float("nan") if self.kernels.plain_only else 1e30
+        self.storage = CacheStorage(self.cache, self.spec.order, self.dtype, self.device, self.max_requests, poison)
         self.workspace = Workspace(self.device, min_rows=min(self.max_tokens_per_step, 256))
         self.control = ControlBlock(self.device, self.cache.groups)
         self.ctx = StepContext(self.kernels, self.workspace, self.dtype, self.device)
@@ -102,8 +110,15 @@ class Engine:
         self._sampled_events = [torch.cuda.Event(), torch.cuda.Event()]  # a step's sampling is done
         self._graphs = {}
         self._graph_stamp = None
-        self.fused = FusedDecodePlan.build(self) if fused_decode else None
-        self._status_checks = 0
+        self.fused, self.fused_reason = (FusedDecodePlan.build(self) if fused_decode
+                                         else (None, "switched off by the caller"))
+        if self.fused is None and fused_decode and self.dtype == torch.bfloat16 and not self.kernels.plain_only:
+            # not an error, but a cliff in speed (a decode step is then some five launches a layer)
+            print(f"[mini_llm_b200] decode steps run part by part, not as one kernel: {self.fused_reason}",
+                  file=sys.stderr, flush=True)
+        self._status_pinned = torch.zeros(2, dtype=torch.int32).pin_memory()   # per step parity: the kernels' status word
+        self._status_host = self._status_pinned.numpy()
+        self.hidden_dump = None               # set by step(dump_hidden=True): the residual stream after every run entry
 
     # ---- requests ---------------------------------------------------------------------------
     def open_request(self) -> int | None:
@@ -119,6 +134,10 @@ class Engine:
         self.cache.close(slot)
         self._kept_valid.discard(slot)
 
+    @property
+    def vocab_size(self) -> int:
+        return self.spec.vocab_size
+
     def cached_tokens(self, slot: int) -> int:
         return self.cache.length(slot)
 
@@ -128,6 +147,7 @@ class Engine:
             raise StepError("a step needs at least one entry")
         seen = set()
         vocab = self.spec.vocab_size
+        total = 0
         for index, entry in enumerate(entries):
             if not self.cache.is_open(entry.slot):
                 raise StepError(f"entry {index}: slot {entry.slot} holds no request")
@@ -137,6 +157,7 @@ class Engine:
             n = len(entry.tokens)
             if n == 0:
                 raise StepError(f"entry {index}: no tokens")
+            total += n
             first = entry.tokens[0]
             if n == 1 and type(first) is int:
                 # a decoding request's one token: the common case, checked without an array
@@ -167,6 +188,9 @@ class Engine:
             for place in entry.want:
                 if not 0 <= int(place) < n:
                     raise StepError(f"entry {index}: wanted place {place} is not among its {n} tokens")
+        if total > self.max_tokens_per_step:
+            raise StepError(f"the step brings {total} tokens, more than the {self.max_tokens_per_step} "
+                            f"this engine takes in one step (max_tokens_per_step)")
 
     def _reserve(self, entries) -> None:
         cache = self.cache
@@ -186,18 +210,32 @@ class Engine:
             if not cache.reserve(entry.slot, len(entry.tokens), mine):
                 raise OutOfPages("page reservation failed after it was checked")   # cannot happen
 
-    def step(self, entries, sampling=None):
+    def step(self, entries, sampling=None, dump_hidden: bool = False):
         """Run one batch.  Returns fp32 logits ``[wanted, vocab]`` on the device
         (in the order of the entries and of each ``want``; valid until the next
         step), or None if nothing is wanted.  With ``sampling`` (one
         ``SamplingParams`` per wanted row) the chosen tokens are then read with
-        ``sampled_tokens()``."""
+        ``sampled_tokens()``.  With ``dump_hidden`` the step runs part by part and
+        ``hidden_dump`` afterwards holds the fp32 residual stream [tokens, width] after the
+        embedding and after every run entry (a test hook, as the reference's per-layer
+        outputs of ``gpt2_gpu_forward_last``, engine/src/gpt2_gpu.cu:224-250).  A step
+        that fails after its check (out of pages, a kernel that reports an error) leaves
+        every request as it was."""
         self._validate(entries)
         n_want = sum(len(e.want) for e in entries)
         if sampling is not None and len(sampling) != n_want:
             raise StepError(f"{len(sampling)} sampling parameters for {n_want} wanted rows")
         self._reserve(entries)
+        try:
+            return self._step_reserved(entries, sampling, n_want, dump_hidden)
+        except BaseException:
+            # nothing was committed: the pages this step reserved go back, and every request
+            # is as long as it was (what the step may have stored lies past that length)
+            for entry in entries:
+                self.cache.unreserve(entry.slot)
+            raise
 
+    def _step_reserved(self, entries, sampling, n_want, dump_hidden):
         n_tokens = sum(len(e.tokens) for e in entries)
         n_items = len(entries)
         any_previous = False
@@ -255,7 +293,7 @@ class Engine:
         # A step of single tokens of few requests goes to the decode attention, which takes no
         # work list: none is made for it.
         decode_only = n_tokens == n_items
-        if decode_only and n_items <= SPLIT_ATTENTION_MAX_ROWS:
+        if not self.model.wants_attention_tiles or (decode_only and n_items <= SPLIT_ATTENTION_MAX_ROWS):
             tiles, n_split, most_parts = [], 0, 1
         else:
             tiles, n_split, most_parts = ops.attention_tiles(ctx.item_offsets, ctx.item_counts, ctx.item_starts)
@@ -267,15 +305,21 @@ class Engine:
             arrays["counters"] = np.array([s.counter for s in sampling], dtype=np.int32)
         # the one-kernel decode step takes its arrays from alternating buffers, so that the next
         # step's copy runs beside it; captured graphs have their addresses fixed
-        alternate = self.fused is not None and self.fused.takes_sizes(n_tokens, decode_only)
-        views = self.control.upload(arrays, n_tokens, n_items, alternate)
+        fused = (self.fused is not None and not dump_hidden and n_want <= n_tokens
+                 and self.fused.takes_sizes(n_tokens, decode_only))
+        alternate = fused
+        # a place may be wanted twice: the per-row arrays have room for the larger count
+        views = self.control.upload(arrays, max(n_tokens, n_want), n_items, alternate)
 
         ctx.n_tokens, ctx.n_items, ctx.n_want = n_tokens, n_items, n_want
-        ctx.token_ids, ctx.positions, ctx.token_item = views["token_ids"], views["positions"], views["token_item"]
+        ctx.token_ids, ctx.positions = views["token_ids"][:n_tokens], views["positions"][:n_tokens]
+        ctx.token_item = views["token_item"][:n_tokens]
         ctx.want_rows = views["want_rows"][:n_want]
         ctx.want_slots = views["want_slots"][:n_want]
         ctx.any_previous = any_previous
         ctx.decode_only = decode_only
+        ctx.fused = fused
+        ctx.dump = [] if dump_hidden else None
         ctx.att_tiles, ctx.n_att_tiles = (views["att_tiles"] if tiles else None), len(tiles)
         ctx.n_split_tiles, ctx.att_parts = n_split, most_parts
         for view in self.storage.views:
@@ -298,6 +342,7 @@ class Engine:
                 compute.wait_event(self._readback[slot][2])
         self._alternated = alternate
         logits = self._run(ctx, sample_views)
+        self.hidden_dump = ctx.dump
         self.control.consumed()
         for entry in entries:
             self.cache.commit(entry.slot, len(entry.tokens))
@@ -309,15 +354,20 @@ class Engine:
             held = self._readback[self._turn]
             if held is None or held[0].shape[0] < n_want:
                 held = (torch.empty(max(n_want, 64), dtype=torch.int32).pin_memory(), 0, torch.cuda.Event())
+            # with them comes the word in which a kernel reports a wait that ran out, so that
+            # no token of a failed step is ever handed on
+            status = self.kernels.status(self.device)
             if alternate:
                 done = self._sampled_events[self._turn]
                 done.record(compute)
                 with torch.cuda.stream(self._readback_stream):
                     self._readback_stream.wait_event(done)
                     held[0][:n_want].copy_(self._sampled[:n_want], non_blocking=True)
+                    self._status_pinned[self._turn:self._turn + 1].copy_(status, non_blocking=True)
                     held[2].record(self._readback_stream)
             else:
                 held[0][:n_want].copy_(self._sampled[:n_want], non_blocking=True)
+                self._status_pinned[self._turn:self._turn + 1].copy_(status, non_blocking=True)
                 held[2].record(compute)
             self._readback[self._turn] = (held[0], n_want, held[2])
             for entry in entries:
@@ -351,7 +401,7 @@ class Engine:
         replay it: a step then costs one launch on the host instead of one per kernel.  The reference removes host work per
         step in the same spirit, by keeping sampled tokens on the device
         (engine/src/gpt2_gpu_greedy.cu:80-119)."""
-        if self.fused is not None and self.fused.takes(ctx):
+        if ctx.fused and self.fused is not None:
             block_table = next(v.block_table for v in self.storage.views if v.kind == "paged")
             try:
                 logits, self._sampled = self.fused.run(ctx, block_table, sample_views, self._any_nucleus)
@@ -359,15 +409,15 @@ class Engine:
             except KernelError as error:
                 # for instance no cooperative launch on this device: say so once, then run the generic path
                 print(f"[mini_llm_b200] fused decode step disabled: {error}", file=sys.stderr, flush=True)
-                self.fused = None
-        if not (self.cuda_graphs and self.model.graph_safe):
+                self.fused, self.fused_reason = None, str(error)
+        if ctx.dump is not None or not (self.cuda_graphs and self.model.graph_safe):
             return self._forward(ctx, sample_views)
         stamp = (self.workspace.generation, self.control.generation, self.kernels.scratch_generation)
         if stamp != self._graph_stamp:
             self._graphs.clear()                      # a buffer moved: captured addresses are stale
             self._graph_stamp = stamp
-        key = (ctx.n_tokens, ctx.n_items, ctx.n_want, ctx.n_att_tiles, ctx.att_parts, sample_views is not None,
-               self._any_nucleus, ctx.any_previous, self.control.parity)
+        key = (ctx.n_tokens, ctx.n_items, ctx.n_want, ctx.n_att_tiles, ctx.n_split_tiles, ctx.att_parts,
+               sample_views is not None, self._any_nucleus, ctx.any_previous, self.control.parity)
         held = self._graphs.get(key)
         # A capture costs as much as about twenty eager steps: a decode shape comes back at once
         # and is captured the second time it is seen, a shape with prompt portions the fourth.
@@ -404,12 +454,45 @@ class Engine:
         if held is None or held[1] == 0:
             return []
         held[2].synchronize()
-        tokens = held[0][:held[1]].tolist()
-        self._status_checks += 1
-        if self._status_checks % 64 == 1:
-            self.kernels.check_status()
-        return tokens
+        code = int(self._status_host[self._turn ^ ago])
+        if code != 0:
+            self._recover(code)
+        return held[0][:held[1]].tolist()
 
     def check_status(self) -> None:
-        """Raise if a kernel gave up on one of its bounded waits since the last check."""
-        self.kernels.check_status()
+        """Raise if a kernel gave up on one of its bounded waits since the last check
+        (synchronises).  ``sampled_tokens`` checks by itself; callers that read logits only
+        (trace replay) call this."""
+        code = self.kernels.read_status()
+        if code != 0:
+            self._recover(code)
+
+    def _recover(self, code: int):
+        """A kernel gave up on a bounded wait: the step's results are invalid.  CTAs of such a
+        kernel leave at different points, so every counter the kernels share across launches
+        (the grid barrier's arrival count, the attention kernels' work and merge counters) is
+        put back to its start, and captured graphs are dropped, before the error is raised:
+        the next step then runs on clean state."""
+        torch.cuda.synchronize(self.device)
+        self.kernels.reset_after_failure()
+        if self.fused is not None:
+            self.fused.reset()
+        self._graphs.clear()
+        self._status_host[:] = 0
+        self._readback = [None, None]
+        raise KernelError(f"a kernel gave up on a bounded wait (code {code}): the step's results are invalid; "
+                          f"the requests of that step should be closed")
+
+    # ---- looking inside (tests) ---------------------------------------------------------------
+    def read_kv(self, slot: int, run_entry: int, first: int = 0, count: int | None = None):
+        """Keys and values of ``count`` cached tokens of the request in ``slot``, from token
+        ``first`` on, as run entry ``run_entry`` holds them: ``(k, v)``, each
+        ``[count, kv_heads, head_size]`` on the device, gathered through the request's block
+        table (the reference's ``gpt2_gpu_kv_cache_copy_layer``, engine/src/gpt2_gpu.cu:185-195)."""
+        length = self.cache.length(slot)
+        if count is None:
+            count = length - first
+        if first < 0 or count < 0 or first + count > length:
+            raise ValueError(f"tokens {first}..{first + count - 1} are not among the {length} the request holds")
+        torch.cuda.current_stream(self.device).synchronize()
+        return self.storage.read_tokens(run_entry, slot, first, count)

@@ -37,7 +37,8 @@ class _Params(ctypes.Structure):
                 ("temperature", P), ("top_p", P), ("seeds", P), ("counters", P), ("out_tokens", P), ("kept", P), ("want_slots", P),
                 ("n_kept", I), ("cand_value", P),
                 ("cand_index", P), ("cand_done", P), ("barrier", P), ("status", P), ("timeline", P),
-                ("att_parts", I), ("att_partial", P), ("att_counters", P)]
+                ("att_parts", I), ("att_partial", P), ("att_counters", P),
+                ("barrier_limit_ns", ctypes.c_ulonglong), ("skip_arrival", I)]
 
 
 _step = Function("fused", "mllm_fused_decode_step", [ctypes.POINTER(_Params), P])
@@ -46,38 +47,63 @@ MAX_ATTENTION_PARTS = 16
 _KINDS = {"norm_1": "layer_norm", "mixer": "causal_self_attention", "norm_2": "layer_norm", "feed_forward": "dense_mlp"}
 
 
-def _matches(spec) -> bool:
-    if spec.embedding.kind != "token_embedding" or spec.final_norm.kind != "layer_norm" or spec.head.kind != "linear_head":
-        return False
+def _mismatch(spec) -> str | None:
+    """Why the description is not of the fused shape, or None if it is."""
+    if spec.embedding.kind != "token_embedding":
+        return f"the embedding is a '{spec.embedding.kind}', not a token_embedding"
+    if spec.final_norm.kind != "layer_norm":
+        return f"the final norm is a '{spec.final_norm.kind}', not a layer_norm"
+    if spec.head.kind != "linear_head":
+        return f"the head is a '{spec.head.kind}', not a linear_head"
     if spec.position is not None and spec.position.kind != "learned_positions":
-        return False
-    for layer in spec.layers:
-        if layer.arrangement != "pre_norm" or {r: p.kind for r, p in layer.parts.items()} != _KINDS:
-            return False
-    return all(entry.cache_of is None for entry in spec.order) and len(spec.order) > 0
+        return f"the position encoding is '{spec.position.kind}', not learned_positions"
+    for index, layer in enumerate(spec.layers):
+        if layer.arrangement != "pre_norm":
+            return f"layer {index} is arranged as '{layer.arrangement}', not pre_norm"
+        for role, kind in _KINDS.items():
+            have = layer.parts[role].kind if role in layer.parts else None
+            if have != kind:
+                return f"layer {index} has a '{have}' as its {role}, not a {kind}"
+        if layer.parts["mixer"].params.get("position") is not None:
+            return f"layer {index}'s mixer has a position encoding of its own"
+        if set(layer.parts) != set(_KINDS):
+            return f"layer {index} has parts beyond {', '.join(_KINDS)}"
+    if not spec.order:
+        return "no layer runs"
+    if any(entry.cache_of is not None for entry in spec.order):
+        return "a run entry reads another entry's cache"
+    return None
 
 
 class FusedDecodePlan:
     @classmethod
     def build(cls, engine):
-        """The plan for ``engine``'s model, or None if the model is not of the fused shape."""
+        """``(plan, None)`` for ``engine``'s model, or ``(None, reason)`` if the model, the
+        element type or a size is not what the kernel takes."""
         spec, model = engine.spec, engine.model
-        if engine.dtype != torch.bfloat16 or engine.kernels.plain_only or not _matches(spec):
-            return None
+        if engine.dtype != torch.bfloat16 or engine.kernels.plain_only:
+            return None, "the kernel is for bfloat16 with the fast kernels"
+        reason = _mismatch(spec)
+        if reason is not None:
+            return None, reason
         mixers = [model.layers[e.layer][1]["mixer"] for e in spec.order]
         mlps = [model.layers[e.layer][1]["feed_forward"] for e in spec.order]
         first = mixers[0]
         same = all((m.width, m.n_heads, m.n_kv_heads, m.head_size) == (first.width, first.n_heads, first.n_kv_heads,
                                                                         first.head_size) for m in mixers)
-        if not same or any(f.inner != mlps[0].inner for f in mlps) or len({v.group for v in engine.storage.views}) != 1:
-            return None
+        if not same or any(f.inner != mlps[0].inner for f in mlps):
+            return None, "the layers differ in their sizes"
+        if len({v.group for v in engine.storage.views}) != 1:
+            return None, "the layers keep their caches in more than one group"
         lib = load("fused")
         if ctypes.sizeof(_Layer) != lib.mllm_fused_layer_bytes() or ctypes.sizeof(_Params) != lib.mllm_fused_params_bytes():
             raise KernelError("fused_decode: the binding's structures do not match the library's")
         if not lib.mllm_fused_takes(1, first.width, first.n_heads, first.n_kv_heads, first.head_size, mlps[0].inner,
                                     engine.cache.groups[0].max_blocks):
-            return None
-        return cls(engine, lib)
+            return None, (f"the kernel does not take width {first.width}, {first.n_heads} heads of {first.head_size}, "
+                          f"inner size {mlps[0].inner} (widths must be multiples of 32, the head size a power of two, "
+                          f"and a step's staging must fit in shared memory)")
+        return cls(engine, lib), None
 
     def __init__(self, engine, lib):
         self.engine = engine
@@ -108,6 +134,9 @@ class FusedDecodePlan:
         self.max_blocks = engine.cache.groups[0].max_blocks
         self._filled = {}             # step shape -> (filled parameters, logits view, sampled view)
         self.timeline = None          # set to an int64 tensor of 5 * layers + 3 entries to record phase times
+        # For tests of the bounded wait (both enter the parameters of every later step):
+        self.barrier_limit_ns = 0     # a barrier wait gives up after this long (0: the kernel's two seconds)
+        self.skip_arrival = False     # one CTA stays away from the step's first barrier, which then runs out
         self.cand_value = torch.empty(MAX_TOKENS * self.grid, dtype=torch.float32, device=device)
         self.cand_index = torch.empty(MAX_TOKENS * self.grid, dtype=torch.int32, device=device)
         self.cand_done = torch.zeros(1, dtype=torch.int32, device=device)
@@ -142,7 +171,7 @@ class FusedDecodePlan:
         # layout depends on the step's sizes only): their parameters are filled once.
         parts = self.attention_parts(ctx)
         key = (ctx.n_tokens, ctx.n_want, sampling, self.timeline is not None, parts, engine.control.parity,
-               engine.workspace.generation, engine.control.generation)
+               engine.workspace.generation, engine.control.generation, self.barrier_limit_ns, self.skip_arrival)
         held = self._filled.get(key)
         if held is None:
             if len(self._filled) > 64:
@@ -196,6 +225,7 @@ class FusedDecodePlan:
         params.cand_done, params.barrier = self.cand_done.data_ptr(), self.barrier.data_ptr()
         params.status = engine.kernels.status(engine.device).data_ptr()
         params.att_parts = parts
+        params.barrier_limit_ns, params.skip_arrival = int(self.barrier_limit_ns), int(self.skip_arrival)
         params.att_partial, params.att_counters = self.att_partial.data_ptr(), self.att_counters.data_ptr()
         return params, logits, sampled
 

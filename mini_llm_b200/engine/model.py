@@ -32,6 +32,8 @@ class Model:
         # A step may be captured into a CUDA graph only if every part launches nothing but
         # kernels whose arguments stay valid from step to step; parts say so themselves.
         self.graph_safe = all(getattr(part, "graph_safe", False) for part in self.parts())
+        # The step makes a work list of attention tiles only if some part says it reads one.
+        self.wants_attention_tiles = any(getattr(part, "wants_attention_tiles", False) for part in self.parts())
 
     def parts(self):
         found = [self.embedding]
@@ -66,9 +68,14 @@ class Model:
     def forward(self, ctx, cache_views):
         """Run the step's tokens; returns fp32 logits [n_want, vocab] or None."""
         hidden = self.embedding.forward(ctx, self.position)
+        dump = getattr(ctx, "dump", None)
+        if dump is not None:
+            dump.append(hidden.clone())
         for index, entry in enumerate(self.spec.order):
             arrangement, parts = self.layers[entry.layer]
             arrangement.run(ctx, parts, hidden, cache_views[index])
+            if dump is not None:
+                dump.append(hidden.clone())
         if ctx.n_want == 0:
             return None
         defer = getattr(self.final_norm, "can_defer", False) and getattr(self.head, "accepts_deferred_norm", False)

@@ -42,6 +42,7 @@ reference does (pytorch/tests/batch_fakes.py:6-45).
 from __future__ import annotations
 
 import collections
+import operator
 from dataclasses import dataclass, field
 from typing import Callable
 
@@ -101,8 +102,20 @@ class Scheduler:
     # ---- requests in ------------------------------------------------------------------------
     def submit(self, request: Request) -> None:
         limit = self.engine.max_positions
+        vocab = getattr(self.engine, "vocab_size", None)
+        # A prompt is checked here, so that a bad one fails alone: the engine checks a whole
+        # batch and refuses all of it.  Ids below zero are never a request's to give (the
+        # engine reads one of them as "what this request sampled last").
+        try:
+            request.tokens = [operator.index(t) for t in request.tokens]
+            bad = next((t for t in request.tokens if t < 0 or (vocab is not None and t >= vocab)), None)
+        except TypeError:
+            bad = next(t for t in request.tokens if not hasattr(t, "__index__"))
         if not request.tokens:
             self._fail(request, "empty prompt")
+        elif bad is not None:
+            self._fail(request, f"token id {bad!r} is not an integer in the vocabulary"
+                                + (f" [0, {vocab})" if vocab is not None else ""))
         elif len(request.tokens) >= limit:
             # The reference's servers trim such prompts from the left (pytorch/src/mini_llm/
             # api_common.py:38-41); the engine itself refuses them.

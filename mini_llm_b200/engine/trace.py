@@ -44,8 +44,10 @@ def replay(args, lines, out=sys.stdout):
     if args.page_size <= 0 or 64 % args.page_size != 0:
         raise SystemExit("--page-size must divide 64")
     os.makedirs(args.out, exist_ok=True)
+    # a step of a trace may bring every token the cache holds at once
     engine = Engine(args.model, dtype=args.dtype, page_size=args.page_size, cache_tokens=args.max_tokens,
-                    max_requests=args.max_requests, plain_kernels=args.plain_kernels)
+                    max_requests=args.max_requests, plain_kernels=args.plain_kernels,
+                    max_tokens_per_step=max(int(args.max_tokens), 1))
     slots = {}
     for line in lines:
         line = line.strip()

@@ -22,11 +22,24 @@ SPLIT_ATTENTION_MAX_ROWS = 64 # up to here attention runs one CTA per (token, he
 
 
 class DeferredNorm:
-    """A layer norm that has not run yet: ``rows`` (or all rows) of the fp32 ``x``."""
+    """A norm that has not run yet: ``rows`` (or all rows) of the fp32 ``x``.
 
-    def __init__(self, x, gamma, beta, eps, rows, tag):
-        self.x, self.gamma, self.beta, self.eps, self.rows, self.tag = x, gamma, beta, float(eps), rows, tag
+    ``kind`` names the arithmetic ("layer_norm": gain ``gamma``, shift ``beta``, ``eps``).  A
+    product kernel that can norm its input on the way in takes a deferred norm only of a
+    kind it knows (``Kernels.FUSED_NORM_KINDS``); any other kind is evaluated first by
+    ``evaluate(ctx, out)``, the norm's own kernel.  A new norm therefore works everywhere
+    from its first day and gets fused once a product kernel learns its kind."""
+
+    def __init__(self, kind, x, rows, tag, evaluate, **params):
+        self.kind, self.x, self.rows, self.tag, self.evaluate = kind, x, rows, tag, evaluate
+        self.params = params
         self._value = None
+
+    def __getattr__(self, name):
+        try:
+            return self.__dict__["params"][name]
+        except KeyError:
+            raise AttributeError(name) from None
 
     @property
     def shape(self):
@@ -35,16 +48,19 @@ class DeferredNorm:
     def materialize(self, ctx):
         if self._value is None:
             out = ctx.buffer(self.tag, self.shape, ctx.act_dtype)
-            ctx.kernels.layernorm(out, self.x, self.gamma, self.beta, self.eps, self.rows)
+            self.evaluate(ctx, out)
             self._value = out
         return self._value
 
 
 class Kernels:
+    FUSED_NORM_KINDS = ("layer_norm",)    # what the few-row product kernel can apply on the way in
+
     def __init__(self, act_dtype: torch.dtype, plain_only: bool = False):
         self.act_dtype = act_dtype
         self.plain_only = bool(plain_only) or act_dtype == torch.float32
         self.launches = 0            # kernels launched (or recorded into a graph) since the start
+        self.choices = {}            # (operation, sizes...) -> name of the kernel that ran it last
         self._split_scratch = None
         self._sample_scratch = None
         self.scratch_generation = 0  # grows when scratch moves (captured graphs are then stale)
@@ -107,54 +123,80 @@ class Kernels:
         """out = epilogue(a @ w.T + bias).  ``a``: an activation tensor or a ``DeferredNorm``."""
         m, k = a.shape
         self.launches += 1
-        if self._skinny(m, k, w.shape[0]):
-            if isinstance(a, DeferredNorm):
+        skinny = self._skinny(m, k, w.shape[0])
+        deferred = isinstance(a, DeferredNorm)
+        if deferred and not (skinny and a.kind in self.FUSED_NORM_KINDS):
+            self.launches += 1               # no kernel here norms this kind on the way in: the norm runs first
+            a, deferred = a.materialize(ctx), False
+        if skinny:
+            self.chose("linear", "skinny_linear", m, w.shape[0], k)
+            if deferred:
                 return ops.skinny_linear(out, a.x, w, bias, epilogue, norm=(a.gamma, a.beta, a.eps, a.rows))
             return ops.skinny_linear(out, a, w, bias, epilogue)
-        if isinstance(a, DeferredNorm):
-            self.launches += 1
-            a = a.materialize(ctx)
         if not self.plain_only and ops.gemm_takes(a, w):
+            self.chose("linear", "gemm_tcgen05", m, w.shape[0], k)
             return ops.gemm_bf16(out, a, w, bias, epilogue, self.status(ctx.device))
+        self.chose("linear", "linear_plain", m, w.shape[0], k)
         return ops.linear_plain(out, a, w, bias, epilogue)
+
+    def chose(self, operation: str, kernel: str, *sizes) -> None:
+        """Note which kernel ran an operation at which sizes (tests pin the choices)."""
+        self.choices[(operation, *sizes)] = kernel
 
     def status(self, device):
         if self._status is None:
             self._status = torch.zeros(1, dtype=torch.int32, device=device)
         return self._status
 
+    def read_status(self) -> int:
+        """The code a kernel left when one of its bounded waits ran out, or 0 (synchronises)."""
+        return int(self._status.item()) if self._status is not None else 0
+
+    def reset_after_failure(self) -> None:
+        """After a kernel gave up: the status word and every counter that kernels leave at
+        zero between launches start over (a tile that was given up left its counter)."""
+        if self._status is not None:
+            self._status.zero_()
+        if self._att_scratch is not None:
+            self._att_scratch[1].zero_()
+        if self._att_work is not None:
+            self._att_work.zero_()
+        if self._split_scratch is not None:
+            self._split_scratch[2].zero_()
+        if self._sample_scratch is not None:
+            self._sample_scratch[2].zero_()
+
     def check_status(self) -> None:
         """Raise if a kernel reported that one of its bounded waits ran out (synchronises)."""
-        if self._status is not None:
-            code = int(self._status.item())
-            if code != 0:
-                self._status.zero_()
-                if self._att_scratch is not None:
-                    self._att_scratch[1].zero_()      # a tile that was given up left its counter
-                if self._att_work is not None:
-                    self._att_work.zero_()
-                raise ops.KernelError(f"a tensor-core kernel gave up waiting (code {code}): its result is invalid")
+        code = self.read_status()
+        if code != 0:
+            self.reset_after_failure()
+            raise ops.KernelError(f"a tensor-core kernel gave up waiting (code {code}): its result is invalid")
 
     def qkv_projection(self, ctx, a, w, bias, cache, q_width, kv_width):
         """The fused query/key/value projection.  Keys and values of the step's tokens go into
         the cache pages (if this entry writes its cache); returns the queries [T, q_width]."""
         m, k = a.shape
-        if cache.writes and self._skinny(m, k):
+        skinny = cache.writes and self._skinny(m, k)
+        deferred = isinstance(a, DeferredNorm)
+        if deferred and not (skinny and a.kind in self.FUSED_NORM_KINDS):
+            self.launches += 1
+            a, deferred = a.materialize(ctx), False
+        if skinny:
             q = ctx.buffer("q", (m, q_width), ctx.act_dtype)
             scatter = (cache.k_pages, cache.v_pages, ctx.positions, ctx.token_item, cache.block_table,
                        cache.page_size, q_width, kv_width)
             self.launches += 1
-            if isinstance(a, DeferredNorm):
+            self.chose("qkv", "skinny_linear", m, w.shape[0], k)
+            if deferred:
                 ops.skinny_linear(q, a.x, w, bias, "store", norm=(a.gamma, a.beta, a.eps, a.rows), scatter=scatter)
             else:
                 ops.skinny_linear(q, a, w, bias, "store", scatter=scatter)
             return q
-        if isinstance(a, DeferredNorm):
-            self.launches += 1
-            a = a.materialize(ctx)
         if cache.writes and not self.plain_only and ops.gemm_qkv_takes(a, w, q_width, kv_width):
             q = ctx.buffer("q", (m, q_width), ctx.act_dtype)
             self.launches += 1
+            self.chose("qkv", "gemm_tcgen05", m, w.shape[0], k)
             return ops.gemm_bf16_qkv(q, a, w, bias, self.status(ctx.device), cache.k_pages, cache.v_pages,
                                      ctx.positions, ctx.token_item, cache.block_table, cache.page_size, q_width,
                                      kv_width)
@@ -183,6 +225,7 @@ class Kernels:
             # as fast or faster (measured at 9 to 64 requests of 12 heads)
             grouped = n_heads // n_kv_heads >= 2 and ops.group_attention_takes(q, n_heads, n_kv_heads, head_size)
             run = ops.group_attention if grouped else ops.split_attention
+            self.chose("attention", "group_attention" if grouped else "split_attention", n, n_heads, head_size)
             return run(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions, ctx.token_item,
                        n_heads, n_kv_heads, head_size, cache.page_size, scale, window, chunk, max_chunks, acc, ml,
                        counters)
@@ -192,11 +235,13 @@ class Kernels:
             if ctx.att_parts > 1:
                 scratch = self._attention_scratch(ctx.device, ctx.n_split_tiles * n_heads, ops.ATTENTION_MAX_PARTS
                                                   * ops.ATTENTION_TILE * (head_size + 4))
+            self.chose("attention", "attention_tcgen05", n, n_heads, head_size)
             return ops.attention_prefill(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.att_tiles,
                                          ctx.n_att_tiles, n_heads, n_kv_heads, head_size, cache.page_size, scale,
                                          window, self.status(ctx.device), self.attention_work(ctx.device), scratch,
                                          ctx.n_split_tiles,
                                          ops.ATTENTION_MAX_PARTS if ctx.att_parts > 1 else 1)
+        self.chose("attention", "attention_plain", n, n_heads, head_size)
         return ops.attention_plain(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
                                    ctx.token_item, n_heads, n_kv_heads, head_size, cache.page_size, scale, window)
 

@@ -12,19 +12,30 @@ result and bias onto the block's input (engine/src/transformer_block.c:60-62).
 The keys and values of this step's tokens are first stored into the request's
 pages; attention then reads the cache only, so a prompt portion and a single
 decoded token take the same path.
+
+A position encoding that acts on queries and keys (a rotation, for instance)
+is a parameter of the mixer: ``position``, the description of a
+``PositionEncoding`` part with ``rotate(ctx, q, k, n_heads, n_kv_heads,
+head_size)``, which changes the step's queries [T, heads * head_size] and
+keys [T, kv_heads * head_size] in place, each row by its ``ctx.positions``.
+The projection then writes q, k and v side by side, the encoding rotates, and
+the keys and values are stored into the pages by a pass of their own (the
+fused projection, which scatters straight into the pages, knows no rotation).
 """
 
 from __future__ import annotations
 
-from .base import Mixer, register_part
+from .base import Mixer, build_part, register_part
 from .spec import PagedKV, WeightSpec
 
 
 class CausalSelfAttention(Mixer):
     graph_safe = True
+    wants_attention_tiles = True      # its prompt kernel reads the step's work list of (128 queries, entry) tiles
     def __init__(self, prefix, width: int, n_heads: int, head_size: int, score_scale: float,
                  n_kv_heads: int | None = None, window: int | None = None,
-                 qkv_name: str = "c_attn", out_name: str = "c_proj", stored_in_out: bool = True):
+                 qkv_name: str = "c_attn", out_name: str = "c_proj", stored_in_out: bool = True,
+                 position=None):
         super().__init__(prefix)
         self.width = int(width)
         self.n_heads = int(n_heads)
@@ -38,6 +49,11 @@ class CausalSelfAttention(Mixer):
             raise ValueError(f"{prefix}: {self.n_heads} heads are not a multiple of {self.n_kv_heads} key/value heads")
         if self.head_size % 16 != 0 or not 16 <= self.head_size <= 256:
             raise ValueError(f"{prefix}: head size {self.head_size} is not a multiple of 16 in 16..256")
+        self.position = build_part(position) if position is not None else None
+        if self.position is not None:
+            if not hasattr(self.position, "rotate"):
+                raise ValueError(f"{prefix}: the position encoding '{position.kind}' has no rotate(ctx, q, k, ...)")
+            self.graph_safe = bool(getattr(self.position, "graph_safe", False))
         self.q_width = self.n_heads * self.head_size
         self.kv_width = self.n_kv_heads * self.head_size
         self.qkv_width = self.q_width + 2 * self.kv_width
@@ -47,7 +63,7 @@ class CausalSelfAttention(Mixer):
 
     def weight_specs(self):
         t = self.stored_in_out
-        return [
+        return (self.position.weight_specs() if self.position is not None else []) + [
             WeightSpec(self.full_name(f"{self.qkv_name}.weight"), self._matrix_shape(self.width, self.qkv_width), transpose=t),
             WeightSpec(self.full_name(f"{self.qkv_name}.bias"), (self.qkv_width,), role="vector", init="bias"),
             WeightSpec(self.full_name(f"{self.out_name}.weight"), self._matrix_shape(self.q_width, self.width), transpose=t,
@@ -60,10 +76,25 @@ class CausalSelfAttention(Mixer):
 
     accepts_deferred_norm = True
 
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        if self.position is not None:
+            self.position.bind({w.name: tensors[w.name] for w in self.position.weight_specs() if w.name in tensors},
+                               runtime)
+
     def forward(self, ctx, x, hidden, cache):
         k = ctx.kernels
-        q = k.qkv_projection(ctx, x, self.w(f"{self.qkv_name}.weight"), self.w(f"{self.qkv_name}.bias"), cache,
-                             self.q_width, self.kv_width)
+        if self.position is None:
+            q = k.qkv_projection(ctx, x, self.w(f"{self.qkv_name}.weight"), self.w(f"{self.qkv_name}.bias"), cache,
+                                 self.q_width, self.kv_width)
+        else:
+            qkv = ctx.buffer("qkv", (x.shape[0], self.qkv_width), ctx.act_dtype)
+            k.linear(ctx, qkv, x, self.w(f"{self.qkv_name}.weight"), self.w(f"{self.qkv_name}.bias"))
+            q, keys = qkv[:, :self.q_width], qkv[:, self.q_width:self.q_width + self.kv_width]
+            self.position.rotate(ctx, q, keys, self.n_heads, self.n_kv_heads, self.head_size)
+            if cache.writes:
+                k.kv_store(cache.k_pages, cache.v_pages, keys, qkv[:, self.q_width + self.kv_width:], ctx.positions,
+                           ctx.token_item, cache.block_table, cache.page_size)
         mixed = ctx.buffer("attn_out", (q.shape[0], self.q_width), ctx.act_dtype)
         k.attention(ctx, mixed, q, cache, self.n_heads, self.n_kv_heads, self.head_size, self.score_scale,
                     self.window or 0)

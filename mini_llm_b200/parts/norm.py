@@ -26,7 +26,10 @@ class LayerNorm(Norm):
 
     def forward(self, ctx, x, rows=None, tag="norm", defer=False):
         if defer:
-            return DeferredNorm(x, self.w("weight"), self.w("bias"), self.eps, rows, tag)
+            gamma, beta = self.w("weight"), self.w("bias")
+            return DeferredNorm("layer_norm", x, rows, tag,
+                                lambda c, out: c.kernels.layernorm(out, x, gamma, beta, self.eps, rows),
+                                gamma=gamma, beta=beta, eps=self.eps)
         n_rows = x.shape[0] if rows is None else rows.shape[0]
         out = ctx.buffer(tag, (n_rows, self.width), ctx.act_dtype)
         ctx.kernels.layernorm(out, x, self.w("weight"), self.w("bias"), self.eps, rows)

@@ -9,7 +9,10 @@ gcc into a shared library in a temporary folder and calls, through ctypes:
 ``embed_tokens`` (engine/src/embedding.c), ``transformer_block_forward``
 (engine/src/transformer_block.c:11-93) once per layer with the fused ``c_attn`` matrix split
 into q, k, v the reference's way (engine/src/gpt2.c:79-90), ``layernorm``
-(engine/src/layernorm.c) for the final norm, and ``gelu`` (the erf form, engine/src/gelu.c:5-9).
+(engine/src/layernorm.c) for the final norm, ``gelu`` (the erf form, engine/src/gelu.c:5-9), and
+``multi_head_attention`` (engine/src/attention.c:78-97) at head size 48, once as it is and once
+with the queries divided by 3 (the score scale of a third layer under
+``scale_attn_by_inverse_layer_idx``).
 ``gpt2_forward`` itself is compiled for GPT-2 small's sizes only (engine/include/gpt2.h:12-19),
 so its last lines, the dot of the normed rows with the token table
 (engine/src/gpt2.c:245-256), are restated here in float32.
@@ -120,6 +123,13 @@ def main(reference):
     lib.multi_head_attention.argtypes = [F, F, F, F, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t]
     lib.multi_head_attention(ptr(q), ptr(k), ptr(v), ptr(att), 11, 2, 48)
     out.update(att_q=q, att_k=k, att_v=v, att_out=att)
+    # GPT-2's option scale_attn_by_inverse_layer_idx multiplies the scores of layer l (0-based)
+    # by 1/(l + 1).  The reference has no such option, but the scores are linear in the
+    # queries, so its own attention fed q/(l + 1) computes exactly that (here l = 2).
+    q_third = np.ascontiguousarray(q / np.float32(3.0))
+    att_third = np.zeros_like(q)
+    lib.multi_head_attention(ptr(q_third), ptr(k), ptr(v), ptr(att_third), 11, 2, 48)
+    out.update(att_out_layer_2=att_third)
 
     here = os.path.dirname(os.path.abspath(__file__))
     np.savez_compressed(os.path.join(here, "reference_tiny.npz"), tokens=tokens,

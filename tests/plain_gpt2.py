@@ -166,9 +166,11 @@ def score_scale(config, layer_index):
     return scale
 
 
-def block(x, tensors, config, layer_index):
+def block(x, tensors, config, layer_index, record=None):
     """r = x + proj(attention(ln_1(x))); out = r + mlp(ln_2(r))
-    (engine/src/transformer_block.c:49-71)."""
+    (engine/src/transformer_block.c:49-71).  ``record``: a dict that receives the layer's
+    keys and values (what a cache would hold: engine/tests/test_gpt2_gpu.c:96-150 compares
+    the stored rows with the CPU's norm + linear)."""
     p = f"h.{layer_index}."
     eps = config.get("layer_norm_epsilon", 1e-5)
     width = config["n_embd"]
@@ -176,6 +178,8 @@ def block(x, tensors, config, layer_index):
     qkv = linear(ln1, tensors[p + "attn.c_attn.weight"], tensors[p + "attn.c_attn.bias"])
     # The fused matrix holds q, k, v as three column blocks (engine/src/gpt2.c:79-90).
     q, k, v = qkv[:, :width], qkv[:, width:2 * width], qkv[:, 2 * width:]
+    if record is not None:
+        record["k"], record["v"] = k, v
     mixed = multi_head_attention(q, k, v, config["n_head"], score_scale(config, layer_index))
     r = x + linear(mixed, tensors[p + "attn.c_proj.weight"], tensors[p + "attn.c_proj.bias"])
     ln2 = layer_norm(r, tensors[p + "ln_2.weight"], tensors[p + "ln_2.bias"], eps)
@@ -184,15 +188,20 @@ def block(x, tensors, config, layer_index):
     return r + linear(act, tensors[p + "mlp.c_proj.weight"], tensors[p + "mlp.c_proj.bias"])
 
 
-def forward(config, tensors, token_ids, dtype=np.float64, return_blocks=False):
+def forward(config, tensors, token_ids, dtype=np.float64, return_blocks=False, records=None):
     """Logits [len, vocab] of a whole sequence: embed, every block, final norm, then the dot
-    with every row of the token table, no bias   (engine/src/gpt2.c:198-256)."""
+    with every row of the token table, no bias   (engine/src/gpt2.c:198-256).  With
+    ``return_blocks`` also the residual stream after the embedding and after every block;
+    ``records``: a list that receives one dict of keys and values per layer."""
     t = {k: (v.astype(dtype) if v.dtype.kind == "f" else v) for k, v in tensors.items()}
     hidden = embed(token_ids, t["wte.weight"], t["wpe.weight"])
-    blocks = []
+    blocks = [hidden]
     for layer in range(config["n_layer"]):
-        hidden = block(hidden, t, config, layer)
+        record = {} if records is not None else None
+        hidden = block(hidden, t, config, layer, record)
         blocks.append(hidden)
+        if records is not None:
+            records.append(record)
     normed = layer_norm(hidden, t["ln_f.weight"], t["ln_f.bias"], config.get("layer_norm_epsilon", 1e-5))
     head = t["wte.weight"] if config.get("tie_word_embeddings", True) else t["lm_head.weight"]
     logits = normed @ head.T

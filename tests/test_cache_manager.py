@@ -134,9 +134,14 @@ def test_random_orders_keep_every_invariant(seed):
             n = rng.choice([1, 1, 1, 2, 3, 7, 13, 30])
             before = (m.pages_free(), m.pages_held(slot))
             if m.reserve(slot, n):
-                if rng.random() < 0.9:
+                if rng.random() < 0.8:
                     m.commit(slot, n)
                     live[slot] += n
+                elif rng.random() < 0.5:
+                    # the step failed after it had reserved: the request holds the pages of
+                    # its committed tokens and no more (an earlier reservation goes back too)
+                    m.unreserve(slot)
+                    assert m.pages_held(slot)[0] == -(-live[slot] // 4) and m.pages_held(slot)[1] <= before[1][1]
             else:
                 refused += 1
                 assert (m.pages_free(), m.pages_held(slot)) == before
@@ -151,3 +156,27 @@ def test_random_orders_keep_every_invariant(seed):
     m.check()
     assert m.pages_free() == [40, 24] and m.free_slots == 5
     assert refused > 0 and m.groups[0].pool.reused > 0
+
+
+def test_unreserve_gives_back_what_a_failed_step_took_and_pages_that_go_back_are_reported():
+    m = CacheManager([FULL, WINDOW], page_size=8, n_pages=[6, 6], max_requests=2, max_tokens_per_request=64)
+    freed = []
+    m.on_free = lambda group, pages: freed.append((group, list(pages)))
+    s = m.open()
+    assert m.reserve(s, 10)
+    m.commit(s, 10)
+    held = m.pages_held(s)
+    assert m.reserve(s, 30) and m.pages_held(s) == [5, 5]
+    m.unreserve(s)
+    assert m.pages_held(s) == held == [2, 2] and m.length(s) == 10 and m.pages_free() == [4, 4]
+    assert sorted(len(pages) for _, pages in freed) == [3, 3]
+    with pytest.raises(PageError):
+        m.commit(s, 7)                       # the reservation is gone
+    m.unreserve(s)                           # nothing to give back: no change
+    assert m.pages_held(s) == [2, 2]
+    assert m.reserve(s, 30)
+    m.commit(s, 30)                          # the window group gives pages back as it passes them
+    assert any(group == 1 for group, _ in freed[2:])
+    m.close(s)
+    assert sum(len(pages) for _, pages in freed) == 3 + 3 + 5 + 5 and m.pages_free() == [6, 6]
+    m.check()

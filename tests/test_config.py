@@ -10,7 +10,7 @@ from tiny_configs import TINY_A, TINY_B
 def test_reads_the_architectures_own_keys():
     c = config_from_dict(TINY_B)
     assert isinstance(c, Gpt2Config)
-    assert (c.n_layer, c.n_embd, c.n_head, c.n_inner, c.vocab_size, c.n_positions) == (3, 96, 2, 160, 1000, 160)
+    assert (c.n_layer, c.n_embd, c.n_head, c.n_inner, c.vocab_size, c.n_positions) == (3, 96, 2, 160, 1000, 64)
     assert c.layer_norm_epsilon == 1e-6 and c.activation == "gelu_erf" and c.scale_attn_by_inverse_layer_idx
     assert c.head_size == 48 and c.architecture == "GPT2LMHeadModel"
 

@@ -12,32 +12,40 @@ import pytest
 
 from engine_helpers import (F32_ATOL, bf16_atol, make_model, plain_logits, random_tokens, run_schedule,
                             schedule_mixed, schedule_portions, schedule_tail_one_by_one, schedule_whole)
-from tiny_configs import RECIPES, TINY_A, TINY_B, TINY_C
+from tiny_configs import RECIPES, SMALL_WIDTHS, TINY_A, TINY_B, TINY_C, TINY_D
 
 pytestmark = pytest.mark.gpu
 
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-PAGE_SIZES = {"A": 16, "B": 8, "C": 16}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "D16": TINY_D}
+# D runs with pages of 64 tokens (the engine's default and the benchmark's) and again with pages of 16
+PAGE_SIZES = {"A": 16, "B": 8, "C": 16, "D": 64, "D16": 16}
 # factor on the query and key weights that brings the scores' spread to about 1 (see
 # engine_helpers.sharpen_attention); it depends on the recipe's weight scale and the width
-SHARPEN = {"A": 6.0, "B": 2.0, "C": 2.0}
+SHARPEN = {"A": 6.0, "B": 2.0, "C": 2.0, "D": 1.5}
 # request lengths per configuration (within n_positions); prompts for the mixed schedule
 LENGTHS = {"A": {"a": 5, "b": 17, "c": 33, "d": 70, "e": 128},
-           "B": {"a": 1, "b": 9, "c": 24, "d": 40, "e": 160, "f": 77},
-           "C": {"a": 300, "b": 45, "c": 131, "d": 2, "e": 640}}
+           "B": {"a": 1, "b": 9, "c": 24, "d": 40, "e": 64, "f": 57},
+           "C": {"a": 300, "b": 45, "c": 131, "d": 2, "e": 640},
+           "D": {"a": 700, "b": 45, "c": 131, "d": 2, "e": 260}}
+LENGTHS["D16"] = LENGTHS["D"]
+ALL_KEYS = ["A", "B", "C", "D", "D16"]
 
 
 @pytest.fixture(scope="session")
 def folders(tmp_path_factory):
     out = {}
     for key, raw in CONFIGS.items():
+        if key == "D16":
+            continue
         recipe, seed = RECIPES[key]
         out[key] = make_model(str(tmp_path_factory.mktemp(f"tiny_{key}")), raw, recipe, seed, sharpen=SHARPEN[key])
+    out["D16"] = out["D"]
     return out
 
 
 def requests_of(key):
     vocab = CONFIGS[key]["vocab_size"]
+    key = "D" if key == "D16" else key
     return {name: random_tokens(zlib.crc32(f"{key}/{name}".encode()) % 1000 + i, n, vocab)
             for i, (name, n) in enumerate(LENGTHS[key].items())}
 
@@ -69,7 +77,7 @@ def check(key, folders, dtype, got, requests):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("key", ["A", "B", "C"])
+@pytest.mark.parametrize("key", ALL_KEYS)
 @pytest.mark.parametrize("cut", ["whole", "tail", "portions"])
 def test_each_request_alone(folders, key, dtype, cut):
     requests = requests_of(key)
@@ -82,7 +90,28 @@ def test_each_request_alone(folders, key, dtype, cut):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("key", ["A", "B", "C"])
+@pytest.mark.parametrize("key", ["D", "D16"])
+def test_portions_of_more_than_a_tile(folders, key, dtype):
+    """Portions longer than the 64 tokens up to which a step goes to the decode kernels, and
+    longer than one tile of 128 queries, beside portions of two and three tokens: the
+    tensor-core products and the tensor-core prompt attention start in the middle of a
+    request, of a page and of a block of 128 keys."""
+    requests = requests_of(key)
+    engine = engine_of(folders, key, dtype)
+    got = run_schedule(engine, requests, schedule_portions(requests, sizes=(130, 2, 257, 65, 3)))
+    check(key, folders, dtype, got, requests)
+    if dtype == "bfloat16":
+        assert "attention_tcgen05" in engine.kernels.choices.values()
+        assert "gemm_tcgen05" in engine.kernels.choices.values()
+    engine.cache.check()
+
+
+# sizes of prompt portions in the mixed schedule: for D some are longer than a tile of 128 queries
+MIXED_PORTIONS = {"D": (130, 3, 70, 9, 257), "D16": (66, 2, 200, 5, 129)}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ALL_KEYS)
 def test_mixed_batches_with_reused_pages(folders, key, dtype):
     requests = requests_of(key)
     longest = sorted(len(t) for t in requests.values())
@@ -95,7 +124,7 @@ def test_mixed_batches_with_reused_pages(folders, key, dtype):
     # twice over, in two orders: the second pass runs entirely on used pages
     for order in (list(requests), list(reversed(list(requests)))):
         ordered = {n: requests[n] for n in order}
-        steps = schedule_mixed(ordered, prompts, max_live=4)
+        steps = schedule_mixed(ordered, prompts, max_live=4, portion_sizes=MIXED_PORTIONS.get(key, (7, 3, 2, 9, 5)))
         assert max(len(s) for s in steps) == min(4, len(requests))
         assert any(len({n for _, n in s}) > 1 and min(n for _, n in s) == 1 for s in steps), "no mixed step"
         got = run_schedule(engine, ordered, steps)

@@ -4,8 +4,9 @@
 reference's unchanged ``engine/src/*.c``.  The whole model there uses gelu_new and the
 1/sqrt(head size) scale, the only block the reference has; the erf gelu, another eps and a
 head size of 48 are compared operator by operator.  The score scale by 1/(layer index + 1)
-exists nowhere in the reference: that option of the plain implementation rests on the
-formula alone."""
+exists nowhere in the reference as an option; since scores are linear in the queries, the
+reference's attention fed q/(layer index + 1) pins the mechanism.  That GPT-2's
+``scale_attn_by_inverse_layer_idx`` means this rests on the key's stated meaning."""
 
 import json
 import os
@@ -26,7 +27,8 @@ def test_embedding():
 
 def test_blocks_and_logits():
     logits, blocks = plain.forward(CONFIG, WEIGHTS, GOLDEN["tokens"], return_blocks=True)
-    for i, hidden in enumerate(blocks):
+    np.testing.assert_allclose(blocks[0], GOLDEN["embedded"], rtol=0, atol=1e-6)
+    for i, hidden in enumerate(blocks[1:]):
         np.testing.assert_allclose(hidden, GOLDEN[f"block_{i}"], rtol=1e-5, atol=2e-5)
     np.testing.assert_allclose(logits, GOLDEN["logits"], rtol=1e-5, atol=5e-5)
     assert (logits.argmax(-1) == GOLDEN["logits"].argmax(-1)).all()
@@ -51,6 +53,17 @@ def test_attention_head_size_48():
     q, k, v = (GOLDEN[n].astype(np.float64) for n in ("att_q", "att_k", "att_v"))
     got = plain.multi_head_attention(q, k, v, 2, 1.0 / np.sqrt(48.0))
     np.testing.assert_allclose(got, GOLDEN["att_out"], rtol=1e-5, atol=1e-5)
+
+
+def test_score_scale_by_inverse_layer_index():
+    """Layer 2 (0-based) of a model with scale_attn_by_inverse_layer_idx: the plain
+    implementation's scale 1/sqrt(head) / 3 against the reference's attention fed q / 3."""
+    q, k, v = (GOLDEN[n].astype(np.float64) for n in ("att_q", "att_k", "att_v"))
+    config = {"n_embd": 96, "n_head": 2, "scale_attn_by_inverse_layer_idx": True}
+    assert abs(plain.score_scale(config, 2) - 1.0 / np.sqrt(48.0) / 3.0) < 1e-15
+    got = plain.multi_head_attention(q, k, v, 2, plain.score_scale(config, 2))
+    np.testing.assert_allclose(got, GOLDEN["att_out_layer_2"], rtol=1e-5, atol=1e-5)
+    assert np.abs(got - GOLDEN["att_out"]).max() > 1e-2          # the option changes the result
 
 
 def test_window_equals_full_when_wide():

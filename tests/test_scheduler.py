@@ -256,6 +256,16 @@ def test_bad_prompts_are_refused_at_once():
     s.submit(empty)
     s.submit(long)
     assert empty.error == "empty prompt" and "16" in long.error and not s.waiting
+    # ids that are no tokens fail their own request, before any batch is built; a negative id
+    # is never a request's to give (the engine reads one as "the token sampled last")
+    engine.vocab_size = VOCAB
+    good, beyond, negative, text = Request(prompt(91, 5)), Request([1, VOCAB]), Request([-1]), Request([3, "x"])
+    for request in (good, beyond, negative, text):
+        s.submit(request)
+    assert good.error is None and list(s.waiting) == [good]
+    assert str(VOCAB) in beyond.error and "-1" in negative.error and "'x'" in text.error
+    s.run()
+    assert len(good.generated) > 0 or good.finish_reason is not None
     with pytest.raises(ValueError):
         Scheduler(engine, max_tokens_per_step=0)
 

@@ -11,7 +11,7 @@ TINY_A = {
 
 TINY_B = {
     "architectures": ["GPT2LMHeadModel"], "model_type": "gpt2",
-    "n_layer": 3, "n_embd": 96, "n_head": 2, "n_inner": 160, "vocab_size": 1000, "n_positions": 160,
+    "n_layer": 3, "n_embd": 96, "n_head": 2, "n_inner": 160, "vocab_size": 1000, "n_positions": 64,
     "activation_function": "gelu", "layer_norm_epsilon": 1e-6,
     "scale_attn_by_inverse_layer_idx": True, "tie_word_embeddings": True,
 }
@@ -25,4 +25,25 @@ TINY_C = {
     "scale_attn_by_inverse_layer_idx": False, "tie_word_embeddings": True,
 }
 
-RECIPES = {"A": ("gpt2", 0), "B": ("varied", 1), "C": ("varied", 2)}
+# Head size 64, the head size of every published GPT-2 size, so that the kernels the
+# benchmark runs (tensor-core prompt attention, the one-kernel decode step at head size 64,
+# split-key decode attention) meet every way of cutting the work; a vocabulary that is odd;
+# requests of up to 700 tokens (six blocks of 128 keys, eleven pages of 64).
+TINY_D = {
+    "architectures": ["GPT2LMHeadModel"], "model_type": "gpt2",
+    "n_layer": 2, "n_embd": 256, "n_head": 4, "n_inner": 1024, "vocab_size": 1031, "n_positions": 704,
+    "activation_function": "gelu_new", "layer_norm_epsilon": 1e-5,
+    "scale_attn_by_inverse_layer_idx": False, "tie_word_embeddings": True,
+}
+
+# The layer sizes of GPT-2 small (width 768, 12 heads of 64, inner size 3072, vocabulary 50257,
+# 1024 positions) with two layers instead of twelve: what one layer computes is what every
+# layer computes, and the plain implementation stays within seconds.
+SMALL_WIDTHS = {
+    "architectures": ["GPT2LMHeadModel"], "model_type": "gpt2",
+    "n_layer": 2, "n_embd": 768, "n_head": 12, "n_inner": 3072, "vocab_size": 50257, "n_positions": 1024,
+    "activation_function": "gelu_new", "layer_norm_epsilon": 1e-5,
+    "scale_attn_by_inverse_layer_idx": False, "tie_word_embeddings": True,
+}
+
+RECIPES = {"A": ("gpt2", 0), "B": ("varied", 1), "C": ("varied", 2), "D": ("varied", 3)}
