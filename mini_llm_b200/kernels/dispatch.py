@@ -126,8 +126,7 @@ class Kernels:
         skinny = self._skinny(m, k, w.shape[0])
         deferred = isinstance(a, DeferredNorm)
         if deferred and not (skinny and a.kind in self.FUSED_NORM_KINDS):
-            self.launches += 1               # no kernel here norms this kind on the way in: the norm runs first
-            a, deferred = a.materialize(ctx), False
+            a, deferred = a.materialize(ctx), False      # no kernel here norms this kind on the way in: the norm runs first
         if skinny:
             self.chose("linear", "skinny_linear", m, w.shape[0], k)
             if deferred:
@@ -180,7 +179,6 @@ class Kernels:
         skinny = cache.writes and self._skinny(m, k)
         deferred = isinstance(a, DeferredNorm)
         if deferred and not (skinny and a.kind in self.FUSED_NORM_KINDS):
-            self.launches += 1
             a, deferred = a.materialize(ctx), False
         if skinny:
             q = ctx.buffer("q", (m, q_width), ctx.act_dtype)

@@ -262,8 +262,9 @@ class ToyRotation(PositionEncoding):
         for tensor, heads in ((q, n_heads), (k, n_kv_heads)):
             view = tensor.unflatten(1, (heads, head_size))        # a view: q and k are column ranges of one buffer
             lo, hi = view[..., :half].float(), view[..., half:].float()
-            view[..., :half] = (lo * cos - hi * sin).to(tensor.dtype)
-            view[..., half:] = (hi * cos + lo * sin).to(tensor.dtype)
+            new_lo, new_hi = lo * cos - hi * sin, hi * cos + lo * sin      # both before either is written
+            view[..., :half] = new_lo.to(tensor.dtype)
+            view[..., half:] = new_hi.to(tensor.dtype)
 
 
 def describe_mix(config):
