@@ -8,7 +8,13 @@ context length (1024).  ``value`` is decoded tokens per second, timed on the dev
 events around exactly K steps; ``e2e`` is the same metric through the Python entry point
 (``LLM.generate``): token ids from the host in, sampled token ids to the host out, every
 step.  The same line carries the prefill of 2,048 tokens (two prompts of 1024), the decode
-step's memory roofline, and decode throughput at batch 1 and 64.
+step's memory roofline, and under ``points``: decode throughput at batch 1 and 64; the decode
+workload as the target states it (512-token prompts, 256 greedy tokens, pages of 16, through
+the scheduler) at batch 1, 8 and 64 with its fraction of the HBM roofline; a mixed serving
+workload; the 32-bit path's decode and prompt steps.  ``reference_tokens`` says whether this
+engine's 32-bit path and the reference's choose the same greedy tokens from the same weights.
+``--model medium`` and ``--model xl`` run those sizes with their scheduler workloads (32 mixed
+requests with prompts in portions of 512; 64 requests side by side at temperature 1.0).
 
 The reference's counterparts are ``engine/bench/bench_batch.c:24-122`` (batched decode:
 prefill untimed, one warm-up step, then timed steps) and ``engine/bench/bench.c`` (prefill).
@@ -55,6 +61,9 @@ def parse_args():
     parser.add_argument("--page-size", type=int, default=None, help="tokens per cache page (the engine's default if not given)")
     parser.add_argument("--only-prefill", action="store_true",
                         help="run the 2,048-token prompt step alone and print its own line (for profiling)")
+    parser.add_argument("--tokens-out", default=None,
+                        help="(--impl reference) write the greedy tokens of the fixed check workload to this file "
+                             "and print nothing else")
     return parser.parse_args()
 
 
@@ -267,6 +276,116 @@ def serving_run(folder, args, vocab: int):
     return best
 
 
+def scheduled_decode_run(folder, args, batch: int, prompt_len: int, new_tokens: int, page_size: int, context: int,
+                         vocab: int, weight_bytes: float, kv_per_token: float, hbm_gbs: float):
+    """The decode workload as the target states it: ``batch`` requests, each a prompt of
+    ``prompt_len`` uniform ids, ``new_tokens`` greedy tokens through the scheduler
+    (``LLM.generate``), pages of ``page_size`` tokens.  The prompts are prefilled outside the
+    timing: the clock runs from every request's first token to its last, host tokens out
+    every step (the reference's bench_batch times its steps after untimed prefills too,
+    engine/bench/bench_batch.c:74-114).  Returns tokens a second and the fraction of the HBM
+    roofline at the mean context."""
+    import numpy as np
+    from mini_llm_b200.generate import LLM
+
+    rng = np.random.default_rng(77 + batch)
+    prompts = [rng.integers(0, vocab, prompt_len).tolist() for _ in range(batch)]
+    llm = LLM(folder, dtype=args.dtype, page_size=page_size, max_sessions=batch, cache_tokens=batch * context,
+              max_tokens_per_step=max(2048, batch * prompt_len), plain_kernels=args.plain_kernels)
+    best = None
+    for _ in range(2):                                  # the second pass finds its step shapes captured
+        stamps = []
+
+        def on_token(index, token, reason):
+            if index == batch - 1:
+                stamps.append(time.perf_counter())
+
+        out = llm.generate(prompts, max_new_tokens=new_tokens, temperature=0.0, on_token=on_token)
+        assert all(len(tokens) == new_tokens for tokens in out)
+        seconds = stamps[-1] - stamps[0]                  # new_tokens - 1 decode steps
+        best = seconds if best is None else min(best, seconds)
+    steps = new_tokens - 1
+    mean_context = prompt_len + new_tokens / 2.0
+    step_bytes = weight_bytes + batch * mean_context * kv_per_token
+    return batch * steps / best, step_bytes / (best / steps) / 1e9 / hbm_gbs
+
+
+def workload_run(folder, args, vocab: int, context: int, n_requests: int, prompt_range, output_range, live: int,
+                 budget: int, chunk: int, temperature: float, top_p: float, page_size: int):
+    """A workload through the continuous-batching scheduler: ``n_requests`` requests with
+    seeded prompt and output lengths, at most ``live`` at a time, a token budget per step and
+    prompts in portions of at most ``chunk`` tokens beside decoding requests.  Returns
+    generated tokens a second (wall clock, host tokens in and out) and the scheduler's
+    counters."""
+    import numpy as np
+    import torch
+    from mini_llm_b200.engine.scheduler import Request
+    from mini_llm_b200.generate import LLM
+
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, vocab, int(rng.integers(prompt_range[0], prompt_range[1] + 1))).tolist()
+               for _ in range(n_requests)]
+    lengths = [int(rng.integers(output_range[0], output_range[1] + 1)) for _ in range(n_requests)]
+    llm = LLM(folder, dtype=args.dtype, page_size=page_size, max_sessions=live, cache_tokens=live * context,
+              max_tokens_per_step=budget, max_prefill_chunk=chunk, plain_kernels=args.plain_kernels)
+    best, stats = 0.0, {}
+    for _ in range(2):                                   # the second pass finds its step shapes captured
+        requests = [Request(p, n, None, temperature, top_p, 100 + i) for i, (p, n) in enumerate(zip(prompts, lengths))]
+        before = dict(llm.scheduler.counters)
+        torch.cuda.synchronize()
+        start = time.perf_counter()
+        for request in requests:
+            llm.scheduler.submit(request)
+        llm.scheduler.run()
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - start
+        assert all(r.error is None and len(r.generated) == n for r, n in zip(requests, lengths))
+        if sum(lengths) / seconds > best:
+            best = sum(lengths) / seconds
+            after = llm.scheduler.counters
+            steps = after["steps"] - before.get("steps", 0)
+            tokens = (after["prefill_tokens"] + after["decode_tokens"] - before.get("prefill_tokens", 0)
+                      - before.get("decode_tokens", 0))
+            stats = {"steps": steps, "tokens_per_step": tokens / max(1, steps),
+                     "preemptions": after["preemptions"] - before.get("preemptions", 0),
+                     "pages": llm.engine.cache.groups[0].pool.n_pages}
+    return best, stats
+
+
+CHECK_PROMPT_SEED, CHECK_PROMPT_TOKENS, CHECK_NEW_TOKENS = 2024, 32, 16
+
+
+def check_prompt(vocab: int):
+    import numpy as np
+    return np.random.default_rng(CHECK_PROMPT_SEED).integers(0, vocab, CHECK_PROMPT_TOKENS).tolist()
+
+
+def compare_with_reference(folder, vocab: int) -> dict:
+    """Whether the two arms choose the same greedy tokens: the 32-bit path of this engine and
+    the reference's 32-bit GPU path, same seeded weights, a prompt of 32 ids and 16 new tokens.
+    The reference runs in a process of its own (``--impl reference --tokens-out``)."""
+    from mini_llm_b200.generate import generate
+    if not os.path.isdir(os.path.join(REFERENCE, "mini_llm")):
+        return {"unavailable": "the reference is not installed under baseline/_ref"}
+    with tempfile.TemporaryDirectory() as scratch:
+        path = os.path.join(scratch, "tokens.json")
+        try:
+            done = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--tokens-out", path],
+                                  capture_output=True, text=True, timeout=600)
+        except subprocess.TimeoutExpired:
+            return {"unavailable": "the reference did not finish in ten minutes"}
+        if done.returncode != 0 or not os.path.isfile(path):
+            return {"unavailable": (done.stdout.strip() or done.stderr.strip())[-200:]}
+        with open(path) as handle:
+            theirs = json.load(handle)["tokens"]
+    (mine,) = generate(folder, [check_prompt(vocab)], max_new_tokens=CHECK_NEW_TOKENS, temperature=0.0, dtype="float32",
+                       page_size=16, max_sessions=2, cache_tokens=1024)
+    same = 0
+    while same < len(mine) and mine[same] == theirs[same]:
+        same += 1
+    return {"agree": same, "of": len(mine)}
+
+
 def run_ours(args):
     import torch
     from mini_llm_b200.engine import Engine
@@ -323,10 +442,39 @@ def run_ours(args):
             peak_flops = (peak["bf16_tflops"] if dtype_bytes == 2 else peak["bf16_tflops"]) * 1e12
             line["prefill"] = {"value": 2048 / (prefill_ms * 1e-3), "tokens": 2048, "ms": prefill_ms,
                                "frac": flops / (prefill_ms * 1e-3) / peak_flops, "flops": flops}
+            line["device"] = engine.device_info()
             del engine
             torch.cuda.empty_cache()
             line["e2e"] = e2e_run(folder, args, context, vocab)
-            line["points"]["serve_mixed_64"] = serving_run(folder, args, vocab)
+            points = line["points"]
+            if args.model == "small" and args.layers is None:
+                # the decode workload as stated: 512-token prompts, 256 greedy tokens, pages of 16, through the scheduler
+                for batch in (1, 8, 64):
+                    value, frac = scheduled_decode_run(folder, args, batch, 512, 256, 16, context, vocab, weight_bytes,
+                                                       kv_per_token, peak["hbm_gbs"])
+                    points[f"sched_p16_b{batch}"] = value
+                    points[f"sched_p16_b{batch}_hbm_frac"] = frac
+                points["serve_mixed_64"] = serving_run(folder, args, vocab)
+                if args.dtype == "bfloat16":
+                    # the true 32-bit path: the same decode step and prompt step through the plain kernels
+                    plain = Engine(folder, dtype="float32", max_requests=8, cache_tokens=8 * context, max_tokens_per_step=2048)
+                    f_ms, _, _ = decode_run(plain, 8, 16, 3, context, vocab)
+                    points["decode_b8_float32"] = 8 / (f_ms * 1e-3)
+                    points["prefill_2048_float32"] = 2048 / (prefill_run(plain, 2, 1024, vocab, repeats=2) * 1e-3)
+                    del plain
+                    torch.cuda.empty_cache()
+                    line["reference_tokens"] = compare_with_reference(folder, vocab)
+            elif args.model == "medium":
+                # 32 requests, prompts of 16 to 768 tokens, 32 to 256 new tokens, prompts in portions of 512
+                value, stats = workload_run(folder, args, vocab, context, 32, (16, 768), (32, 256), 32, 512, 512, 0.0, 1.0, 16)
+                points["sched_medium_32"] = value
+                points.update({f"sched_medium_32_{k}": v for k, v in stats.items()})
+            elif args.model == "xl":
+                # 64 requests side by side, 256-token prompts and 768 new tokens each, temperature 1.0, pages of 16
+                value, stats = workload_run(folder, args, vocab, context, 64, (256, 256), (768, 768), 64, 2048, 2048, 1.0,
+                                            1.0, 16)
+                points["sched_xl_64"] = value
+                points.update({f"sched_xl_64_{k}": v for k, v in stats.items()})
     print(json.dumps(line))
     return 0
 
@@ -404,7 +552,18 @@ def run_reference(args):
     with tempfile.TemporaryDirectory() as folder:
         export_reference_weights(config, folder)
         engine = NativeGPT2(folder, library, backend="gpu",
-                            options=EngineOptions(use_kv_cache=True, max_sessions=16, fp16_decode=True))
+                            options=EngineOptions(use_kv_cache=True, max_sessions=16, fp16_decode=not args.tokens_out))
+    if args.tokens_out:
+        # the fixed check workload, 32-bit weights: greedy tokens for the other arm to compare with
+        cache = engine.try_take_cache()
+        tokens = [engine.prefill_greedy(cache, check_prompt(vocab))]
+        while len(tokens) < CHECK_NEW_TOKENS:
+            tokens.append(engine.decode_batch([cache], [tokens[-1]])[0])
+        engine.release_cache(cache)
+        engine.close()
+        with open(args.tokens_out, "w") as handle:
+            json.dump({"tokens": [int(t) for t in tokens]}, handle)
+        return 0
     sampler = ClockSampler()
     caches = [engine.try_take_cache() for _ in range(batch)]
     tokens = [engine.prefill_greedy(cache, rng.integers(0, vocab, prompt_len).tolist()) for cache in caches]

@@ -365,3 +365,21 @@ extern "C" int mllm_plain_attention(void* out, long ld_out, const void* q, long 
         return fail("attention: unknown dtype");
     return check_launch("attention_plain_kernel");
 }
+
+// The current device, for a benchmark's record: name, compute capability, SM count, memory,
+// runtime and driver versions (the reference's gpt2_gpu_device_info, engine/src/gpt2_gpu.cu:369-383).
+// values: [major, minor, SMs, runtime version, driver version]; memory in bytes.
+extern "C" int mllm_plain_device_info(char* name, int name_bytes, int* values, long* memory_bytes) {
+    int device = 0;
+    cudaDeviceProp properties;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaGetDeviceProperties(&properties, device) != cudaSuccess)
+        return fail("device_info: no CUDA device");
+    snprintf(name, (size_t)name_bytes, "%s", properties.name);
+    values[0] = properties.major;
+    values[1] = properties.minor;
+    values[2] = properties.multiProcessorCount;
+    *memory_bytes = (long)properties.totalGlobalMem;
+    if (cudaRuntimeGetVersion(&values[3]) != cudaSuccess || cudaDriverGetVersion(&values[4]) != cudaSuccess)
+        return fail("device_info: cannot read the versions");
+    return 0;
+}

@@ -134,6 +134,11 @@ class Engine:
         self.cache.close(slot)
         self._kept_valid.discard(slot)
 
+    def device_info(self) -> dict:
+        """Name, compute capability, SM count, memory and CUDA versions of the engine's device."""
+        with torch.cuda.device(self.device):
+            return ops.device_info()
+
     @property
     def vocab_size(self) -> int:
         return self.spec.vocab_size

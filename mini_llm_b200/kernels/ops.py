@@ -647,3 +647,18 @@ def resolve_tokens(token_ids, kept):
     _check(kept, "resolve_tokens.kept", torch.int32, 1)
     _resolve_tokens(token_ids.data_ptr(), kept.data_ptr(), token_ids.shape[0], kept.shape[0], _stream())
     return token_ids
+
+
+_device_info = Function("plain", "mllm_plain_device_info", [ctypes.c_char_p, I, ctypes.POINTER(ctypes.c_int),
+                                                            ctypes.POINTER(ctypes.c_long)])
+
+
+def device_info() -> dict:
+    """The current device as the kernel library sees it: name, compute capability, SM count,
+    memory, CUDA runtime and driver versions."""
+    name = ctypes.create_string_buffer(256)
+    values = (ctypes.c_int * 5)()
+    memory = ctypes.c_long()
+    _device_info(name, 256, values, ctypes.byref(memory))
+    return {"name": name.value.decode(), "compute": f"{values[0]}.{values[1]}", "sms": values[2],
+            "memory_bytes": memory.value, "runtime": values[3], "driver": values[4]}
