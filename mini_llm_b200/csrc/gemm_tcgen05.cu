@@ -1,20 +1,23 @@
 // Matrix products on the fifth-generation tensor cores: out = epilogue(x W^T + bias),
 // bfloat16 operands, fp32 accumulation in tensor memory.
 //
-// One CTA computes one 128 x BN tile.  A producer warp streams 128 x 64 and BN x 64 operand
-// blocks into a ring of shared-memory stages with TMA (128-byte swizzle); one thread of the
-// MMA warp issues tcgen05.mma on each filled stage (four K=16 instructions per block) and
-// releases the stage with tcgen05.commit; four epilogue warps wait for the accumulator,
-// read their 32 TMEM lanes with tcgen05.ld, and fuse bias, gelu or the residual sum into the
-// store.  The reference runs every prefill product as a naive one-thread-per-output kernel
-// followed by separate bias, gelu and add launches (engine/src/matrixmult.cu:7-34,
-// engine/src/linear.cu:9-18, engine/src/transformer_block.cu:153-202).
+// Operand blocks of 64 along K come into a ring of shared-memory stages by TMA (128-byte
+// swizzle) from a producer warp; one thread of the MMA warp issues tcgen05.mma on each filled
+// stage (four K=16 instructions per block) and releases the stage with tcgen05.commit; eight
+// epilogue warps read the accumulator from tensor memory with tcgen05.ld and fuse bias, gelu
+// or the residual sum into the store.  The reference runs every prefill product as a naive
+// one-thread-per-output kernel followed by separate bias, gelu and add launches
+// (engine/src/matrixmult.cu:7-34, engine/src/linear.cu:9-18,
+// engine/src/transformer_block.cu:153-202).
 //
-// Two orientations:
-//   rows    the 128 tile rows are rows of x (tokens), the BN tile columns rows of W.
-//   swapped the 128 tile rows are rows of W (outputs), the BN columns are tokens: for steps
-//           of few tokens, where a 128-row token tile would be mostly padding.  When such a
-//           product has few tiles, each is shared along K by a cluster of CTAs.
+// Two kernels:
+//   rows     (more than 64 tokens) tiles of 128 tokens x BN output features, walked by
+//            persistent CTAs with two accumulators, so that a tile's epilogue runs under the
+//            next tile's products; the fused query/key/value product scatters keys and values
+//            straight into the cache pages.
+//   swapped  (up to 64 tokens) the 128 tile rows are rows of W (output features), the BN
+//            columns are tokens: a 128-row token tile would be mostly padding.  When such a
+//            product has few tiles, each is shared along K by a cluster of CTAs.
 //
 // Every wait on an mbarrier is bounded: when the bound is hit the kernel writes a code to
 // its status word, stops issuing work, waits (bounded again) for its own copies in flight,
@@ -34,7 +37,7 @@ namespace {
 
 constexpr int BM = 128;             // tile rows = TMEM lanes
 constexpr int BK = 64;              // 64 bf16 = 128 bytes = one swizzle row
-constexpr int THREADS = 320;        // warps 0-7 epilogue, 8 producer, 9 MMA
+constexpr int THREADS = 320;        // warps 0-7 epilogue, 8 producer, 9 MMA (both kernels)
 enum { STATUS_OK = 0, STATUS_TIMEOUT_PRODUCER = 1, STATUS_TIMEOUT_MMA = 2, STATUS_TIMEOUT_EPILOGUE = 3 };
 
 struct GemmParams {
@@ -122,11 +125,11 @@ __device__ __forceinline__ void store_rows_bf16(const float* turn, bf16* base, R
     else store_rows_bf16_as<EPI_STORE>(turn, base, row_offset, paired, col_ok, lane, rows_left, bias);
 }
 
-template <int BN, int STAGES, bool SWAP, int CTAS_PER_SM>
-__global__ void __launch_bounds__(THREADS, CTAS_PER_SM)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_swapped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmParams p) {
-    // map_a: the operand whose 128 rows fill the tile's rows; map_b: the operand of BN rows.
+    // map_a: W, whose rows (output features) fill the tile's 128 rows; map_b: x, BN tokens.
     extern __shared__ unsigned char smem_raw[];
     // The swizzled tiles must start on 1024-byte boundaries; the launch asks for 1024 spare bytes.
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -143,13 +146,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     long* kv_off = reinterpret_cast<long*>(smem + STAGES * (A_BYTES + B_BYTES) + (2 * STAGES + 1) * 8 + 16);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile_a = SWAP ? blockIdx.x : blockIdx.y;      // which block of 128 rows of map_a
-    const int tile_b = SWAP ? blockIdx.y : blockIdx.x;      // which block of BN rows of map_b
+    const int tile_a = blockIdx.x;      // which block of 128 output features
+    const int tile_b = blockIdx.y;      // which block of BN tokens
     // k blocks of this CTA: all of them, or its share when the tile is split along K
     const int all_k = (p.K + BK - 1) / BK;
     const int per_split = (all_k + p.splits - 1) / p.splits;
-    const int kb_first = SWAP ? (int)blockIdx.z * per_split : 0;
-    const int num_k = SWAP ? max(0, min(all_k, kb_first + per_split) - kb_first) : all_k;
+    const int kb_first = (int)blockIdx.z * per_split;
+    const int num_k = max(0, min(all_k, kb_first + per_split) - kb_first);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -224,8 +227,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // ---- epilogue: warps w and w + 4 own TMEM lanes 32w .. 32w+31 and split the columns ----
         const int quarter = warp & 3, col_half = warp >> 2;
         if (p.k_pages != nullptr) {
-            const int t = (SWAP ? tile_b * BN : tile_a * BM) + threadIdx.x;
-            if (t < p.M && threadIdx.x < (SWAP ? BN : BM)) {
+            const int t = tile_b * BN + threadIdx.x;
+            if (t < p.M && threadIdx.x < BN) {
                 const int pos = p.positions[t];
                 const int page = p.block_table[(long)p.token_item[t] * p.max_blocks + pos / p.page_size];
                 kv_off[threadIdx.x] = ((long)page * p.page_size + pos % p.page_size) * p.kv_width;
@@ -248,65 +251,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             constexpr int SPAN = BN >= 32 ? BN / 2 : BN;
             const int c_first = BN >= 32 ? col_half * SPAN : 0;
             const bool has_columns = BN >= 32 || col_half == 0;
-            if (!SWAP) {
-                // Lane t of warp w holds row 32w + t of the tile.  To write whole rows with
-                // consecutive lanes on consecutive columns (coalesced, and with the bias and the
-                // old values of a residual sum read the same way), each block of 32 columns is
-                // turned through shared memory: the operand stages are free by now.
-                float* turn = reinterpret_cast<float*>(smem) + warp * (32 * 33);
-                const int row0 = tile_a * BM + quarter * 32;
-#pragma unroll 1
-                for (int c0 = c_first; c0 < c_first + SPAN; c0 += 32) {
-                    float v[32];
-                    __syncwarp();
-                    tmem_load_32(lane_base + c0, v);
-#pragma unroll
-                    for (int i = 0; i < 32; i++) turn[lane * 33 + i] = v[i];
-                    __syncwarp();
-                    const int n = tile_b * BN + c0 + lane;
-                    if (tile_b * BN + c0 >= p.N) break;
-                    const bool col_ok = n < p.N;
-                    const float b = (col_ok && p.bias != nullptr) ? p.bias[n] : 0.0f;
-                    if (p.epilogue == EPI_ADD) {
-                        float* o = reinterpret_cast<float*>(p.out) + (long)row0 * p.ldo + n;
-#pragma unroll 1
-                        for (int r0 = 0; r0 < 32; r0 += 8) {
-                            float old[8];
-#pragma unroll
-                            for (int u = 0; u < 8; u++)
-                                old[u] = (col_ok && row0 + r0 + u < p.M) ? o[(long)(r0 + u) * p.ldo] : 0.0f;
-#pragma unroll
-                            for (int u = 0; u < 8; u++)
-                                if (col_ok && row0 + r0 + u < p.M)
-                                    o[(long)(r0 + u) * p.ldo] = old[u] + turn[(r0 + u) * 33 + lane] + b;
-                        }
-                    } else if (p.out_f32) {
-                        float* o = reinterpret_cast<float*>(p.out) + (long)row0 * p.ldo + n;
-#pragma unroll 4
-                        for (int r = 0; r < 32; r++)
-                            if (col_ok && row0 + r < p.M) o[(long)r * p.ldo] = turn[r * 33 + lane] + b;
-                    } else {
-                        // bfloat16 output.  Where row r of this block of 32 columns goes: the output, or (scatter) a cache page
-                        const int n0 = tile_b * BN + c0;
-                        const int region = p.k_pages == nullptr || n0 < p.q_width ? 0 : (n0 < p.q_width + p.kv_width ? 1 : 2);
-                        bf16* const region_base = region == 0 ? reinterpret_cast<bf16*>(p.out) + (long)row0 * p.ldo + n0
-                                                  : (region == 1 ? p.k_pages + (n0 - p.q_width)
-                                                                 : p.v_pages + (n0 - p.q_width - p.kv_width));
-                        const bool paired = n0 + 32 <= p.N && (p.ldo & 1) == 0 && (p.kv_width & 1) == 0 &&
-                                            (reinterpret_cast<uintptr_t>(region_base) & 3) == 0;
-                        // the loop over the 32 rows is compiled twice: rows of the output (a fixed
-                        // stride), and cache slots (offsets from shared memory)
-                        const long ldo = p.ldo;
-                        const long* slots = kv_off + quarter * 32;
-                        if (region == 0)
-                            store_rows_bf16(turn, region_base, [ldo](int r) { return (long)r * ldo; }, paired, col_ok, lane,
-                                            p.M - row0, p.bias != nullptr ? p.bias + n0 : nullptr, p.epilogue);
-                        else
-                            store_rows_bf16(turn, region_base, [slots](int r) { return slots[r]; }, paired, col_ok, lane,
-                                            p.M - row0, p.bias != nullptr ? p.bias + n0 : nullptr, p.epilogue);
-                    }
-                }
-            } else {
+            {
                 // r: an output feature; columns: tokens.  Consecutive lanes write consecutive
                 // features of one token: coalesced.
                 const bool row_ok = r < p.N;
@@ -367,7 +312,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
     }
 
-    if (SWAP && p.splits > 1) {
+    if (p.splits > 1) {
         // Every thread of every CTA of the cluster comes by here, whatever happened above.
         __syncthreads();
         __syncwarp();
@@ -402,6 +347,217 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 9) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
     }
+}
+
+// ---- steps of many tokens: a persistent kernel ---------------------------------------------
+//
+// One CTA per SM walks tiles of 128 tokens x BN output features (tile t of CTA b is number
+// b + t * gridDim.x; the row tile runs fastest, so CTAs that run side by side share a block
+// of W in L2).  The producer warp keeps the ring of operand stages full across tile
+// boundaries; the MMA thread accumulates tile t in one half of the allocated tensor memory
+// while the eight epilogue warps drain tile t - 1 from the other half, so bias, activation,
+// residual sum and the stores run under the next tile's products.  BN is 64, 96, 128, 192 or
+// 256: wide tiles read less of x and W per output from L2 (what bounds these products),
+// narrow ones spread a product with few output features over more SMs.
+constexpr int TURN_FLOATS = 32 * 33;          // one epilogue warp's block of 32 x 32, turned through shared memory
+enum { STATUS_TIMEOUT_ROWS_PRODUCER = 5, STATUS_TIMEOUT_ROWS_MMA = 6, STATUS_TIMEOUT_ROWS_EPILOGUE = 7 };
+
+
+template <int BN, int STAGES>
+constexpr size_t rows_shared_bytes() {
+    return (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 8 * TURN_FLOATS * 4 + (2 * STAGES + 4) * 8 + 16 + BM * 8 + 1024;
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const GemmParams p, const int tiles_m, const int n_tiles) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    constexpr int TMEM_COLS = BN <= 64 ? 128 : (BN <= 128 ? 256 : 512), ACC_STRIDE = TMEM_COLS / 2, CHUNKS = BN / 32;
+    unsigned char* stage_a = smem;
+    unsigned char* stage_b = smem + STAGES * A_BYTES;
+    float* turn_all = reinterpret_cast<float*>(smem + STAGES * (A_BYTES + B_BYTES));
+    uint64_t* full = reinterpret_cast<uint64_t*>(turn_all + 8 * TURN_FLOATS);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;        // [2]: the MMAs of a tile have finished
+    uint64_t* acc_empty = acc_full + 2;         // [2]: the epilogue warps have read the tile out
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* tile_ok = reinterpret_cast<volatile int*>(tmem_slot + 2);     // [2], by the tile's parity
+    long* kv_off = reinterpret_cast<long*>(tmem_slot + 4);    // element offset of each of the tile's tokens in the cache pages
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_k = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_empty[a], 8);         // one arrival per epilogue warp
+        }
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) tmem_alloc(tmem_slot, TMEM_COLS);
+    tcgen05_before_sync();
+    __syncthreads();
+    tcgen05_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    auto give_up = [&](int code) {
+        if (!*failed) {
+            *failed = code;
+            atomicExch(p.status, code);
+        }
+    };
+
+    if (warp == 8) {
+        // ---- producer: the ring runs on across tiles ----
+        if (lane == 0) {
+            int it = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && !*failed; tile += gridDim.x) {
+                const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+                for (int kb = 0; kb < num_k; kb++, it++) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1) || *failed) {
+                        give_up(STATUS_TIMEOUT_ROWS_PRODUCER);
+                        break;
+                    }
+                    mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+                    tma_load_2d(stage_a + s * A_BYTES, &map_a, &full[s], kb * BK, tile_m * BM);
+                    tma_load_2d(stage_b + s * B_BYTES, &map_b, &full[s], kb * BK, tile_n * BN);
+                }
+            }
+            if (*failed) {
+                // copies that were issued still land: wait for them (bounded) so that none is in flight at the end
+                for (int i = max(0, it - STAGES); i < it; i++) mbar_wait(&full[i % STAGES], (i / STAGES) & 1);
+            }
+        }
+    } else if (warp == 9) {
+        // ---- MMA issue: tile t into accumulator t % 2 ----
+        if (lane == 0) {
+            const uint32_t idesc = make_instr_desc(BM, BN);
+            int it = 0, local = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && !*failed; tile += gridDim.x, local++) {
+                const int acc = local & 1;
+                if (!mbar_wait(&acc_empty[acc], ((local >> 1) & 1) ^ 1) || *failed) {
+                    give_up(STATUS_TIMEOUT_ROWS_MMA);
+                    break;
+                }
+                tcgen05_after_sync();
+                const uint32_t tmem_acc = tmem_base + (uint32_t)(acc * ACC_STRIDE);
+                for (int kb = 0; kb < num_k; kb++, it++) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&full[s], (it / STAGES) & 1) || *failed) {
+                        give_up(STATUS_TIMEOUT_ROWS_MMA);
+                        break;
+                    }
+                    tcgen05_after_sync();
+                    const uint64_t desc_a = make_smem_desc(smem_u32(stage_a + s * A_BYTES));
+                    const uint64_t desc_b = make_smem_desc(smem_u32(stage_b + s * B_BYTES));
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++)
+                        umma(tmem_acc, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&empty[s]);
+                }
+                umma_commit(&acc_full[acc]);
+            }
+        }
+    } else {
+        // ---- epilogue: warps w and w + 4 own TMEM lanes 32 (w % 4) .. +31 and take the tile's
+        // blocks of 32 columns in turn ----
+        const int quarter = warp & 3, col_half = warp >> 2;
+        float* turn = turn_all + warp * TURN_FLOATS;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        int local = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, local++) {
+            const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+            const int acc = local & 1;
+            if (p.k_pages != nullptr && threadIdx.x < BM) {
+                const int t = tile_m * BM + threadIdx.x;
+                if (t < p.M) {
+                    const int pos = p.positions[t];
+                    const int page = p.block_table[(long)p.token_item[t] * p.max_blocks + pos / p.page_size];
+                    kv_off[threadIdx.x] = ((long)page * p.page_size + pos % p.page_size) * p.kv_width;
+                }
+            }
+            // One thread waits for the accumulator; all eight warps learn the outcome at one
+            // barrier, so that they go on or leave together.
+            if (threadIdx.x == 0) {
+                const bool ok = mbar_wait(&acc_full[acc], (local >> 1) & 1) && !*failed;
+                if (!ok) give_up(STATUS_TIMEOUT_ROWS_EPILOGUE);
+                tile_ok[acc] = ok ? 1 : 0;
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (tile_ok[acc] == 0) break;
+            tcgen05_after_sync();
+            const int row0 = tile_m * BM + quarter * 32;
+            const uint32_t acc_base = lane_base + (uint32_t)(acc * ACC_STRIDE);
+#pragma unroll 1
+            for (int c = col_half; c < CHUNKS; c += 2) {
+                const int c0 = c * 32, n0 = tile_n * BN + c0;
+                if (n0 >= p.N) continue;
+                float v[32];
+                __syncwarp();
+                tmem_load_32(acc_base + c0, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) turn[lane * 33 + i] = v[i];
+                __syncwarp();
+                const int n = n0 + lane;
+                const bool col_ok = n < p.N;
+                const float b = (col_ok && p.bias != nullptr) ? p.bias[n] : 0.0f;
+                if (p.epilogue == EPI_ADD) {
+                    float* o = reinterpret_cast<float*>(p.out) + (long)row0 * p.ldo + n;
+#pragma unroll 1
+                    for (int r0 = 0; r0 < 32; r0 += 8) {
+                        float old[8];
+#pragma unroll
+                        for (int u = 0; u < 8; u++)
+                            old[u] = (col_ok && row0 + r0 + u < p.M) ? o[(long)(r0 + u) * p.ldo] : 0.0f;
+#pragma unroll
+                        for (int u = 0; u < 8; u++)
+                            if (col_ok && row0 + r0 + u < p.M)
+                                o[(long)(r0 + u) * p.ldo] = old[u] + turn[(r0 + u) * 33 + lane] + b;
+                    }
+                } else if (p.out_f32) {
+                    float* o = reinterpret_cast<float*>(p.out) + (long)row0 * p.ldo + n;
+#pragma unroll 4
+                    for (int r = 0; r < 32; r++)
+                        if (col_ok && row0 + r < p.M) o[(long)r * p.ldo] = turn[r * 33 + lane] + b;
+                } else {
+                    // bfloat16: rows of the output, or (scatter) slots of the cache pages
+                    const int region = p.k_pages == nullptr || n0 < p.q_width ? 0 : (n0 < p.q_width + p.kv_width ? 1 : 2);
+                    bf16* const region_base = region == 0 ? reinterpret_cast<bf16*>(p.out) + (long)row0 * p.ldo + n0
+                                              : (region == 1 ? p.k_pages + (n0 - p.q_width)
+                                                             : p.v_pages + (n0 - p.q_width - p.kv_width));
+                    const bool paired = n0 + 32 <= p.N && (p.ldo & 1) == 0 && (p.kv_width & 1) == 0 &&
+                                        (reinterpret_cast<uintptr_t>(region_base) & 3) == 0;
+                    const long ldo = p.ldo;
+                    const long* slots = kv_off + quarter * 32;
+                    if (region == 0)
+                        store_rows_bf16(turn, region_base, [ldo](int r) { return (long)r * ldo; }, paired, col_ok, lane,
+                                        p.M - row0, p.bias != nullptr ? p.bias + n0 : nullptr, p.epilogue);
+                    else
+                        store_rows_bf16(turn, region_base, [slots](int r) { return slots[r]; }, paired, col_ok, lane,
+                                        p.M - row0, p.bias != nullptr ? p.bias + n0 : nullptr, p.epilogue);
+                }
+            }
+            // the accumulator may be overwritten once every warp has read its part
+            tcgen05_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[acc]);
+            // the next tile's cache offsets wait until every warp is done with this tile's
+            if (p.k_pages != nullptr) asm volatile("bar.sync 1, 256;" ::: "memory");
+        }
+    }
+
+    tcgen05_before_sync();
+    __syncthreads();
+    if (warp == 9) tmem_free(tmem_base, TMEM_COLS);
 }
 
 // ---- host side: tensor maps ------------------------------------------------------------
@@ -466,12 +622,12 @@ int tensor_map(const void* base, long rows, long cols, long ld, int box_rows, CU
     return 0;
 }
 
-template <int BN, int STAGES, bool SWAP, int CTAS_PER_SM = 1>
-int launch(const CUtensorMap& a, const CUtensorMap& b, const GemmParams& p, dim3 grid, cudaStream_t s) {
+template <int BN, int STAGES>
+int launch_swapped(const CUtensorMap& a, const CUtensorMap& b, const GemmParams& p, dim3 grid, cudaStream_t s) {
     constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + BM * 8 + 1024;   // barriers, TMEM slot, flag, ticket, cache offsets
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, SWAP, CTAS_PER_SM>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_swapped_kernel<BN, STAGES>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail("gemm: cannot raise the shared memory limit");
         configured = true;
@@ -490,15 +646,31 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const GemmParams& p, dim3
         attribute.val.clusterDim.z = grid.z;
         config.attrs = &attribute;
         config.numAttrs = 1;
-        cudaError_t e = cudaLaunchKernelEx(&config, gemm_tcgen05_kernel<BN, STAGES, SWAP, CTAS_PER_SM>, a, b, p);
+        cudaError_t e = cudaLaunchKernelEx(&config, gemm_swapped_kernel<BN, STAGES>, a, b, p);
         if (e != cudaSuccess) {
-            snprintf(g_error_text, MLLM_ERROR_BUFFER, "gemm_tcgen05_kernel (cluster of %u): %s", grid.z, cudaGetErrorString(e));
+            snprintf(g_error_text, MLLM_ERROR_BUFFER, "gemm_swapped_kernel (cluster of %u): %s", grid.z, cudaGetErrorString(e));
             return 2;
         }
         return 0;
     }
-    gemm_tcgen05_kernel<BN, STAGES, SWAP, CTAS_PER_SM><<<grid, THREADS, smem, s>>>(a, b, p);
-    return check_launch("gemm_tcgen05_kernel");
+    gemm_swapped_kernel<BN, STAGES><<<grid, THREADS, smem, s>>>(a, b, p);
+    return check_launch("gemm_swapped_kernel");
+}
+
+template <int BN, int STAGES>
+int launch_rows(const CUtensorMap& a, const CUtensorMap& b, const GemmParams& p, int sms, cudaStream_t s) {
+    constexpr size_t smem = rows_shared_bytes<BN, STAGES>();
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_rows_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+            cudaSuccess)
+            return fail("gemm: cannot raise the shared memory limit");
+        configured = true;
+    }
+    const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+    const int n_tiles = tiles_m * tiles_n;
+    gemm_rows_kernel<BN, STAGES><<<std::min(n_tiles, sms), THREADS, smem, s>>>(a, b, p, tiles_m, n_tiles);
+    return check_launch("gemm_rows_kernel");
 }
 
 }  // namespace
@@ -537,8 +709,31 @@ struct GemmScatter {
     int max_blocks, page_size, q_width, kv_width;
 };
 
+// Tile width of the persistent kernel for a product of M x N x K: the width with the least
+// estimated time.  The products are bound by operand traffic from L2, (128 + BN) * 128 bytes
+// per tile and block of K, and a product ends with its slowest CTA, which has
+// ceil(tiles / SMs) tiles; the last tile's epilogue (about BN columns of stores) is not hidden.
+static int rows_tile_width(int M, int N, int K, int sms) {
+    const int widths[5] = {256, 192, 128, 96, 64};
+    const long tiles_m = (M + BM - 1) / BM, num_k = (K + BK - 1) / BK;
+    int best = 128;
+    long best_cost = -1;
+    for (int i = 0; i < 5; i++) {
+        const int bn = widths[i];
+        if (bn > 64 && bn >= 2 * N) continue;                     // mostly padding
+        const long tiles = tiles_m * ((N + bn - 1) / bn);
+        const long rounds = (tiles + sms - 1) / sms;
+        const long cost = rounds * num_k * (128 + bn) + 6L * bn;
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best = bn;
+        }
+    }
+    return best;
+}
+
 static int gemm_bf16(void* out, const void* x, const void* w, const float* bias, int M, int N, int K, long ldx, long ldo,
-                     int epilogue, int out_f32, int* status, const GemmScatter* scatter, void* stream) {
+                     int epilogue, int out_f32, int* status, const GemmScatter* scatter, void* stream, int forced_bn) {
     if (M <= 0 || N <= 0) return 0;
     if (!mllm_gemm_takes(K, ldx, x, w)) return fail("gemm: K and the row stride of x must be multiples of 8, bases 16-byte aligned");
     if (epilogue == EPI_ADD && !out_f32) return fail("gemm: the residual sum is kept in 32-bit");
@@ -562,34 +757,32 @@ static int gemm_bf16(void* out, const void* x, const void* w, const float* bias,
         p.kv_width = scatter->kv_width;
     }
     CUtensorMap map_x, map_w;
-    const bool swap = M <= 64;
-    int bn = 128;
-    if (swap) {
-        bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-    } else {
-        // Tile width by how the tiles fill the SMs (measured on the layer shapes of GPT-2 small):
-        // narrow tiles when 128-wide ones would leave SMs idle, 256 columns only for many waves.
-        const long row_tiles = (M + BM - 1) / BM;
-        const long tiles_128 = row_tiles * ((N + 127) / 128), tiles_256 = row_tiles * ((N + 255) / 256);
-        const int sms = sm_count();
-        if (tiles_128 < sms) bn = 64;
-        else if (tiles_256 >= 4 * sms) bn = 256;
-    }
-    int rc = tensor_map(x, M, K, ldx, swap ? bn : BM, &map_x);
-    if (rc) return rc;
-    rc = tensor_map(w, N, K, K, swap ? BM : bn, &map_w);
-    if (rc) return rc;
+    const int sms = sm_count();
+    const bool swap = M <= 64 && forced_bn == 0;
     if (!swap) {
-        dim3 grid((N + bn - 1) / bn, (M + BM - 1) / BM);
-        if (bn == 64) return launch<64, 4, false, 2>(map_x, map_w, p, grid, s);
-        if (bn == 256) return launch<256, 4, false, 1>(map_x, map_w, p, grid, s);
-        return launch<128, 3, false, 2>(map_x, map_w, p, grid, s);
+        const int bn = forced_bn != 0 ? forced_bn : rows_tile_width(M, N, K, sms);
+        int rc = tensor_map(x, M, K, ldx, BM, &map_x);
+        if (rc) return rc;
+        rc = tensor_map(w, N, K, K, bn, &map_w);
+        if (rc) return rc;
+        switch (bn) {
+        case 256: return launch_rows<256, 3>(map_x, map_w, p, sms, s);
+        case 192: return launch_rows<192, 4>(map_x, map_w, p, sms, s);
+        case 128: return launch_rows<128, 5>(map_x, map_w, p, sms, s);
+        case 96: return launch_rows<96, 6>(map_x, map_w, p, sms, s);
+        case 64: return launch_rows<64, 6>(map_x, map_w, p, sms, s);
+        default: return fail("gemm: the tile width is 64, 96, 128, 192 or 256");
+        }
     }
+    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    int rc = tensor_map(x, M, K, ldx, bn, &map_x);
+    if (rc) return rc;
+    rc = tensor_map(w, N, K, K, BM, &map_w);
+    if (rc) return rc;
     dim3 grid((N + BM - 1) / BM, (M + bn - 1) / bn);
     {
         // Few tiles: share each among a cluster of 8, 4 or 2 CTAs along K, so that more SMs
         // stream the weights (at least two k blocks per CTA; not with the cache scatter)
-        const int sms = sm_count();
         const int tiles = grid.x * grid.y, all_k = (K + BK - 1) / BK;
         if (scatter == nullptr)
             for (int splits = 8; splits >= 2; splits /= 2)
@@ -599,14 +792,25 @@ static int gemm_bf16(void* out, const void* x, const void* w, const float* bias,
                     break;
                 }
     }
-    if (bn == 16) return launch<16, 8, true>(map_w, map_x, p, grid, s);
-    if (bn == 32) return launch<32, 8, true>(map_w, map_x, p, grid, s);
-    return launch<64, 8, true>(map_w, map_x, p, grid, s);
+    if (bn == 16) return launch_swapped<16, 8>(map_w, map_x, p, grid, s);
+    if (bn == 32) return launch_swapped<32, 8>(map_w, map_x, p, grid, s);
+    return launch_swapped<64, 8>(map_w, map_x, p, grid, s);
 }
 
 extern "C" int mllm_gemm_bf16(void* out, const void* x, const void* w, const float* bias, int M, int N, int K,
                               long ldx, long ldo, int epilogue, int out_f32, int* status, void* stream) {
-    return gemm_bf16(out, x, w, bias, M, N, K, ldx, ldo, epilogue, out_f32, status, nullptr, stream);
+    return gemm_bf16(out, x, w, bias, M, N, K, ldx, ldo, epilogue, out_f32, status, nullptr, stream, 0);
+}
+
+// The same through the persistent kernel with a given tile width (64, 96, 128, 192 or 256),
+// whatever the number of rows: for tests, which run every width at sizes that leave tiles
+// partly empty, and for measurements of the widths against each other.
+extern "C" int mllm_gemm_bf16_tile(void* out, const void* x, const void* w, const float* bias, int M, int N, int K,
+                                   long ldx, long ldo, int epilogue, int out_f32, int* status, int tile_width,
+                                   void* stream) {
+    if (tile_width != 64 && tile_width != 96 && tile_width != 128 && tile_width != 192 && tile_width != 256)
+        return fail("gemm: the tile width is 64, 96, 128, 192 or 256");
+    return gemm_bf16(out, x, w, bias, M, N, K, ldx, ldo, epilogue, out_f32, status, nullptr, stream, tile_width);
 }
 
 // The fused query/key/value product of a layer: out [M, q_width] gets the queries; keys and
@@ -617,5 +821,5 @@ extern "C" int mllm_gemm_bf16_qkv(void* out, const void* x, const void* w, const
                                   const int* token_item, const int* block_table, int max_blocks, int page_size,
                                   int q_width, int kv_width, void* stream) {
     GemmScatter scatter{k_pages, v_pages, positions, token_item, block_table, max_blocks, page_size, q_width, kv_width};
-    return gemm_bf16(out, x, w, bias, M, N, K, ldx, ldo, EPI_STORE, 0, status, &scatter, stream);
+    return gemm_bf16(out, x, w, bias, M, N, K, ldx, ldo, EPI_STORE, 0, status, &scatter, stream, 0);
 }

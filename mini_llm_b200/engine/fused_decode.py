@@ -146,6 +146,7 @@ class FusedDecodePlan:
         self.att_partial = torch.empty(MAX_TOKENS * heads * MAX_ATTENTION_PARTS * (head_size + 2), dtype=torch.float32,
                                        device=device)
         self.att_counters = torch.zeros(MAX_TOKENS * heads, dtype=torch.int32, device=device)
+        self.force_parts = None       # tests and measurements: this many CTAs share every pair's keys
 
     def takes(self, ctx) -> bool:
         return self.takes_sizes(ctx.n_tokens, ctx.decode_only)
@@ -159,6 +160,8 @@ class FusedDecodePlan:
         """How many CTAs share the keys of one (token, head) pair: as many as leave every CTA at
         most one part (a part's hand-over costs more than a second part would save), with at
         least 64 keys each."""
+        if self.force_parts is not None:
+            return int(self.force_parts)
         pairs = ctx.n_tokens * self.sizes[1]
         longest = max(ctx.item_starts) + 1
         return max(1, min(MAX_ATTENTION_PARTS, self.grid // pairs, longest // 64))

@@ -418,6 +418,30 @@ def gemm_bf16(out, a, w, bias, epilogue, status):
     return out
 
 
+_gemm_bf16_tile = Function("gemm", "mllm_gemm_bf16_tile", [P, P, P, P, I, I, I, L, L, I, I, P, I, P])
+GEMM_TILE_WIDTHS = (64, 96, 128, 192, 256)
+
+
+def gemm_bf16_tile(out, a, w, bias, epilogue, status, tile_width):
+    """``gemm_bf16`` through the persistent kernel with tiles of 128 x ``tile_width``, whatever
+    the number of rows (tests run every width; the engine lets the library choose)."""
+    _check(a, "gemm.a", torch.bfloat16, 2)
+    _check(w, "gemm.w", torch.bfloat16, 2)
+    _check(out, "gemm.out", None, 2)
+    _check(status, "gemm.status", torch.int32)
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape[0] != m or out.shape[1] != n or not gemm_takes(a, w):
+        raise KernelError("gemm: operands are not laid out for the tensor-core kernel")
+    if out.dtype not in (torch.bfloat16, torch.float32) or (epilogue == "add" and out.dtype != torch.float32):
+        raise KernelError("gemm: out must be bfloat16, or float32 for logits and the residual sum")
+    if bias is not None:
+        _check(bias, "gemm.bias", torch.float32, 1)
+    _gemm_bf16_tile(out.data_ptr(), a.data_ptr(), w.data_ptr(), _ptr(bias), m, n, k, a.stride(0), out.stride(0),
+                    EPILOGUES[epilogue], int(out.dtype == torch.float32), status.data_ptr(), int(tile_width), _stream())
+    return out
+
+
 _gemm_bf16_qkv = Function("gemm", "mllm_gemm_bf16_qkv", [P, P, P, P, I, I, I, L, L, P, P, P, P, P, P, I, I, I, I, P])
 
 

@@ -109,6 +109,32 @@ def test_decode_steps_of_forty_requests(folder_d, dtype, page_size):
     engine.cache.check()
 
 
+@pytest.mark.parametrize("parts", [1, 2, 3, 5, 16])
+def test_the_one_kernel_step_with_keys_in_parts(folder_d, parts):
+    """In the one-kernel decode step several CTAs may share the keys of a (token, head) pair;
+    the one that finishes last merges their states.  With any number of parts (more parts than
+    a short request has keys, and more units than CTAs among them) the logits are the plain
+    implementation's."""
+    from mini_llm_b200.engine import Engine, StepEntry
+    vocab = TINY_D["vocab_size"]
+    lengths = {"s": 3, "m": 90, "l": 500, "x": 33, "y": 257}
+    requests = {n: random_tokens(300 + i, count + 4, vocab) for i, (n, count) in enumerate(lengths.items())}
+    engine = Engine(folder_d, dtype="bfloat16", page_size=16, cache_tokens=2048, max_requests=8)
+    assert engine.fused is not None, engine.fused_reason
+    engine.fused.force_parts = parts
+    slots = {n: engine.open_request() for n in requests}
+    engine.step([StepEntry(slots[n], t[:-4], []) for n, t in requests.items()])
+    got = {n: np.full((len(t), vocab), np.nan, dtype=np.float32) for n, t in requests.items()}
+    before = engine.kernels.launches
+    for step in range(4):
+        logits = engine.step([StepEntry(slots[n], [t[len(t) - 4 + step]], [0]) for n, t in requests.items()]).cpu().numpy()
+        for row, (n, t) in zip(logits, requests.items()):
+            got[n][len(t) - 4 + step] = row
+    assert engine.kernels.launches - before == 4
+    engine.check_status()
+    compare(folder_d, "bfloat16", got, requests, {n: range(len(t) - 4, len(t)) for n, t in requests.items()})
+
+
 # ---- captured graphs of prompt steps -------------------------------------------------------------
 
 def test_prompt_steps_replayed_from_a_captured_graph(folder_d):

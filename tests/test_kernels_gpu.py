@@ -483,6 +483,43 @@ def test_gemm_tcgen05(m, n, k, epilogue):
     np.testing.assert_allclose(f64(out), expected, rtol=0, atol=atol)
 
 
+@pytest.mark.parametrize("width", [64, 96, 128, 192, 256])
+@pytest.mark.parametrize("m, n, k, epilogue", [(300, 1000, 160, "gelu_tanh"), (513, 768, 3072, "add"), (17, 777, 96, "store"),
+                                               (2048, 2304, 768, "store"), (4000, 1100, 72, "add"), (129, 50257, 64, "logits"),
+                                               (2100, 3072, 256, "gelu_erf")])
+def test_gemm_tcgen05_every_tile_width(m, n, k, epilogue, width):
+    """The persistent kernel at each of its tile widths: tiles that are partly empty in rows
+    and in columns, one tile for some CTAs and a dozen for others (so that both accumulators
+    and every phase of the ring are in use), every epilogue; bitwise the same result twice."""
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(m + n + k + width)
+    a, w = dev(rng.normal(size=(m, k)), torch.bfloat16), dev(rng.normal(size=(n, k)) / math.sqrt(k), torch.bfloat16)
+    bias = dev(rng.normal(size=n), torch.float32)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    acc = f64(a) @ f64(w).T
+    runs = []
+    for _ in range(2):
+        if epilogue == "add":
+            start = dev(np.random.default_rng(3).normal(size=(m, n)), torch.float32)
+            out = start.clone()
+            ops.gemm_bf16_tile(out, a, w, bias, "add", status, width)
+            expected, atol = f64(start) + acc + f64(bias), 2e-4
+        elif epilogue == "logits":
+            out = torch.full((m, n), float("nan"), device="cuda", dtype=torch.float32)
+            ops.gemm_bf16_tile(out, a, w, None, "store", status, width)
+            expected, atol = acc, 2e-4
+        else:
+            out = torch.full((m, n), float("nan"), device="cuda", dtype=torch.bfloat16)
+            ops.gemm_bf16_tile(out, a, w, bias, epilogue, status, width)
+            full = acc + f64(bias)
+            expected = {"store": full, "gelu_tanh": plain.gelu_tanh(full), "gelu_erf": plain.gelu_erf(full)}[epilogue]
+            atol = tol(torch.bfloat16, 4)
+        assert int(status.item()) == 0, "a bounded wait inside the kernel ran out"
+        np.testing.assert_allclose(f64(out), expected, rtol=0, atol=atol)
+        runs.append(f64(out))
+    np.testing.assert_array_equal(runs[0], runs[1])
+
+
 def test_gemm_tcgen05_strided_input_and_twin():
     """A column slice as input (the row stride differs from K), against the plain twin."""
     from mini_llm_b200.kernels import ops
@@ -655,7 +692,7 @@ def test_gemm_tcgen05_shared_along_k(m, n, k, epilogue):
     np.testing.assert_array_equal(runs[0], runs[2])
 
 
-@pytest.mark.parametrize("m, q_width, kv_width, k, page", [(300, 768, 768, 256, 16), (40, 256, 64, 128, 8),
+@pytest.mark.parametrize("m, q_width, kv_width, k, page", [(300, 768, 768, 256, 16), (40, 256, 64, 128, 8), (5000, 512, 256, 64, 16),
                                                            (130, 96, 32, 64, 64), (64, 128, 128, 512, 4),
                                                            (17, 64, 32, 96, 16)])
 def test_gemm_tcgen05_scatters_keys_and_values_into_the_pages(m, q_width, kv_width, k, page):
