@@ -58,6 +58,11 @@ struct GemmParams {
     const int* token_item;
     const int* block_table;
     int max_blocks, page_size, q_width, kv_width;
+    // Optional (rows kernel): seven time stamps of CTA 0, in nanoseconds of %globaltimer: start,
+    // set-up done, first operands landed, last product issued, first accumulator ready, first
+    // epilogue done, end.  Null in the engine; measurements and a test pass a buffer.
+    unsigned long long* timeline;
+    int out_by_tma;           // rows kernel: blocks of `out` leave through shared memory and TMA (map_out is valid)
 };
 
 __device__ __forceinline__ float activate(float v, int epilogue) {
@@ -359,37 +364,97 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // residual sum and the stores run under the next tile's products.  BN is 64, 96, 128, 192 or
 // 256: wide tiles read less of x and W per output from L2 (what bounds these products),
 // narrow ones spread a product with few output features over more SMs.
-constexpr int TURN_FLOATS = 32 * 33;          // one epilogue warp's block of 32 x 32, turned through shared memory
-enum { STATUS_TIMEOUT_ROWS_PRODUCER = 5, STATUS_TIMEOUT_ROWS_MMA = 6, STATUS_TIMEOUT_ROWS_EPILOGUE = 7 };
-
-
-template <int BN, int STAGES>
-constexpr size_t rows_shared_bytes() {
-    return (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 8 * TURN_FLOATS * 4 + (2 * STAGES + 4) * 8 + 16 + BM * 8 + 1024;
+__device__ __forceinline__ float4 lds128(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-template <int BN, int STAGES>
+// A thread's 32 values of one row of the accumulator plus the 32 biases at shared address
+// `bias32`, activated, as bfloat16 (EPI) or fp32 into this thread's row of a block in shared
+// memory at address `dst` (rows of 64 or 128 bytes).
+// The block is laid out as TMA's 64-byte (bfloat16) or 128-byte (fp32) swizzle reads it: the
+// 16-byte piece j of row r lies at piece j ^ ((r / 2) % 4), respectively j ^ (r % 8), of its
+// row, so that the lanes of a warp, each writing the same piece of its own row, hit different
+// banks (all eight epilogue warps share one path into shared memory: a conflict costs them all).
+template <int EPI>
+__device__ __forceinline__ void stage_row_bf16(const float* v, uint32_t bias32, uint32_t block, int row) {
+    const uint32_t dst = block + row * 64;
+    const int twist = (row >> 1) & 3;
+    float4 b[8];                                   // all loads first: they are in flight together
+#pragma unroll
+    for (int j = 0; j < 8; j++) b[j] = lds128(bias32 + j * 16);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float4 b0 = b[2 * j], b1 = b[2 * j + 1];
+        const __nv_bfloat162 p0 = __floats2bfloat162_rn(activate_as<EPI>(v[8 * j] + b0.x), activate_as<EPI>(v[8 * j + 1] + b0.y));
+        const __nv_bfloat162 p1 = __floats2bfloat162_rn(activate_as<EPI>(v[8 * j + 2] + b0.z), activate_as<EPI>(v[8 * j + 3] + b0.w));
+        const __nv_bfloat162 p2 = __floats2bfloat162_rn(activate_as<EPI>(v[8 * j + 4] + b1.x), activate_as<EPI>(v[8 * j + 5] + b1.y));
+        const __nv_bfloat162 p3 = __floats2bfloat162_rn(activate_as<EPI>(v[8 * j + 6] + b1.z), activate_as<EPI>(v[8 * j + 7] + b1.w));
+        sts128(dst + ((j ^ twist) << 4), *reinterpret_cast<const uint32_t*>(&p0), *reinterpret_cast<const uint32_t*>(&p1),
+               *reinterpret_cast<const uint32_t*>(&p2), *reinterpret_cast<const uint32_t*>(&p3));
+    }
+}
+__device__ __forceinline__ void stage_row_f32(const float* v, uint32_t bias32, uint32_t block, int row) {
+    const uint32_t dst = block + row * 128;
+    const int twist = row & 7;
+    float4 b[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) b[j] = lds128(bias32 + j * 16);
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+        sts128(dst + ((j ^ twist) << 4), __float_as_uint(v[4 * j] + b[j].x), __float_as_uint(v[4 * j + 1] + b[j].y),
+               __float_as_uint(v[4 * j + 2] + b[j].z), __float_as_uint(v[4 * j + 3] + b[j].w));
+}
+
+// (a block of 32 x 32 floats turned through shared memory, rows 33 floats apart, fits two of these)
+constexpr int WARP_BLOCKS_BYTES = 2 * 4096;   // per epilogue warp: two blocks of 32 rows x 128 bytes for TMA, 1024-byte aligned
+enum { STATUS_TIMEOUT_ROWS_PRODUCER = 5, STATUS_TIMEOUT_ROWS_MMA = 6, STATUS_TIMEOUT_ROWS_EPILOGUE = 7, STATUS_PAIR_TMEM_DIFFERS = 8 };
+
+
+template <int BN, int STAGES, bool PAIR>
+constexpr size_t rows_shared_bytes() {
+    // stages, the epilogue warps' turning blocks, barriers, a few words, two sets of cache offsets, two of biases
+    return (size_t)STAGES * (BM * BK * 2 + (PAIR ? BN / 2 : BN) * BK * 2) + 8 * WARP_BLOCKS_BYTES + (2 * STAGES + 4) * 8 + 16 +
+           2 * BM * 8 + 2 * 256 * 4 + 1024;
+}
+
+template <int BN, int STAGES, bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 const GemmParams p, const int tiles_m, const int n_tiles) {
+                 const __grid_constant__ CUtensorMap map_out, const GemmParams p, const int tiles_m, const int n_tiles) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    constexpr int B_ROWS = PAIR ? BN / 2 : BN;             // rows of W this CTA loads per block of K
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = B_ROWS * BK * 2;
+    constexpr int TILE_ROWS = PAIR ? 2 * BM : BM;          // tokens per tile (of the pair)
     constexpr int TMEM_COLS = BN <= 64 ? 128 : (BN <= 128 ? 256 : 512), ACC_STRIDE = TMEM_COLS / 2, CHUNKS = BN / 32;
     unsigned char* stage_a = smem;
     unsigned char* stage_b = smem + STAGES * A_BYTES;
     float* turn_all = reinterpret_cast<float*>(smem + STAGES * (A_BYTES + B_BYTES));
-    uint64_t* full = reinterpret_cast<uint64_t*>(turn_all + 8 * TURN_FLOATS);
+    uint64_t* full = reinterpret_cast<uint64_t*>(turn_all + 8 * WARP_BLOCKS_BYTES / 4);
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;        // [2]: the MMAs of a tile have finished
     uint64_t* acc_empty = acc_full + 2;         // [2]: the epilogue warps have read the tile out
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* tile_ok = reinterpret_cast<volatile int*>(tmem_slot + 2);     // [2], by the tile's parity
-    long* kv_off = reinterpret_cast<long*>(tmem_slot + 4);    // element offset of each of the tile's tokens in the cache pages
+    // by the tile's parity, so that a warp may start on the next tile while another finishes this one:
+    long* kv_off_all = reinterpret_cast<long*>(tmem_slot + 4);            // [2][128] element offset of each token in the cache pages
+    float* bias_all = reinterpret_cast<float*>(kv_off_all + 2 * BM);      // [2][256] the tile's biases (zeros without a bias)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_k = (p.K + BK - 1) / BK;
+    const bool stamps = p.timeline != nullptr && blockIdx.x == 0;
+    if (stamps && threadIdx.x == 0) p.timeline[0] = now_ns();
+    // A pair is the two CTAs of a cluster; it walks the tiles as one.
+    const uint32_t rank = PAIR ? cluster_cta_rank() : 0u;
+    const bool leader = rank == 0;
+    const int walker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int walkers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -398,7 +463,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         for (int a = 0; a < 2; a++) {
             mbar_init(&acc_full[a], 1);
-            mbar_init(&acc_empty[a], 8);         // one arrival per epilogue warp
+            mbar_init(&acc_empty[a], PAIR ? 16 : 8);     // one arrival per epilogue warp (of both CTAs, at the leader)
         }
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -406,6 +471,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (warp == 9) tmem_alloc(tmem_slot, TMEM_COLS);
     tcgen05_before_sync();
     __syncthreads();
+    if (PAIR) cluster_barrier();                 // the other CTA's barriers are initialised before anything arrives there
     tcgen05_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     auto give_up = [&](int code) {
@@ -414,12 +480,22 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             atomicExch(p.status, code);
         }
     };
+    if (PAIR) {
+        // An MMA of the pair writes the accumulator at one address in both CTAs' tensor
+        // memories: the two allocations must have given the same one.
+        if (threadIdx.x == 0 && load_u32_from_rank(tmem_slot, rank ^ 1u) != tmem_base) give_up(STATUS_PAIR_TMEM_DIFFERS);
+        cluster_barrier();                       // both CTAs know before either starts
+        if (threadIdx.x == 0 && leader && load_u32_from_rank(reinterpret_cast<const uint32_t*>(const_cast<const int*>(failed)), 1u) != 0u)
+            give_up(STATUS_PAIR_TMEM_DIFFERS);
+        __syncthreads();
+    }
 
+    if (stamps && threadIdx.x == 0) p.timeline[1] = now_ns();
     if (warp == 8) {
         // ---- producer: the ring runs on across tiles ----
         if (lane == 0) {
             int it = 0;
-            for (int tile = blockIdx.x; tile < n_tiles && !*failed; tile += gridDim.x) {
+            for (int tile = walker; tile < n_tiles && !*failed; tile += walkers) {
                 const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
                 for (int kb = 0; kb < num_k; kb++, it++) {
                     const int s = it % STAGES;
@@ -427,22 +503,30 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         give_up(STATUS_TIMEOUT_ROWS_PRODUCER);
                         break;
                     }
-                    mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-                    tma_load_2d(stage_a + s * A_BYTES, &map_a, &full[s], kb * BK, tile_m * BM);
-                    tma_load_2d(stage_b + s * B_BYTES, &map_b, &full[s], kb * BK, tile_n * BN);
+                    if (PAIR) {
+                        // both CTAs' bytes count on the leader's barrier, which expects them all
+                        const uint32_t bar = cluster_address_of(&full[s], 0);
+                        if (leader) mbar_expect_tx(&full[s], 2 * (A_BYTES + B_BYTES));
+                        tma_load_2d_pair(stage_a + s * A_BYTES, &map_a, bar, kb * BK, tile_m * TILE_ROWS + (int)rank * BM);
+                        tma_load_2d_pair(stage_b + s * B_BYTES, &map_b, bar, kb * BK, tile_n * BN + (int)rank * B_ROWS);
+                    } else {
+                        mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+                        tma_load_2d(stage_a + s * A_BYTES, &map_a, &full[s], kb * BK, tile_m * BM);
+                        tma_load_2d(stage_b + s * B_BYTES, &map_b, &full[s], kb * BK, tile_n * BN);
+                    }
                 }
             }
-            if (*failed) {
+            if (*failed && leader) {
                 // copies that were issued still land: wait for them (bounded) so that none is in flight at the end
                 for (int i = max(0, it - STAGES); i < it; i++) mbar_wait(&full[i % STAGES], (i / STAGES) & 1);
             }
         }
     } else if (warp == 9) {
         // ---- MMA issue: tile t into accumulator t % 2 ----
-        if (lane == 0) {
-            const uint32_t idesc = make_instr_desc(BM, BN);
+        if (lane == 0 && leader) {
+            const uint32_t idesc = make_instr_desc(TILE_ROWS, BN);
             int it = 0, local = 0;
-            for (int tile = blockIdx.x; tile < n_tiles && !*failed; tile += gridDim.x, local++) {
+            for (int tile = walker; tile < n_tiles && !*failed; tile += walkers, local++) {
                 const int acc = local & 1;
                 if (!mbar_wait(&acc_empty[acc], ((local >> 1) & 1) ^ 1) || *failed) {
                     give_up(STATUS_TIMEOUT_ROWS_MMA);
@@ -457,33 +541,47 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         break;
                     }
                     tcgen05_after_sync();
+                    if (stamps && it == 0) p.timeline[2] = now_ns();
                     const uint64_t desc_a = make_smem_desc(smem_u32(stage_a + s * A_BYTES));
                     const uint64_t desc_b = make_smem_desc(smem_u32(stage_b + s * B_BYTES));
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; k++)
-                        umma(tmem_acc, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                    umma_commit(&empty[s]);
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        if (PAIR) umma_pair(tmem_acc, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        else umma(tmem_acc, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    if (PAIR) umma_commit_pair(&empty[s]);
+                    else umma_commit(&empty[s]);
                 }
-                umma_commit(&acc_full[acc]);
+                if (PAIR) umma_commit_pair(&acc_full[acc]);
+                else umma_commit(&acc_full[acc]);
+                if (stamps && local == 0) p.timeline[3] = now_ns();
             }
         }
     } else {
         // ---- epilogue: warps w and w + 4 own TMEM lanes 32 (w % 4) .. +31 and take the tile's
         // blocks of 32 columns in turn ----
         const int quarter = warp & 3, col_half = warp >> 2;
-        float* turn = turn_all + warp * TURN_FLOATS;
+        float* turn = turn_all + warp * (WARP_BLOCKS_BYTES / 4);      // both blocks together hold a turned block too
+        int boxes = 0;                       // boxes this warp has sent: box b leaves from block b % 2
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
         int local = 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, local++) {
+        for (int tile = walker; tile < n_tiles; tile += walkers, local++) {
             const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
             const int acc = local & 1;
+            const int first_row = tile_m * TILE_ROWS + (int)rank * BM;      // this CTA's 128 tokens of the tile
+            long* kv_off = kv_off_all + acc * BM;
+            float* bias_s = bias_all + acc * 256;
             if (p.k_pages != nullptr && threadIdx.x < BM) {
-                const int t = tile_m * BM + threadIdx.x;
+                const int t = first_row + threadIdx.x;
                 if (t < p.M) {
                     const int pos = p.positions[t];
                     const int page = p.block_table[(long)p.token_item[t] * p.max_blocks + pos / p.page_size];
                     kv_off[threadIdx.x] = ((long)page * p.page_size + pos % p.page_size) * p.kv_width;
                 }
+            }
+            if (threadIdx.x < BN) {
+                const int n = tile_n * BN + threadIdx.x;
+                bias_s[threadIdx.x] = (p.bias != nullptr && n < p.N) ? p.bias[n] : 0.0f;
             }
             // One thread waits for the accumulator; all eight warps learn the outcome at one
             // barrier, so that they go on or leave together.
@@ -495,7 +593,8 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             asm volatile("bar.sync 1, 256;" ::: "memory");
             if (tile_ok[acc] == 0) break;
             tcgen05_after_sync();
-            const int row0 = tile_m * BM + quarter * 32;
+            if (stamps && local == 0 && threadIdx.x == 0) p.timeline[4] = now_ns();
+            const int row0 = first_row + quarter * 32;
             const uint32_t acc_base = lane_base + (uint32_t)(acc * ACC_STRIDE);
 #pragma unroll 1
             for (int c = col_half; c < CHUNKS; c += 2) {
@@ -504,12 +603,63 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 float v[32];
                 __syncwarp();
                 tmem_load_32(acc_base + c0, v);
+                const float* bs = bias_s + c0;
+                const bool whole = n0 + 32 <= p.N;
+                // Where the block of 32 x 32 goes.  A block of `out` leaves through shared memory
+                // and one TMA box (stored, or added to what is there: the residual sum) when the
+                // tensor is laid out for it.  A block of keys or values goes to scattered cache
+                // slots: each thread stores its own row's 64 bytes from its registers.  Whatever
+                // is laid out for neither is turned through shared memory, so that consecutive
+                // lanes write consecutive columns.
+                const bool wide = p.epilogue == EPI_ADD || p.out_f32;
+                const int region = wide || p.k_pages == nullptr || n0 < p.q_width ? 0 : (n0 < p.q_width + p.kv_width ? 1 : 2);
+                if (region == 0 && p.out_by_tma) {
+                    if (row0 >= p.M) continue;
+                    if (lane == 0) bulk_wait_read_but_one();     // the box before the last one has left its block
+                    __syncwarp();
+                    unsigned char* mine = reinterpret_cast<unsigned char*>(turn) + (boxes & 1) * 4096;
+                    boxes++;
+                    const uint32_t bias32 = smem_u32(bs), block = smem_u32(mine);
+                    if (wide) stage_row_f32(v, bias32, block, lane);
+                    else if (p.epilogue == EPI_GELU_TANH) stage_row_bf16<EPI_GELU_TANH>(v, bias32, block, lane);
+                    else if (p.epilogue == EPI_GELU_ERF) stage_row_bf16<EPI_GELU_ERF>(v, bias32, block, lane);
+                    else stage_row_bf16<EPI_STORE>(v, bias32, block, lane);
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (p.epilogue == EPI_ADD) tma_reduce_add_2d(&map_out, mine, n0, row0);
+                        else tma_store_2d(&map_out, mine, n0, row0);
+                        bulk_commit();
+                    }
+                    continue;
+                }
+                if (region != 0 && whole && (p.kv_width & 7) == 0 &&
+                    (reinterpret_cast<uintptr_t>(region == 1 ? p.k_pages : p.v_pages) & 15) == 0) {
+                    // Keys or values: the block is staged as bfloat16 like a box, then four lanes
+                    // write one row's 64 bytes to its cache slot, eight rows per instruction.
+                    if (lane == 0) bulk_wait_read();
+                    __syncwarp();
+                    const uint32_t block = smem_u32(turn);
+                    stage_row_bf16<EPI_STORE>(v, smem_u32(bs), block, lane);
+                    __syncwarp();
+                    bf16* pages = region == 1 ? p.k_pages + (n0 - p.q_width) : p.v_pages + (n0 - p.q_width - p.kv_width);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int row = i * 8 + (lane >> 2), piece = lane & 3;
+                        const float4 x = lds128(block + row * 64 + ((piece ^ ((row >> 1) & 3)) << 4));
+                        if (row0 + row < p.M)
+                            *reinterpret_cast<float4*>(pages + kv_off[quarter * 32 + row] + piece * 8) = x;
+                    }
+                    continue;
+                }
+                if (lane == 0) bulk_wait_read();             // (a box may still be leaving the block)
+                __syncwarp();
 #pragma unroll
                 for (int i = 0; i < 32; i++) turn[lane * 33 + i] = v[i];
                 __syncwarp();
                 const int n = n0 + lane;
                 const bool col_ok = n < p.N;
-                const float b = (col_ok && p.bias != nullptr) ? p.bias[n] : 0.0f;
+                const float b = col_ok ? bs[lane] : 0.0f;
                 if (p.epilogue == EPI_ADD) {
                     float* o = reinterpret_cast<float*>(p.out) + (long)row0 * p.ldo + n;
 #pragma unroll 1
@@ -526,37 +676,41 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 } else if (p.out_f32) {
                     float* o = reinterpret_cast<float*>(p.out) + (long)row0 * p.ldo + n;
 #pragma unroll 4
-                    for (int r = 0; r < 32; r++)
-                        if (col_ok && row0 + r < p.M) o[(long)r * p.ldo] = turn[r * 33 + lane] + b;
+                    for (int rr = 0; rr < 32; rr++)
+                        if (col_ok && row0 + rr < p.M) o[(long)rr * p.ldo] = turn[rr * 33 + lane] + b;
                 } else {
                     // bfloat16: rows of the output, or (scatter) slots of the cache pages
-                    const int region = p.k_pages == nullptr || n0 < p.q_width ? 0 : (n0 < p.q_width + p.kv_width ? 1 : 2);
                     bf16* const region_base = region == 0 ? reinterpret_cast<bf16*>(p.out) + (long)row0 * p.ldo + n0
                                               : (region == 1 ? p.k_pages + (n0 - p.q_width)
                                                              : p.v_pages + (n0 - p.q_width - p.kv_width));
-                    const bool paired = n0 + 32 <= p.N && (p.ldo & 1) == 0 && (p.kv_width & 1) == 0 &&
+                    const bool paired = whole && (p.ldo & 1) == 0 && (p.kv_width & 1) == 0 &&
                                         (reinterpret_cast<uintptr_t>(region_base) & 3) == 0;
                     const long ldo = p.ldo;
                     const long* slots = kv_off + quarter * 32;
                     if (region == 0)
-                        store_rows_bf16(turn, region_base, [ldo](int r) { return (long)r * ldo; }, paired, col_ok, lane,
+                        store_rows_bf16(turn, region_base, [ldo](int rr) { return (long)rr * ldo; }, paired, col_ok, lane,
                                         p.M - row0, p.bias != nullptr ? p.bias + n0 : nullptr, p.epilogue);
                     else
-                        store_rows_bf16(turn, region_base, [slots](int r) { return slots[r]; }, paired, col_ok, lane,
+                        store_rows_bf16(turn, region_base, [slots](int rr) { return slots[rr]; }, paired, col_ok, lane,
                                         p.M - row0, p.bias != nullptr ? p.bias + n0 : nullptr, p.epilogue);
                 }
             }
             // the accumulator may be overwritten once every warp has read its part
             tcgen05_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[acc]);
-            // the next tile's cache offsets wait until every warp is done with this tile's
-            if (p.k_pages != nullptr) asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (lane == 0) {
+                if (PAIR) mbar_arrive_cluster(cluster_address_of(&acc_empty[acc], 0));
+                else mbar_arrive(&acc_empty[acc]);
+            }
+            if (stamps && local == 0 && threadIdx.x == 0) p.timeline[5] = now_ns();
         }
+        if (lane == 0) bulk_wait_done();         // this warp's boxes have arrived before the kernel ends
     }
 
     tcgen05_before_sync();
     __syncthreads();
+    if (PAIR) cluster_barrier();                 // neither CTA frees or leaves while the other may still use it
+    if (stamps && threadIdx.x == 0) p.timeline[6] = now_ns();
     if (warp == 9) tmem_free(tmem_base, TMEM_COLS);
 }
 
@@ -572,7 +726,7 @@ std::mutex g_lock;
 struct MapKey {
     const void* base;
     long rows, cols, ld;
-    int box_rows;
+    int box_rows;             // operands: rows of a box of 64 bf16 columns; results: -2 (bf16) or -4 (fp32), boxes of 32 x 32
     bool operator==(const MapKey& o) const {
         return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
     }
@@ -657,20 +811,70 @@ int launch_swapped(const CUtensorMap& a, const CUtensorMap& b, const GemmParams&
     return check_launch("gemm_swapped_kernel");
 }
 
-template <int BN, int STAGES>
-int launch_rows(const CUtensorMap& a, const CUtensorMap& b, const GemmParams& p, int sms, cudaStream_t s) {
-    constexpr size_t smem = rows_shared_bytes<BN, STAGES>();
+// The map of a result [rows, cols] (bfloat16 or fp32, row stride ld elements) for boxes of 32
+// rows x 32 columns, rows of 64 or 128 bytes in shared memory with the swizzle of that width.  Returns 1 (no error text) if the
+// tensor is not laid out for TMA: a base or a row stride off 16-byte boundaries.
+int output_map(const void* base, long rows, long cols, long ld, bool f32, CUtensorMap* out) {
+    const int elem = f32 ? 4 : 2;
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * elem) % 16 != 0 || g_encode == nullptr) return 1;
+    std::lock_guard<std::mutex> guard(g_lock);
+    MapKey key{base, rows, cols, ld, f32 ? -4 : -2};
+    auto found = g_maps.find(key);
+    if (found != g_maps.end()) {
+        *out = found->second;
+        return 0;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * elem};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t step[2] = {1, 1};
+    CUresult r = g_encode(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                          const_cast<void*>(base), dims, strides, box, step, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          f32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return 1;
+    if (g_maps.size() > 4096) g_maps.clear();
+    g_maps.emplace(key, *out);
+    return 0;
+}
+
+template <int BN, int STAGES, bool PAIR>
+int launch_rows(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& o, const GemmParams& p, int sms,
+                cudaStream_t s) {
+    constexpr size_t smem = rows_shared_bytes<BN, STAGES, PAIR>();
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(gemm_rows_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-            cudaSuccess)
+        if (cudaFuncSetAttribute(gemm_rows_kernel<BN, STAGES, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess)
             return fail("gemm: cannot raise the shared memory limit");
         configured = true;
     }
-    const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+    const int tile_rows = PAIR ? 2 * BM : BM;
+    const int tiles_m = (p.M + tile_rows - 1) / tile_rows, tiles_n = (p.N + BN - 1) / BN;
     const int n_tiles = tiles_m * tiles_n;
-    gemm_rows_kernel<BN, STAGES><<<std::min(n_tiles, sms), THREADS, smem, s>>>(a, b, p, tiles_m, n_tiles);
-    return check_launch("gemm_rows_kernel");
+    if (!PAIR) {
+        gemm_rows_kernel<BN, STAGES, PAIR><<<std::min(n_tiles, sms), THREADS, smem, s>>>(a, b, o, p, tiles_m, n_tiles);
+        return check_launch("gemm_rows_kernel");
+    }
+    // two CTAs per tile: a cluster of two
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2 * std::min(n_tiles, sms / 2));
+    config.blockDim = dim3(THREADS);
+    config.dynamicSmemBytes = smem;
+    config.stream = s;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = 2;
+    attribute.val.clusterDim.y = 1;
+    attribute.val.clusterDim.z = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&config, gemm_rows_kernel<BN, STAGES, PAIR>, a, b, o, p, tiles_m, n_tiles);
+    if (e != cudaSuccess) {
+        snprintf(g_error_text, MLLM_ERROR_BUFFER, "gemm_rows_kernel (pairs): %s", cudaGetErrorString(e));
+        return 2;
+    }
+    return 0;
 }
 
 }  // namespace
@@ -733,14 +937,15 @@ static int rows_tile_width(int M, int N, int K, int sms) {
 }
 
 static int gemm_bf16(void* out, const void* x, const void* w, const float* bias, int M, int N, int K, long ldx, long ldo,
-                     int epilogue, int out_f32, int* status, const GemmScatter* scatter, void* stream, int forced_bn) {
+                     int epilogue, int out_f32, int* status, const GemmScatter* scatter, void* stream, int forced_bn,
+                     unsigned long long* timeline = nullptr) {
     if (M <= 0 || N <= 0) return 0;
     if (!mllm_gemm_takes(K, ldx, x, w)) return fail("gemm: K and the row stride of x must be multiples of 8, bases 16-byte aligned");
     if (epilogue == EPI_ADD && !out_f32) return fail("gemm: the residual sum is kept in 32-bit");
     if (status == nullptr) return fail("gemm: a status word is required");
     cudaStream_t s = (cudaStream_t)stream;
     GemmParams p{out, bias, status, M, N, K, ldo, epilogue, out_f32, 1,
-                 nullptr, nullptr, nullptr, nullptr, nullptr, 0, 1, 0, 0};
+                 nullptr, nullptr, nullptr, nullptr, nullptr, 0, 1, 0, 0, timeline, 0};
     if (scatter != nullptr) {
         if (out_f32 || epilogue != EPI_STORE) return fail("gemm: the scatter goes with a plain bfloat16 store");
         if (scatter->q_width % 32 != 0 || scatter->kv_width % 32 != 0 || scatter->q_width + 2 * scatter->kv_width != N ||
@@ -760,17 +965,28 @@ static int gemm_bf16(void* out, const void* x, const void* w, const float* bias,
     const int sms = sm_count();
     const bool swap = M <= 64 && forced_bn == 0;
     if (!swap) {
-        const int bn = forced_bn != 0 ? forced_bn : rows_tile_width(M, N, K, sms);
+        // a tile: 128 tokens x bn features on one CTA, or (code 1000 + bn) 256 tokens x bn on a pair of CTAs
+        const int code = forced_bn != 0 ? forced_bn : rows_tile_width(M, N, K, sms);
+        const bool pair = code >= 1000;
+        const int bn = pair ? code - 1000 : code;
         int rc = tensor_map(x, M, K, ldx, BM, &map_x);
         if (rc) return rc;
-        rc = tensor_map(w, N, K, K, bn, &map_w);
+        rc = tensor_map(w, N, K, K, pair ? bn / 2 : bn, &map_w);
         if (rc) return rc;
-        switch (bn) {
-        case 256: return launch_rows<256, 3>(map_x, map_w, p, sms, s);
-        case 192: return launch_rows<192, 4>(map_x, map_w, p, sms, s);
-        case 128: return launch_rows<128, 5>(map_x, map_w, p, sms, s);
-        case 96: return launch_rows<96, 6>(map_x, map_w, p, sms, s);
-        case 64: return launch_rows<64, 6>(map_x, map_w, p, sms, s);
+        // results leave by TMA when `out` is laid out for it (with the scatter, out is [M, q_width])
+        CUtensorMap map_out = map_x;
+        p.out_by_tma = output_map(out, M, scatter != nullptr ? scatter->q_width : N, ldo, out_f32 != 0, &map_out) == 0;
+        switch (code) {
+        case 256: return launch_rows<256, 3, false>(map_x, map_w, map_out, p, sms, s);
+        case 192: return launch_rows<192, 3, false>(map_x, map_w, map_out, p, sms, s);
+        case 128: return launch_rows<128, 4, false>(map_x, map_w, map_out, p, sms, s);
+        case 96: return launch_rows<96, 5, false>(map_x, map_w, map_out, p, sms, s);
+        case 64: return launch_rows<64, 6, false>(map_x, map_w, map_out, p, sms, s);
+        case 1256: return launch_rows<256, 4, true>(map_x, map_w, map_out, p, sms, s);
+        case 1192: return launch_rows<192, 5, true>(map_x, map_w, map_out, p, sms, s);
+        case 1128: return launch_rows<128, 6, true>(map_x, map_w, map_out, p, sms, s);
+        case 1096: return launch_rows<96, 6, true>(map_x, map_w, map_out, p, sms, s);
+        case 1064: return launch_rows<64, 6, true>(map_x, map_w, map_out, p, sms, s);
         default: return fail("gemm: the tile width is 64, 96, 128, 192 or 256");
         }
     }
@@ -807,10 +1023,11 @@ extern "C" int mllm_gemm_bf16(void* out, const void* x, const void* w, const flo
 // partly empty, and for measurements of the widths against each other.
 extern "C" int mllm_gemm_bf16_tile(void* out, const void* x, const void* w, const float* bias, int M, int N, int K,
                                    long ldx, long ldo, int epilogue, int out_f32, int* status, int tile_width,
-                                   void* stream) {
-    if (tile_width != 64 && tile_width != 96 && tile_width != 128 && tile_width != 192 && tile_width != 256)
+                                   unsigned long long* timeline, void* stream) {
+    const int width = tile_width >= 1000 ? tile_width - 1000 : tile_width;       // 1000 + width: on a pair of CTAs
+    if (width != 64 && width != 96 && width != 128 && width != 192 && width != 256)
         return fail("gemm: the tile width is 64, 96, 128, 192 or 256");
-    return gemm_bf16(out, x, w, bias, M, N, K, ldx, ldo, epilogue, out_f32, status, nullptr, stream, tile_width);
+    return gemm_bf16(out, x, w, bias, M, N, K, ldx, ldo, epilogue, out_f32, status, nullptr, stream, tile_width, timeline);
 }
 
 // The fused query/key/value product of a layer: out [M, q_width] gets the queries; keys and

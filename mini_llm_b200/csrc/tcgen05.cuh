@@ -182,3 +182,94 @@ __device__ __forceinline__ void tcgen05_before_sync() { asm volatile("tcgen05.fe
 __device__ __forceinline__ void tcgen05_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 // Make shared-memory writes of this thread visible to the tensor core and TMA (async proxy).
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// ---- two CTAs on one tile (cta_group::2) ---------------------------------------------------
+//
+// The two CTAs of a cluster of two form a pair: the even one (the leader) issues every
+// tcgen05.mma, which multiplies 256 rows: each CTA holds its own 128 rows of A and its own
+// half of the columns of B in its shared memory, at the same offsets, and gets its own 128
+// rows of the accumulator in its own tensor memory.  Each CTA loads its operands itself (no
+// multicast: every TMA load brings one box into the shared memory of the CTA that issued
+// it); the loads of both CTAs complete on the LEADER's barrier, which the `.cta_group::2`
+// form of the copy allows.  tcgen05.commit arrives on the barrier at the same offset in both
+// CTAs.  Each CTA allocates its own tensor memory (the same number of columns from an empty
+// tensor memory gives the same address in both; the kernel checks that it does).
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// The address, in the cluster's shared window, of what `local` is in CTA `rank`.
+__device__ __forceinline__ uint32_t cluster_address_of(const void* local, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    return remote;
+}
+
+__device__ __forceinline__ void cluster_barrier() {         // by every thread of both CTAs
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// One box into this CTA's shared memory; the bytes count on the barrier at cluster address
+// `bar_cluster`, which may lie in the other CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {         // by one thread of the leader
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Arrives, once the MMAs issued so far have finished, on the barrier at `bar`'s offset in
+// both CTAs of the pair.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(both)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+
+__device__ __forceinline__ uint32_t load_u32_from_rank(const uint32_t* local, uint32_t rank) {
+    uint32_t v;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_address_of(local, rank)) : "memory");
+    return v;
+}
+
+// ---- results back to global memory by TMA -------------------------------------------------
+// A box of shared memory (written by this warp, then fence_async_smem() and __syncwarp())
+// goes to the tensor at (x, y); what lies outside the tensor is left out.  One thread issues.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(src)), "r"(x), "r"(y)
+                 : "memory");
+}
+
+// The same, added to what the tensor holds (one addition per element, done at the memory).
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* src, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(src)), "r"(x), "r"(y)
+                 : "memory");
+}
+
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// The issuing thread's earlier boxes have been read out of shared memory (it may be written again);
+// the second form leaves the latest box alone.
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+// The issuing thread's earlier boxes have arrived in global memory.
+__device__ __forceinline__ void bulk_wait_done() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }

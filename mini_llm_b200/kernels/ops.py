@@ -418,13 +418,20 @@ def gemm_bf16(out, a, w, bias, epilogue, status):
     return out
 
 
-_gemm_bf16_tile = Function("gemm", "mllm_gemm_bf16_tile", [P, P, P, P, I, I, I, L, L, I, I, P, I, P])
-GEMM_TILE_WIDTHS = (64, 96, 128, 192, 256)
+_gemm_bf16_tile = Function("gemm", "mllm_gemm_bf16_tile", [P, P, P, P, I, I, I, L, L, I, I, P, I, P, P])
+GEMM_TILE_WIDTHS = (64, 96, 128, 192, 256)        # 1000 + width: tiles of 256 tokens on pairs of CTAs
 
 
-def gemm_bf16_tile(out, a, w, bias, epilogue, status, tile_width):
+def gemm_bf16_tile(out, a, w, bias, epilogue, status, tile_width, timeline=None):
     """``gemm_bf16`` through the persistent kernel with tiles of 128 x ``tile_width``, whatever
-    the number of rows (tests run every width; the engine lets the library choose)."""
+    the number of rows (tests run every width; the engine lets the library choose).
+    ``timeline``: an int64 device tensor of seven entries that receives time stamps of CTA 0
+    (start, set-up done, first operands landed, last product of the first tile issued, first
+    accumulator ready, first epilogue done, end), in nanoseconds."""
+    if timeline is not None:
+        _check(timeline, "gemm.timeline", torch.int64, 1)
+        if timeline.shape[0] < 7:
+            raise KernelError("gemm: the timeline has seven entries")
     _check(a, "gemm.a", torch.bfloat16, 2)
     _check(w, "gemm.w", torch.bfloat16, 2)
     _check(out, "gemm.out", None, 2)
@@ -438,7 +445,8 @@ def gemm_bf16_tile(out, a, w, bias, epilogue, status, tile_width):
     if bias is not None:
         _check(bias, "gemm.bias", torch.float32, 1)
     _gemm_bf16_tile(out.data_ptr(), a.data_ptr(), w.data_ptr(), _ptr(bias), m, n, k, a.stride(0), out.stride(0),
-                    EPILOGUES[epilogue], int(out.dtype == torch.float32), status.data_ptr(), int(tile_width), _stream())
+                    EPILOGUES[epilogue], int(out.dtype == torch.float32), status.data_ptr(), int(tile_width),
+                    _ptr(timeline), _stream())
     return out
 
 

@@ -483,13 +483,15 @@ def test_gemm_tcgen05(m, n, k, epilogue):
     np.testing.assert_allclose(f64(out), expected, rtol=0, atol=atol)
 
 
-@pytest.mark.parametrize("width", [64, 96, 128, 192, 256])
+@pytest.mark.parametrize("width", [64, 96, 128, 192, 256, 1064, 1096, 1128, 1192, 1256])
 @pytest.mark.parametrize("m, n, k, epilogue", [(300, 1000, 160, "gelu_tanh"), (513, 768, 3072, "add"), (17, 777, 96, "store"),
                                                (2048, 2304, 768, "store"), (4000, 1100, 72, "add"), (129, 50257, 64, "logits"),
                                                (2100, 3072, 256, "gelu_erf")])
 def test_gemm_tcgen05_every_tile_width(m, n, k, epilogue, width):
-    """The persistent kernel at each of its tile widths: tiles that are partly empty in rows
-    and in columns, one tile for some CTAs and a dozen for others (so that both accumulators
+    """The persistent kernel at each of its tile widths, on single CTAs (128 tokens a tile) and
+    on pairs of CTAs (1000 + width: 256 tokens a tile, each CTA loading half of the tile's
+    block of W): tiles that are partly empty in rows and in columns, a pair whose second CTA
+    has no rows at all, one tile for some CTAs and a dozen for others (so that both accumulators
     and every phase of the ring are in use), every epilogue; bitwise the same result twice."""
     from mini_llm_b200.kernels import ops
     rng = np.random.default_rng(m + n + k + width)
@@ -731,3 +733,20 @@ def test_gemm_tcgen05_scatters_keys_and_values_into_the_pages(m, q_width, kv_wid
         want_v[pg, positions[t] % page] = expected[t, q_width + kv_width:]
     np.testing.assert_allclose(f64(k_pages), want_k, rtol=0, atol=atol)
     np.testing.assert_allclose(f64(v_pages), want_v, rtol=0, atol=atol)
+
+
+def test_gemm_tcgen05_time_stamps():
+    """The persistent kernel can note when its first CTA passed seven points (start, set-up,
+    first operands, last product of the first tile, accumulator ready, first epilogue done,
+    end): the stamps come in that order and span less than a millisecond."""
+    from mini_llm_b200.kernels import ops
+    a = torch.randn(600, 256, device="cuda").bfloat16()
+    w = (torch.randn(512, 256, device="cuda") / 16).bfloat16()
+    out = torch.empty(600, 512, device="cuda", dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stamps = torch.zeros(7, dtype=torch.int64, device="cuda")
+    ops.gemm_bf16_tile(out, a, w, None, "store", status, 128, stamps)
+    torch.cuda.synchronize()
+    times = stamps.tolist()
+    assert int(status.item()) == 0 and all(b >= a for a, b in zip(times, times[1:])) and 0 < times[6] - times[0] < 1_000_000
+    np.testing.assert_allclose(f64(out), f64(a) @ f64(w).T, rtol=0, atol=tol(torch.bfloat16, 4))
