@@ -262,7 +262,7 @@ def serving_run(folder, args, vocab: int):
     llm = LLM(folder, dtype=args.dtype, max_sessions=32, cache_tokens=24 * 1024, max_tokens_per_step=512,
               max_prefill_chunk=512, plain_kernels=args.plain_kernels)
     best = 0.0
-    for _ in range(2):                                   # the second pass finds its step shapes captured
+    for _ in range(3):                                   # later passes find their step shapes captured
         requests = [Request(p, n, None, 0.8, 0.95, 100 + i) for i, (p, n) in enumerate(zip(prompts, lengths))]
         torch.cuda.synchronize()
         start = time.perf_counter()

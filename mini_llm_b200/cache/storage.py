@@ -59,11 +59,14 @@ class CacheStorage:
         self.device = device
         self.max_items = int(max_items)
         self.poison = poison
+        self.spare_page = True                # every pool has a page past its last (index n_pages)
         self.keys, self.values, self.states, self.block_tables = {}, {}, {}, {}
         for group in manager.groups:
             n_entries = len(group.entries)
             if isinstance(group.need, PagedKV):
-                shape = (n_entries, max(group.pool.n_pages, 1), manager.page_size, group.need.n_kv_heads,
+                # one page beyond the pool's last: no request ever owns it; steps that are filled up
+                # to a round shape let their filler tokens store there
+                shape = (n_entries, group.pool.n_pages + 1, manager.page_size, group.need.n_kv_heads,
                          group.need.head_size)
                 fill = 0.0 if poison is None else poison
                 self.keys[group.index] = torch.full(shape, fill, dtype=dtype, device=device)

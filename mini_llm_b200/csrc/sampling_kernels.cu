@@ -84,11 +84,16 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 // reaches top_p, ties at its edge included: tokens with p >= t*, where t* is
 // the largest t with sum_{p_v >= t} p_v >= top_p, found by bisection on the
 // bit pattern of t.
+// With `cached` the row's probabilities are computed once into dynamic shared memory (vocab
+// floats) and the bisection's thirty passes read them there: the same values, compared and
+// summed in the same order as without, so the draw is bit for bit the same; it only stops
+// costing thirty passes of exponentials over global memory.
 __global__ void __launch_bounds__(1024)
 sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, long ld, int vocab,
                    const float* __restrict__ temperature, const float* __restrict__ top_p,
                    const unsigned long long* __restrict__ seeds, const int* __restrict__ counters,
-                   int only_nucleus) {
+                   int only_nucleus, int cached) {
+    extern __shared__ float probs[];
     __shared__ float sv[33];
     __shared__ int si[32];
     int r = blockIdx.x;
@@ -118,16 +123,29 @@ sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, long
         for (int v = threadIdx.x; v < vocab; v += blockDim.x) mx = fmaxf(mx, x[v]);
         big = block_max(mx, sv);
         float sum = 0.0f;
-        for (int v = threadIdx.x; v < vocab; v += blockDim.x) sum += expf((x[v] - big) * inv_t);
+        for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
+            const float e = expf((x[v] - big) * inv_t);
+            if (cached) probs[v] = e;
+            sum += e;
+        }
         z = block_sum(sum, sv);
+        if (cached)
+            for (int v = threadIdx.x; v < vocab; v += blockDim.x) probs[v] = probs[v] / z;      // each thread its own entries
         unsigned lo = 0u, hi = 0x3f800000u;      // bit patterns of 0.0f and 1.0f
         while (lo < hi) {
             unsigned mid = lo + (hi - lo + 1u) / 2u;
             float t = __uint_as_float(mid);
             float mass = 0.0f;
-            for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
-                float pv = expf((x[v] - big) * inv_t) / z;
-                if (pv >= t) mass += pv;
+            if (cached) {
+                for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
+                    const float pv = probs[v];
+                    if (pv >= t) mass += pv;
+                }
+            } else {
+                for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
+                    float pv = expf((x[v] - big) * inv_t) / z;
+                    if (pv >= t) mass += pv;
+                }
             }
             mass = block_sum(mass, sv);
             if (mass >= nucleus) lo = mid; else hi = mid - 1u;
@@ -139,7 +157,7 @@ sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, long
     unsigned counter = counters ? (unsigned)counters[r] : 0u;
     for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
         float xv = x[v];
-        if (nucleus < 1.0f && !(expf((xv - big) * inv_t) / z >= cut)) continue;
+        if (nucleus < 1.0f && !((cached ? probs[v] : expf((xv - big) * inv_t) / z) >= cut)) continue;
         float u = uniform_of(seed, counter, (unsigned)v);
         float score = xv * inv_t - logf(-logf(u));
         if (better(score, v, best, best_i)) { best = score; best_i = v; }
@@ -208,6 +226,32 @@ sample_rows_sliced_kernel(int* __restrict__ out, const float* __restrict__ logit
     if (threadIdx.x == 0) out[r] = i;
 }
 
+// Launches the one-block-per-row kernel, with the row's probabilities kept in shared memory
+// when the vocabulary fits there.
+static int launch_sample_rows(int* out, const float* logits, long ld, int n_rows, int vocab, const float* temperature,
+                              const float* top_p, const unsigned long long* seeds, const int* counters, int only_nucleus,
+                              cudaStream_t s) {
+    static int smem_limit = -1;
+    if (smem_limit < 0) {
+        int device = 0, optin = 0;
+        cudaFuncAttributes attributes;
+        if (cudaGetDevice(&device) == cudaSuccess &&
+            cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) == cudaSuccess &&
+            cudaFuncGetAttributes(&attributes, sample_rows_kernel) == cudaSuccess) {
+            const int room = optin - (int)attributes.sharedSizeBytes - 1024;
+            smem_limit = (room > 0 && cudaFuncSetAttribute(sample_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                           room) == cudaSuccess) ? room : 0;
+        } else {
+            smem_limit = 0;
+        }
+        cudaGetLastError();
+    }
+    const bool cached = top_p != nullptr && (long)vocab * 4 <= (long)smem_limit;
+    sample_rows_kernel<<<n_rows, 1024, cached ? (size_t)vocab * 4 : 0, s>>>(out, logits, ld, vocab, temperature, top_p, seeds,
+                                                                           counters, only_nucleus, cached ? 1 : 0);
+    return check_launch("sample_rows_kernel");
+}
+
 // any_nucleus: some row has temperature > 0 and top_p < 1 (the host knows); those rows are
 // then drawn by the one-block kernel, which skips all others.
 extern "C" int mllm_sampling_sample_rows_sliced(int* out, const float* logits, long ld, int n_rows, int vocab,
@@ -220,10 +264,9 @@ extern "C" int mllm_sampling_sample_rows_sliced(int* out, const float* logits, l
     cudaStream_t s = (cudaStream_t)stream;
     sample_rows_sliced_kernel<<<dim3(n_rows, SAMPLE_SLICES), 256, 0, s>>>(out, logits, ld, vocab, temperature, top_p,
                                                                          seeds, counters, part_value, part_index, done);
-    if (any_nucleus) {
-        sample_rows_kernel<<<n_rows, 1024, 0, s>>>(out, logits, ld, vocab, temperature, top_p, seeds, counters, 1);
-    }
-    return check_launch("sample_rows_sliced_kernel");
+    int rc = check_launch("sample_rows_sliced_kernel");
+    if (rc == 0 && any_nucleus) rc = launch_sample_rows(out, logits, ld, n_rows, vocab, temperature, top_p, seeds, counters, 1, s);
+    return rc;
 }
 
 // Only the rows with a nucleus cut (temperature > 0 and top_p < 1); every other row of
@@ -232,9 +275,7 @@ extern "C" int mllm_sampling_sample_rows_nucleus(int* out, const float* logits, 
                                                  const float* temperature, const float* top_p,
                                                  const unsigned long long* seeds, const int* counters, void* stream) {
     if (n_rows <= 0) return 0;
-    sample_rows_kernel<<<n_rows, 1024, 0, (cudaStream_t)stream>>>(out, logits, ld, vocab, temperature, top_p, seeds,
-                                                                  counters, 1);
-    return check_launch("sample_rows_kernel");
+    return launch_sample_rows(out, logits, ld, n_rows, vocab, temperature, top_p, seeds, counters, 1, (cudaStream_t)stream);
 }
 
 extern "C" int mllm_sampling_sample_rows(int* out, const float* logits, long ld, int n_rows, int vocab,
@@ -242,9 +283,7 @@ extern "C" int mllm_sampling_sample_rows(int* out, const float* logits, long ld,
                                          const unsigned long long* seeds, const int* counters, void* stream) {
     if (n_rows <= 0) return 0;
     if (vocab <= 0) return fail("sample_rows: empty vocabulary");
-    sample_rows_kernel<<<n_rows, 1024, 0, (cudaStream_t)stream>>>(out, logits, ld, vocab, temperature, top_p,
-                                                                  seeds, counters, 0);
-    return check_launch("sample_rows_kernel");
+    return launch_sample_rows(out, logits, ld, n_rows, vocab, temperature, top_p, seeds, counters, 0, (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------

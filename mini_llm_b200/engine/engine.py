@@ -110,6 +110,8 @@ class Engine:
         self._sampled_events = [torch.cuda.Event(), torch.cuda.Event()]  # a step's sampling is done
         self._graphs = {}
         self._graph_stamp = None
+        self.step_kinds = {"one_kernel": 0, "eager": 0, "captured": 0, "replayed": 0}      # how steps ran
+        self._can_pad = self.storage.spare_page          # steps may be filled up to round shapes (see _step_reserved)
         self.fused, self.fused_reason = (FusedDecodePlan.build(self) if fused_decode
                                          else (None, "switched off by the caller"))
         if self.fused is None and fused_decode and self.dtype == torch.bfloat16 and not self.kernels.plain_only:
@@ -290,11 +292,7 @@ class Engine:
                 ctx.item_counts.append(n)
                 ctx.item_offsets.append(row)
                 row += n
-        arrays = {"token_ids": token_ids, "positions": positions, "token_item": token_item, "want_rows": want_rows,
-                  "want_slots": want_slots}
-        for group in self.cache.groups:
-            if group.paged:
-                arrays[("block_table", group.index)] = group.table[ctx.item_slots]
+        tables = {group.index: group.table[ctx.item_slots] for group in self.cache.groups if group.paged}
         # A step of single tokens of few requests goes to the decode attention, which takes no
         # work list: none is made for it.
         decode_only = n_tokens == n_items
@@ -302,12 +300,55 @@ class Engine:
             tiles, n_split, most_parts = [], 0, 1
         else:
             tiles, n_split, most_parts = ops.attention_tiles(ctx.item_offsets, ctx.item_counts, ctx.item_starts)
-        arrays["att_tiles"] = np.array(tiles, dtype=np.int32)
+        temperature = top_p = seeds = counters = None
         if sampling is not None:
-            arrays["temperature"] = np.array([s.temperature for s in sampling], dtype=np.float32)
-            arrays["top_p"] = np.array([s.top_p for s in sampling], dtype=np.float32)
-            arrays["seeds"] = np.array([s.seed & 0xFFFFFFFFFFFFFFFF for s in sampling], dtype=np.uint64)
-            arrays["counters"] = np.array([s.counter for s in sampling], dtype=np.int32)
+            temperature = np.array([s.temperature for s in sampling], dtype=np.float32)
+            top_p = np.array([s.top_p for s in sampling], dtype=np.float32)
+            seeds = np.array([s.seed & 0xFFFFFFFFFFFFFFFF for s in sampling], dtype=np.uint64)
+            counters = np.array([s.counter for s in sampling], dtype=np.int32)
+        n_real_want = n_want
+        if (not decode_only and not dump_hidden and self.cuda_graphs and self.model.graph_safe
+                and n_want <= n_tokens and self._can_pad):
+            # Steps with prompt portions come in endless shapes, and a captured graph serves one
+            # shape.  So such a step is filled up to a round shape: tokens of a request that does
+            # not exist (id 0 at position 0; its block table names the spare page that every
+            # pool has beyond its last) bring the token count to a multiple of 64 (128 past 512
+            # tokens), the entries to a multiple of 8, the wanted rows to a multiple of 8 (more
+            # rows of the filler, drawn greedily and kept for no request), the attention work
+            # list to a multiple of 4 (more tiles of the filler's first row).  Rows never mix, so
+            # the real rows' results are what they would be alone; steps of one round shape
+            # replay one graph.
+            step = 64 if n_tokens < 512 else 128
+            filled = -(-(n_tokens + 1) // step) * step
+            extra = filled - n_tokens
+            token_ids = np.concatenate([token_ids, np.zeros(extra, dtype=np.int32)])
+            positions = np.concatenate([positions, np.zeros(extra, dtype=np.int32)])
+            token_item = np.concatenate([token_item, np.full(extra, n_items, dtype=np.int32)])
+            items_filled = -(-(n_items + 1) // 8) * 8
+            for group in self.cache.groups:
+                if group.paged:
+                    spare = np.full((items_filled - n_items, group.max_blocks), group.pool.n_pages, dtype=np.int32)
+                    tables[group.index] = np.concatenate([tables[group.index], spare])
+            if n_want > 0:
+                want_filled = -(-n_want // 8) * 8
+                more = want_filled - n_want
+                want_rows = np.concatenate([want_rows, np.full(more, n_tokens, dtype=np.int32)])
+                want_slots = np.concatenate([want_slots, np.full(more, -1, dtype=np.int32)])
+                if sampling is not None:
+                    temperature = np.concatenate([temperature, np.zeros(more, dtype=np.float32)])
+                    top_p = np.concatenate([top_p, np.ones(more, dtype=np.float32)])
+                    seeds = np.concatenate([seeds, np.zeros(more, dtype=np.uint64)])
+                    counters = np.concatenate([counters, np.zeros(more, dtype=np.int32)])
+                n_want = want_filled
+            if tiles:
+                tiles = tiles + [(n_items, n_tokens, 1, 0, 0, 1, 0, 1)] * (-len(tiles) % 4)
+            n_tokens, n_items = filled, items_filled
+        arrays = {"token_ids": token_ids, "positions": positions, "token_item": token_item, "want_rows": want_rows,
+                  "want_slots": want_slots, "att_tiles": np.array(tiles, dtype=np.int32)}
+        for index, table in tables.items():
+            arrays[("block_table", index)] = table
+        if sampling is not None:
+            arrays.update(temperature=temperature, top_p=top_p, seeds=seeds, counters=counters)
         # the one-kernel decode step takes its arrays from alternating buffers, so that the next
         # step's copy runs beside it; captured graphs have their addresses fixed
         fused = (self.fused is not None and not dump_hidden and n_want <= n_tokens
@@ -352,6 +393,9 @@ class Engine:
         for entry in entries:
             self.cache.commit(entry.slot, len(entry.tokens))
         self.steps += 1
+        n_want = n_real_want                  # rows of the filler are nobody's
+        if logits is not None and logits.shape[0] != n_want:
+            logits = logits[:n_want]
         if self._sampled is not None:
             # the sampled ids start for the host right behind the step's kernels; for the steps
             # that alternate on a stream of their own, so that the next step's kernels do not
@@ -410,12 +454,14 @@ class Engine:
             block_table = next(v.block_table for v in self.storage.views if v.kind == "paged")
             try:
                 logits, self._sampled = self.fused.run(ctx, block_table, sample_views, self._any_nucleus)
+                self.step_kinds["one_kernel"] += 1
                 return logits
             except KernelError as error:
                 # for instance no cooperative launch on this device: say so once, then run the generic path
                 print(f"[mini_llm_b200] fused decode step disabled: {error}", file=sys.stderr, flush=True)
                 self.fused, self.fused_reason = None, str(error)
         if ctx.dump is not None or not (self.cuda_graphs and self.model.graph_safe):
+            self.step_kinds["eager"] += 1
             return self._forward(ctx, sample_views)
         stamp = (self.workspace.generation, self.control.generation, self.kernels.scratch_generation)
         if stamp != self._graph_stamp:
@@ -431,6 +477,7 @@ class Engine:
             if held is None and len(self._graphs) >= 48:
                 self._graphs.clear()                  # many shapes came by: start over rather than grow
             self._graphs[key] = (held or 0) + 1       # run eagerly: every buffer gets allocated
+            self.step_kinds["eager"] += 1
             return self._forward(ctx, sample_views)
         if isinstance(held, int):
             before = self.kernels.launches
@@ -444,8 +491,11 @@ class Engine:
             held = (graph, logits, self._sampled, self.kernels.launches - before)
             self._graphs[key] = held
             self.kernels.launches = before
+            self.step_kinds["captured"] += 1
+            self.step_kinds["replayed"] -= 1
         graph, logits, self._sampled, launches = held
         graph.replay()
+        self.step_kinds["replayed"] += 1
         self.kernels.launches += launches
         return logits
 
