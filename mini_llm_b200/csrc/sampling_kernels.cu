@@ -226,6 +226,136 @@ sample_rows_sliced_kernel(int* __restrict__ out, const float* __restrict__ logit
     if (threadIdx.x == 0) out[r] = i;
 }
 
+// ---------------------------------------------------------------------------
+// Rows with a nucleus cut, four CTAs (a cluster) per row.  Each thread keeps its share of the
+// row's probabilities in registers (PER of them: the row's entries 4096 i + 1024 rank +
+// thread), so a pass of the bisection is PER compares and adds, a sum over the block, and an
+// exchange of the four blocks' sums through distributed shared memory, added in rank order:
+// the thirty passes cost microseconds instead of thirty sweeps over shared memory, and the
+// result depends on nothing but the row.  Takes vocabularies of up to 4096 PER entries.
+// ---------------------------------------------------------------------------
+constexpr int NUCLEUS_CLUSTER = 4;
+
+__device__ __forceinline__ uint32_t cluster_rank_of_cta() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float read_float_of_rank(const float* local, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ int read_int_of_rank(const int* local, uint32_t rank) {
+    uint32_t remote;
+    int v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+// The blocks' values, each already the same in all threads of its block, combined over the
+// cluster in rank order.  `slots`: two floats of shared memory, used in turn (`turn` counts
+// the exchanges), so that one cluster barrier per exchange is enough.
+template <bool MAX>
+__device__ __forceinline__ float cluster_combine(float v, float* slots, int& turn) {
+    float* mine = slots + (turn & 1);
+    turn++;
+    if (threadIdx.x == 0) *mine = v;
+    cluster_sync_all();
+    float total = MAX ? -INFINITY : 0.0f;
+#pragma unroll
+    for (uint32_t rank = 0; rank < NUCLEUS_CLUSTER; rank++) {
+        const float other = read_float_of_rank(mine, rank);
+        total = MAX ? fmaxf(total, other) : total + other;
+    }
+    return total;
+}
+
+template <int PER>
+__global__ void __cluster_dims__(NUCLEUS_CLUSTER, 1, 1) __launch_bounds__(1024)
+nucleus_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, long ld, int vocab,
+                    const float* __restrict__ temperature, const float* __restrict__ top_p,
+                    const unsigned long long* __restrict__ seeds, const int* __restrict__ counters) {
+    __shared__ float sv[33];
+    __shared__ int si[32];
+    __shared__ float slots[2];
+    __shared__ float best_value;
+    __shared__ int best_index;
+    const int r = blockIdx.x / NUCLEUS_CLUSTER;
+    const uint32_t rank = cluster_rank_of_cta();
+    const float temp = temperature[r], nucleus = top_p[r];
+    if (!(temp > 0.0f && nucleus < 1.0f)) return;          // the whole cluster alike: drawn by the sliced kernel
+    const float* x = logits + (long)r * ld;
+    const float inv_t = 1.0f / temp;
+    const int first = (int)rank * 1024 + threadIdx.x;
+    int turn = 0;
+    float p[PER];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+        const int v = first + i * (NUCLEUS_CLUSTER * 1024);
+        p[i] = v < vocab ? x[v] : -INFINITY;
+        mx = fmaxf(mx, p[i]);
+    }
+    const float big = cluster_combine<true>(block_max(mx, sv), slots, turn);
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+        p[i] = expf((p[i] - big) * inv_t);                  // 0 for the entries past the vocabulary
+        sum += p[i];
+    }
+    const float z = cluster_combine<false>(block_sum(sum, sv), slots, turn);
+#pragma unroll
+    for (int i = 0; i < PER; i++) p[i] = p[i] / z;
+    // the largest t with sum over p >= t of p >= nucleus, by bisection on t's bit pattern
+    unsigned lo = 0u, hi = 0x3f800000u;
+    while (lo < hi) {
+        const unsigned mid = lo + (hi - lo + 1u) / 2u;
+        const float t = __uint_as_float(mid);
+        float mass = 0.0f;
+#pragma unroll
+        for (int i = 0; i < PER; i++)
+            if (p[i] >= t) mass += p[i];
+        mass = cluster_combine<false>(block_sum(mass, sv), slots, turn);
+        if (mass >= nucleus) lo = mid; else hi = mid - 1u;
+    }
+    const float cut = __uint_as_float(lo);
+    const unsigned long long seed = seeds ? seeds[r] : 0ull;
+    const unsigned counter = counters ? (unsigned)counters[r] : 0u;
+    float best = 0.0f;
+    int best_i = -1;
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+        const int v = first + i * (NUCLEUS_CLUSTER * 1024);
+        if (v >= vocab || !(p[i] >= cut)) continue;
+        const float score = x[v] * inv_t - logf(-logf(uniform_of(seed, counter, (unsigned)v)));
+        if (better(score, v, best, best_i)) { best = score; best_i = v; }
+    }
+    block_argmax(best, best_i, sv, si);
+    if (threadIdx.x == 0) {
+        best_value = best;
+        best_index = best_i;
+    }
+    cluster_sync_all();
+    if (rank == 0 && threadIdx.x == 0) {
+        for (uint32_t other = 1; other < NUCLEUS_CLUSTER; other++) {
+            const float ov = read_float_of_rank(&best_value, other);
+            const int oi = read_int_of_rank(&best_index, other);
+            if (better(ov, oi, best, best_i)) { best = ov; best_i = oi; }
+        }
+        out[r] = best_i;
+    }
+    cluster_sync_all();                                     // nobody leaves while its shared memory may be read
+}
+
+constexpr int NUCLEUS_PER = 16;       // vocabularies of up to 65,536 entries
+
 // Launches the one-block-per-row kernel, with the row's probabilities kept in shared memory
 // when the vocabulary fits there.
 static int launch_sample_rows(int* out, const float* logits, long ld, int n_rows, int vocab, const float* temperature,
@@ -252,6 +382,19 @@ static int launch_sample_rows(int* out, const float* logits, long ld, int n_rows
     return check_launch("sample_rows_kernel");
 }
 
+// The rows with a nucleus cut only: by the cluster kernel when the vocabulary fits its
+// registers, else by the one-block kernel.
+static int launch_nucleus_rows(int* out, const float* logits, long ld, int n_rows, int vocab, const float* temperature,
+                               const float* top_p, const unsigned long long* seeds, const int* counters, cudaStream_t s) {
+    if (temperature == nullptr || top_p == nullptr) return 0;        // no row has a cut
+    if (vocab <= NUCLEUS_CLUSTER * 1024 * NUCLEUS_PER) {
+        nucleus_rows_kernel<NUCLEUS_PER><<<n_rows * NUCLEUS_CLUSTER, 1024, 0, s>>>(out, logits, ld, vocab, temperature, top_p,
+                                                                                   seeds, counters);
+        return check_launch("nucleus_rows_kernel");
+    }
+    return launch_sample_rows(out, logits, ld, n_rows, vocab, temperature, top_p, seeds, counters, 1, s);
+}
+
 // any_nucleus: some row has temperature > 0 and top_p < 1 (the host knows); those rows are
 // then drawn by the one-block kernel, which skips all others.
 extern "C" int mllm_sampling_sample_rows_sliced(int* out, const float* logits, long ld, int n_rows, int vocab,
@@ -265,7 +408,7 @@ extern "C" int mllm_sampling_sample_rows_sliced(int* out, const float* logits, l
     sample_rows_sliced_kernel<<<dim3(n_rows, SAMPLE_SLICES), 256, 0, s>>>(out, logits, ld, vocab, temperature, top_p,
                                                                          seeds, counters, part_value, part_index, done);
     int rc = check_launch("sample_rows_sliced_kernel");
-    if (rc == 0 && any_nucleus) rc = launch_sample_rows(out, logits, ld, n_rows, vocab, temperature, top_p, seeds, counters, 1, s);
+    if (rc == 0 && any_nucleus) rc = launch_nucleus_rows(out, logits, ld, n_rows, vocab, temperature, top_p, seeds, counters, s);
     return rc;
 }
 
@@ -275,7 +418,7 @@ extern "C" int mllm_sampling_sample_rows_nucleus(int* out, const float* logits, 
                                                  const float* temperature, const float* top_p,
                                                  const unsigned long long* seeds, const int* counters, void* stream) {
     if (n_rows <= 0) return 0;
-    return launch_sample_rows(out, logits, ld, n_rows, vocab, temperature, top_p, seeds, counters, 1, (cudaStream_t)stream);
+    return launch_nucleus_rows(out, logits, ld, n_rows, vocab, temperature, top_p, seeds, counters, (cudaStream_t)stream);
 }
 
 extern "C" int mllm_sampling_sample_rows(int* out, const float* logits, long ld, int n_rows, int vocab,

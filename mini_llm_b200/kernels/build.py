@@ -149,8 +149,22 @@ def _compile(source: str, target: str, name: str) -> None:
             os.remove(partial)
         raise BuildError(f"nvcc failed on {source}:\n{''.join(output)}")
     os.replace(partial, target)      # atomic: a concurrent process never sees half a file
+    _drop_older_builds(target, name)
     print(f"[mini_llm_b200] built {os.path.basename(target)} in {time.time() - started:.0f} s",
           file=sys.stderr, flush=True)
+
+
+def _drop_older_builds(target: str, name: str) -> None:
+    """Builds of earlier versions of the same source (other hashes) in the folder of a fresh
+    build are of no use any more.  A process that still has one mapped keeps its mapping."""
+    folder, keep = os.path.dirname(target), os.path.basename(target)
+    prefix = f"libmllm_{name}-"
+    for entry in os.listdir(folder):
+        if entry.startswith(prefix) and entry.endswith(".so") and entry != keep:
+            try:
+                os.remove(os.path.join(folder, entry))
+            except OSError:
+                pass
 
 
 def build_all() -> dict[str, str]:
