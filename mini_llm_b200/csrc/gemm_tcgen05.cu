@@ -914,21 +914,23 @@ struct GemmScatter {
 };
 
 // Tile width of the persistent kernel for a product of M x N x K: the width with the least
-// estimated time.  The products are bound by operand traffic from L2, (128 + BN) * 128 bytes
-// per tile and block of K, and a product ends with its slowest CTA, which has
-// ceil(tiles / SMs) tiles; the last tile's epilogue (about BN columns of stores) is not hidden.
+// estimated time.  Measured on a B200 (time stamps inside the kernel, GPT-2 small's four
+// products): a block of 64 along K takes a CTA about 0.34 us at every width (0.35 us at 256,
+// where the tensor pipe itself needs 0.28 us), so wide tiles do more per block; a product
+// lasts as long as its busiest CTA, which walks ceil(tiles / SMs) tiles; epilogues run under
+// the next tile's blocks except the last one, about 0.0105 us per column of the tile.
 static int rows_tile_width(int M, int N, int K, int sms) {
     const int widths[5] = {256, 192, 128, 96, 64};
     const long tiles_m = (M + BM - 1) / BM, num_k = (K + BK - 1) / BK;
     int best = 128;
-    long best_cost = -1;
+    double best_cost = -1.0;
     for (int i = 0; i < 5; i++) {
         const int bn = widths[i];
         if (bn > 64 && bn >= 2 * N) continue;                     // mostly padding
         const long tiles = tiles_m * ((N + bn - 1) / bn);
         const long rounds = (tiles + sms - 1) / sms;
-        const long cost = rounds * num_k * (128 + bn) + 6L * bn;
-        if (best_cost < 0 || cost < best_cost) {
+        const double cost = (double)(rounds * num_k) * (bn > 192 ? 0.35 : 0.34) + 0.0105 * bn;
+        if (best_cost < 0.0 || cost < best_cost) {
             best_cost = cost;
             best = bn;
         }

@@ -314,13 +314,13 @@ class Engine:
             # not exist (id 0 at position 0; its block table names the spare page that every
             # pool has beyond its last) bring the token count to a multiple of 64 (128 past 512
             # tokens), the entries to a multiple of 8, the wanted rows to a multiple of 8 (more
-            # rows of the filler, drawn greedily and kept for no request), the attention work
-            # list to a multiple of 4 (more tiles of the filler's first row).  Rows never mix, so
-            # the real rows' results are what they would be alone; steps of one round shape
-            # replay one graph.
+            # rows of the filler, or of row 0 when there is no filler row; drawn greedily and kept
+            # for no request), the attention work list to a multiple of 4 (more tiles of the
+            # filler's first row, if there is one).  Rows never mix, so the real rows' results
+            # are what they would be alone; steps of one round shape replay one graph.
             step = 64 if n_tokens < 512 else 128
-            filled = -(-(n_tokens + 1) // step) * step
-            extra = filled - n_tokens
+            filled = -(-n_tokens // step) * step
+            extra = filled - n_tokens                     # (none, if the step is round already)
             token_ids = np.concatenate([token_ids, np.zeros(extra, dtype=np.int32)])
             positions = np.concatenate([positions, np.zeros(extra, dtype=np.int32)])
             token_item = np.concatenate([token_item, np.full(extra, n_items, dtype=np.int32)])
@@ -332,7 +332,7 @@ class Engine:
             if n_want > 0:
                 want_filled = -(-n_want // 8) * 8
                 more = want_filled - n_want
-                want_rows = np.concatenate([want_rows, np.full(more, n_tokens, dtype=np.int32)])
+                want_rows = np.concatenate([want_rows, np.full(more, n_tokens if extra else 0, dtype=np.int32)])
                 want_slots = np.concatenate([want_slots, np.full(more, -1, dtype=np.int32)])
                 if sampling is not None:
                     temperature = np.concatenate([temperature, np.zeros(more, dtype=np.float32)])
@@ -340,7 +340,7 @@ class Engine:
                     seeds = np.concatenate([seeds, np.zeros(more, dtype=np.uint64)])
                     counters = np.concatenate([counters, np.zeros(more, dtype=np.int32)])
                 n_want = want_filled
-            if tiles:
+            if tiles and extra:
                 tiles = tiles + [(n_items, n_tokens, 1, 0, 0, 1, 0, 1)] * (-len(tiles) % 4)
             n_tokens, n_items = filled, items_filled
         arrays = {"token_ids": token_ids, "positions": positions, "token_item": token_item, "want_rows": want_rows,
