@@ -415,6 +415,118 @@ constexpr int WARP_BLOCKS_BYTES = 2 * 4096;   // per epilogue warp: two blocks o
 enum { STATUS_TIMEOUT_ROWS_PRODUCER = 5, STATUS_TIMEOUT_ROWS_MMA = 6, STATUS_TIMEOUT_ROWS_EPILOGUE = 7, STATUS_PAIR_TMEM_DIFFERS = 8 };
 
 
+// Where an epilogue warp's blocks of 32 rows x 32 columns go, for finish_block().
+struct BlockOut {
+    const CUtensorMap* map_out;
+    float* turn;               // the warp's two blocks of shared memory (8 KB, 1024-byte aligned)
+    const float* bias_s;       // the tile's biases (zeros without a bias), in shared memory
+    const long* kv_off;        // the tile's 128 cache offsets (scatter only)
+    int quarter, lane;
+    int boxes;                 // boxes this warp has sent: box b leaves from block b % 2
+};
+
+// One block of a tile's accumulator, v[i] = column c0 + i of this thread's row (row0 + lane),
+// to where it belongs: bias, activation, conversion, and the way out.
+__device__ __forceinline__ void finish_block(BlockOut& o, const GemmParams& p, const CUtensorMap& map_out, float* v, int c0,
+                                             int n0, int row0) {
+    float* turn = o.turn;
+    const float* bias_s = o.bias_s;
+    const long* kv_off = o.kv_off;
+    const int quarter = o.quarter, lane = o.lane;
+    int& boxes = o.boxes;
+        const float* bs = bias_s + c0;
+        const bool whole = n0 + 32 <= p.N;
+        // Where the block of 32 x 32 goes.  A block of `out` leaves through shared memory
+        // and one TMA box (stored, or added to what is there: the residual sum) when the
+        // tensor is laid out for it.  A block of keys or values goes to scattered cache
+        // slots: each thread stores its own row's 64 bytes from its registers.  Whatever
+        // is laid out for neither is turned through shared memory, so that consecutive
+        // lanes write consecutive columns.
+        const bool wide = p.epilogue == EPI_ADD || p.out_f32;
+        const int region = wide || p.k_pages == nullptr || n0 < p.q_width ? 0 : (n0 < p.q_width + p.kv_width ? 1 : 2);
+        if (region == 0 && p.out_by_tma) {
+            if (row0 >= p.M) return;
+            if (lane == 0) bulk_wait_read_but_one();     // the box before the last one has left its block
+            __syncwarp();
+            unsigned char* mine = reinterpret_cast<unsigned char*>(turn) + (boxes & 1) * 4096;
+            boxes++;
+            const uint32_t bias32 = smem_u32(bs), block = smem_u32(mine);
+            if (wide) stage_row_f32(v, bias32, block, lane);
+            else if (p.epilogue == EPI_GELU_TANH) stage_row_bf16<EPI_GELU_TANH>(v, bias32, block, lane);
+            else if (p.epilogue == EPI_GELU_ERF) stage_row_bf16<EPI_GELU_ERF>(v, bias32, block, lane);
+            else stage_row_bf16<EPI_STORE>(v, bias32, block, lane);
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                if (p.epilogue == EPI_ADD) tma_reduce_add_2d(&map_out, mine, n0, row0);
+                else tma_store_2d(&map_out, mine, n0, row0);
+                bulk_commit();
+            }
+            return;
+        }
+        if (region != 0 && whole && (p.kv_width & 7) == 0 &&
+            (reinterpret_cast<uintptr_t>(region == 1 ? p.k_pages : p.v_pages) & 15) == 0) {
+            // Keys or values: the block is staged as bfloat16 like a box, then four lanes
+            // write one row's 64 bytes to its cache slot, eight rows per instruction.
+            if (lane == 0) bulk_wait_read();
+            __syncwarp();
+            const uint32_t block = smem_u32(turn);
+            stage_row_bf16<EPI_STORE>(v, smem_u32(bs), block, lane);
+            __syncwarp();
+            bf16* pages = region == 1 ? p.k_pages + (n0 - p.q_width) : p.v_pages + (n0 - p.q_width - p.kv_width);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int row = i * 8 + (lane >> 2), piece = lane & 3;
+                const float4 x = lds128(block + row * 64 + ((piece ^ ((row >> 1) & 3)) << 4));
+                if (row0 + row < p.M)
+                    *reinterpret_cast<float4*>(pages + kv_off[quarter * 32 + row] + piece * 8) = x;
+            }
+            return;
+        }
+        if (lane == 0) bulk_wait_read();             // (a box may still be leaving the block)
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 32; i++) turn[lane * 33 + i] = v[i];
+        __syncwarp();
+        const int n = n0 + lane;
+        const bool col_ok = n < p.N;
+        const float b = col_ok ? bs[lane] : 0.0f;
+        if (p.epilogue == EPI_ADD) {
+            float* o = reinterpret_cast<float*>(p.out) + (long)row0 * p.ldo + n;
+#pragma unroll 1
+            for (int r0 = 0; r0 < 32; r0 += 8) {
+                float old[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++)
+                    old[u] = (col_ok && row0 + r0 + u < p.M) ? o[(long)(r0 + u) * p.ldo] : 0.0f;
+#pragma unroll
+                for (int u = 0; u < 8; u++)
+                    if (col_ok && row0 + r0 + u < p.M)
+                        o[(long)(r0 + u) * p.ldo] = old[u] + turn[(r0 + u) * 33 + lane] + b;
+            }
+        } else if (p.out_f32) {
+            float* o = reinterpret_cast<float*>(p.out) + (long)row0 * p.ldo + n;
+#pragma unroll 4
+            for (int rr = 0; rr < 32; rr++)
+                if (col_ok && row0 + rr < p.M) o[(long)rr * p.ldo] = turn[rr * 33 + lane] + b;
+        } else {
+            // bfloat16: rows of the output, or (scatter) slots of the cache pages
+            bf16* const region_base = region == 0 ? reinterpret_cast<bf16*>(p.out) + (long)row0 * p.ldo + n0
+                                      : (region == 1 ? p.k_pages + (n0 - p.q_width)
+                                                     : p.v_pages + (n0 - p.q_width - p.kv_width));
+            const bool paired = whole && (p.ldo & 1) == 0 && (p.kv_width & 1) == 0 &&
+                                (reinterpret_cast<uintptr_t>(region_base) & 3) == 0;
+            const long ldo = p.ldo;
+            const long* slots = kv_off + quarter * 32;
+            if (region == 0)
+                store_rows_bf16(turn, region_base, [ldo](int rr) { return (long)rr * ldo; }, paired, col_ok, lane,
+                                p.M - row0, p.bias != nullptr ? p.bias + n0 : nullptr, p.epilogue);
+            else
+                store_rows_bf16(turn, region_base, [slots](int rr) { return slots[rr]; }, paired, col_ok, lane,
+                                p.M - row0, p.bias != nullptr ? p.bias + n0 : nullptr, p.epilogue);
+        }
+}
+
 template <int BN, int STAGES, bool PAIR>
 constexpr size_t rows_shared_bytes() {
     // stages, the epilogue warps' turning blocks, barriers, a few words, two sets of cache offsets, two of biases
@@ -561,8 +673,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // ---- epilogue: warps w and w + 4 own TMEM lanes 32 (w % 4) .. +31 and take the tile's
         // blocks of 32 columns in turn ----
         const int quarter = warp & 3, col_half = warp >> 2;
-        float* turn = turn_all + warp * (WARP_BLOCKS_BYTES / 4);      // both blocks together hold a turned block too
-        int boxes = 0;                       // boxes this warp has sent: box b leaves from block b % 2
+        BlockOut out_ctx{&map_out, turn_all + warp * (WARP_BLOCKS_BYTES / 4), nullptr, nullptr, quarter, lane, 0};
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
         int local = 0;
         for (int tile = walker; tile < n_tiles; tile += walkers, local++) {
@@ -571,6 +682,8 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const int first_row = tile_m * TILE_ROWS + (int)rank * BM;      // this CTA's 128 tokens of the tile
             long* kv_off = kv_off_all + acc * BM;
             float* bias_s = bias_all + acc * 256;
+            out_ctx.kv_off = kv_off;
+            out_ctx.bias_s = bias_s;
             if (p.k_pages != nullptr && threadIdx.x < BM) {
                 const int t = first_row + threadIdx.x;
                 if (t < p.M) {
@@ -603,97 +716,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 float v[32];
                 __syncwarp();
                 tmem_load_32(acc_base + c0, v);
-                const float* bs = bias_s + c0;
-                const bool whole = n0 + 32 <= p.N;
-                // Where the block of 32 x 32 goes.  A block of `out` leaves through shared memory
-                // and one TMA box (stored, or added to what is there: the residual sum) when the
-                // tensor is laid out for it.  A block of keys or values goes to scattered cache
-                // slots: each thread stores its own row's 64 bytes from its registers.  Whatever
-                // is laid out for neither is turned through shared memory, so that consecutive
-                // lanes write consecutive columns.
-                const bool wide = p.epilogue == EPI_ADD || p.out_f32;
-                const int region = wide || p.k_pages == nullptr || n0 < p.q_width ? 0 : (n0 < p.q_width + p.kv_width ? 1 : 2);
-                if (region == 0 && p.out_by_tma) {
-                    if (row0 >= p.M) continue;
-                    if (lane == 0) bulk_wait_read_but_one();     // the box before the last one has left its block
-                    __syncwarp();
-                    unsigned char* mine = reinterpret_cast<unsigned char*>(turn) + (boxes & 1) * 4096;
-                    boxes++;
-                    const uint32_t bias32 = smem_u32(bs), block = smem_u32(mine);
-                    if (wide) stage_row_f32(v, bias32, block, lane);
-                    else if (p.epilogue == EPI_GELU_TANH) stage_row_bf16<EPI_GELU_TANH>(v, bias32, block, lane);
-                    else if (p.epilogue == EPI_GELU_ERF) stage_row_bf16<EPI_GELU_ERF>(v, bias32, block, lane);
-                    else stage_row_bf16<EPI_STORE>(v, bias32, block, lane);
-                    fence_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (p.epilogue == EPI_ADD) tma_reduce_add_2d(&map_out, mine, n0, row0);
-                        else tma_store_2d(&map_out, mine, n0, row0);
-                        bulk_commit();
-                    }
-                    continue;
-                }
-                if (region != 0 && whole && (p.kv_width & 7) == 0 &&
-                    (reinterpret_cast<uintptr_t>(region == 1 ? p.k_pages : p.v_pages) & 15) == 0) {
-                    // Keys or values: the block is staged as bfloat16 like a box, then four lanes
-                    // write one row's 64 bytes to its cache slot, eight rows per instruction.
-                    if (lane == 0) bulk_wait_read();
-                    __syncwarp();
-                    const uint32_t block = smem_u32(turn);
-                    stage_row_bf16<EPI_STORE>(v, smem_u32(bs), block, lane);
-                    __syncwarp();
-                    bf16* pages = region == 1 ? p.k_pages + (n0 - p.q_width) : p.v_pages + (n0 - p.q_width - p.kv_width);
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const int row = i * 8 + (lane >> 2), piece = lane & 3;
-                        const float4 x = lds128(block + row * 64 + ((piece ^ ((row >> 1) & 3)) << 4));
-                        if (row0 + row < p.M)
-                            *reinterpret_cast<float4*>(pages + kv_off[quarter * 32 + row] + piece * 8) = x;
-                    }
-                    continue;
-                }
-                if (lane == 0) bulk_wait_read();             // (a box may still be leaving the block)
-                __syncwarp();
-#pragma unroll
-                for (int i = 0; i < 32; i++) turn[lane * 33 + i] = v[i];
-                __syncwarp();
-                const int n = n0 + lane;
-                const bool col_ok = n < p.N;
-                const float b = col_ok ? bs[lane] : 0.0f;
-                if (p.epilogue == EPI_ADD) {
-                    float* o = reinterpret_cast<float*>(p.out) + (long)row0 * p.ldo + n;
-#pragma unroll 1
-                    for (int r0 = 0; r0 < 32; r0 += 8) {
-                        float old[8];
-#pragma unroll
-                        for (int u = 0; u < 8; u++)
-                            old[u] = (col_ok && row0 + r0 + u < p.M) ? o[(long)(r0 + u) * p.ldo] : 0.0f;
-#pragma unroll
-                        for (int u = 0; u < 8; u++)
-                            if (col_ok && row0 + r0 + u < p.M)
-                                o[(long)(r0 + u) * p.ldo] = old[u] + turn[(r0 + u) * 33 + lane] + b;
-                    }
-                } else if (p.out_f32) {
-                    float* o = reinterpret_cast<float*>(p.out) + (long)row0 * p.ldo + n;
-#pragma unroll 4
-                    for (int rr = 0; rr < 32; rr++)
-                        if (col_ok && row0 + rr < p.M) o[(long)rr * p.ldo] = turn[rr * 33 + lane] + b;
-                } else {
-                    // bfloat16: rows of the output, or (scatter) slots of the cache pages
-                    bf16* const region_base = region == 0 ? reinterpret_cast<bf16*>(p.out) + (long)row0 * p.ldo + n0
-                                              : (region == 1 ? p.k_pages + (n0 - p.q_width)
-                                                             : p.v_pages + (n0 - p.q_width - p.kv_width));
-                    const bool paired = whole && (p.ldo & 1) == 0 && (p.kv_width & 1) == 0 &&
-                                        (reinterpret_cast<uintptr_t>(region_base) & 3) == 0;
-                    const long ldo = p.ldo;
-                    const long* slots = kv_off + quarter * 32;
-                    if (region == 0)
-                        store_rows_bf16(turn, region_base, [ldo](int rr) { return (long)rr * ldo; }, paired, col_ok, lane,
-                                        p.M - row0, p.bias != nullptr ? p.bias + n0 : nullptr, p.epilogue);
-                    else
-                        store_rows_bf16(turn, region_base, [slots](int rr) { return slots[rr]; }, paired, col_ok, lane,
-                                        p.M - row0, p.bias != nullptr ? p.bias + n0 : nullptr, p.epilogue);
-                }
+                finish_block(out_ctx, p, map_out, v, c0, n0, row0);
             }
             // the accumulator may be overwritten once every warp has read its part
             tcgen05_before_sync();
