@@ -37,7 +37,7 @@ namespace {
 
 constexpr int BM = 128;             // tile rows = TMEM lanes
 constexpr int BK = 64;              // 64 bf16 = 128 bytes = one swizzle row
-constexpr int THREADS = 320;        // warps 0-7 epilogue, 8 producer, 9 MMA (both kernels)
+constexpr int THREADS = 320;        // warps 0-7 epilogue, 8 producer, 9 MMA (both kernels; a second issuing warp 10 where the rows kernel has one)
 enum { STATUS_OK = 0, STATUS_TIMEOUT_PRODUCER = 1, STATUS_TIMEOUT_MMA = 2, STATUS_TIMEOUT_EPILOGUE = 3 };
 
 struct GemmParams {
@@ -528,14 +528,20 @@ __device__ __forceinline__ void finish_block(BlockOut& o, const GemmParams& p, c
 }
 
 template <int BN, int STAGES, bool PAIR>
-constexpr size_t rows_shared_bytes() {
+constexpr size_t rows_shared_bytes() {   // the same for one and for two issuing threads
     // stages, the epilogue warps' turning blocks, barriers, a few words, two sets of cache offsets, two of biases
-    return (size_t)STAGES * (BM * BK * 2 + (PAIR ? BN / 2 : BN) * BK * 2) + 8 * WARP_BLOCKS_BYTES + (2 * STAGES + 4) * 8 + 16 +
+    return (size_t)STAGES * (BM * BK * 2 + (PAIR ? BN / 2 : BN) * BK * 2) + 8 * WARP_BLOCKS_BYTES + (2 * STAGES + 6) * 8 + 16 +
            2 * BM * 8 + 2 * 256 * 4 + 1024;
 }
 
-template <int BN, int STAGES, bool PAIR>
-__global__ void __launch_bounds__(THREADS, 1)
+// ISSUERS: the threads that issue the tile's products.  One thread spends about 560 clocks on a
+// block of 64 along K (the wait for its operands, four tcgen05.mma, the commit), whatever the
+// tile's width, while the tensor pipe needs 4 x 57 clocks for a width of 96 and 4 x 128 for 256
+// (measured with operands resident in shared memory).  Narrow tiles are therefore issued by two
+// threads of two warps: the first takes the even blocks of K into one accumulator, the second
+// the odd ones into another, and the epilogue adds the two, always in that order.
+template <int BN, int STAGES, bool PAIR, int ISSUERS>
+__global__ void __launch_bounds__(THREADS + 32 * (ISSUERS - 1), 1)
 gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_out, const GemmParams p, const int tiles_m, const int n_tiles) {
     extern __shared__ unsigned char smem_raw[];
@@ -543,7 +549,8 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     constexpr int B_ROWS = PAIR ? BN / 2 : BN;             // rows of W this CTA loads per block of K
     constexpr int A_BYTES = BM * BK * 2, B_BYTES = B_ROWS * BK * 2;
     constexpr int TILE_ROWS = PAIR ? 2 * BM : BM;          // tokens per tile (of the pair)
-    constexpr int TMEM_COLS = BN <= 64 ? 128 : (BN <= 128 ? 256 : 512), ACC_STRIDE = TMEM_COLS / 2, CHUNKS = BN / 32;
+    static_assert(ISSUERS == 1 || (ISSUERS == 2 && BN <= 128 && !PAIR), "two issuers: four accumulators of at most 128 columns");
+    constexpr int ACC_STRIDE = BN <= 64 ? 64 : (BN <= 128 ? 128 : 256), TMEM_COLS = 2 * ISSUERS * ACC_STRIDE, CHUNKS = BN / 32;
     unsigned char* stage_a = smem;
     unsigned char* stage_b = smem + STAGES * A_BYTES;
     float* turn_all = reinterpret_cast<float*>(smem + STAGES * (A_BYTES + B_BYTES));
@@ -551,7 +558,8 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;        // [2]: the MMAs of a tile have finished
     uint64_t* acc_empty = acc_full + 2;         // [2]: the epilogue warps have read the tile out
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    uint64_t* drained = acc_empty + 2;          // [2]: after a failure, an issuing thread's products have all finished
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drained + 2);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* tile_ok = reinterpret_cast<volatile int*>(tmem_slot + 2);     // [2], by the tile's parity
     // by the tile's parity, so that a warp may start on the next tile while another finishes this one:
@@ -574,8 +582,9 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             mbar_init(&empty[s], 1);
         }
         for (int a = 0; a < 2; a++) {
-            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_full[a], ISSUERS);            // one commit per issuing thread
             mbar_init(&acc_empty[a], PAIR ? 16 : 8);     // one arrival per epilogue warp (of both CTAs, at the leader)
+            mbar_init(&drained[a], 1);
         }
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -603,16 +612,27 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
 
     if (stamps && threadIdx.x == 0) p.timeline[1] = now_ns();
+    // Each issuing thread has a ring of stages of its own (the first RING0 stages, the rest),
+    // filled by the producer in the order in which that thread takes its blocks.  A stage that
+    // two threads took in turn would let one of them look at a barrier two phases after it last
+    // saw it, and a wait by parity cannot tell a phase from the one two before it.
+    constexpr int RING0 = ISSUERS == 2 ? (STAGES + 1) / 2 : STAGES, RING1 = STAGES - RING0;
+    static_assert(ISSUERS == 1 || RING1 >= 2, "two issuers: at least two stages each");
     if (warp == 8) {
-        // ---- producer: the ring runs on across tiles ----
+        // ---- producer: the rings run on across tiles ----
         if (lane == 0) {
-            int it = 0;
-            for (int tile = walker; tile < n_tiles && !*failed; tile += walkers) {
+            int pos[2] = {0, 0};                     // the next stage of each ring
+            uint32_t phase[2] = {0u, 0u};            // the parity of the round that stage is in
+            int issued[2] = {0, 0};
+            bool ok = true;
+            for (int tile = walker; tile < n_tiles && ok && !*failed; tile += walkers) {
                 const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
-                for (int kb = 0; kb < num_k; kb++, it++) {
-                    const int s = it % STAGES;
-                    if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1) || *failed) {
+                for (int kb = 0; kb < num_k; kb++) {
+                    const int ring = ISSUERS == 2 ? (kb & 1) : 0;
+                    const int s = ring == 0 ? pos[0] : RING0 + pos[1];
+                    if (!mbar_wait(&empty[s], phase[ring] ^ 1u) || *failed) {
                         give_up(STATUS_TIMEOUT_ROWS_PRODUCER);
+                        ok = false;
                         break;
                     }
                     if (PAIR) {
@@ -626,47 +646,90 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         tma_load_2d(stage_a + s * A_BYTES, &map_a, &full[s], kb * BK, tile_m * BM);
                         tma_load_2d(stage_b + s * B_BYTES, &map_b, &full[s], kb * BK, tile_n * BN);
                     }
+                    issued[ring]++;
+                    if (++pos[ring] == (ring == 0 ? RING0 : RING1)) {
+                        pos[ring] = 0;
+                        phase[ring] ^= 1u;
+                    }
                 }
             }
             if (*failed && leader) {
                 // copies that were issued still land: wait for them (bounded) so that none is in flight at the end
-                for (int i = max(0, it - STAGES); i < it; i++) mbar_wait(&full[i % STAGES], (i / STAGES) & 1);
+                for (int ring = 0; ring < ISSUERS; ring++) {
+                    const int size = ring == 0 ? RING0 : RING1;
+                    for (int i = max(0, issued[ring] - size); i < issued[ring]; i++)
+                        mbar_wait(&full[(ring == 0 ? 0 : RING0) + i % size], (uint32_t)(i / size) & 1u);
+                }
             }
         }
-    } else if (warp == 9) {
-        // ---- MMA issue: tile t into accumulator t % 2 ----
+    } else if (warp >= 9) {
+        // ---- MMA issue: tile t into the accumulators of parity t % 2; issuer i takes the blocks
+        // of K with kb % ISSUERS == i from its own ring.  The flag `failed` is looked at once a
+        // tile: every other role's waits are bounded too, so a failure elsewhere ends this loop
+        // by a wait running out.
+        const int issuer = warp - 9;
         if (lane == 0 && leader) {
+            // This thread's instructions between two blocks are what bounds the loop, so it keeps
+            // the ring's position and the descriptors as running values.
             const uint32_t idesc = make_instr_desc(TILE_ROWS, BN);
-            int it = 0, local = 0;
-            for (int tile = walker; tile < n_tiles && !*failed; tile += walkers, local++) {
+            const int ring_base = issuer == 0 ? 0 : RING0, ring_size = issuer == 0 ? RING0 : RING1;
+            // the address field counts 16 bytes and stays below its 14 bits for any stage
+            const uint64_t desc_a0 = make_smem_desc(smem_u32(stage_a + ring_base * A_BYTES));
+            const uint64_t desc_b0 = make_smem_desc(smem_u32(stage_b + ring_base * B_BYTES));
+            uint64_t* const ring_full = full + ring_base;
+            uint64_t* const ring_empty = empty + ring_base;
+            int local = 0, pos = 0;
+            uint32_t phase = 0u;
+            long long looked = 0, not_there = 0;
+            bool ok = true;
+            for (int tile = walker; tile < n_tiles && ok && !*failed; tile += walkers, local++) {
                 const int acc = local & 1;
                 if (!mbar_wait(&acc_empty[acc], ((local >> 1) & 1) ^ 1) || *failed) {
                     give_up(STATUS_TIMEOUT_ROWS_MMA);
                     break;
                 }
                 tcgen05_after_sync();
-                const uint32_t tmem_acc = tmem_base + (uint32_t)(acc * ACC_STRIDE);
-                for (int kb = 0; kb < num_k; kb++, it++) {
-                    const int s = it % STAGES;
-                    if (!mbar_wait(&full[s], (it / STAGES) & 1) || *failed) {
-                        give_up(STATUS_TIMEOUT_ROWS_MMA);
-                        break;
+                const uint32_t tmem_acc = tmem_base + (uint32_t)((acc * ISSUERS + issuer) * ACC_STRIDE);
+                for (int kb = issuer; kb < num_k; kb += ISSUERS) {
+                    looked++;
+                    if (!mbar_try_wait(&ring_full[pos], phase)) {
+                        not_there++;
+                        if (!mbar_wait(&ring_full[pos], phase)) {
+                            give_up(STATUS_TIMEOUT_ROWS_MMA);
+                            ok = false;
+                            break;
+                        }
                     }
                     tcgen05_after_sync();
-                    if (stamps && it == 0) p.timeline[2] = now_ns();
-                    const uint64_t desc_a = make_smem_desc(smem_u32(stage_a + s * A_BYTES));
-                    const uint64_t desc_b = make_smem_desc(smem_u32(stage_b + s * B_BYTES));
+                    if (stamps && local == 0 && kb == 0) p.timeline[2] = now_ns();
+                    const uint64_t desc_a = desc_a0 + (uint64_t)(pos * (A_BYTES >> 4));
+                    const uint64_t desc_b = desc_b0 + (uint64_t)(pos * (B_BYTES >> 4));
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; k++) {
                         if (PAIR) umma_pair(tmem_acc, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                        else umma(tmem_acc, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        else umma(tmem_acc, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb >= ISSUERS || k > 0) ? 1u : 0u);
                     }
-                    if (PAIR) umma_commit_pair(&empty[s]);
-                    else umma_commit(&empty[s]);
+                    if (PAIR) umma_commit_pair(&ring_empty[pos]);
+                    else umma_commit(&ring_empty[pos]);
+                    if (++pos == ring_size) {
+                        pos = 0;
+                        phase ^= 1u;
+                    }
                 }
+                // (after a wait that ran out too: the epilogue is not left waiting for this thread)
                 if (PAIR) umma_commit_pair(&acc_full[acc]);
                 else umma_commit(&acc_full[acc]);
-                if (stamps && local == 0) p.timeline[3] = now_ns();
+                if (stamps && local == 0 && issuer == 0) p.timeline[3] = now_ns();
+            }
+            if (stamps && issuer == 0) {
+                p.timeline[7] = (unsigned long long)looked;
+                p.timeline[8] = (unsigned long long)not_there;
+            }
+            if (*failed) {
+                // products that were issued still run: wait for them (bounded) before the tensor memory is freed
+                if (PAIR) umma_commit_pair(&drained[issuer]);
+                else umma_commit(&drained[issuer]);
+                mbar_wait(&drained[issuer], 0);
             }
         }
     } else {
@@ -708,7 +771,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             tcgen05_after_sync();
             if (stamps && local == 0 && threadIdx.x == 0) p.timeline[4] = now_ns();
             const int row0 = first_row + quarter * 32;
-            const uint32_t acc_base = lane_base + (uint32_t)(acc * ACC_STRIDE);
+            const uint32_t acc_base = lane_base + (uint32_t)(acc * ISSUERS * ACC_STRIDE);
 #pragma unroll 1
             for (int c = col_half; c < CHUNKS; c += 2) {
                 const int c0 = c * 32, n0 = tile_n * BN + c0;
@@ -716,6 +779,12 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 float v[32];
                 __syncwarp();
                 tmem_load_32(acc_base + c0, v);
+                if (ISSUERS == 2 && num_k > 1) {         // the second issuer's blocks (none when K has one block)
+                    float odd[32];
+                    tmem_load_32(acc_base + ACC_STRIDE + c0, odd);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) v[i] += odd[i];
+                }
                 finish_block(out_ctx, p, map_out, v, c0, n0, row0);
             }
             // the accumulator may be overwritten once every warp has read its part
@@ -861,13 +930,13 @@ int output_map(const void* base, long rows, long cols, long ld, bool f32, CUtens
     return 0;
 }
 
-template <int BN, int STAGES, bool PAIR>
+template <int BN, int STAGES, bool PAIR, int ISSUERS = 1>
 int launch_rows(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& o, const GemmParams& p, int sms,
                 cudaStream_t s) {
     constexpr size_t smem = rows_shared_bytes<BN, STAGES, PAIR>();
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(gemm_rows_kernel<BN, STAGES, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(gemm_rows_kernel<BN, STAGES, PAIR, ISSUERS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess)
             return fail("gemm: cannot raise the shared memory limit");
         configured = true;
@@ -876,7 +945,7 @@ int launch_rows(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& o
     const int tiles_m = (p.M + tile_rows - 1) / tile_rows, tiles_n = (p.N + BN - 1) / BN;
     const int n_tiles = tiles_m * tiles_n;
     if (!PAIR) {
-        gemm_rows_kernel<BN, STAGES, PAIR><<<std::min(n_tiles, sms), THREADS, smem, s>>>(a, b, o, p, tiles_m, n_tiles);
+        gemm_rows_kernel<BN, STAGES, PAIR, ISSUERS><<<std::min(n_tiles, sms), THREADS + 32 * (ISSUERS - 1), smem, s>>>(a, b, o, p, tiles_m, n_tiles);
         return check_launch("gemm_rows_kernel");
     }
     // two CTAs per tile: a cluster of two
@@ -892,7 +961,7 @@ int launch_rows(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& o
     attribute.val.clusterDim.z = 1;
     config.attrs = &attribute;
     config.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&config, gemm_rows_kernel<BN, STAGES, PAIR>, a, b, o, p, tiles_m, n_tiles);
+    cudaError_t e = cudaLaunchKernelEx(&config, gemm_rows_kernel<BN, STAGES, PAIR, ISSUERS>, a, b, o, p, tiles_m, n_tiles);
     if (e != cudaSuccess) {
         snprintf(g_error_text, MLLM_ERROR_BUFFER, "gemm_rows_kernel (pairs): %s", cudaGetErrorString(e));
         return 2;
@@ -991,9 +1060,11 @@ static int gemm_bf16(void* out, const void* x, const void* w, const float* bias,
     const bool swap = M <= 64 && forced_bn == 0;
     if (!swap) {
         // a tile: 128 tokens x bn features on one CTA, or (code 1000 + bn) 256 tokens x bn on a pair of CTAs
-        const int code = forced_bn != 0 ? forced_bn : rows_tile_width(M, N, K, sms);
-        const bool pair = code >= 1000;
-        const int bn = pair ? code - 1000 : code;
+        // (narrow tiles are issued by two threads: see gemm_rows_kernel)
+        int code = forced_bn != 0 ? forced_bn : rows_tile_width(M, N, K, sms);
+        if (forced_bn == 0 && code <= 128) code += 2000;
+        const bool pair = code >= 1000 && code < 2000;
+        const int bn = code % 1000;
         int rc = tensor_map(x, M, K, ldx, BM, &map_x);
         if (rc) return rc;
         rc = tensor_map(w, N, K, K, pair ? bn / 2 : bn, &map_w);
@@ -1007,12 +1078,15 @@ static int gemm_bf16(void* out, const void* x, const void* w, const float* bias,
         case 128: return launch_rows<128, 4, false>(map_x, map_w, map_out, p, sms, s);
         case 96: return launch_rows<96, 5, false>(map_x, map_w, map_out, p, sms, s);
         case 64: return launch_rows<64, 6, false>(map_x, map_w, map_out, p, sms, s);
+        case 2128: return launch_rows<128, 4, false, 2>(map_x, map_w, map_out, p, sms, s);
+        case 2096: return launch_rows<96, 5, false, 2>(map_x, map_w, map_out, p, sms, s);
+        case 2064: return launch_rows<64, 6, false, 2>(map_x, map_w, map_out, p, sms, s);
         case 1256: return launch_rows<256, 4, true>(map_x, map_w, map_out, p, sms, s);
         case 1192: return launch_rows<192, 5, true>(map_x, map_w, map_out, p, sms, s);
         case 1128: return launch_rows<128, 6, true>(map_x, map_w, map_out, p, sms, s);
         case 1096: return launch_rows<96, 6, true>(map_x, map_w, map_out, p, sms, s);
         case 1064: return launch_rows<64, 6, true>(map_x, map_w, map_out, p, sms, s);
-        default: return fail("gemm: the tile width is 64, 96, 128, 192 or 256");
+        default: return fail("gemm: the tile width is 64, 96, 128, 192 or 256 (1000 + width on pairs of CTAs, 2000 + width up to 128 with two issuing threads)");
         }
     }
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
@@ -1049,9 +1123,8 @@ extern "C" int mllm_gemm_bf16(void* out, const void* x, const void* w, const flo
 extern "C" int mllm_gemm_bf16_tile(void* out, const void* x, const void* w, const float* bias, int M, int N, int K,
                                    long ldx, long ldo, int epilogue, int out_f32, int* status, int tile_width,
                                    unsigned long long* timeline, void* stream) {
-    const int width = tile_width >= 1000 ? tile_width - 1000 : tile_width;       // 1000 + width: on a pair of CTAs
-    if (width != 64 && width != 96 && width != 128 && width != 192 && width != 256)
-        return fail("gemm: the tile width is 64, 96, 128, 192 or 256");
+    // 1000 + width: on a pair of CTAs; 2000 + width: two issuing threads (the launcher refuses what it has not)
+    if (tile_width < 0 || tile_width >= 3000) return fail("gemm: the tile width is 64, 96, 128, 192 or 256");
     return gemm_bf16(out, x, w, bias, M, N, K, ldx, ldo, epilogue, out_f32, status, nullptr, stream, tile_width, timeline);
 }
 

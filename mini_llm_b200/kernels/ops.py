@@ -419,19 +419,20 @@ def gemm_bf16(out, a, w, bias, epilogue, status):
 
 
 _gemm_bf16_tile = Function("gemm", "mllm_gemm_bf16_tile", [P, P, P, P, I, I, I, L, L, I, I, P, I, P, P])
-GEMM_TILE_WIDTHS = (64, 96, 128, 192, 256)        # 1000 + width: tiles of 256 tokens on pairs of CTAs
+GEMM_TILE_WIDTHS = (64, 96, 128, 192, 256)        # 1000 + width: tiles of 256 tokens on pairs of CTAs; 2000 + width (to 128): two issuing threads
 
 
 def gemm_bf16_tile(out, a, w, bias, epilogue, status, tile_width, timeline=None):
     """``gemm_bf16`` through the persistent kernel with tiles of 128 x ``tile_width``, whatever
     the number of rows (tests run every width; the engine lets the library choose).
-    ``timeline``: an int64 device tensor of seven entries that receives time stamps of CTA 0
+    ``timeline``: an int64 device tensor of nine entries that receives time stamps of CTA 0
     (start, set-up done, first operands landed, last product of the first tile issued, first
-    accumulator ready, first epilogue done, end), in nanoseconds."""
+    accumulator ready, first epilogue done, end), in nanoseconds, then the number of blocks of K
+    that CTA's first issuing thread took and how many of them had not arrived at its first look."""
     if timeline is not None:
         _check(timeline, "gemm.timeline", torch.int64, 1)
-        if timeline.shape[0] < 7:
-            raise KernelError("gemm: the timeline has seven entries")
+        if timeline.shape[0] < 9:
+            raise KernelError("gemm: the timeline has nine entries")
     _check(a, "gemm.a", torch.bfloat16, 2)
     _check(w, "gemm.w", torch.bfloat16, 2)
     _check(out, "gemm.out", None, 2)

@@ -21,7 +21,10 @@ CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "D16": TINY_D}
 PAGE_SIZES = {"A": 16, "B": 8, "C": 16, "D": 64, "D16": 16}
 # factor on the query and key weights that brings the scores' spread to about 1 (see
 # engine_helpers.sharpen_attention); it depends on the recipe's weight scale and the width
-SHARPEN = {"A": 6.0, "B": 2.0, "C": 2.0, "D": 1.5}
+# (D: at 1.5 the bfloat16 path's worst error over the schedules below lies at 0.95 to 1.02 of
+# the bound for every seed of the weights, from the rounding of activations alone, so that the
+# order of a sum decides whether a test passes; at 1.25 it lies at 0.7)
+SHARPEN = {"A": 6.0, "B": 2.0, "C": 2.0, "D": 1.25}
 # request lengths per configuration (within n_positions); prompts for the mixed schedule
 LENGTHS = {"A": {"a": 5, "b": 17, "c": 33, "d": 70, "e": 128},
            "B": {"a": 1, "b": 9, "c": 24, "d": 40, "e": 64, "f": 57},

@@ -16,7 +16,8 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(scope="module")
 def folder_d(tmp_path_factory):
-    return make_model(str(tmp_path_factory.mktemp("more_d")), TINY_D, "varied", 3, sharpen=1.5)
+    # (sharpened as in test_engine_gpu.py, which says why not more)
+    return make_model(str(tmp_path_factory.mktemp("more_d")), TINY_D, "varied", 3, sharpen=1.25)
 
 
 @pytest.fixture(scope="module")

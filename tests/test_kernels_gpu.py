@@ -483,14 +483,14 @@ def test_gemm_tcgen05(m, n, k, epilogue):
     np.testing.assert_allclose(f64(out), expected, rtol=0, atol=atol)
 
 
-@pytest.mark.parametrize("width", [64, 96, 128, 192, 256, 1064, 1096, 1128, 1192, 1256])
+@pytest.mark.parametrize("width", [64, 96, 128, 192, 256, 1064, 1096, 1128, 1192, 1256, 2064, 2096, 2128])
 @pytest.mark.parametrize("m, n, k, epilogue", [(300, 1000, 160, "gelu_tanh"), (513, 768, 3072, "add"), (17, 777, 96, "store"),
                                                (2048, 2304, 768, "store"), (4000, 1100, 72, "add"), (129, 50257, 64, "logits"),
                                                (2100, 3072, 256, "gelu_erf")])
 def test_gemm_tcgen05_every_tile_width(m, n, k, epilogue, width):
     """The persistent kernel at each of its tile widths, on single CTAs (128 tokens a tile) and
     on pairs of CTAs (1000 + width: 256 tokens a tile, each CTA loading half of the tile's
-    block of W): tiles that are partly empty in rows and in columns, a pair whose second CTA
+    block of W), and with two issuing threads and two accumulators a tile (2000 + width): tiles that are partly empty in rows and in columns, a pair whose second CTA
     has no rows at all, one tile for some CTAs and a dozen for others (so that both accumulators
     and every phase of the ring are in use), every epilogue; bitwise the same result twice."""
     from mini_llm_b200.kernels import ops
@@ -735,18 +735,47 @@ def test_gemm_tcgen05_scatters_keys_and_values_into_the_pages(m, q_width, kv_wid
     np.testing.assert_allclose(f64(v_pages), want_v, rtol=0, atol=atol)
 
 
+@pytest.mark.parametrize("width", [2064, 2096, 2128, 96, 256])
+def test_gemm_tcgen05_long_runs_of_tiles(width):
+    """Many tiles per CTA and an odd number of blocks along K, thirty launches in a row: with two
+    issuing threads each thread's blocks change between even and odd places of the K range from
+    tile to tile, and every launch must give the same, right result (a thread that looked at a
+    stage's barrier two phases late would take operands that are not there yet)."""
+    from mini_llm_b200.kernels import ops
+    m, n, k = 6000, 800, 1088                      # 47 x 7..13 tiles on 148 CTAs, 17 blocks of K
+    g = torch.Generator(device="cuda").manual_seed(width)
+    a = torch.randn(m, k, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(n, k, device="cuda", generator=g) / math.sqrt(k)).bfloat16()
+    bias = torch.randn(n, device="cuda", generator=g)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    expected = a.float().double() @ w.float().double().T + bias.double()
+    first = None
+    for launch in range(30):
+        out = torch.zeros(m, n, device="cuda", dtype=torch.float32)
+        ops.gemm_bf16_tile(out, a, w, bias, "add", status, width)
+        if first is None:
+            first = out
+            assert float((out.double() - expected).abs().max()) < 2e-4
+        else:
+            assert torch.equal(out, first), f"launch {launch} differs from the first"
+    assert int(status.item()) == 0, "a bounded wait inside the kernel ran out"
+
+
 def test_gemm_tcgen05_time_stamps():
     """The persistent kernel can note when its first CTA passed seven points (start, set-up,
     first operands, last product of the first tile, accumulator ready, first epilogue done,
-    end): the stamps come in that order and span less than a millisecond."""
+    end): the stamps come in that order and span less than a millisecond.  Two counters
+    follow: the blocks of K its first issuing thread took (4 blocks for each of its tiles:
+    20 tiles over at most 20 CTAs, so one tile) and how many had not arrived at its first look."""
     from mini_llm_b200.kernels import ops
     a = torch.randn(600, 256, device="cuda").bfloat16()
     w = (torch.randn(512, 256, device="cuda") / 16).bfloat16()
     out = torch.empty(600, 512, device="cuda", dtype=torch.bfloat16)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    stamps = torch.zeros(7, dtype=torch.int64, device="cuda")
+    stamps = torch.zeros(9, dtype=torch.int64, device="cuda")
     ops.gemm_bf16_tile(out, a, w, None, "store", status, 128, stamps)
     torch.cuda.synchronize()
-    times = stamps.tolist()
+    times, (looked, not_there) = stamps.tolist()[:7], stamps.tolist()[7:]
+    assert looked == 4 and 0 <= not_there <= looked
     assert int(status.item()) == 0 and all(b >= a for a, b in zip(times, times[1:])) and 0 < times[6] - times[0] < 1_000_000
     np.testing.assert_allclose(f64(out), f64(a) @ f64(w).T, rtol=0, atol=tol(torch.bfloat16, 4))
