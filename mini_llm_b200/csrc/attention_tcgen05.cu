@@ -82,6 +82,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // kernel, so the dynamic part starts the CTA's window; should it ever not be aligned, the
     // CTA reports that and does nothing (two CTAs per SM leave no room for slack).
     extern __shared__ __align__(1024) unsigned char smem[];
+    dependents_may_start();
     if ((smem_u32(smem) & 1023u) != 0) {
         if (threadIdx.x == 0) atomicExch(p.status, 14);
         return;
@@ -117,6 +118,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     tcgen05_after_sync();
     const uint32_t tmem_base = *tmem_slot;         // buffer b: columns 128 b ..
     const int total_work = p.n_tiles * p.n_heads;
+    wait_for_earlier_kernels();                    // nothing above reads or writes the step's memory
 
   for (int round = 0;; round++) {
     // ---- the next (record, head); fresh barriers for it ----
@@ -544,8 +546,9 @@ int launch(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v, con
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
         sms = 148;
     const long total = (long)n_tiles * p.n_heads, resident = (long)sms * (D <= 64 ? 2 : 1);
-    attention_tcgen05_kernel<D><<<(unsigned)std::min(total, resident), THREADS, smem, s>>>(q, k, v, p);
-    return check_launch("attention_tcgen05_kernel");
+    const cudaError_t launch_error = launch_kernel(g_dependent_launch != 0, attention_tcgen05_kernel<D>,
+                                                   dim3((unsigned)std::min(total, resident)), dim3(THREADS), smem, s, q, k, v, p);
+    return launched(launch_error, "attention_tcgen05_kernel");
 }
 
 }  // namespace

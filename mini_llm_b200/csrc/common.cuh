@@ -95,6 +95,53 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 #define MLLM_ERROR_BUFFER 512
 
+// ---- programmatic dependent launch ---------------------------------------------------------
+//
+// A kernel launched with launch_kernel(true, ...) may be scheduled while the kernel before it
+// on the stream still runs: its CTAs take the SMs that the earlier kernel's CTAs leave, set up
+// what needs no memory of the step (barriers, tensor memory, index arithmetic) and then wait
+// in wait_for_earlier_kernels(), which returns when every earlier kernel has completed and its
+// writes are visible.  No thread reads or writes global memory that another kernel of the
+// stream touches before it has passed that wait.  A kernel says with dependents_may_start(),
+// at its start, that the next one may be scheduled as soon as all of its own CTAs run.  Both
+// calls do nothing in a kernel that was launched the ordinary way, and stream capture keeps the
+// dependency as an edge of the graph.
+__device__ __forceinline__ void dependents_may_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void wait_for_earlier_kernels() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// (cluster: the CTAs of a thread block cluster, or x = 0 for a launch without clusters)
+template <typename... Params, typename... Args>
+static cudaError_t launch_kernel_in_clusters(bool dependent, dim3 cluster, void (*kernel)(Params...), dim3 grid, dim3 block,
+                                             size_t shared_bytes, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared_bytes;
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2];
+    unsigned count = 0;
+    if (dependent) {
+        attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attributes[count].val.programmaticStreamSerializationAllowed = 1;
+        count++;
+    }
+    if (cluster.x != 0) {
+        attributes[count].id = cudaLaunchAttributeClusterDimension;
+        attributes[count].val.clusterDim.x = cluster.x;
+        attributes[count].val.clusterDim.y = cluster.y;
+        attributes[count].val.clusterDim.z = cluster.z;
+        count++;
+    }
+    config.attrs = attributes;
+    config.numAttrs = count;
+    return cudaLaunchKernelEx(&config, kernel, Params(args)...);
+}
+template <typename... Params, typename... Args>
+static cudaError_t launch_kernel(bool dependent, void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared_bytes,
+                                 cudaStream_t stream, Args... args) {
+    return launch_kernel_in_clusters(dependent, dim3(0, 1, 1), kernel, grid, block, shared_bytes, stream, args...);
+}
+
 #define MLLM_DEFINE_ERROR_API(prefix)                                              \
     static thread_local char g_error_text[MLLM_ERROR_BUFFER] = "";                 \
     extern "C" const char* prefix##_last_error(void) { return g_error_text; }      \
@@ -105,6 +152,15 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     static int check_launch(const char* kernel) {                                  \
         cudaError_t e = cudaGetLastError();                                        \
         if (e == cudaSuccess) return 0;                                            \
+        snprintf(g_error_text, MLLM_ERROR_BUFFER, "%s: %s", kernel,                \
+                 cudaGetErrorString(e));                                           \
+        return 2;                                                                  \
+    }                                                                              \
+    /* whether this library's kernels are launched as dependents (see above) */    \
+    static int g_dependent_launch = 1;                                             \
+    extern "C" void prefix##_set_dependent_launch(int on) { g_dependent_launch = on; } \
+    static int launched(cudaError_t e, const char* kernel) {                       \
+        if (e == cudaSuccess) return check_launch(kernel);                         \
         snprintf(g_error_text, MLLM_ERROR_BUFFER, "%s: %s", kernel,                \
                  cudaGetErrorString(e));                                           \
         return 2;                                                                  \

@@ -59,6 +59,8 @@ template <int MT>      // rows of x per CTA (compile-time bound; M may be smalle
 __global__ void __launch_bounds__(256)
 skinny_linear_kernel(const SkinnyParams p, int n_per_cta) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    dependents_may_start();
+    wait_for_earlier_kernels();
     bf16* xs = reinterpret_cast<bf16*>(smem_raw);            // [MT][K]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * MT;
@@ -189,8 +191,8 @@ static int launch_skinny(const SkinnyParams& p, cudaStream_t s) {
     // columns per CTA: enough CTAs to fill the GPU, at least one column per warp
     int n_per_cta = p.N >= 8192 ? 32 : (p.N >= 2048 ? 16 : 8);
     dim3 grid((p.N + n_per_cta - 1) / n_per_cta, (p.M + MT - 1) / MT);
-    skinny_linear_kernel<MT><<<grid, 256, smem, s>>>(p, n_per_cta);
-    return check_launch("skinny_linear_kernel");
+    return launched(launch_kernel(g_dependent_launch != 0, skinny_linear_kernel<MT>, grid, dim3(256), smem, s, p, n_per_cta),
+                    "skinny_linear_kernel");
 }
 
 extern "C" int mllm_decode_skinny_linear(const SkinnyParams* params, void* stream) {
@@ -229,6 +231,8 @@ split_attention_kernel(bf16* __restrict__ out, long ld_out, const bf16* __restri
                        float* __restrict__ part_ml, int* __restrict__ counters) {
     constexpr int LPK = D / 8;             // lanes per key: each lane owns 8 of the head's dimensions
     constexpr int KPW = 32 / LPK;          // keys per warp per step
+    dependents_may_start();
+    wait_for_earlier_kernels();
     const int t = blockIdx.x, h = blockIdx.y, c = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane % LPK, group = lane / LPK;
@@ -389,10 +393,10 @@ extern "C" int mllm_decode_split_attention(void* out, long ld_out, const void* q
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_tokens, n_heads, max_chunks);
 #define LAUNCH_SPLIT(D)                                                                                              \
-    split_attention_kernel<D><<<grid, 128, 0, s>>>((bf16*)out, ld_out, (const bf16*)q, ld_q, (const bf16*)k_pages,   \
-                                                   (const bf16*)v_pages, block_table, max_blocks, positions,         \
-                                                   token_item, n_heads, n_kv_heads, page_size, scale, window, chunk, \
-                                                   max_chunks, part_acc, part_ml, counters)
+    launch_kernel(g_dependent_launch != 0, split_attention_kernel<D>, grid, dim3(128), 0, s, (bf16*)out, ld_out,     \
+                  (const bf16*)q, ld_q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_blocks,         \
+                  positions, token_item, n_heads, n_kv_heads, page_size, scale, window, chunk, max_chunks, part_acc, \
+                  part_ml, counters)
     switch (head_size) {
     case 16: LAUNCH_SPLIT(16); break;
     case 32: LAUNCH_SPLIT(32); break;
@@ -452,6 +456,8 @@ group_attention_kernel(bf16* __restrict__ out, long ld_out, const bf16* __restri
     constexpr int RING = 256 / D;          // tiles of 16 keys in flight per warp: 4 (D = 64) or 2
     constexpr int TILE_BYTES = 16 * D * 2; // one tile of keys (or values)
     extern __shared__ __align__(16) unsigned char ga_smem[];
+    dependents_may_start();
+    wait_for_earlier_kernels();
     const int t = blockIdx.x, hk = blockIdx.y, c = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tq = lane & 3;
@@ -665,10 +671,10 @@ extern "C" int mllm_decode_group_attention(void* out, long ld_out, const void* q
         configured = true;
     }
 #define LAUNCH_GROUP(D)                                                                                              \
-    group_attention_kernel<D><<<grid, 128, smem, s>>>((bf16*)out, ld_out, (const bf16*)q, ld_q, (const bf16*)k_pages, \
-                                                      (const bf16*)v_pages, block_table, max_blocks, positions,      \
-                                                      token_item, n_heads, n_kv_heads, page_size, scale, window,     \
-                                                      chunk, max_chunks, part_acc, part_ml, counters)
+    launch_kernel(g_dependent_launch != 0, group_attention_kernel<D>, grid, dim3(128), smem, s, (bf16*)out, ld_out,  \
+                  (const bf16*)q, ld_q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_blocks,         \
+                  positions, token_item, n_heads, n_kv_heads, page_size, scale, window, chunk, max_chunks, part_acc, \
+                  part_ml, counters)
     if (head_size == 64) LAUNCH_GROUP(64);
     else LAUNCH_GROUP(128);
 #undef LAUNCH_GROUP
@@ -685,6 +691,8 @@ __global__ void __launch_bounds__(256)
 layernorm_warp_kernel(bf16* __restrict__ out, const float* __restrict__ x, const float* __restrict__ gamma,
                       const float* __restrict__ beta, const int* __restrict__ rows, int n_rows, int width, float eps) {
     constexpr int HELD = 8;
+    dependents_may_start();
+    wait_for_earlier_kernels();
     const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (r >= n_rows) return;
@@ -743,9 +751,9 @@ extern "C" int mllm_decode_layernorm(void* out, const float* x, const float* gam
                                      int n_rows, int width, float eps, void* stream) {
     if (n_rows <= 0) return 0;
     if (width <= 0 || width % 4 != 0) return fail("layernorm: the width must be a multiple of 4");
-    layernorm_warp_kernel<<<(n_rows + 7) / 8, 256, 0, (cudaStream_t)stream>>>((bf16*)out, x, gamma, beta, rows, n_rows,
-                                                                              width, eps);
-    return check_launch("layernorm_warp_kernel");
+    return launched(launch_kernel(g_dependent_launch != 0, layernorm_warp_kernel, dim3((n_rows + 7) / 8), dim3(256), 0,
+                                  (cudaStream_t)stream, (bf16*)out, x, gamma, beta, rows, n_rows, width, eps),
+                    "layernorm_warp_kernel");
 }
 
 // ---------------------------------------------------------------------------

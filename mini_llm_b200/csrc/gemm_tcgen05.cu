@@ -150,6 +150,7 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // element offset of each of the tile's tokens in the cache pages (scatter only)
     long* kv_off = reinterpret_cast<long*>(smem + STAGES * (A_BYTES + B_BYTES) + (2 * STAGES + 1) * 8 + 16);
 
+    dependents_may_start();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_a = blockIdx.x;      // which block of 128 output features
     const int tile_b = blockIdx.y;      // which block of BN tokens
@@ -177,6 +178,7 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    wait_for_earlier_kernels();          // nothing above reads or writes the step's memory
 
     if (warp == 8) {
         // ---- producer ----
@@ -566,6 +568,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     long* kv_off_all = reinterpret_cast<long*>(tmem_slot + 4);            // [2][128] element offset of each token in the cache pages
     float* bias_all = reinterpret_cast<float*>(kv_off_all + 2 * BM);      // [2][256] the tile's biases (zeros without a bias)
 
+    dependents_may_start();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_k = (p.K + BK - 1) / BK;
     const bool stamps = p.timeline != nullptr && blockIdx.x == 0;
@@ -611,6 +614,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         __syncthreads();
     }
 
+    wait_for_earlier_kernels();          // nothing above reads or writes the step's memory (the stamps are the caller's own)
     if (stamps && threadIdx.x == 0) p.timeline[1] = now_ns();
     // Each issuing thread has a ring of stages of its own (the first RING0 stages, the rest),
     // filled by the producer in the order in which that thread takes its blocks.  A stage that
@@ -880,27 +884,12 @@ int launch_swapped(const CUtensorMap& a, const CUtensorMap& b, const GemmParams&
     }
     if (grid.z > 1) {
         // the CTAs that share a tile along K form a cluster (they read each other's shared memory)
-        cudaLaunchConfig_t config = {};
-        config.gridDim = grid;
-        config.blockDim = dim3(THREADS);
-        config.dynamicSmemBytes = smem;
-        config.stream = s;
-        cudaLaunchAttribute attribute;
-        attribute.id = cudaLaunchAttributeClusterDimension;
-        attribute.val.clusterDim.x = 1;
-        attribute.val.clusterDim.y = 1;
-        attribute.val.clusterDim.z = grid.z;
-        config.attrs = &attribute;
-        config.numAttrs = 1;
-        cudaError_t e = cudaLaunchKernelEx(&config, gemm_swapped_kernel<BN, STAGES>, a, b, p);
-        if (e != cudaSuccess) {
-            snprintf(g_error_text, MLLM_ERROR_BUFFER, "gemm_swapped_kernel (cluster of %u): %s", grid.z, cudaGetErrorString(e));
-            return 2;
-        }
-        return 0;
+        return launched(launch_kernel_in_clusters(g_dependent_launch != 0, dim3(1, 1, grid.z), gemm_swapped_kernel<BN, STAGES>, grid,
+                                                  dim3(THREADS), smem, s, a, b, p),
+                        "gemm_swapped_kernel (clusters)");
     }
-    gemm_swapped_kernel<BN, STAGES><<<grid, THREADS, smem, s>>>(a, b, p);
-    return check_launch("gemm_swapped_kernel");
+    return launched(launch_kernel(g_dependent_launch != 0, gemm_swapped_kernel<BN, STAGES>, grid, dim3(THREADS), smem, s, a, b, p),
+                    "gemm_swapped_kernel");
 }
 
 // The map of a result [rows, cols] (bfloat16 or fp32, row stride ld elements) for boxes of 32
@@ -944,29 +933,15 @@ int launch_rows(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& o
     const int tile_rows = PAIR ? 2 * BM : BM;
     const int tiles_m = (p.M + tile_rows - 1) / tile_rows, tiles_n = (p.N + BN - 1) / BN;
     const int n_tiles = tiles_m * tiles_n;
-    if (!PAIR) {
-        gemm_rows_kernel<BN, STAGES, PAIR, ISSUERS><<<std::min(n_tiles, sms), THREADS + 32 * (ISSUERS - 1), smem, s>>>(a, b, o, p, tiles_m, n_tiles);
-        return check_launch("gemm_rows_kernel");
-    }
+    if (!PAIR)
+        return launched(launch_kernel(g_dependent_launch != 0, gemm_rows_kernel<BN, STAGES, PAIR, ISSUERS>, dim3(std::min(n_tiles, sms)),
+                                      dim3(THREADS + 32 * (ISSUERS - 1)), smem, s, a, b, o, p, tiles_m, n_tiles),
+                        "gemm_rows_kernel");
     // two CTAs per tile: a cluster of two
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(2 * std::min(n_tiles, sms / 2));
-    config.blockDim = dim3(THREADS);
-    config.dynamicSmemBytes = smem;
-    config.stream = s;
-    cudaLaunchAttribute attribute;
-    attribute.id = cudaLaunchAttributeClusterDimension;
-    attribute.val.clusterDim.x = 2;
-    attribute.val.clusterDim.y = 1;
-    attribute.val.clusterDim.z = 1;
-    config.attrs = &attribute;
-    config.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&config, gemm_rows_kernel<BN, STAGES, PAIR, ISSUERS>, a, b, o, p, tiles_m, n_tiles);
-    if (e != cudaSuccess) {
-        snprintf(g_error_text, MLLM_ERROR_BUFFER, "gemm_rows_kernel (pairs): %s", cudaGetErrorString(e));
-        return 2;
-    }
-    return 0;
+    return launched(launch_kernel_in_clusters(g_dependent_launch != 0, dim3(2, 1, 1), gemm_rows_kernel<BN, STAGES, PAIR, ISSUERS>,
+                                              dim3(2 * std::min(n_tiles, sms / 2)), dim3(THREADS), smem, s, a, b, o, p, tiles_m,
+                                              n_tiles),
+                    "gemm_rows_kernel (pairs)");
 }
 
 }  // namespace

@@ -23,6 +23,8 @@ template <typename W>
 __global__ void embed_kernel(float* __restrict__ out, const int* __restrict__ ids,
                              const int* __restrict__ positions, const W* __restrict__ table,
                              const W* __restrict__ position_table, int width) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
     int t = blockIdx.x;
     long row = (long)ids[t] * width;
     if (position_table != nullptr) {
@@ -52,11 +54,11 @@ extern "C" int mllm_plain_embed(float* out, const int* ids, const int* positions
     cudaStream_t s = (cudaStream_t)stream;
     int threads = width >= 256 ? 256 : 64;
     if (table_dtype == DT_F32)
-        embed_kernel<float><<<n_tokens, threads, 0, s>>>(out, ids, positions, (const float*)table,
-                                                         (const float*)position_table, width);
+        launch_kernel(g_dependent_launch != 0, embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, out, ids, positions,
+                      (const float*)table, (const float*)position_table, width);
     else if (table_dtype == DT_BF16)
-        embed_kernel<bf16><<<n_tokens, threads, 0, s>>>(out, ids, positions, (const bf16*)table,
-                                                        (const bf16*)position_table, width);
+        launch_kernel(g_dependent_launch != 0, embed_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, out, ids, positions,
+                      (const bf16*)table, (const bf16*)position_table, width);
     else
         return fail("embed: unknown table dtype");
     return check_launch("embed_kernel");

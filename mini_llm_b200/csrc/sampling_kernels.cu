@@ -96,6 +96,8 @@ sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, long
     extern __shared__ float probs[];
     __shared__ float sv[33];
     __shared__ int si[32];
+    dependents_may_start();
+    wait_for_earlier_kernels();
     int r = blockIdx.x;
     const float* x = logits + (long)r * ld;
     float temp = temperature ? temperature[r] : 0.0f;
@@ -181,6 +183,8 @@ sample_rows_sliced_kernel(int* __restrict__ out, const float* __restrict__ logit
     __shared__ float sv[33];
     __shared__ int si[32];
     __shared__ int is_last;
+    dependents_may_start();
+    wait_for_earlier_kernels();
     const int r = blockIdx.x, slice = blockIdx.y;
     if (top_p != nullptr && top_p[r] < 1.0f && temperature != nullptr && temperature[r] > 0.0f) return;
     const float* x = logits + (long)r * ld;
@@ -287,6 +291,8 @@ nucleus_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, lon
     __shared__ float slots[2];
     __shared__ float best_value;
     __shared__ int best_index;
+    dependents_may_start();
+    wait_for_earlier_kernels();
     const int r = blockIdx.x / NUCLEUS_CLUSTER;
     const uint32_t rank = cluster_rank_of_cta();
     const float temp = temperature[r], nucleus = top_p[r];
@@ -377,9 +383,10 @@ static int launch_sample_rows(int* out, const float* logits, long ld, int n_rows
         cudaGetLastError();
     }
     const bool cached = top_p != nullptr && (long)vocab * 4 <= (long)smem_limit;
-    sample_rows_kernel<<<n_rows, 1024, cached ? (size_t)vocab * 4 : 0, s>>>(out, logits, ld, vocab, temperature, top_p, seeds,
-                                                                           counters, only_nucleus, cached ? 1 : 0);
-    return check_launch("sample_rows_kernel");
+    return launched(launch_kernel(g_dependent_launch != 0, sample_rows_kernel, dim3(n_rows), dim3(1024),
+                                  cached ? (size_t)vocab * 4 : 0, s, out, logits, ld, vocab, temperature, top_p, seeds, counters,
+                                  only_nucleus, cached ? 1 : 0),
+                    "sample_rows_kernel");
 }
 
 // The rows with a nucleus cut only: by the cluster kernel when the vocabulary fits its
@@ -388,9 +395,10 @@ static int launch_nucleus_rows(int* out, const float* logits, long ld, int n_row
                                const float* top_p, const unsigned long long* seeds, const int* counters, cudaStream_t s) {
     if (temperature == nullptr || top_p == nullptr) return 0;        // no row has a cut
     if (vocab <= NUCLEUS_CLUSTER * 1024 * NUCLEUS_PER) {
-        nucleus_rows_kernel<NUCLEUS_PER><<<n_rows * NUCLEUS_CLUSTER, 1024, 0, s>>>(out, logits, ld, vocab, temperature, top_p,
-                                                                                   seeds, counters);
-        return check_launch("nucleus_rows_kernel");
+        // (the cluster's size is part of the kernel's declaration)
+        return launched(launch_kernel(g_dependent_launch != 0, nucleus_rows_kernel<NUCLEUS_PER>, dim3(n_rows * NUCLEUS_CLUSTER),
+                                      dim3(1024), 0, s, out, logits, ld, vocab, temperature, top_p, seeds, counters),
+                        "nucleus_rows_kernel");
     }
     return launch_sample_rows(out, logits, ld, n_rows, vocab, temperature, top_p, seeds, counters, 1, s);
 }
@@ -405,9 +413,9 @@ extern "C" int mllm_sampling_sample_rows_sliced(int* out, const float* logits, l
     if (n_rows <= 0) return 0;
     if (vocab <= 0) return fail("sample_rows: empty vocabulary");
     cudaStream_t s = (cudaStream_t)stream;
-    sample_rows_sliced_kernel<<<dim3(n_rows, SAMPLE_SLICES), 256, 0, s>>>(out, logits, ld, vocab, temperature, top_p,
-                                                                         seeds, counters, part_value, part_index, done);
-    int rc = check_launch("sample_rows_sliced_kernel");
+    int rc = launched(launch_kernel(g_dependent_launch != 0, sample_rows_sliced_kernel, dim3(n_rows, SAMPLE_SLICES), dim3(256), 0, s,
+                                    out, logits, ld, vocab, temperature, top_p, seeds, counters, part_value, part_index, done),
+                      "sample_rows_sliced_kernel");
     if (rc == 0 && any_nucleus) rc = launch_nucleus_rows(out, logits, ld, n_rows, vocab, temperature, top_p, seeds, counters, s);
     return rc;
 }
@@ -439,6 +447,8 @@ extern "C" int mllm_sampling_sample_rows(int* out, const float* logits, long ld,
 // ---------------------------------------------------------------------------
 __global__ void keep_tokens_kernel(int* __restrict__ kept, const int* __restrict__ slots,
                                    const int* __restrict__ tokens, int n, int n_kept) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= n) return;
     const int slot = slots[r];
@@ -446,6 +456,8 @@ __global__ void keep_tokens_kernel(int* __restrict__ kept, const int* __restrict
 }
 
 __global__ void resolve_tokens_kernel(int* __restrict__ ids, const int* __restrict__ kept, int n, int n_kept) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= n) return;
     const int id = ids[t];
@@ -457,12 +469,14 @@ __global__ void resolve_tokens_kernel(int* __restrict__ ids, const int* __restri
 extern "C" int mllm_sampling_keep_tokens(int* kept, const int* slots, const int* tokens, int n, int n_kept,
                                          void* stream) {
     if (n <= 0) return 0;
-    keep_tokens_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(kept, slots, tokens, n, n_kept);
-    return check_launch("keep_tokens_kernel");
+    return launched(launch_kernel(g_dependent_launch != 0, keep_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0,
+                                  (cudaStream_t)stream, kept, slots, tokens, n, n_kept),
+                    "keep_tokens_kernel");
 }
 
 extern "C" int mllm_sampling_resolve_tokens(int* ids, const int* kept, int n, int n_kept, void* stream) {
     if (n <= 0) return 0;
-    resolve_tokens_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(ids, kept, n, n_kept);
-    return check_launch("resolve_tokens_kernel");
+    return launched(launch_kernel(g_dependent_launch != 0, resolve_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0,
+                                  (cudaStream_t)stream, ids, kept, n, n_kept),
+                    "resolve_tokens_kernel");
 }

@@ -12,6 +12,7 @@ argument types).
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 
 from . import build
@@ -23,6 +24,20 @@ class KernelError(RuntimeError):
 
 _libraries: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
+_dependent_launch = os.environ.get("MLLM_DEPENDENT_LAUNCH", "1") != "0"
+
+
+def set_dependent_launch(on: bool) -> None:
+    """Whether kernels are launched as programmatic dependents of the kernel before them on
+    their stream (they may be scheduled and set themselves up while it still runs, and wait
+    for its end before they touch memory), in every library, loaded already or later.  On by
+    default; off, every kernel starts after the one before it has ended."""
+    global _dependent_launch
+    with _lock:
+        _dependent_launch = bool(on)
+        for name, lib in _libraries.items():
+            getattr(lib, f"mllm_{name}_set_dependent_launch")(int(_dependent_launch))
+
 
 
 def load(name: str) -> ctypes.CDLL:
@@ -39,6 +54,9 @@ def load(name: str) -> ctypes.CDLL:
                 raise KernelError(f"cannot load kernel library {path}: {error}") from None
             last_error = getattr(_libraries[name], f"mllm_{name}_last_error")
             last_error.restype = ctypes.c_char_p
+            switch = getattr(_libraries[name], f"mllm_{name}_set_dependent_launch")
+            switch.argtypes, switch.restype = [ctypes.c_int], None
+            switch(int(_dependent_launch))
         return _libraries[name]
 
 

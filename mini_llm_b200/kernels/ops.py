@@ -12,7 +12,7 @@ import ctypes
 
 import torch
 
-from .lib import F, I, L, P, Function, KernelError
+from .lib import F, I, L, P, Function, KernelError, set_dependent_launch  # noqa: F401  (re-exported)
 
 DT_F32, DT_BF16 = 0, 1
 EPILOGUES = {"store": 0, "gelu_tanh": 1, "gelu_erf": 2, "add": 3}

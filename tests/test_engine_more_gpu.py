@@ -180,6 +180,48 @@ def test_prompt_steps_replayed_from_a_captured_graph(folder_d):
 
 # ---- looking inside ------------------------------------------------------------------------------
 
+def test_kernels_launched_as_dependents_give_the_same_logits(folder_d):
+    """Kernels are launched so that each may be scheduled, and set itself up, while the one
+    before it still runs; it waits for that kernel's end before it touches memory.  With that
+    switched off every kernel starts after the last has ended.  Both ways give the same logits
+    bit for bit, step by step and from captured graphs: prompts in portions beside decoding
+    requests on pages that are used again, and decode steps of forty requests (part by part)."""
+    from mini_llm_b200.engine import Engine, StepEntry
+    from mini_llm_b200.kernels import ops
+    vocab, decode_steps = TINY_D["vocab_size"], 6
+    lengths = {"a": 300, "b": 45, "c": 131, "d": 2, "e": 260, "f": 90}
+    requests = {n: random_tokens(900 + i, count, vocab) for i, (n, count) in enumerate(lengths.items())}
+    prompts = {n: max(1, 2 * len(t) // 3) for n, t in requests.items()}
+    many = {f"m{i}": random_tokens(950 + i, 20 + 3 * i + decode_steps, vocab) for i in range(40)}
+    results = {}
+    try:
+        for on in (True, False):
+            ops.set_dependent_launch(on)
+            engine = Engine(folder_d, dtype="bfloat16", page_size=16, cache_tokens=304 + 272 + 144 + 96, max_requests=4)
+            steps = schedule_mixed(requests, prompts, max_live=4, portion_sizes=(66, 2, 140, 5, 31))
+            got = run_schedule(engine, requests, steps)
+            engine.check_status()
+            wide = Engine(folder_d, dtype="bfloat16", page_size=16, cache_tokens=8192, max_requests=40, max_tokens_per_step=4096)
+            slots = {name: wide.open_request() for name in many}
+            names = list(many)
+            for first in range(0, 40, 10):
+                wide.step([StepEntry(slots[n], many[n][:-decode_steps], []) for n in names[first:first + 10]])
+            rows = []
+            for step in range(decode_steps):
+                rows.append(wide.step([StepEntry(slots[n], [many[n][len(many[n]) - decode_steps + step]], [0])
+                                       for n in names]).cpu().numpy())
+            wide.check_status()
+            assert wide.step_kinds["replayed"] > 0
+            got["forty"] = np.stack(rows)
+            results[on] = got
+            del engine, wide
+    finally:
+        ops.set_dependent_launch(True)
+    compare(folder_d, "bfloat16", results[True], requests)
+    for name in results[True]:
+        assert np.array_equal(results[True][name], results[False][name]), name
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_stored_keys_and_values_and_the_residual_stream(folder_d, dtype):
     """What the cache holds for a request that came in portions equals norm + projection of
