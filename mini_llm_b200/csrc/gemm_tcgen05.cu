@@ -130,6 +130,55 @@ __device__ __forceinline__ void store_rows_bf16(const float* turn, bf16* base, R
     else store_rows_bf16_as<EPI_STORE>(turn, base, row_offset, paired, col_ok, lane, rows_left, bias);
 }
 
+// The end of a tile that the SPLITS CTAs of a cluster share along K.  Every CTA has left its
+// partial sums in its shared memory ([token][128 features]); CTA `rank` finishes the tokens
+// rank, rank + SPLITS, ...: thread (feature r, half) takes every other one of them.  All loads
+// are asked for before any sum is formed: a load from another CTA's shared memory, and the old
+// value of a residual sum from global memory, each take hundreds of cycles, and one after the
+// other they were most of this kernel's time.  A CTA starts with its own part and goes round
+// the cluster from there, so that the CTAs do not all read from the same one at once; the
+// order of a sum depends on the token only, never on timing.
+template <int BN, int SPLITS>
+__device__ __forceinline__ void finish_split(const GemmParams& p, const float* part, const long* kv_off, float b, int r, int tile_b,
+                                             int tokens, int rank, int half) {
+    constexpr int MINE = (BN + 2 * SPLITS - 1) / (2 * SPLITS);
+    const int c0 = rank + SPLITS * half;
+    float value[MINE][SPLITS], old[MINE];
+#pragma unroll
+    for (int i = 0; i < MINE; i++) {
+        const int c = c0 + i * 2 * SPLITS;
+        old[i] = 0.0f;
+        if (p.epilogue == EPI_ADD && c < tokens) old[i] = reinterpret_cast<const float*>(p.out)[(long)(tile_b * BN + c) * p.ldo + r];
+    }
+#pragma unroll
+    for (int z = 0; z < SPLITS; z++)
+#pragma unroll
+        for (int i = 0; i < MINE; i++) {
+            const int c = c0 + i * 2 * SPLITS;
+            value[i][z] = c < tokens ? load_from_rank(part + c * BM, (uint32_t)((rank + z) % SPLITS)) : 0.0f;
+        }
+#pragma unroll
+    for (int i = 0; i < MINE; i++) {
+        const int c = c0 + i * 2 * SPLITS;
+        if (c >= tokens) continue;
+        float sum = 0.0f;
+#pragma unroll
+        for (int z = 0; z < SPLITS; z++) sum += value[i][z];
+        const float x = sum + b;
+        const int t = tile_b * BN + c;
+        if (p.k_pages != nullptr && r >= p.q_width) {
+            const long slot = kv_off[c];
+            if (r < p.q_width + p.kv_width) p.k_pages[slot + r - p.q_width] = __float2bfloat16_rn(x);
+            else p.v_pages[slot + r - p.q_width - p.kv_width] = __float2bfloat16_rn(x);
+            continue;
+        }
+        const long at = (long)t * p.ldo + r;
+        if (p.epilogue == EPI_ADD) reinterpret_cast<float*>(p.out)[at] = old[i] + x;
+        else if (p.out_f32) reinterpret_cast<float*>(p.out)[at] = x;
+        else reinterpret_cast<bf16*>(p.out)[at] = __float2bfloat16_rn(activate(x, p.epilogue));
+    }
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_swapped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -326,23 +375,20 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         cluster_sync();
         if (warp < 8 && !*failed) {
             // CTA `rank` finishes the tokens rank, rank + splits, ...: it adds the partial sums
-            // of all CTAs in their order, so the result does not depend on timing.  Thread t
-            // keeps feature t % 128 (the row it read from tensor memory) and every other token.
+            // of all CTAs in an order that the token fixes, so the result does not depend on
+            // timing.  Thread t keeps feature t % 128 (the row it read from tensor memory).
             const int quarter = warp & 3;
             const int r = tile_a * BM + quarter * 32 + lane;
             const bool row_ok = r < p.N;
             const float b = (row_ok && p.bias != nullptr) ? p.bias[r] : 0.0f;
             const float* part = reinterpret_cast<const float*>(smem) + quarter * 32 + lane;
             const int tokens = min(BN, p.M - tile_b * BN), rank = (int)cluster_rank();
-            for (int c = rank + p.splits * (warp >> 2); row_ok && c < tokens; c += 2 * p.splits) {
-                float sum = 0.0f;
-                for (int z = 0; z < p.splits; z++) sum += load_from_rank(part + c * BM, (uint32_t)z);
-                const float x = sum + b;
-                const int t = tile_b * BN + c;
-                const long at = (long)t * p.ldo + r;
-                if (p.epilogue == EPI_ADD) reinterpret_cast<float*>(p.out)[at] += x;
-                else if (p.out_f32) reinterpret_cast<float*>(p.out)[at] = x;
-                else reinterpret_cast<bf16*>(p.out)[at] = __float2bfloat16_rn(activate(x, p.epilogue));
+            if (row_ok) {
+                switch (p.splits) {
+                case 2: finish_split<BN, 2>(p, part, kv_off, b, r, tile_b, tokens, rank, warp >> 2); break;
+                case 4: finish_split<BN, 4>(p, part, kv_off, b, r, tile_b, tokens, rank, warp >> 2); break;
+                default: finish_split<BN, 8>(p, part, kv_off, b, r, tile_b, tokens, rank, warp >> 2); break;
+                }
             }
         }
         __syncwarp();
@@ -1072,15 +1118,14 @@ static int gemm_bf16(void* out, const void* x, const void* w, const float* bias,
     dim3 grid((N + BM - 1) / BM, (M + bn - 1) / bn);
     {
         // Few tiles: share each among a cluster of 8, 4 or 2 CTAs along K, so that more SMs
-        // stream the weights (at least two k blocks per CTA; not with the cache scatter)
+        // stream the weights (at least two k blocks per CTA)
         const int tiles = grid.x * grid.y, all_k = (K + BK - 1) / BK;
-        if (scatter == nullptr)
-            for (int splits = 8; splits >= 2; splits /= 2)
-                if (tiles * splits <= sms && all_k / splits >= 2) {
-                    p.splits = splits;
-                    grid.z = splits;
-                    break;
-                }
+        for (int splits = 8; splits >= 2; splits /= 2)
+            if (tiles * splits <= sms && all_k / splits >= 2) {
+                p.splits = splits;
+                grid.z = splits;
+                break;
+            }
     }
     if (bn == 16) return launch_swapped<16, 8>(map_w, map_x, p, grid, s);
     if (bn == 32) return launch_swapped<32, 8>(map_w, map_x, p, grid, s);
