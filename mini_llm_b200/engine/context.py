@@ -190,6 +190,7 @@ class StepContext:
         self.n_att_tiles = 0          # records (CTAs) of the work list
         self.n_split_tiles = 0        # tiles among them that come in several parts
         self.att_parts = 1            # most parts of a tile
+        self.att_units = False        # the work list holds units of up to 256 tokens (two tiles) instead of tiles
 
     def buffer(self, tag: str, shape, dtype):
         return self.workspace.get(tag, shape, dtype)

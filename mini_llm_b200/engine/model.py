@@ -34,6 +34,11 @@ class Model:
         self.graph_safe = all(getattr(part, "graph_safe", False) for part in self.parts())
         # The step makes a work list of attention tiles only if some part says it reads one.
         self.wants_attention_tiles = any(getattr(part, "wants_attention_tiles", False) for part in self.parts())
+        # A step of long portions may bring its work list as units of 256 tokens instead, if
+        # every part that reads the list can read those too: then this is their number of heads
+        # (the step shares long units among so many CTAs that heads x CTAs fill the GPU), else 0.
+        heads = {getattr(part, "attention_unit_heads", 0) for part in self.parts() if getattr(part, "wants_attention_tiles", False)}
+        self.attention_unit_heads = heads.pop() if len(heads) == 1 else 0
 
     def parts(self):
         found = [self.embedding]

@@ -230,9 +230,17 @@ class Kernels:
         if (not self.plain_only and ctx.att_tiles is not None
                 and ops.attention_prefill_takes(q, head_size, cache.page_size)):
             scratch = None
+            rows = ops.ATTENTION_UNIT if ctx.att_units else ops.ATTENTION_TILE
             if ctx.att_parts > 1:
                 scratch = self._attention_scratch(ctx.device, ctx.n_split_tiles * n_heads, ops.ATTENTION_MAX_PARTS
-                                                  * ops.ATTENTION_TILE * (head_size + 4))
+                                                  * rows * (head_size + 4))
+            if ctx.att_units:
+                self.chose("attention", "attention_two_tiles", n, n_heads, head_size)
+                return ops.attention_prefill_two_tiles(out, q, cache.k_pages, cache.v_pages, cache.block_table,
+                                                       ctx.att_tiles, ctx.n_att_tiles, n_heads, n_kv_heads, head_size,
+                                                       cache.page_size, scale, window, self.status(ctx.device),
+                                                       self.attention_work(ctx.device), scratch, ctx.n_split_tiles,
+                                                       ops.ATTENTION_MAX_PARTS if ctx.att_parts > 1 else 1)
             self.chose("attention", "attention_tcgen05", n, n_heads, head_size)
             return ops.attention_prefill(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.att_tiles,
                                          ctx.n_att_tiles, n_heads, n_kv_heads, head_size, cache.page_size, scale,

@@ -589,6 +589,88 @@ def attention_prefill(out, q, k_pages, v_pages, block_table, tiles, n_tiles, n_h
     return out
 
 
+_attention_prefill_two_tiles = Function("attention", "mllm_attention_prefill_two_tiles",
+                                        [P, L, P, L, L, L, P, P, I, I, P, I, P, I, I, I, I, F, I, P, P, P, I, P, P])
+ATTENTION_UNIT = 2 * ATTENTION_TILE     # queries per CTA of attention_prefill_two_tiles
+
+
+def attention_units(item_offsets, item_counts, item_starts, n_heads=1, n_sms=148):
+    """The work list of attention_prefill_two_tiles: units of up to 256 consecutive tokens of
+    one entry, one record per CTA: (entry, first row, rows, position of the first row, part,
+    parts, number of the unit among the split ones, key blocks of the part), sorted by falling
+    number of key blocks.  While the step's records times ``n_heads`` leave SMs idle, the unit
+    with the most key blocks per part is given one more part (up to eight, and not below two
+    blocks a part), so that the step's longest CTA gets shorter.
+    Returns (records, number of split units, most parts of a unit)."""
+    units = []
+    for item, (offset, count, start) in enumerate(zip(item_offsets, item_counts, item_starts)):
+        for first in range(0, count, ATTENTION_UNIT):
+            rows = min(ATTENTION_UNIT, count - first)
+            units.append([item, offset + first, rows, start + first, (start + first + rows - 1) // ATTENTION_TILE + 1, 1])
+    n_records = len(units)
+    while units and (n_records + 1) * n_heads <= n_sms:
+        longest = max(units, key=lambda u: -(-u[4] // u[5]))
+        if -(-longest[4] // longest[5]) < 3 or longest[5] >= ATTENTION_MAX_PARTS:
+            break
+        longest[5] += 1
+        n_records += 1
+    records, n_split, most = [], 0, 1
+    for item, first_row, rows, position, blocks, parts in units:
+        share = -(-blocks // parts)
+        for part in range(parts):
+            records.append((item, first_row, rows, position, part, parts, n_split if parts > 1 else 0,
+                            max(0, min(share, blocks - part * share))))
+        if parts > 1:
+            n_split += 1
+            most = max(most, parts)
+    records.sort(key=lambda record: -record[7])
+    return records, n_split, most
+
+
+def attention_prefill_two_tiles(out, q, k_pages, v_pages, block_table, units, n_units, n_heads, n_kv_heads, head_size,
+                                page_size, scale, window, status, work, scratch=None, n_split=0, max_parts=1):
+    """``attention_prefill`` for steps with long portions: one CTA per (record of the work
+    list, head), each half of the unit with softmax warps of its own, one thread per query
+    row; head size 64.  ``units``: device int32 [>= n_units, 8] from ``attention_units``.
+    ``scratch``: (fp32 partial states, zeroed int32 counters) when units come in parts:
+    n_split * heads * max_parts * 256 * (head_size + 4) floats and n_split * heads counters."""
+    _check(out, "attention_prefill.out", torch.bfloat16, 2)
+    _check(q, "attention_prefill.q", torch.bfloat16, 2)
+    _check(k_pages, "attention_prefill.k_pages", torch.bfloat16, 4)
+    _check(v_pages, "attention_prefill.v_pages", torch.bfloat16, 4)
+    _check(block_table, "attention_prefill.block_table", torch.int32, 2)
+    _check(units, "attention_prefill.units", torch.int32)
+    _check(status, "attention_prefill.status", torch.int32)
+    _check(work, "attention_prefill.work", torch.int32, 1)
+    if work.shape[0] < 2:
+        raise KernelError("attention_prefill: the work counter has two entries")
+    if head_size != 64 or not attention_prefill_takes(q, head_size, page_size):
+        raise KernelError(f"attention_prefill_two_tiles does not take head size {head_size} with pages of {page_size}")
+    n_pages = k_pages.shape[0]
+    if tuple(k_pages.shape) != (n_pages, page_size, n_kv_heads, head_size) or v_pages.shape != k_pages.shape:
+        raise KernelError("attention_prefill: pages must be [n_pages, page_size, kv_heads, head_size]")
+    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous():
+        raise KernelError("attention_prefill: pages and block table must be contiguous")
+    if q.shape[1] != n_heads * head_size or out.shape != q.shape or units.numel() < ATTENTION_TILE_RECORD * n_units:
+        raise KernelError("attention_prefill: q / out / units do not fit")
+    partial = counters = None
+    if max_parts > 1:
+        if scratch is None:
+            raise KernelError("attention_prefill: units in parts need scratch")
+        partial, counters = scratch
+        _check(partial, "attention_prefill.scratch", torch.float32, 1)
+        _check(counters, "attention_prefill.scratch", torch.int32, 1)
+        if (partial.shape[0] < n_split * n_heads * max_parts * ATTENTION_UNIT * (head_size + 4)
+                or counters.shape[0] < n_split * n_heads):
+            raise KernelError("attention_prefill: scratch too small")
+    _attention_prefill_two_tiles(out.data_ptr(), out.stride(0), q.data_ptr(), q.shape[0], q.shape[1], q.stride(0),
+                                 k_pages.data_ptr(), v_pages.data_ptr(), n_pages, page_size, block_table.data_ptr(),
+                                 block_table.shape[1], units.data_ptr(), n_units, n_heads, n_kv_heads, head_size,
+                                 float(scale), int(window or 0), status.data_ptr(), _ptr(partial), _ptr(counters),
+                                 int(max_parts), work.data_ptr(), _stream())
+    return out
+
+
 _sample_rows_sliced = Function("sampling", "mllm_sampling_sample_rows_sliced",
                                [P, P, L, I, I, P, P, P, P, P, P, P, I, P])
 SAMPLE_SLICES = 32

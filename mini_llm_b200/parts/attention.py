@@ -32,6 +32,8 @@ from .spec import PagedKV, WeightSpec
 class CausalSelfAttention(Mixer):
     graph_safe = True
     wants_attention_tiles = True      # its prompt kernel reads the step's work list of (128 queries, entry) tiles
+    # (set per instance: its head count if it can also read a work list of units of 256 queries, else 0)
+    attention_unit_heads = 0
     def __init__(self, prefix, width: int, n_heads: int, head_size: int, score_scale: float,
                  n_kv_heads: int | None = None, window: int | None = None,
                  qkv_name: str = "c_attn", out_name: str = "c_proj", stored_in_out: bool = True,
@@ -41,6 +43,7 @@ class CausalSelfAttention(Mixer):
         self.n_heads = int(n_heads)
         self.n_kv_heads = int(n_kv_heads if n_kv_heads is not None else n_heads)
         self.head_size = int(head_size)
+        self.attention_unit_heads = self.n_heads if self.head_size == 64 else 0
         self.score_scale = float(score_scale)
         self.window = int(window) if window else None
         self.qkv_name, self.out_name = qkv_name, out_name

@@ -58,8 +58,11 @@ def test_the_layer_sizes_of_gpt2_small(folder_small, dtype):
             compare(folder_small, dtype, got, requests)
         if dtype == "bfloat16":
             assert engine.fused is not None, engine.fused_reason
-            # (the whole-request step of 200 tokens was filled up to 256, the next round shape)
-            assert engine.kernels.choices[("attention", 256, 12, 64)] == "attention_tcgen05"
+            # (the whole-request step of 200 tokens was filled up to 256, the next round shape; a
+            # portion longer than a tile goes to the kernel with two tiles per CTA, shorter ones
+            # to the kernel with one)
+            assert engine.kernels.choices[("attention", 256, 12, 64)] == "attention_two_tiles"
+            assert engine.kernels.choices[("attention", 128, 12, 64)] == "attention_tcgen05"
             assert engine.kernels.choices[("qkv", 256, 2304, 768)] == "gemm_tcgen05"
         engine.check_status()
         engine.cache.check()
@@ -400,10 +403,11 @@ def test_launch_counts_and_kernel_choices(folder_d):
     # embed; per layer norm, qkv, attention, proj, norm, fc, down; the head with the final norm on its way in
     assert kernels.launches - before == 7 * layers + 2
     assert kernels.choices[("qkv", 300, 768, 256)] == "gemm_tcgen05"
-    assert kernels.choices[("attention", 300, 4, 64)] == "attention_tcgen05"
+    assert kernels.choices[("attention", 300, 4, 64)] == "attention_two_tiles"        # one long portion: units of 256 tokens
     assert kernels.choices[("linear", 300, 1024, 256)] == "gemm_tcgen05"
     assert kernels.choices[("linear", 1, 1031, 256)] == "skinny_linear"     # the head on the one wanted row
     engine.step([StepEntry(s, random_tokens(2 + i, 10 + i, vocab), []) for i, s in enumerate(slots[1:], 1)])
+    assert kernels.choices[("attention", 380, 4, 64)] == "attention_tcgen05"          # nineteen short portions: tiles
     for count in (1, 8, 16):
         before = kernels.launches
         engine.step([StepEntry(s, [7], [0]) for s in slots[:count]], [SamplingParams(0.0, 1.0, 0, 0)] * count)

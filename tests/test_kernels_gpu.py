@@ -618,6 +618,87 @@ def test_attention_prefill_finds_one_far_key_and_respects_the_windows_edge():
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("n_heads, n_kv_heads, page, window", [
+    (2, 2, 16, 0), (3, 1, 8, 0), (4, 2, 32, 0), (1, 1, 128, 0), (2, 1, 64, 0), (2, 2, 16, 100), (2, 2, 8, 128),
+    (2, 2, 64, 300), (12, 12, 64, 0)])
+def test_attention_prefill_two_tiles_over_pages(n_heads, n_kv_heads, page, window):
+    """Two tiles of queries per CTA, one thread per query row: units of 256 tokens that are
+    full, that have a ragged second tile or none, that start deep in a cached context and whose
+    first tile ends a block of keys before the second; twice, so that the work counter is back
+    at zero; against the plain attention over the same pages."""
+    from mini_llm_b200.kernels import ops
+    head = 64
+    rng = np.random.default_rng(n_heads * head + page + window + 1)
+    lengths, n_new = [300, 520, 1, 128, 900, 77, 260, 1000], [300, 257, 1, 128, 385, 1, 4, 256]
+    k_pages, v_pages, table, positions, items, dense = paged_case(rng, lengths, n_new, n_heads, n_kv_heads, head,
+                                                                  page, torch.bfloat16)
+    kv_shape = (k_pages.shape[0], page, n_kv_heads, head)
+    dense = [(f64(dev(k, torch.bfloat16)), f64(dev(v, torch.bfloat16))) for k, v in dense]
+    n = len(f64(positions))
+    q = dev(rng.normal(size=(n, n_heads * head)), torch.bfloat16)
+    offsets = np.concatenate([[0], np.cumsum(n_new)[:-1]]).tolist()
+    starts = [l - m for l, m in zip(lengths, n_new)]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    scale = 1.0 / math.sqrt(head)
+    expected = attention_expected(f64(q), dense, f64(positions).astype(int), f64(items).astype(int), n_heads,
+                                  n_kv_heads, head, scale, window)
+    work = torch.zeros(2, dtype=torch.int32, device="cuda")
+    # every unit by one CTA (a GPU of few SMs), then the long units in parts (as many SMs as it takes)
+    for n_sms in (1, 10 ** 6):
+        units, n_split, most = ops.attention_units(offsets, n_new, starts, n_heads, n_sms)
+        whole = [u for u in units if u[4] == 0]
+        assert sum(u[2] for u in whole) == n and max(u[2] for u in whole) == 256
+        assert [u[7] for u in units] == sorted((u[7] for u in units), reverse=True)     # the longest records first
+        if n_sms == 1:
+            assert (n_split, most) == (0, 1) and max(u[7] for u in units) == 8
+        else:
+            assert n_split >= 4 and most == 4 and max(u[7] for u in units) == 2
+        scratch = None if n_split == 0 else (
+            torch.full((n_split * n_heads * most * 256 * (head + 4),), float("nan"), device="cuda"),
+            torch.zeros(n_split * n_heads, dtype=torch.int32, device="cuda"))
+        for _ in range(2):
+            out = torch.full_like(q, float("nan"))
+            ops.attention_prefill_two_tiles(out, q, k_pages.view(kv_shape), v_pages.view(kv_shape), table,
+                                            dev(np.array(units, dtype=np.int32)), len(units), n_heads, n_kv_heads, head,
+                                            page, scale, window, status, work, scratch, n_split, most)
+            np.testing.assert_allclose(f64(out), expected, rtol=0, atol=tol(torch.bfloat16, 2))
+        assert int(status.item()) == 0 and int(work.abs().sum().item()) == 0
+        assert scratch is None or int(scratch[1].abs().sum().item()) == 0
+
+
+def test_attention_prefill_two_tiles_finds_one_far_key_and_respects_the_windows_edge():
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(8)
+    head, page, length, new = 64, 16, 700, 250
+    far = 3 * page + 5
+    k_pages, v_pages, table, positions, items, dense = paged_case(rng, [length], [new], 1, 1, head, page, torch.bfloat16)
+    k, v = dense[0]
+    q = rng.normal(size=(new, head))
+    k[far] = q[-1] * 4.0                                  # stands out for the last query (a row of the second tile)
+    v[far] = 100.0 + np.arange(head)
+    block, offset = int(f64(table)[0, far // page]), far % page
+    k_pages[block, offset] = dev(k[far], torch.bfloat16)
+    v_pages[block, offset] = dev(v[far], torch.bfloat16)
+    kv_shape = (k_pages.shape[0], page, 1, head)
+    qd = dev(q, torch.bfloat16)
+    out = torch.empty_like(qd)
+    units, n_split, most = ops.attention_units([0], [new], [length - new])
+    assert len(units) == 3 and (n_split, most) == (1, 3)                # six blocks of keys: three parts of two
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    work = torch.zeros(2, dtype=torch.int32, device="cuda")
+    scratch = (torch.empty(3 * 256 * (head + 4), device="cuda"), torch.zeros(1, dtype=torch.int32, device="cuda"))
+    run = lambda window: ops.attention_prefill_two_tiles(out, qd, k_pages.view(kv_shape), v_pages.view(kv_shape), table,
+                                                         dev(np.array(units, dtype=np.int32)), 3, 1, 1, head, page,
+                                                         1.0 / math.sqrt(head), window, status, work, scratch, 1, 3)
+    run(0)
+    np.testing.assert_allclose(f64(out)[-1], f64(dev(v[far], torch.bfloat16)), rtol=2e-2, atol=0.5)
+    run(length - 1 - far)
+    assert float(out[-1].float().abs().max()) < 10.0
+    run(length - far)
+    np.testing.assert_allclose(f64(out)[-1], f64(dev(v[far], torch.bfloat16)), rtol=2e-2, atol=0.5)
+    assert int(status.item()) == 0
+
+
 @pytest.mark.parametrize("vocab", [1000, 50257])
 def test_sliced_sampling_draws_what_the_one_block_kernel_draws(vocab):
     from mini_llm_b200.kernels import ops
