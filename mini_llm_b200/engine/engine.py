@@ -476,14 +476,15 @@ class Engine:
         if stamp != self._graph_stamp:
             self._graphs.clear()                      # a buffer moved: captured addresses are stale
             self._graph_stamp = stamp
-        key = (ctx.n_tokens, ctx.n_items, ctx.n_want, ctx.n_att_tiles, ctx.n_split_tiles, ctx.att_parts, ctx.att_units,
+        # (how many units come in parts is data; that some do decides whether the kernel gets scratch)
+        key = (ctx.n_tokens, ctx.n_items, ctx.n_want, ctx.n_att_tiles, ctx.att_parts > 1, ctx.att_units,
                sample_views is not None, self._any_nucleus, ctx.any_previous, self.control.parity)
         held = self._graphs.get(key)
         # A capture costs as much as about twenty eager steps: a decode shape comes back at once
         # and is captured the second time it is seen, a shape with prompt portions the fourth.
         wait = 1 if ctx.decode_only else 3
         if held is None or (isinstance(held, int) and held < wait):
-            if held is None and len(self._graphs) >= 48:
+            if held is None and len(self._graphs) >= 192:
                 self._graphs.clear()                  # many shapes came by: start over rather than grow
             self._graphs[key] = (held or 0) + 1       # run eagerly: every buffer gets allocated
             self.step_kinds["eager"] += 1

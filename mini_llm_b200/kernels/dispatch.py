@@ -230,10 +230,14 @@ class Kernels:
         if (not self.plain_only and ctx.att_tiles is not None
                 and ops.attention_prefill_takes(q, head_size, cache.page_size)):
             scratch = None
-            rows = ops.ATTENTION_UNIT if ctx.att_units else ops.ATTENTION_TILE
             if ctx.att_parts > 1:
-                scratch = self._attention_scratch(ctx.device, ctx.n_split_tiles * n_heads, ops.ATTENTION_MAX_PARTS
-                                                  * rows * (head_size + 4))
+                # Room for the most cells a step can have, whatever this one has: a step replayed
+                # from a graph brings its number of split tiles as data and passes by here no more.
+                # (Tiles are split in steps of at most eight of them; units while records x heads
+                # stay within the SMs, of which no GPU has 256.)
+                most = max(ctx.n_split_tiles * n_heads, 8 * n_heads, 256)
+                # (cells of a unit's 256 rows, also for the kernel with tiles of 128: one size, no regrowth)
+                scratch = self._attention_scratch(ctx.device, most, ops.ATTENTION_MAX_PARTS * ops.ATTENTION_UNIT * (head_size + 4))
             if ctx.att_units:
                 self.chose("attention", "attention_two_tiles", n, n_heads, head_size)
                 return ops.attention_prefill_two_tiles(out, q, cache.k_pages, cache.v_pages, cache.block_table,
