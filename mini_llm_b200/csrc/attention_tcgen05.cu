@@ -693,9 +693,10 @@ attention_two_tiles_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         float m = -INFINITY, l = 0.0f;
         bool ok = true;
         auto wait_for = [&](uint64_t* bar, uint32_t parity) -> bool {
-            bool done = true;
-            if (lane == 0) done = mbar_wait(bar, parity) && !*failed;
-            return __shfl_sync(0xffffffffu, done, 0);
+            // (every lane looks for itself: the barrier's word is one broadcast read, and a vote
+            // keeps the warp together should the lanes' limits run out apart)
+            const bool done = mbar_wait(bar, parity) && !*failed;
+            return __all_sync(0xffffffffu, done);
         };
         for (int j = 0; j < my_blocks; j++) {
             ok = wait_for(&s_ready[t], j & 1);
