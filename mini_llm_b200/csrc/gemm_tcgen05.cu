@@ -141,41 +141,46 @@ __device__ __forceinline__ void store_rows_bf16(const float* turn, bf16* base, R
 template <int BN, int SPLITS>
 __device__ __forceinline__ void finish_split(const GemmParams& p, const float* part, const long* kv_off, float b, int r, int tile_b,
                                              int tokens, int rank, int half) {
-    constexpr int MINE = (BN + 2 * SPLITS - 1) / (2 * SPLITS);
-    const int c0 = rank + SPLITS * half;
-    float value[MINE][SPLITS], old[MINE];
+    constexpr int MINE = (BN + 2 * SPLITS - 1) / (2 * SPLITS);      // this thread's tokens
+    constexpr int PER = MINE < 32 / SPLITS ? MINE : 32 / SPLITS;      // of them at a time: 32 loads on their way
+#pragma unroll 1
+    for (int first = 0; first < MINE; first += PER) {
+        const int c0 = rank + SPLITS * half + first * 2 * SPLITS;
+        if (c0 >= tokens) break;
+        float value[PER][SPLITS], old[PER];
 #pragma unroll
-    for (int i = 0; i < MINE; i++) {
-        const int c = c0 + i * 2 * SPLITS;
-        old[i] = 0.0f;
-        if (p.epilogue == EPI_ADD && c < tokens) old[i] = reinterpret_cast<const float*>(p.out)[(long)(tile_b * BN + c) * p.ldo + r];
-    }
-#pragma unroll
-    for (int z = 0; z < SPLITS; z++)
-#pragma unroll
-        for (int i = 0; i < MINE; i++) {
+        for (int i = 0; i < PER; i++) {
             const int c = c0 + i * 2 * SPLITS;
-            value[i][z] = c < tokens ? load_from_rank(part + c * BM, (uint32_t)((rank + z) % SPLITS)) : 0.0f;
+            old[i] = 0.0f;
+            if (p.epilogue == EPI_ADD && c < tokens) old[i] = reinterpret_cast<const float*>(p.out)[(long)(tile_b * BN + c) * p.ldo + r];
         }
 #pragma unroll
-    for (int i = 0; i < MINE; i++) {
-        const int c = c0 + i * 2 * SPLITS;
-        if (c >= tokens) continue;
-        float sum = 0.0f;
+        for (int z = 0; z < SPLITS; z++)
 #pragma unroll
-        for (int z = 0; z < SPLITS; z++) sum += value[i][z];
-        const float x = sum + b;
-        const int t = tile_b * BN + c;
-        if (p.k_pages != nullptr && r >= p.q_width) {
-            const long slot = kv_off[c];
-            if (r < p.q_width + p.kv_width) p.k_pages[slot + r - p.q_width] = __float2bfloat16_rn(x);
-            else p.v_pages[slot + r - p.q_width - p.kv_width] = __float2bfloat16_rn(x);
-            continue;
+            for (int i = 0; i < PER; i++) {
+                const int c = c0 + i * 2 * SPLITS;
+                value[i][z] = c < tokens ? load_from_rank(part + c * BM, (uint32_t)((rank + z) % SPLITS)) : 0.0f;
+            }
+#pragma unroll
+        for (int i = 0; i < PER; i++) {
+            const int c = c0 + i * 2 * SPLITS;
+            if (c >= tokens) continue;
+            float sum = 0.0f;
+#pragma unroll
+            for (int z = 0; z < SPLITS; z++) sum += value[i][z];
+            const float x = sum + b;
+            const int t = tile_b * BN + c;
+            if (p.k_pages != nullptr && r >= p.q_width) {
+                const long slot = kv_off[c];
+                if (r < p.q_width + p.kv_width) p.k_pages[slot + r - p.q_width] = __float2bfloat16_rn(x);
+                else p.v_pages[slot + r - p.q_width - p.kv_width] = __float2bfloat16_rn(x);
+                continue;
+            }
+            const long at = (long)t * p.ldo + r;
+            if (p.epilogue == EPI_ADD) reinterpret_cast<float*>(p.out)[at] = old[i] + x;
+            else if (p.out_f32) reinterpret_cast<float*>(p.out)[at] = x;
+            else reinterpret_cast<bf16*>(p.out)[at] = __float2bfloat16_rn(activate(x, p.epilogue));
         }
-        const long at = (long)t * p.ldo + r;
-        if (p.epilogue == EPI_ADD) reinterpret_cast<float*>(p.out)[at] = old[i] + x;
-        else if (p.out_f32) reinterpret_cast<float*>(p.out)[at] = x;
-        else reinterpret_cast<bf16*>(p.out)[at] = __float2bfloat16_rn(activate(x, p.epilogue));
     }
 }
 
@@ -920,7 +925,7 @@ int tensor_map(const void* base, long rows, long cols, long ld, int box_rows, CU
 
 template <int BN, int STAGES>
 int launch_swapped(const CUtensorMap& a, const CUtensorMap& b, const GemmParams& p, dim3 grid, cudaStream_t s) {
-    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + BM * 8 + 1024;   // barriers, TMEM slot, flag, ticket, cache offsets
+    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + (BN > BM ? BN : BM) * 8 + 1024;   // barriers, TMEM slot, flag, ticket, cache offsets
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_swapped_kernel<BN, STAGES>,
@@ -1078,7 +1083,17 @@ static int gemm_bf16(void* out, const void* x, const void* w, const float* bias,
     }
     CUtensorMap map_x, map_w;
     const int sms = sm_count();
-    const bool swap = M <= 64 && forced_bn == 0;
+    // Which kernel: up to 64 tokens the one with swapped operands.  It also takes products of up
+    // to 512 tokens with a long K and few output features (the feed-forward's second product in
+    // steps of prompt portions): there the persistent kernel is one chain of K / 64 dependent
+    // blocks on few CTAs (17 us at 768 x 3072 whatever the tokens), and tiles of 128 tokens
+    // shared along K by a cluster take 8.4 to 11.4 us (measured at 128 to 512 tokens; from
+    // 1,024 tokens on the persistent kernel is as fast or faster, as it is for a short K).
+    // (A forced code 5000 + t: the kernel with swapped operands and tiles of t tokens.)
+    const int blocks_of_k = (K + BK - 1) / BK;
+    const bool long_k_few_tokens = M <= 512 && blocks_of_k >= 32 && scatter == nullptr &&
+                                   (long)((N + BM - 1) / BM) * ((M + 127) / 128) * 2 <= sms;
+    const bool swap = forced_bn == 0 ? M <= 64 || long_k_few_tokens : forced_bn >= 5000;
     if (!swap) {
         // a tile: 128 tokens x bn features on one CTA, or (code 1000 + bn) 256 tokens x bn on a pair of CTAs
         // (narrow tiles are issued by two threads: see gemm_rows_kernel)
@@ -1110,7 +1125,8 @@ static int gemm_bf16(void* out, const void* x, const void* w, const float* bias,
         default: return fail("gemm: the tile width is 64, 96, 128, 192 or 256 (1000 + width on pairs of CTAs, 2000 + width up to 128 with two issuing threads)");
         }
     }
-    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    const int bn = forced_bn >= 5000 ? forced_bn - 5000 : (M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)));
+    if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return fail("gemm: tiles of 16, 32, 64, 128 or 256 tokens");
     int rc = tensor_map(x, M, K, ldx, bn, &map_x);
     if (rc) return rc;
     rc = tensor_map(w, N, K, K, BM, &map_w);
@@ -1129,7 +1145,9 @@ static int gemm_bf16(void* out, const void* x, const void* w, const float* bias,
     }
     if (bn == 16) return launch_swapped<16, 8>(map_w, map_x, p, grid, s);
     if (bn == 32) return launch_swapped<32, 8>(map_w, map_x, p, grid, s);
-    return launch_swapped<64, 8>(map_w, map_x, p, grid, s);
+    if (bn == 64) return launch_swapped<64, 8>(map_w, map_x, p, grid, s);
+    if (bn == 128) return launch_swapped<128, 6>(map_w, map_x, p, grid, s);
+    return launch_swapped<256, 4>(map_w, map_x, p, grid, s);
 }
 
 extern "C" int mllm_gemm_bf16(void* out, const void* x, const void* w, const float* bias, int M, int N, int K,
@@ -1144,7 +1162,8 @@ extern "C" int mllm_gemm_bf16_tile(void* out, const void* x, const void* w, cons
                                    long ldx, long ldo, int epilogue, int out_f32, int* status, int tile_width,
                                    unsigned long long* timeline, void* stream) {
     // 1000 + width: on a pair of CTAs; 2000 + width: two issuing threads (the launcher refuses what it has not)
-    if (tile_width < 0 || tile_width >= 3000) return fail("gemm: the tile width is 64, 96, 128, 192 or 256");
+    if (tile_width <= 0 || (tile_width >= 3000 && tile_width < 5000) || tile_width > 5256)
+        return fail("gemm: the tile width is 64, 96, 128, 192 or 256");
     return gemm_bf16(out, x, w, bias, M, N, K, ldx, ldo, epilogue, out_f32, status, nullptr, stream, tile_width, timeline);
 }
 

@@ -424,7 +424,8 @@ GEMM_TILE_WIDTHS = (64, 96, 128, 192, 256)        # 1000 + width: tiles of 256 t
 
 def gemm_bf16_tile(out, a, w, bias, epilogue, status, tile_width, timeline=None):
     """``gemm_bf16`` through the persistent kernel with tiles of 128 x ``tile_width``, whatever
-    the number of rows (tests run every width; the engine lets the library choose).
+    the number of rows (tests run every width; the engine lets the library choose).  A code
+    5000 + t runs the kernel with swapped operands and tiles of t tokens (16 to 256) instead.
     ``timeline``: an int64 device tensor of nine entries that receives time stamps of CTA 0
     (start, set-up done, first operands landed, last product of the first tile issued, first
     accumulator ready, first epilogue done, end), in nanoseconds, then the number of blocks of K

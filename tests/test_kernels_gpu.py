@@ -816,6 +816,39 @@ def test_gemm_tcgen05_scatters_keys_and_values_into_the_pages(m, q_width, kv_wid
     np.testing.assert_allclose(f64(v_pages), want_v, rtol=0, atol=atol)
 
 
+@pytest.mark.parametrize("code", [5128, 5256, 5064])
+@pytest.mark.parametrize("m, n, k, epilogue", [(300, 768, 3072, "add"), (513, 777, 2048, "gelu_tanh"), (100, 1000, 96, "store"),
+                                               (129, 3072, 768, "add"), (512, 768, 3072, "add")])
+def test_gemm_tcgen05_swapped_operands_with_wide_token_tiles(m, n, k, epilogue, code):
+    """The kernel with swapped operands (the weights fill the tile's 128 rows) with tiles of 64,
+    128 and 256 tokens (code 5000 + tokens), its tiles shared along K by a cluster where the
+    tiles are few: the engine takes it for up to 512 tokens when K is long.  Right, the same
+    bits twice, and what the library chooses by itself agrees."""
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(m + n + k + code)
+    a, w = dev(rng.normal(size=(m, k)), torch.bfloat16), dev(rng.normal(size=(n, k)) / math.sqrt(k), torch.bfloat16)
+    bias = dev(rng.normal(size=n), torch.float32)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    acc = f64(a) @ f64(w).T + f64(bias)
+    start = dev(rng.normal(size=(m, n)), torch.float32)
+    runs = []
+    for forced in (code, code, None):
+        if epilogue == "add":
+            out = start.clone()
+            expected, atol = f64(start) + acc, 2e-4
+        else:
+            out = torch.full((m, n), float("nan"), device="cuda", dtype=torch.bfloat16)
+            expected, atol = {"store": acc, "gelu_tanh": plain.gelu_tanh(acc)}[epilogue], tol(torch.bfloat16, 4)
+        if forced is None:
+            ops.gemm_bf16(out, a, w, bias, epilogue, status)
+        else:
+            ops.gemm_bf16_tile(out, a, w, bias, epilogue, status, forced)
+        assert int(status.item()) == 0, "a bounded wait inside the kernel ran out"
+        np.testing.assert_allclose(f64(out), expected, rtol=0, atol=atol)
+        runs.append(out)
+    assert torch.equal(runs[0], runs[1])
+
+
 @pytest.mark.parametrize("width", [2064, 2096, 2128, 96, 256])
 def test_gemm_tcgen05_long_runs_of_tiles(width):
     """Many tiles per CTA and an odd number of blocks along K, thirty launches in a row: with two
