@@ -195,27 +195,45 @@ def decode_run(engine, batch: int, steps: int, warmup: int, context: int, vocab:
     return ms, launches, mean_cached
 
 
-def prefill_run(engine, n_prompts: int, length: int, vocab: int, repeats: int = 5):
+def prefill_run(engine, n_prompts: int, length: int, vocab: int, repeats: int = 5, from_idle: bool = False):
+    """Milliseconds of one prompt step of ``n_prompts`` x ``length`` tokens.  The steps run one
+    behind the other (a step's host work, the filling of its control block, then falls beside
+    the step before it on the GPU, as in serving) between two events with a synchronise on
+    both sides; the first five steps, which run eagerly and capture the graph, are not timed.
+    ``from_idle``: each step alone instead, from an idle GPU, host work included (the median)."""
     import numpy as np
     import torch
     from mini_llm_b200.engine import StepEntry
 
     rng = np.random.default_rng(99)
     prompts = [rng.integers(0, vocab, length).tolist() for _ in range(n_prompts)]
-    times = []
-    for repeat in range(repeats + 5):                    # the first runs are eager, then one captures a graph
+
+    def one_step():
         slots = [engine.open_request() for _ in range(n_prompts)]
-        torch.cuda.synchronize()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
         engine.step([StepEntry(slot, prompt, [length - 1]) for slot, prompt in zip(slots, prompts)])
-        stop.record()
-        torch.cuda.synchronize()
-        if repeat >= 5:
-            times.append(start.elapsed_time(stop))
         for slot in slots:
             engine.close_request(slot)
-    return statistics.median(times)
+
+    for _ in range(5):
+        one_step()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if from_idle:
+        times = []
+        for _ in range(repeats):
+            torch.cuda.synchronize()
+            start.record()
+            one_step()
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop))
+        return statistics.median(times)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(repeats):
+        one_step()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / repeats
 
 
 def e2e_run(folder, args, context: int, vocab: int):
@@ -420,8 +438,9 @@ def run_ours(args):
 
         if args.only_prefill:
             prefill_ms = prefill_run(engine, 2, 1024, vocab, repeats=max(1, args.steps))
-            print(json.dumps({"metric": "prefill of 2,048 tokens", "ms": prefill_ms, "n_layer": config["n_layer"],
-                              "value": 2048 / (prefill_ms * 1e-3), "unit": "tokens/s"}))
+            idle_ms = prefill_run(engine, 2, 1024, vocab, repeats=max(1, min(args.steps, 20)), from_idle=True)
+            print(json.dumps({"metric": "prefill of 2,048 tokens", "ms": prefill_ms, "ms_from_idle": idle_ms,
+                              "n_layer": config["n_layer"], "value": 2048 / (prefill_ms * 1e-3), "unit": "tokens/s"}))
             return 0
         sampler = ClockSampler()
         sampler.start()
@@ -451,11 +470,15 @@ def run_ours(args):
                 p_ms, _, _ = decode_run(engine, batch, min(args.steps, 64), max(3, min(args.warmup, 8)), context, vocab)
                 points[f"decode_b{batch}"] = batch / (p_ms * 1e-3)
             line["points"] = points
-            prefill_ms = prefill_run(engine, 2, 1024, vocab)
+            # K steps one behind the other between two events; and one step alone from an idle GPU,
+            # which also holds the host's filling of the step's control block
+            prefill_ms = prefill_run(engine, 2, 1024, vocab, repeats=32)
+            idle_ms = prefill_run(engine, 2, 1024, vocab, repeats=7, from_idle=True)
             flops = prefill_flops(config, 2, 1024, 2)
             peak_flops = (peak["bf16_tflops"] if dtype_bytes == 2 else peak["bf16_tflops"]) * 1e12
             line["prefill"] = {"value": 2048 / (prefill_ms * 1e-3), "tokens": 2048, "ms": prefill_ms,
-                               "frac": flops / (prefill_ms * 1e-3) / peak_flops, "flops": flops}
+                               "frac": flops / (prefill_ms * 1e-3) / peak_flops, "flops": flops, "steps": 32,
+                               "ms_from_idle": idle_ms}
             line["device"] = engine.device_info()
             del engine
             torch.cuda.empty_cache()

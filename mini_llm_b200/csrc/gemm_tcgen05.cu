@@ -142,18 +142,12 @@ template <int BN, int SPLITS>
 __device__ __forceinline__ void finish_split(const GemmParams& p, const float* part, const long* kv_off, float b, int r, int tile_b,
                                              int tokens, int rank, int half) {
     constexpr int MINE = (BN + 2 * SPLITS - 1) / (2 * SPLITS);      // this thread's tokens
-    constexpr int PER = MINE < 32 / SPLITS ? MINE : 32 / SPLITS;      // of them at a time: 32 loads on their way
+    constexpr int PER = MINE < 64 / SPLITS ? MINE : 64 / SPLITS;      // of them at a time: 64 loads on their way
 #pragma unroll 1
     for (int first = 0; first < MINE; first += PER) {
         const int c0 = rank + SPLITS * half + first * 2 * SPLITS;
         if (c0 >= tokens) break;
-        float value[PER][SPLITS], old[PER];
-#pragma unroll
-        for (int i = 0; i < PER; i++) {
-            const int c = c0 + i * 2 * SPLITS;
-            old[i] = 0.0f;
-            if (p.epilogue == EPI_ADD && c < tokens) old[i] = reinterpret_cast<const float*>(p.out)[(long)(tile_b * BN + c) * p.ldo + r];
-        }
+        float value[PER][SPLITS];
 #pragma unroll
         for (int z = 0; z < SPLITS; z++)
 #pragma unroll
@@ -177,7 +171,9 @@ __device__ __forceinline__ void finish_split(const GemmParams& p, const float* p
                 continue;
             }
             const long at = (long)t * p.ldo + r;
-            if (p.epilogue == EPI_ADD) reinterpret_cast<float*>(p.out)[at] = old[i] + x;
+            // (the residual sum as one addition at the memory: this thread is the only one that
+            // adds to the element in this launch, and nothing waits for the old value)
+            if (p.epilogue == EPI_ADD) atomicAdd(reinterpret_cast<float*>(p.out) + at, x);
             else if (p.out_f32) reinterpret_cast<float*>(p.out)[at] = x;
             else reinterpret_cast<bf16*>(p.out)[at] = __float2bfloat16_rn(activate(x, p.epilogue));
         }
