@@ -1139,8 +1139,12 @@ static int gemm_bf16(void* out, const void* x, const void* w, const float* bias,
                 break;
             }
     }
-    if (bn == 16) return launch_swapped<16, 8>(map_w, map_x, p, grid, s);
-    if (bn == 32) return launch_swapped<32, 8>(map_w, map_x, p, grid, s);
+    // (many tiles, as for a vocabulary: fewer stages, so that two or three CTAs share an SM and
+    // one's start and end fall under another's main loop)
+    const bool many_tiles = (long)grid.x * grid.y > 2L * sms && p.splits <= 1;
+    if (bn == 16) return many_tiles ? launch_swapped<16, 4>(map_w, map_x, p, grid, s) : launch_swapped<16, 8>(map_w, map_x, p, grid, s);
+    if (bn == 32) return many_tiles ? launch_swapped<32, 4>(map_w, map_x, p, grid, s) : launch_swapped<32, 8>(map_w, map_x, p, grid, s);
+    if (bn == 64 && many_tiles) return launch_swapped<64, 4>(map_w, map_x, p, grid, s);
     if (bn == 64) return launch_swapped<64, 8>(map_w, map_x, p, grid, s);
     if (bn == 128) return launch_swapped<128, 6>(map_w, map_x, p, grid, s);
     return launch_swapped<256, 4>(map_w, map_x, p, grid, s);
