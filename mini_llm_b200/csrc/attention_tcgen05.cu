@@ -816,6 +816,24 @@ attention_two_tiles_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                     __threadfence();
                     const float* all = p.partial + (cell * p.max_parts * 2 + t) * (ROW * TILE) + r;
                     const long step = (long)2 * ROW * TILE;
+                    if (n_parts == 2) {
+                        // Two parts, the usual case: this thread still holds its own part, so one
+                        // round trip to L2 brings all of the other.  The sum is written so that it
+                        // has the same bits whichever of the two parts arrived last.
+                        const float* other = all + (part ^ 1) * step;
+                        float x[D];
+#pragma unroll
+                        for (int d = 0; d < D; d++) x[d] = __ldcg(other + d * TILE);
+                        const float m_other = __ldcg(other + D * TILE), l_other = __ldcg(other + (D + 1) * TILE);
+                        const float m0 = part == 0 ? m : m_other, m1 = part == 0 ? m_other : m;
+                        const float l0 = part == 0 ? l : l_other, l1 = part == 0 ? l_other : l;
+                        const float top = fmaxf(m0, m1);
+                        const float w0 = (m0 == -INFINITY) ? 0.0f : fast_exp2(m0 - top);
+                        const float w1 = (m1 == -INFINITY) ? 0.0f : fast_exp2(m1 - top);
+                        l = fmaf(l1, w1, l0 * w0);
+#pragma unroll
+                        for (int d = 0; d < D; d++) o[d] = part == 0 ? fmaf(x[d], w1, o[d] * w0) : fmaf(o[d], w1, x[d] * w0);
+                    } else {
                     float top = -INFINITY;
                     for (int q = 0; q < n_parts; q++) top = fmaxf(top, __ldcg(all + q * step + D * TILE));
                     l = 0.0f;
@@ -831,6 +849,7 @@ attention_two_tiles_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                         l += __ldcg(theirs + (D + 1) * TILE) * weight;
 #pragma unroll
                         for (int d = 0; d < D; d++) o[d] += x[d] * weight;
+                    }
                     }
                 }
                 if (threadIdx.x == 0 && *next_work == n_parts - 1) p.counters[cell] = 0;     // ready for the next launch
