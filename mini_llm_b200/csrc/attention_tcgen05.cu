@@ -786,7 +786,6 @@ attention_two_tiles_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
             atomicExch(p.status, 17);
         }
         {
-            // (a tile whose wait ran out still comes by the barriers below: the other tile's threads wait there)
             float o[D];
             if (ok && my_blocks > 0) {
                 tcgen05_after_sync();
@@ -807,11 +806,18 @@ attention_two_tiles_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                 for (int d = 0; d < D; d++) __stcg(mine + d * TILE, o[d]);
                 __stcg(mine + D * TILE, m);
                 __stcg(mine + (D + 1) * TILE, l);
+                // (each tile of the unit on its own: a counter and a barrier of the tile's four warps)
                 __threadfence();
-                asm volatile("bar.sync 3, 256;" ::: "memory");
-                if (threadIdx.x == 0) *next_work = atomicAdd(p.counters + cell, 1);     // (the slot is free until the next round)
-                asm volatile("bar.sync 3, 256;" ::: "memory");
-                writes = ok && *next_work == n_parts - 1 && !*failed;
+                int* const ticket = next_work + 1 + t;
+                int* const counter = p.counters + 2 * cell + t;
+                auto tile_barrier = [&]() {
+                    if (t == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+                    else asm volatile("bar.sync 2, 128;" ::: "memory");
+                };
+                tile_barrier();
+                if (r == 0) *ticket = atomicAdd(counter, 1);
+                tile_barrier();
+                writes = ok && *ticket == n_parts - 1 && !*failed;
                 if (writes) {
                     __threadfence();
                     const float* all = p.partial + (cell * p.max_parts * 2 + t) * (ROW * TILE) + r;
@@ -852,8 +858,7 @@ attention_two_tiles_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                     }
                     }
                 }
-                if (threadIdx.x == 0 && *next_work == n_parts - 1) p.counters[cell] = 0;     // ready for the next launch
-                asm volatile("bar.sync 3, 256;" ::: "memory");     // (the slot's next use comes after everyone has read it)
+                if (r == 0 && *ticket == n_parts - 1) *counter = 0;     // ready for the next launch
             }
             if (writes && r < my_rows) {
                 const float inv = 1.0f / l;
@@ -1068,7 +1073,7 @@ extern "C" int mllm_attention_prefill(void* out, long ld_out, const void* q, lon
 // among the split ones, 0); rows of one unit belong to one request and are consecutive; a unit
 // of several parts (each a share of its key blocks) has one record per part.  partial /
 // counters (may be null if no unit has parts): fp32 [split units, heads, max_parts, 256,
-// head_size + 4] and zeroed int32 [split units, heads] (left zero).  The records should be
+// head_size + 4] and zeroed int32 [split units, heads, 2] (left zero).  The records should be
 // sorted by falling number of key blocks.  work: two zeroed ints (left zero).
 extern "C" int mllm_attention_prefill_two_tiles(void* out, long ld_out, const void* q, long q_rows, long q_cols, long ld_q,
                                                 const void* k_pages, const void* v_pages, int n_pages, int page_size,

@@ -266,10 +266,11 @@ class Kernels:
         """Partial states and counters of prompt attention tiles that come in parts; grows
         (doubling) when a step has more split tiles than any before."""
         held = self._att_scratch
-        if held is None or held[1].shape[0] < cells or held[0].shape[0] < cells * floats_per_cell:
-            cells = max(cells, 2 * held[1].shape[0] if held is not None else 256)
+        if held is None or held[1].shape[0] < 2 * cells or held[0].shape[0] < cells * floats_per_cell:
+            cells = max(cells, held[1].shape[0] if held is not None else 256)
+            # (two counters a cell: the kernel with two tiles per CTA counts each tile's parts apart)
             self._att_scratch = held = (torch.empty(cells * floats_per_cell, dtype=torch.float32, device=device),
-                                        torch.zeros(cells, dtype=torch.int32, device=device))
+                                        torch.zeros(2 * cells, dtype=torch.int32, device=device))
             self.scratch_generation += 1
         return held
 

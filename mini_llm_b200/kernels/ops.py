@@ -634,7 +634,7 @@ def attention_prefill_two_tiles(out, q, k_pages, v_pages, block_table, units, n_
     list, head), each half of the unit with softmax warps of its own, one thread per query
     row; head size 64.  ``units``: device int32 [>= n_units, 8] from ``attention_units``.
     ``scratch``: (fp32 partial states, zeroed int32 counters) when units come in parts:
-    n_split * heads * max_parts * 256 * (head_size + 4) floats and n_split * heads counters."""
+    n_split * heads * max_parts * 256 * (head_size + 4) floats and 2 * n_split * heads counters."""
     _check(out, "attention_prefill.out", torch.bfloat16, 2)
     _check(q, "attention_prefill.q", torch.bfloat16, 2)
     _check(k_pages, "attention_prefill.k_pages", torch.bfloat16, 4)
@@ -662,7 +662,7 @@ def attention_prefill_two_tiles(out, q, k_pages, v_pages, block_table, units, n_
         _check(partial, "attention_prefill.scratch", torch.float32, 1)
         _check(counters, "attention_prefill.scratch", torch.int32, 1)
         if (partial.shape[0] < n_split * n_heads * max_parts * ATTENTION_UNIT * (head_size + 4)
-                or counters.shape[0] < n_split * n_heads):
+                or counters.shape[0] < 2 * n_split * n_heads):
             raise KernelError("attention_prefill: scratch too small")
     _attention_prefill_two_tiles(out.data_ptr(), out.stride(0), q.data_ptr(), q.shape[0], q.shape[1], q.stride(0),
                                  k_pages.data_ptr(), v_pages.data_ptr(), n_pages, page_size, block_table.data_ptr(),

@@ -655,7 +655,7 @@ def test_attention_prefill_two_tiles_over_pages(n_heads, n_kv_heads, page, windo
             assert n_split >= 4 and most == 4 and max(u[7] for u in units) == 2
         scratch = None if n_split == 0 else (
             torch.full((n_split * n_heads * most * 256 * (head + 4),), float("nan"), device="cuda"),
-            torch.zeros(n_split * n_heads, dtype=torch.int32, device="cuda"))
+            torch.zeros(2 * n_split * n_heads, dtype=torch.int32, device="cuda"))
         for _ in range(2):
             out = torch.full_like(q, float("nan"))
             ops.attention_prefill_two_tiles(out, q, k_pages.view(kv_shape), v_pages.view(kv_shape), table,
@@ -686,7 +686,7 @@ def test_attention_prefill_two_tiles_finds_one_far_key_and_respects_the_windows_
     assert len(units) == 3 and (n_split, most) == (1, 3)                # six blocks of keys: three parts of two
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     work = torch.zeros(2, dtype=torch.int32, device="cuda")
-    scratch = (torch.empty(3 * 256 * (head + 4), device="cuda"), torch.zeros(1, dtype=torch.int32, device="cuda"))
+    scratch = (torch.empty(3 * 256 * (head + 4), device="cuda"), torch.zeros(2, dtype=torch.int32, device="cuda"))
     run = lambda window: ops.attention_prefill_two_tiles(out, qd, k_pages.view(kv_shape), v_pages.view(kv_shape), table,
                                                          dev(np.array(units, dtype=np.int32)), 3, 1, 1, head, page,
                                                          1.0 / math.sqrt(head), window, status, work, scratch, 1, 3)
