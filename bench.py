@@ -283,7 +283,7 @@ def serving_run(folder, args, vocab: int):
     llm = LLM(folder, dtype=args.dtype, max_sessions=32, cache_tokens=24 * 1024, max_tokens_per_step=512,
               max_prefill_chunk=512, plain_kernels=args.plain_kernels)
     # The same 64 requests pass after pass: a step shape with prompt portions is captured as a
-    # CUDA graph the fourth time it is seen, so the first passes run many steps eagerly and pay
+    # CUDA graph the second time it is seen, so the first passes run some steps eagerly and pay
     # for captures; the passes go on until one ran every step from a graph or the one kernel
     # (eight at most).  Returns the first pass's and the best pass's tokens a second and the
     # number of passes.

@@ -480,15 +480,16 @@ class Engine:
         key = (ctx.n_tokens, ctx.n_items, ctx.n_want, ctx.n_att_tiles, ctx.att_parts > 1, ctx.att_units,
                sample_views is not None, self._any_nucleus, ctx.any_previous, self.control.parity)
         held = self._graphs.get(key)
-        # A capture costs as much as about twenty eager steps: a decode shape comes back at once
-        # and is captured the second time it is seen, a shape with prompt portions the fourth.
-        wait = 1 if ctx.decode_only else 3
-        if held is None or (isinstance(held, int) and held < wait):
-            if held is None and len(self._graphs) >= 192:
+        # A shape runs eagerly the first time (every buffer it needs gets allocated) and is
+        # captured when it comes back: a capture costs about as much as two eager steps of a
+        # prompt shape, so a shape that was seen twice pays for it at its third appearance.
+        if held is None:
+            if len(self._graphs) >= 192:
                 self._graphs.clear()                  # many shapes came by: start over rather than grow
-            self._graphs[key] = (held or 0) + 1       # run eagerly: every buffer gets allocated
             self.step_kinds["eager"] += 1
-            return self._forward(ctx, sample_views)
+            logits = self._forward(ctx, sample_views)
+            self._graphs[key] = 1                     # ran once, its buffers exist: captured when it comes back
+            return logits
         if isinstance(held, int):
             before = self.kernels.launches
             graph = torch.cuda.CUDAGraph()

@@ -143,8 +143,8 @@ def test_the_one_kernel_step_with_keys_in_parts(folder_d, parts):
 # ---- captured graphs of prompt steps -------------------------------------------------------------
 
 def test_prompt_steps_replayed_from_a_captured_graph(folder_d):
-    """Steps with prompt portions are filled up to round shapes; steps of one round shape run
-    eagerly three times, are captured the fourth time and replayed from then on: eight requests
+    """Steps with prompt portions are filled up to round shapes; a round shape runs
+    eagerly once, is captured the second time and replayed from then on: eight requests
     of the same length, each whole in a step of its own, then a portion of another length
     beside a decoding request, which falls into the same round shape; every step's logits are
     checked, the replayed ones among them."""
