@@ -857,6 +857,215 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (warp == 9) tmem_free(tmem_base, TMEM_COLS);
 }
 
+// ---- tiles of the rows orientation shared along K by the CTAs of a cluster ----------------
+//
+// A product with few output features and a long inner size (the second product of a
+// feed-forward at a few thousand tokens) has too few wide tiles for the SMs, and with narrow
+// tiles its main loop is bound by what the SMs can pull from L2.  Here the 2 to 4 CTAs of a
+// cluster take one tile of 128 x BN together, each a share of the blocks of K into its own
+// accumulator.  The tile's blocks of 32 columns number rank, rank + splits, ... are finished by
+// the CTA of that rank: after a cluster barrier (every CTA is done with its stages, over which
+// the exchanges lie) each CTA writes its partial sums of a block as fp32 into the shared memory
+// of the CTA that finishes it (stores through distributed shared memory wait for no answer;
+// loads would, once per block and rank); after a second barrier the finishing CTA adds the parts
+// in the order of the ranks from its own shared memory and sends the block on like the rows
+// kernel does.  The sum of a block is therefore formed in one place in a fixed order.
+enum { STATUS_TIMEOUT_SPLIT_PRODUCER = 16, STATUS_TIMEOUT_SPLIT_MMA = 17, STATUS_TIMEOUT_SPLIT_EPILOGUE = 18 };
+
+// Slots of 32 columns x 128 rows in a CTA's exchange: the blocks it finishes times the parts of each,
+// for the number of CTAs (2 to 4) that needs the most.
+__host__ __device__ constexpr int exchange_slots(int chunks) {
+    int most = 0;
+    for (int splits = 2; splits <= 4; splits++) {
+        const int slots = (chunks + splits - 1) / splits * splits;
+        most = slots > most ? slots : most;
+    }
+    return most;
+}
+
+template <int BN, int STAGES>
+constexpr size_t rows_split_shared_bytes() {
+    // stages (the exchange of BM x BN floats lies over them), the epilogue warps' turning blocks, barriers, words, biases
+    constexpr size_t stages = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2), exchange = (size_t)exchange_slots(BN / 32) * BM * 128;
+    return (stages > exchange ? stages : exchange) + 8 * WARP_BLOCKS_BYTES + (2 * STAGES + 2) * 8 + 16 + 256 * 4 + 1024;
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_rows_split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const __grid_constant__ CUtensorMap map_out, const GemmParams p, const int tiles_m, const int splits) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, CHUNKS = BN / 32;
+    constexpr size_t STAGE_BYTES = (size_t)STAGES * (A_BYTES + B_BYTES), EXCHANGE_BYTES = (size_t)exchange_slots(CHUNKS) * BM * 128;
+    constexpr size_t FRONT = STAGE_BYTES > EXCHANGE_BYTES ? STAGE_BYTES : EXCHANGE_BYTES;
+    unsigned char* stage_a = smem;
+    unsigned char* stage_b = smem + STAGES * A_BYTES;
+    float* turn_all = reinterpret_cast<float*>(smem + FRONT);
+    uint64_t* full = reinterpret_cast<uint64_t*>(turn_all + 8 * WARP_BLOCKS_BYTES / 4);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
+    uint64_t* drained = acc_full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drained + 1);
+    volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* tile_ok = reinterpret_cast<volatile int*>(tmem_slot + 2);
+    float* bias_s = reinterpret_cast<float*>(tmem_slot + 4);              // [256] the tile's biases (zeros without a bias)
+
+    dependents_may_start();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool stamps = p.timeline != nullptr && blockIdx.x == 0;
+    if (stamps && threadIdx.x == 0) p.timeline[0] = now_ns();
+    const int num_k = (p.K + BK - 1) / BK;
+    const uint32_t rank = cluster_rank();
+    const int tile = (int)blockIdx.x / splits;
+    const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+    const int share = (num_k + splits - 1) / splits;
+    const int kb_lo = min(num_k, (int)rank * share), kb_hi = min(num_k, kb_lo + share);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(acc_full, 1);
+        mbar_init(drained, 1);
+        *failed = 0;
+        *tile_ok = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) tmem_alloc(tmem_slot, BN);
+    tcgen05_before_sync();
+    __syncthreads();
+    tcgen05_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    auto give_up = [&](int code) {
+        if (!*failed) {
+            *failed = code;
+            atomicExch(p.status, code);
+        }
+    };
+    wait_for_earlier_kernels();
+    if (stamps && threadIdx.x == 0) p.timeline[1] = now_ns();
+    const uint32_t exchange = smem_u32(smem);        // [block of this CTA][rank][8 pieces of 4 columns][BM rows][4 floats]: a warp's rows lie side by side
+    if (warp == 8) {
+        if (lane == 0) {
+            int issued = 0;
+            for (int kb = kb_lo; kb < kb_hi; kb++) {
+                const int i = kb - kb_lo, s = i % STAGES;
+                if (!mbar_wait(&empty[s], (((uint32_t)(i / STAGES)) & 1u) ^ 1u) || *failed) {
+                    give_up(STATUS_TIMEOUT_SPLIT_PRODUCER);
+                    break;
+                }
+                mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+                tma_load_2d(stage_a + s * A_BYTES, &map_a, &full[s], kb * BK, tile_m * BM);
+                tma_load_2d(stage_b + s * B_BYTES, &map_b, &full[s], kb * BK, tile_n * BN);
+                issued = i + 1;
+            }
+            if (*failed)       // copies that were issued still land: none may be in flight when the stages are written over
+                for (int i = max(0, issued - STAGES); i < issued; i++) mbar_wait(&full[i % STAGES], (uint32_t)(i / STAGES) & 1u);
+        }
+    } else if (warp == 9) {
+        if (lane == 0) {
+            const uint32_t idesc = make_instr_desc(BM, BN);
+            const uint64_t desc_a0 = make_smem_desc(smem_u32(stage_a)), desc_b0 = make_smem_desc(smem_u32(stage_b));
+            for (int kb = kb_lo; kb < kb_hi; kb++) {
+                const int i = kb - kb_lo, s = i % STAGES;
+                if (!mbar_wait(&full[s], (uint32_t)(i / STAGES) & 1u)) {
+                    give_up(STATUS_TIMEOUT_SPLIT_MMA);
+                    break;
+                }
+                tcgen05_after_sync();
+                if (stamps && i == 0) p.timeline[2] = now_ns();
+                const uint64_t desc_a = desc_a0 + (uint64_t)(s * (A_BYTES >> 4)), desc_b = desc_b0 + (uint64_t)(s * (B_BYTES >> 4));
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; k++) umma(tmem_base, desc_a + 2 * k, desc_b + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&empty[s]);
+            }
+            umma_commit(acc_full);       // (after a wait that ran out too: the epilogue is not left waiting)
+            if (stamps) p.timeline[3] = now_ns();
+            if (*failed) {
+                umma_commit(drained);
+                mbar_wait(drained, 0);
+            }
+        }
+    } else {
+        if (threadIdx.x < BN) {
+            const int n = tile_n * BN + threadIdx.x;
+            bias_s[threadIdx.x] = (p.bias != nullptr && n < p.N) ? p.bias[n] : 0.0f;
+        }
+        if (threadIdx.x == 0) {
+            const bool ok = mbar_wait(acc_full, 0) && !*failed;
+            if (!ok) give_up(STATUS_TIMEOUT_SPLIT_EPILOGUE);
+            *tile_ok = ok ? 1 : 0;
+        }
+    }
+    // every CTA of the cluster is done with its stages (or has failed, and the step is lost anyway):
+    // the exchanges, which lie over them, may be written
+    tcgen05_before_sync();
+    __syncthreads();
+    cluster_sync();
+    if (stamps && threadIdx.x == 0) p.timeline[4] = now_ns();
+    const int owned = (CHUNKS + splits - 1) / splits;        // blocks of 32 columns a CTA finishes, at most
+    if (warp < 8 && *tile_ok) {
+        // ---- this CTA's partial sums: tensor memory -> the exchange of the CTA that finishes the block ----
+        tcgen05_after_sync();
+        const int quarter = warp & 3, col_half = warp >> 2;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const int row = quarter * 32 + lane;
+#pragma unroll 1
+        for (int c = col_half; c < CHUNKS; c += 2) {
+            float v[32];
+            if (kb_hi > kb_lo) {
+                tmem_load_32(lane_base + c * 32, v);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; i++) v[i] = 0.0f;           // no block of K fell to this CTA
+            }
+            // block c is finished by rank c % splits, as its block number c / splits; this CTA's part is slot `rank` of it
+            const uint32_t local = exchange + (uint32_t)((((c / splits) * splits + (int)rank) * 8) * BM + row) * 16;
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"((uint32_t)(c % splits)));
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote + j * (BM * 16)), "f"(v[4 * j]),
+                             "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                             : "memory");
+        }
+    }
+    tcgen05_before_sync();
+    __syncthreads();
+    cluster_sync();                              // all parts of this CTA's blocks have arrived
+    if (stamps && threadIdx.x == 0) p.timeline[5] = now_ns();
+    if (warp < 8 && *tile_ok) {
+        const int quarter = warp & 3, col_half = warp >> 2;
+        BlockOut out_ctx{&map_out, turn_all + warp * (WARP_BLOCKS_BYTES / 4), bias_s, nullptr, quarter, lane, 0};
+        const int row = quarter * 32 + lane, row0 = tile_m * BM + quarter * 32;
+        // this CTA's blocks: rank, rank + splits, ...; the two warps of a quarter take them in turn
+#pragma unroll 1
+        for (int mine = col_half; mine < owned; mine += 2) {
+            const int c = mine * splits + (int)rank;
+            if (c >= CHUNKS) break;
+            const int c0 = c * 32, n0 = tile_n * BN + c0;
+            if (n0 >= p.N) continue;
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; i++) v[i] = 0.0f;
+            for (int r = 0; r < splits; r++) {            // in the order of the ranks
+                const uint32_t src = exchange + (uint32_t)(((mine * splits + r) * 8) * BM + row) * 16;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const float4 x = lds128(src + j * (BM * 16));
+                    v[4 * j] += x.x; v[4 * j + 1] += x.y; v[4 * j + 2] += x.z; v[4 * j + 3] += x.w;
+                }
+            }
+            finish_block(out_ctx, p, map_out, v, c0, n0, row0);
+        }
+        if (lane == 0) bulk_wait_done();         // this warp's boxes have arrived before the kernel ends
+    }
+    __syncthreads();
+    if (stamps && threadIdx.x == 0) p.timeline[6] = now_ns();
+    if (warp == 9) tmem_free(tmem_base, BN);
+}
+
 // ---- host side: tensor maps ------------------------------------------------------------
 
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -991,6 +1200,23 @@ int launch_rows(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& o
                     "gemm_rows_kernel (pairs)");
 }
 
+template <int BN, int STAGES>
+int launch_rows_split(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& o, const GemmParams& p, int splits,
+                      cudaStream_t s) {
+    constexpr size_t smem = rows_split_shared_bytes<BN, STAGES>();
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_rows_split_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+            cudaSuccess)
+            return fail("gemm: cannot raise the shared memory limit");
+        configured = true;
+    }
+    const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+    return launched(launch_kernel_in_clusters(g_dependent_launch != 0, dim3(splits, 1, 1), gemm_rows_split_kernel<BN, STAGES>,
+                                              dim3(splits * tiles_m * tiles_n), dim3(THREADS), smem, s, a, b, o, p, tiles_m, splits),
+                    "gemm_rows_split_kernel");
+}
+
 }  // namespace
 
 // The SM count of the current device (asked once per device).
@@ -1052,6 +1278,36 @@ static int rows_tile_width(int M, int N, int K, int sms) {
     return best;
 }
 
+// Whether tiles shared along K by clusters (gemm_rows_split_kernel) beat the persistent kernel's
+// best width, and with which code (7000 + CTAs: tiles of 256 features; 7100 + CTAs: of 128); 0 if
+// not.  Measured in replayed graphs: such a product takes 1.2 us + its share of the blocks of K
+// (0.35 us each at 256 features, 0.30 at 128) + 9 us (5.5 at 128) for two cluster barriers, the
+// exchange, the finishing and the launch of clusters; the persistent kernel 1.25 us + its blocks
+// + its last epilogue.  Clusters of two fill the GPU; clusters of four were placed in one
+// round at 120 CTAs and not at 144, and clusters of three not at 144 CTAs.
+static int rows_split_code(int M, int N, int K, int sms, int width, bool scatter) {
+    if (scatter) return 0;
+    const long tiles_m = (M + BM - 1) / BM, num_k = (K + BK - 1) / BK;
+    const long rounds = (tiles_m * ((N + width - 1) / width) + sms - 1) / sms;
+    const double whole = 1.25 + (double)(rounds * num_k) * (width > 192 ? 0.35 : 0.34) + 0.0105 * width;
+    int best = 0;
+    double best_cost = 0.93 * whole;               // (not for less than the estimates are good for)
+    for (int wide = 0; wide < 2; wide++) {
+        const int bn = wide ? 256 : 128;
+        if (bn >= 2 * N) continue;
+        const long tiles = tiles_m * ((N + bn - 1) / bn);
+        for (int splits = 2; splits <= 4; splits += 2) {
+            if (tiles * splits > (splits == 2 ? sms : 13 * sms / 16) || num_k / splits < 4) continue;
+            const double cost = 1.2 + (double)((num_k + splits - 1) / splits) * (wide ? 0.35 : 0.30) + (wide ? 9.0 : 5.5);
+            if (cost < best_cost) {
+                best_cost = cost;
+                best = (wide ? 7000 : 7100) + splits;
+            }
+        }
+    }
+    return best;
+}
+
 static int gemm_bf16(void* out, const void* x, const void* w, const float* bias, int M, int N, int K, long ldx, long ldo,
                      int epilogue, int out_f32, int* status, const GemmScatter* scatter, void* stream, int forced_bn,
                      unsigned long long* timeline = nullptr) {
@@ -1089,12 +1345,29 @@ static int gemm_bf16(void* out, const void* x, const void* w, const float* bias,
     const int blocks_of_k = (K + BK - 1) / BK;
     const bool long_k_few_tokens = M <= 512 && blocks_of_k >= 32 && scatter == nullptr &&
                                    (long)((N + BM - 1) / BM) * ((M + 127) / 128) * 2 <= sms;
-    const bool swap = forced_bn == 0 ? M <= 64 || long_k_few_tokens : forced_bn >= 5000;
+    const bool swap = forced_bn == 0 ? M <= 64 || long_k_few_tokens : (forced_bn >= 5000 && forced_bn < 7000);
     if (!swap) {
         // a tile: 128 tokens x bn features on one CTA, or (code 1000 + bn) 256 tokens x bn on a pair of CTAs
         // (narrow tiles are issued by two threads: see gemm_rows_kernel)
         int code = forced_bn != 0 ? forced_bn : rows_tile_width(M, N, K, sms);
-        if (forced_bn == 0 && code <= 128) code += 2000;
+        if (forced_bn == 0) {
+            const int split_code = rows_split_code(M, N, K, sms, code, scatter != nullptr);
+            if (split_code != 0) code = split_code;
+            else if (code <= 128) code += 2000;
+        }
+        if (code >= 7000) {
+            // (code 7000 + s: tiles of 256 features shared along K by clusters of s CTAs; 7100 + s: tiles of 128)
+            const int splits = code % 100, bn_split = code < 7100 ? 256 : 128;
+            if (splits < 2 || splits > 4 || scatter != nullptr) return fail("gemm: tiles are shared along K by 2 to 4 CTAs, without scatter");
+            int rc = tensor_map(x, M, K, ldx, BM, &map_x);
+            if (rc) return rc;
+            rc = tensor_map(w, N, K, K, bn_split, &map_w);
+            if (rc) return rc;
+            CUtensorMap map_out = map_x;
+            p.out_by_tma = output_map(out, M, N, ldo, out_f32 != 0, &map_out) == 0;
+            if (bn_split == 256) return launch_rows_split<256, 3>(map_x, map_w, map_out, p, splits, s);
+            return launch_rows_split<128, 4>(map_x, map_w, map_out, p, splits, s);
+        }
         const bool pair = code >= 1000 && code < 2000;
         const int bn = code % 1000;
         int rc = tensor_map(x, M, K, ldx, BM, &map_x);
@@ -1162,7 +1435,7 @@ extern "C" int mllm_gemm_bf16_tile(void* out, const void* x, const void* w, cons
                                    long ldx, long ldo, int epilogue, int out_f32, int* status, int tile_width,
                                    unsigned long long* timeline, void* stream) {
     // 1000 + width: on a pair of CTAs; 2000 + width: two issuing threads (the launcher refuses what it has not)
-    if (tile_width <= 0 || (tile_width >= 3000 && tile_width < 5000) || tile_width > 5256)
+    if (tile_width <= 0 || (tile_width >= 3000 && tile_width < 5000) || (tile_width > 5256 && tile_width < 7002) || tile_width > 7104)
         return fail("gemm: the tile width is 64, 96, 128, 192 or 256");
     return gemm_bf16(out, x, w, bias, M, N, K, ldx, ldo, epilogue, out_f32, status, nullptr, stream, tile_width, timeline);
 }

@@ -419,13 +419,14 @@ def gemm_bf16(out, a, w, bias, epilogue, status):
 
 
 _gemm_bf16_tile = Function("gemm", "mllm_gemm_bf16_tile", [P, P, P, P, I, I, I, L, L, I, I, P, I, P, P])
-GEMM_TILE_WIDTHS = (64, 96, 128, 192, 256)        # 1000 + width: tiles of 256 tokens on pairs of CTAs; 2000 + width (to 128): two issuing threads
+GEMM_TILE_WIDTHS = (64, 96, 128, 192, 256)        # 1000 + width: tiles of 256 tokens on pairs of CTAs; 2000 + width (to 128): two issuing threads; 7000 / 7100 + CTAs: shared along K
 
 
 def gemm_bf16_tile(out, a, w, bias, epilogue, status, tile_width, timeline=None):
     """``gemm_bf16`` through the persistent kernel with tiles of 128 x ``tile_width``, whatever
     the number of rows (tests run every width; the engine lets the library choose).  A code
-    5000 + t runs the kernel with swapped operands and tiles of t tokens (16 to 256) instead.
+    5000 + t runs the kernel with swapped operands and tiles of t tokens (16 to 256) instead; a
+    code 7000 + c (7100 + c) tiles of 256 (128) features shared along K by clusters of c = 2 to 4 CTAs.
     ``timeline``: an int64 device tensor of nine entries that receives time stamps of CTA 0
     (start, set-up done, first operands landed, last product of the first tile issued, first
     accumulator ready, first epilogue done, end), in nanoseconds, then the number of blocks of K

@@ -483,14 +483,17 @@ def test_gemm_tcgen05(m, n, k, epilogue):
     np.testing.assert_allclose(f64(out), expected, rtol=0, atol=atol)
 
 
-@pytest.mark.parametrize("width", [64, 96, 128, 192, 256, 1064, 1096, 1128, 1192, 1256, 2064, 2096, 2128])
+@pytest.mark.parametrize("width", [64, 96, 128, 192, 256, 1064, 1096, 1128, 1192, 1256, 2064, 2096, 2128,
+                                   7002, 7003, 7004, 7102, 7103, 7104])
 @pytest.mark.parametrize("m, n, k, epilogue", [(300, 1000, 160, "gelu_tanh"), (513, 768, 3072, "add"), (17, 777, 96, "store"),
                                                (2048, 2304, 768, "store"), (4000, 1100, 72, "add"), (129, 50257, 64, "logits"),
                                                (2100, 3072, 256, "gelu_erf")])
 def test_gemm_tcgen05_every_tile_width(m, n, k, epilogue, width):
     """The persistent kernel at each of its tile widths, on single CTAs (128 tokens a tile) and
     on pairs of CTAs (1000 + width: 256 tokens a tile, each CTA loading half of the tile's
-    block of W), and with two issuing threads and two accumulators a tile (2000 + width): tiles that are partly empty in rows and in columns, a pair whose second CTA
+    block of W), with two issuing threads and two accumulators a tile (2000 + width), and with
+    tiles of 256 or 128 features shared along K by clusters of 2 to 4 CTAs (7000 / 7100 + CTAs;
+    with one or two blocks of K some CTAs of a cluster have none): tiles that are partly empty in rows and in columns, a pair whose second CTA
     has no rows at all, one tile for some CTAs and a dozen for others (so that both accumulators
     and every phase of the ring are in use), every epilogue; bitwise the same result twice."""
     from mini_llm_b200.kernels import ops
@@ -849,7 +852,7 @@ def test_gemm_tcgen05_swapped_operands_with_wide_token_tiles(m, n, k, epilogue, 
     assert torch.equal(runs[0], runs[1])
 
 
-@pytest.mark.parametrize("width", [2064, 2096, 2128, 96, 256])
+@pytest.mark.parametrize("width", [2064, 2096, 2128, 96, 256, 7002, 7104])
 def test_gemm_tcgen05_long_runs_of_tiles(width):
     """Many tiles per CTA and an odd number of blocks along K, thirty launches in a row: with two
     issuing threads each thread's blocks change between even and odd places of the K range from
