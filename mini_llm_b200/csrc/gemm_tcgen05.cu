@@ -865,19 +865,41 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 // cluster take one tile of 128 x BN together, each a share of the blocks of K into its own
 // accumulator.  The tile's blocks of 32 columns number rank, rank + splits, ... are finished by
 // the CTA of that rank: after a cluster barrier (every CTA is done with its stages, over which
-// the exchanges lie) each CTA writes its partial sums of a block as fp32 into the shared memory
-// of the CTA that finishes it (stores through distributed shared memory wait for no answer;
-// loads would, once per block and rank); after a second barrier the finishing CTA adds the parts
-// in the order of the ranks from its own shared memory and sends the block on like the rows
+// the exchanges lie) each CTA stores its partial sums of the other CTAs' blocks as fp32 into
+// their shared memory (stores through distributed shared memory wait for no answer; loads
+// would, once per block and rank) and arrives at their barriers; a CTA whose barrier is
+// complete adds, for each of its blocks, the parts in the order of the ranks, its own from
+// tensor memory and the others' from its shared memory, and sends the block on like the rows
 // kernel does.  The sum of a block is therefore formed in one place in a fixed order.
-enum { STATUS_TIMEOUT_SPLIT_PRODUCER = 16, STATUS_TIMEOUT_SPLIT_MMA = 17, STATUS_TIMEOUT_SPLIT_EPILOGUE = 18 };
+// Wait (bounded) for a phase of a barrier at which other CTAs of the cluster arrive after
+// storing into this CTA's shared memory: the acquire is at cluster scope.
+__device__ __forceinline__ bool mbar_wait_parts(uint64_t* bar, uint32_t parity) {
+    const unsigned long long start = now_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; i++) {
+            uint32_t ok;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(ok)
+                : "r"(smem_u32(bar)), "r"(parity)
+                : "memory");
+            if (ok) return true;
+        }
+        if (now_ns() - start > WAIT_LIMIT_NS) return false;
+    }
+}
 
-// Slots of 32 columns x 128 rows in a CTA's exchange: the blocks it finishes times the parts of each,
-// for the number of CTAs (2 to 4) that needs the most.
+enum { STATUS_TIMEOUT_SPLIT_PRODUCER = 16, STATUS_TIMEOUT_SPLIT_MMA = 17, STATUS_TIMEOUT_SPLIT_EPILOGUE = 18, STATUS_TIMEOUT_SPLIT_PARTS = 19 };
+
+// Slots of 32 columns x 128 rows in a CTA's exchange: the blocks it finishes times the other CTAs'
+// parts of each, for the number of CTAs (2 to 4) that needs the most.
 __host__ __device__ constexpr int exchange_slots(int chunks) {
     int most = 0;
     for (int splits = 2; splits <= 4; splits++) {
-        const int slots = (chunks + splits - 1) / splits * splits;
+        const int slots = (chunks + splits - 1) / splits * (splits - 1);
         most = slots > most ? slots : most;
     }
     return most;
@@ -885,9 +907,9 @@ __host__ __device__ constexpr int exchange_slots(int chunks) {
 
 template <int BN, int STAGES>
 constexpr size_t rows_split_shared_bytes() {
-    // stages (the exchange of BM x BN floats lies over them), the epilogue warps' turning blocks, barriers, words, biases
+    // stages (the exchange lies over them), the epilogue warps' turning blocks, barriers, words, biases
     constexpr size_t stages = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2), exchange = (size_t)exchange_slots(BN / 32) * BM * 128;
-    return (stages > exchange ? stages : exchange) + 8 * WARP_BLOCKS_BYTES + (2 * STAGES + 2) * 8 + 16 + 256 * 4 + 1024;
+    return (stages > exchange ? stages : exchange) + 8 * WARP_BLOCKS_BYTES + (2 * STAGES + 4) * 8 + 16 + 256 * 4 + 1024;
 }
 
 template <int BN, int STAGES>
@@ -906,7 +928,8 @@ gemm_rows_split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;
     uint64_t* drained = acc_full + 1;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drained + 1);
+    uint64_t* parts_full = drained + 1;         // the other CTAs' parts of this CTA's blocks have arrived
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(parts_full + 2);     // (one slot left out: the biases below stay on a 16-byte boundary)
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* tile_ok = reinterpret_cast<volatile int*>(tmem_slot + 2);
     float* bias_s = reinterpret_cast<float*>(tmem_slot + 4);              // [256] the tile's biases (zeros without a bias)
@@ -928,6 +951,7 @@ gemm_rows_split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         }
         mbar_init(acc_full, 1);
         mbar_init(drained, 1);
+        mbar_init(parts_full, 8 * (splits - 1));    // one arrival per epilogue warp of every other CTA
         *failed = 0;
         *tile_ok = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -945,7 +969,7 @@ gemm_rows_split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     };
     wait_for_earlier_kernels();
     if (stamps && threadIdx.x == 0) p.timeline[1] = now_ns();
-    const uint32_t exchange = smem_u32(smem);        // [block of this CTA][rank][8 pieces of 4 columns][BM rows][4 floats]: a warp's rows lie side by side
+    const uint32_t exchange = smem_u32(smem);        // [block of this CTA][other CTA][8 pieces of 4 columns][BM rows][4 floats]: a warp's rows lie side by side
     if (warp == 8) {
         if (lane == 0) {
             int issued = 0;
@@ -1005,62 +1029,86 @@ gemm_rows_split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     cluster_sync();
     if (stamps && threadIdx.x == 0) p.timeline[4] = now_ns();
     const int owned = (CHUNKS + splits - 1) / splits;        // blocks of 32 columns a CTA finishes, at most
-    if (warp < 8 && *tile_ok) {
-        // ---- this CTA's partial sums: tensor memory -> the exchange of the CTA that finishes the block ----
-        tcgen05_after_sync();
+    if (warp < 8) {
+        // ---- the parts of the blocks that other CTAs finish: tensor memory -> their exchanges ----
         const int quarter = warp & 3, col_half = warp >> 2;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const int row = quarter * 32 + lane;
+        if (*tile_ok) {
+            tcgen05_after_sync();
 #pragma unroll 1
-        for (int c = col_half; c < CHUNKS; c += 2) {
-            float v[32];
-            if (kb_hi > kb_lo) {
-                tmem_load_32(lane_base + c * 32, v);
-            } else {
+            for (int c = col_half; c < CHUNKS; c += 2) {
+                const int owner = c % splits;
+                if (owner == (int)rank) continue;
+                float v[32];
+                if (kb_hi > kb_lo) {
+                    tmem_load_32(lane_base + c * 32, v);
+                } else {
 #pragma unroll
-                for (int i = 0; i < 32; i++) v[i] = 0.0f;           // no block of K fell to this CTA
-            }
-            // block c is finished by rank c % splits, as its block number c / splits; this CTA's part is slot `rank` of it
-            const uint32_t local = exchange + (uint32_t)((((c / splits) * splits + (int)rank) * 8) * BM + row) * 16;
-            uint32_t remote;
-            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"((uint32_t)(c % splits)));
-#pragma unroll
-            for (int j = 0; j < 8; j++)
-                asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote + j * (BM * 16)), "f"(v[4 * j]),
-                             "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
-                             : "memory");
-        }
-    }
-    tcgen05_before_sync();
-    __syncthreads();
-    cluster_sync();                              // all parts of this CTA's blocks have arrived
-    if (stamps && threadIdx.x == 0) p.timeline[5] = now_ns();
-    if (warp < 8 && *tile_ok) {
-        const int quarter = warp & 3, col_half = warp >> 2;
-        BlockOut out_ctx{&map_out, turn_all + warp * (WARP_BLOCKS_BYTES / 4), bias_s, nullptr, quarter, lane, 0};
-        const int row = quarter * 32 + lane, row0 = tile_m * BM + quarter * 32;
-        // this CTA's blocks: rank, rank + splits, ...; the two warps of a quarter take them in turn
-#pragma unroll 1
-        for (int mine = col_half; mine < owned; mine += 2) {
-            const int c = mine * splits + (int)rank;
-            if (c >= CHUNKS) break;
-            const int c0 = c * 32, n0 = tile_n * BN + c0;
-            if (n0 >= p.N) continue;
-            float v[32];
-#pragma unroll
-            for (int i = 0; i < 32; i++) v[i] = 0.0f;
-            for (int r = 0; r < splits; r++) {            // in the order of the ranks
-                const uint32_t src = exchange + (uint32_t)(((mine * splits + r) * 8) * BM + row) * 16;
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const float4 x = lds128(src + j * (BM * 16));
-                    v[4 * j] += x.x; v[4 * j + 1] += x.y; v[4 * j + 2] += x.z; v[4 * j + 3] += x.w;
+                    for (int i = 0; i < 32; i++) v[i] = 0.0f;       // no block of K fell to this CTA
                 }
+                // block c is the owner's block number c / splits; among its other CTAs this one is number `slot`
+                const int slot = (int)rank < owner ? (int)rank : (int)rank - 1;
+                const uint32_t local = exchange + (uint32_t)((((c / splits) * (splits - 1) + slot) * 8) * BM + row) * 16;
+                uint32_t remote;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"((uint32_t)owner));
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote + j * (BM * 16)), "f"(v[4 * j]),
+                                 "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                                 : "memory");
             }
-            finish_block(out_ctx, p, map_out, v, c0, n0, row0);
         }
-        if (lane == 0) bulk_wait_done();         // this warp's boxes have arrived before the kernel ends
+        // (a CTA that failed arrives too: the others are not left waiting, the status word says that the step is lost)
+        __syncwarp();
+        if (lane == 0)
+            for (int other = 0; other < splits; other++)
+                if (other != (int)rank) mbar_arrive_cluster(cluster_address_of(parts_full, (uint32_t)other));
+        if (stamps && threadIdx.x == 0) p.timeline[5] = now_ns();
+        // ---- this CTA's blocks: its own part from tensor memory, the others' from the exchange, in rank order ----
+        // (waited for in any case: no CTA leaves while another may still store into its shared memory)
+        const bool parts_there = mbar_wait_parts(parts_full, 0);
+        if (!parts_there) give_up(STATUS_TIMEOUT_SPLIT_PARTS);
+        if (*tile_ok && parts_there) {
+            BlockOut out_ctx{&map_out, turn_all + warp * (WARP_BLOCKS_BYTES / 4), bias_s, nullptr, quarter, lane, 0};
+            const int row0 = tile_m * BM + quarter * 32;
+#pragma unroll 1
+            for (int mine = col_half; mine < owned; mine += 2) {
+                const int c = mine * splits + (int)rank;
+                if (c >= CHUNKS) break;
+                const int c0 = c * 32, n0 = tile_n * BN + c0;
+                if (n0 >= p.N) continue;
+                float v[32], own[32];
+                if (kb_hi > kb_lo) {
+                    tmem_load_32(lane_base + c0, own);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) own[i] = 0.0f;
+                }
+#pragma unroll
+                for (int i = 0; i < 32; i++) v[i] = 0.0f;
+                for (int r = 0; r < splits; r++) {
+                    if (r == (int)rank) {
+#pragma unroll
+                        for (int i = 0; i < 32; i++) v[i] += own[i];
+                        continue;
+                    }
+                    const int slot = r < (int)rank ? r : r - 1;
+                    const uint32_t src = exchange + (uint32_t)(((mine * (splits - 1) + slot) * 8) * BM + row) * 16;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const float4 x = lds128(src + j * (BM * 16));
+                        v[4 * j] += x.x; v[4 * j + 1] += x.y; v[4 * j + 2] += x.z; v[4 * j + 3] += x.w;
+                    }
+                }
+                finish_block(out_ctx, p, map_out, v, c0, n0, row0);
+            }
+            if (lane == 0) bulk_wait_done();     // this warp's boxes have arrived before the kernel ends
+        }
     }
+    // No CTA stores into another's shared memory after it has arrived there, and none reads
+    // another's: a CTA may leave when it is done.
+    tcgen05_before_sync();
     __syncthreads();
     if (stamps && threadIdx.x == 0) p.timeline[6] = now_ns();
     if (warp == 9) tmem_free(tmem_base, BN);
