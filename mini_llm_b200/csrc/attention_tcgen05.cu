@@ -513,7 +513,8 @@ attention_two_tiles_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     uint64_t* s_taken = s_ready + 2;               // [tile]: every softmax warp of the tile holds that S in registers
     uint64_t* p_ready = s_taken + 2;               // [tile]: P of the block is in shared memory (and O is scaled)
     uint64_t* o_ready = p_ready + 2;               // [tile]: O += P V of the block has finished
-    constexpr int N_BARS = 1 + 4 * WIDE_STAGES + 8;
+    uint64_t* exp_done = o_ready + 2;              // [tile]: every softmax warp of the tile has taken the block's exponentials
+    constexpr int N_BARS = 1 + 4 * WIDE_STAGES + 10;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* next_work = reinterpret_cast<int*>(tmem_slot + 2);
@@ -546,6 +547,7 @@ attention_two_tiles_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
             mbar_init(&s_taken[t], 4);             // one arrival per softmax warp of the tile
             mbar_init(&p_ready[t], 1);
             mbar_init(&o_ready[t], 1);
+            mbar_init(&exp_done[t], 4);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -738,6 +740,19 @@ attention_two_tiles_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
             // probabilities as bfloat16, first into registers (a masked score is -inf: its exponential is 0)
             uint32_t packed[TILE / 2];
             float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};     // (four sums side by side, as above)
+            {
+                // The two tiles take their exponentials in turn (A0 B0 A1 B1 ...): together they
+                // would share the SM's exponential units and then both leave them idle while they
+                // do the rest of a block; in turn, one tile's rest falls under the other's
+                // exponentials (20.4 -> 19.3 us for two prompts of 1,024 tokens).  A tile waits
+                // only for turns that the other tile does take.
+                const int other_blocks = t == 0 ? blocks_b : blocks_a;
+                const int need = t == 0 ? j - 1 : j;       // the other tile's block whose exponentials come before these
+                if (need >= 0 && need < other_blocks) {
+                    ok = wait_for(&exp_done[t ^ 1], need & 1);
+                    if (!ok) break;
+                }
+            }
 #pragma unroll
             for (int i = 0; i < TILE; i += 2) {
                 const float e0 = fast_exp2(v[i] * p.scale_log2 - base), e1 = fast_exp2(v[i + 1] * p.scale_log2 - base);
@@ -745,6 +760,8 @@ attention_two_tiles_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                 __nv_bfloat162 two = __floats2bfloat162_rn(e0, e1);
                 packed[i / 2] = *reinterpret_cast<uint32_t*>(&two);
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&exp_done[t]);
             if (j > 0) {
                 // the product of the block before has finished (it had the exponentials' time for
                 // it): P may be written again, and O may be scaled down where a row's maximum rose
@@ -994,7 +1011,7 @@ int launch(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v, con
 template <int D>
 int launch_two_tiles(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v, const AttentionParams& p, int n_units,
                      cudaStream_t s) {
-    constexpr size_t smem = (size_t)(2 + 2 * WIDE_STAGES + 4) * TILE * 64 * 2 + (1 + 4 * WIDE_STAGES + 8) * 8 + 64;
+    constexpr size_t smem = (size_t)(2 + 2 * WIDE_STAGES + 4) * TILE * 64 * 2 + (1 + 4 * WIDE_STAGES + 10) * 8 + 64;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(attention_two_tiles_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
