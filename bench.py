@@ -61,6 +61,9 @@ def parse_args():
     parser.add_argument("--page-size", type=int, default=None, help="tokens per cache page (the engine's default if not given)")
     parser.add_argument("--only-prefill", action="store_true",
                         help="run the 2,048-token prompt step alone and print its own line (for profiling)")
+    parser.add_argument("--kernels", action="store_true",
+                        help="time single kernels (matrix products at forced tile widths, prompt attention) back to "
+                             "back in a replayed graph and print one line each: the tables of profiles/ come from this")
     parser.add_argument("--tokens-out", default=None,
                         help="(--impl reference) write the greedy tokens of the fixed check workload to this file "
                              "and print nothing else")
@@ -656,6 +659,91 @@ def run_reference(args):
     return 0
 
 
+def replayed_us(torch, launch, repeats=12):
+    """Microseconds per call of ``launch(i)``, i = 0 .. repeats - 1 (each on operands of its own,
+    so that nothing stays in L2 from call to call), captured once and replayed: the best of five."""
+    launch(0)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(repeats):
+            launch(i)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    best = float("inf")
+    for _ in range(5):
+        first.record()
+        graph.replay()
+        last.record()
+        torch.cuda.synchronize()
+        best = min(best, first.elapsed_time(last) * 1000.0 / repeats)
+    return best
+
+
+def run_kernels():
+    """Single kernels at the sizes the profiles quote: the residual-sum product at every tile
+    code the launcher knows (0: its own choice), and the prompt attention with one and with two
+    tiles per CTA.  One JSON line per measurement."""
+    import math
+    import torch
+    from mini_llm_b200.kernels import ops
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    codes = (0, 2064, 2096, 2128, 192, 256, 7002, 7004, 7102, 7104)
+    shapes = ((640, 768, 3072), (1024, 768, 3072), (1536, 768, 3072), (2048, 768, 3072), (4096, 768, 3072),
+              (2048, 768, 768), (1024, 1024, 4096), (2048, 1024, 4096), (1024, 1600, 6400), (2048, 1600, 6400))
+    for m, n, k in shapes:
+        xs = [torch.randn(m, k, device="cuda").bfloat16() for _ in range(12)]
+        ws = [(torch.randn(n, k, device="cuda") / math.sqrt(k)).bfloat16() for _ in range(12)]
+        bias, out = torch.randn(n, device="cuda"), torch.zeros(m, n, device="cuda")
+        for code in codes:
+            def launch(i, code=code):
+                if code == 0:
+                    ops.gemm_bf16(out, xs[i], ws[i], bias, "add", status)
+                else:
+                    ops.gemm_bf16_tile(out, xs[i], ws[i], bias, "add", status, code)
+            print(json.dumps({"kernel": "gemm, residual sum", "m": m, "n": n, "k": k, "tile_code": code,
+                              "us": round(replayed_us(torch, launch), 2)}), flush=True)
+    heads, head, page = 12, 64, 64
+    work = torch.zeros(2, dtype=torch.int32, device="cuda")
+    for name, lengths, new in (("2 x 1024", [1024, 1024], [1024, 1024]), ("1 x 1024", [1024], [1024]),
+                               ("4 x 512", [512] * 4, [512] * 4), ("8 x 256 after 768", [1024] * 8, [256] * 8),
+                               ("700 + 300 + 1000 + 48 after 976", [700, 300, 1000, 1024], [700, 300, 1000, 48])):
+        blocks = [-(-length // page) for length in lengths]
+        k_pages = torch.randn(sum(blocks) + 1, page, heads, head, device="cuda").bfloat16()
+        v_pages = torch.randn(sum(blocks) + 1, page, heads, head, device="cuda").bfloat16()
+        table = torch.zeros(len(lengths), max(blocks), dtype=torch.int32)
+        at = 0
+        for i, count in enumerate(blocks):
+            table[i, :count] = torch.arange(at, at + count, dtype=torch.int32)
+            at += count
+        table = table.cuda()
+        q = torch.randn(sum(new), heads * head, device="cuda").bfloat16()
+        out = torch.empty_like(q)
+        offsets = [sum(new[:i]) for i in range(len(new))]
+        starts = [length - count for length, count in zip(lengths, new)]
+        tiles, _, _ = ops.attention_tiles(offsets, new, starts, split=False)
+        tiles_d = torch.tensor(tiles, dtype=torch.int32, device="cuda")
+        units, n_split, most = ops.attention_units(offsets, new, starts, heads, torch.cuda.get_device_properties(0).multi_processor_count)
+        units_d = torch.tensor(units, dtype=torch.int32, device="cuda")
+        scratch = None
+        if n_split:
+            scratch = (torch.empty(n_split * heads * most * ops.ATTENTION_UNIT * (head + 4), device="cuda"),
+                       torch.zeros(2 * n_split * heads, dtype=torch.int32, device="cuda"))
+        one = replayed_us(torch, lambda i: ops.attention_prefill(out, q, k_pages, v_pages, table, tiles_d, len(tiles), heads, heads,
+                                                                head, page, 0.125, 0, status, work))
+        two = replayed_us(torch, lambda i: ops.attention_prefill_two_tiles(out, q, k_pages, v_pages, table, units_d, len(units), heads,
+                                                                          heads, head, page, 0.125, 0, status, work, scratch, n_split,
+                                                                          most))
+        print(json.dumps({"kernel": "prompt attention, 12 heads of 64", "prompts": name, "one_tile_per_cta_us": round(one, 2),
+                          "two_tiles_per_cta_us": round(two, 2)}), flush=True)
+    if int(status.item()) != 0:
+        print(json.dumps({"error": "a bounded wait inside a kernel ran out", "status": int(status.item())}))
+        return 1
+    return 0
+
+
 def main():
     args = parse_args()
     if args.gpus != 1:
@@ -665,6 +753,8 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         return run_reference(args)
+    if args.kernels:
+        return run_kernels()
     return run_ours(args)
 
 
